@@ -1,0 +1,135 @@
+/*
+ * keepvq.h - C ABI of libkeepvq.so: KEEP's E8P lattice codes decoded and applied on an
+ * NVIDIA B200 (sm_100a) for RAMP's routed expert path.
+ *
+ * Conventions
+ *   - Every pointer is a DEVICE pointer unless its comment says "host".  Callers own all
+ *     memory; no entry point allocates, frees or synchronises.  Work is enqueued on `stream`
+ *     (a cudaStream_t passed as void*; NULL is the legacy default stream).
+ *   - Every entry point returns KEEPVQ_OK (0) or a negative keepvq_status.  Bad shapes, dtypes
+ *     or alignment are reported that way; nothing aborts.  keepvq_status_string() names a code.
+ *   - Tensors are dense and row-major.  `codes` is [experts, out_dim, in_dim/8]: uint16 for
+ *     16-bit E8P codes, uint8 for the 8-bit E8 residual.  `scales` is
+ *     [experts, out_dim, groups]; scale g of a row covers in_dim/groups consecutive inputs.
+ *   - A codebook is the 256-word packed table of the reference (src/keep/vq/e8.py:127-139
+ *     for E8P, :165-174 for the residual).  It is read on every call; nothing is cached
+ *     between calls, so a caller may overwrite codes, scales or tables between calls.
+ *
+ * Citations (file:line) name the interface of the reference (jackmaxwil/keep) that an entry
+ * point stands in for.
+ */
+#ifndef KEEPVQ_H
+#define KEEPVQ_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define KEEPVQ_ABI_VERSION 1
+
+typedef enum keepvq_status {
+  KEEPVQ_OK = 0,
+  KEEPVQ_ERR_NULL = -1,        /* a required pointer is NULL */
+  KEEPVQ_ERR_SHAPE = -2,       /* sizes are inconsistent (in_dim % 8, in_dim % groups, ...) */
+  KEEPVQ_ERR_DTYPE = -3,       /* unknown dtype tag or code width */
+  KEEPVQ_ERR_ALIGN = -4,       /* a pointer or row pitch misses the alignment the kernel needs */
+  KEEPVQ_ERR_UNSUPPORTED = -5, /* valid, but no kernel serves this combination */
+  KEEPVQ_ERR_LAUNCH = -6,      /* the CUDA runtime refused the launch; see keepvq_last_cuda_error */
+  KEEPVQ_ERR_CAPACITY = -7     /* a fixed-size buffer is too small for the request */
+} keepvq_status;
+
+typedef enum keepvq_dtype {
+  KEEPVQ_F32 = 0,
+  KEEPVQ_F16 = 1,
+  KEEPVQ_BF16 = 2
+} keepvq_dtype;
+
+/* Layout of the 8-bit residual's table argument. */
+typedef enum keepvq_table_layout {
+  KEEPVQ_TABLE_PACKED = 0,      /* uint32[256], nibble d = dim d        (e8.py:165-174)          */
+  KEEPVQ_TABLE_PAIR_PACKED = 1, /* uint32[256], nibbles k,k+4 = dims 2k,2k+1 (e8_1bit_m1.py:25-33) */
+  KEEPVQ_TABLE_HALF2_PAIRS = 2  /* uint32[256][4], fp16 bits of dims 2k|2k+1 (e8p_nested_m1.py:29-36) */
+} keepvq_table_layout;
+
+/* Route index that means "this route has no residual" (e8_1bit_m1.py:22). */
+#define KEEPVQ_NO_RESIDUAL 0xFFFFFFFFu
+
+int keepvq_abi_version(void);
+const char* keepvq_status_string(int status);
+/* Text of the last CUDA runtime error an entry point saw on this host thread ("" if none). */
+const char* keepvq_last_cuda_error(void);
+
+/* ------------------------------------------------------------------------------------------
+ * Code-to-weight decode.  Stands in for keep.vq.e8.decode_weight_matrix
+ * (src/keep/vq/e8.py:542-571): out[r, 8c+d] = decode(codes[r, c])[d] * scales[r, c / (cw/groups)].
+ * The product is exact in fp32, so an fp32 output is bit-identical to the reference.
+ * ------------------------------------------------------------------------------------------ */
+typedef struct keepvq_decode_args {
+  const void* codes;        /* [rows, codewords] uint16 (code_bits 16) or uint8 (8) */
+  int32_t code_bits;        /* 8 or 16 */
+  const void* scales;       /* [rows, groups], or NULL for unit scales */
+  int32_t scales_dtype;     /* keepvq_dtype */
+  const uint32_t* codebook; /* uint32[256], KEEPVQ_TABLE_PACKED */
+  int64_t rows;
+  int64_t codewords;        /* in_dim / 8 */
+  int64_t groups;
+  void* out;                /* [rows, codewords*8] */
+  int32_t out_dtype;        /* keepvq_dtype */
+} keepvq_decode_args;
+
+int keepvq_decode_weights(const keepvq_decode_args* args, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Routed matrix-vector products, few activation rows.  One entry point behind
+ *   vq_qmv                  src/ramp/kernels/vq_qmv.py:163-232    (experts=1, routes=1)
+ *   vq_qmm                  src/ramp/kernels/vq_qmm.py:93-152     (experts=1, rhs=0, lhs=row)
+ *   gather_vqmm (direct)    src/ramp/ops/vq_switch.py:916-932, kernels/gather_vqmm.py:473-594
+ *   e8p_m1_token_layout / e8p_m1_per_route          src/ramp/kernels/e8p_m1.py:134-183
+ *   e8_1bit_m1_token_layout / _per_route            src/ramp/kernels/e8_1bit_m1.py:76-97
+ *   e8p_nested_m1_token_layout / _per_route         src/ramp/kernels/e8p_nested_m1.py:90-112
+ *
+ * out[r, n] = sum_k W[rhs[r]][n, k] * x[row(r), k], fp32 accumulation, one rounding to
+ * out_dtype.  row(r) = lhs[r] if lhs != NULL else r / x_div.  With a residual,
+ * W = base + residual[hot_of_slot[rhs[r]]] for slots whose entry is not KEEPVQ_NO_RESIDUAL;
+ * base and residual are accumulated apart and added once in fp32.  With code_bits 8 and no
+ * residual block, a route whose rhs is KEEPVQ_NO_RESIDUAL writes zeros.
+ * Indices are not range-checked (vq_switch.py:637,646-648).
+ * ------------------------------------------------------------------------------------------ */
+typedef struct keepvq_matvec_args {
+  const void* x;            /* [x_rows, in_dim] */
+  int32_t x_dtype;          /* keepvq_dtype */
+  int64_t x_rows;
+  const void* codes;        /* [experts, out_dim, in_dim/8] */
+  int32_t code_bits;        /* 8 or 16 */
+  const void* scales;       /* [experts, out_dim, groups] */
+  int32_t scales_dtype;
+  int64_t experts;
+  int64_t out_dim;
+  int64_t in_dim;
+  int64_t groups;
+  const uint32_t* codebook; /* table of `codes` */
+  int32_t codebook_layout;  /* keepvq_table_layout; 16-bit codes take KEEPVQ_TABLE_PACKED only */
+  const uint32_t* rhs;      /* [routes] first-axis index into codes per route */
+  const int32_t* lhs;       /* [routes] activation row per route, or NULL */
+  int32_t x_div;            /* used when lhs == NULL: top_k (token layout) or 1 (per route) */
+  int64_t routes;
+  /* optional nested residual; res_codes == NULL turns it off */
+  const uint8_t* res_codes;    /* [res_rows, out_dim, in_dim/8] */
+  const void* res_scales;      /* [res_rows, out_dim, res_groups] */
+  int32_t res_scales_dtype;
+  int64_t res_rows;
+  int64_t res_groups;
+  const uint32_t* res_table;   /* KEEPVQ_TABLE_HALF2_PAIRS */
+  const uint32_t* hot_of_slot; /* [experts] */
+  void* out;                /* [routes, out_dim] */
+  int32_t out_dtype;
+} keepvq_matvec_args;
+
+int keepvq_routed_matvec(const keepvq_matvec_args* args, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* KEEPVQ_H */

@@ -1,0 +1,128 @@
+"""ctypes binding of ``libkeepvq.so`` (declarations in ``include/keepvq.h``).
+
+The library is the only compute path: if it is missing or fails to load, every operator raises.
+There is no CPU or eager fallback.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import threading
+from ctypes import POINTER, Structure, c_char_p, c_int, c_int32, c_int64, c_void_p
+from pathlib import Path
+
+import torch
+
+LIBRARY_PATH = Path(__file__).resolve().parent / "libkeepvq.so"
+
+F32, F16, BF16 = 0, 1, 2
+TABLE_PACKED, TABLE_PAIR_PACKED, TABLE_HALF2_PAIRS = 0, 1, 2
+NO_RESIDUAL = 0xFFFFFFFF
+
+_DTYPE_TAG = {torch.float32: F32, torch.float16: F16, torch.bfloat16: BF16}
+
+
+class KeepVQError(RuntimeError):
+    """A non-zero status from the native library."""
+
+
+class DecodeArgs(Structure):
+    _fields_ = [
+        ("codes", c_void_p), ("code_bits", c_int32),
+        ("scales", c_void_p), ("scales_dtype", c_int32),
+        ("codebook", c_void_p),
+        ("rows", c_int64), ("codewords", c_int64), ("groups", c_int64),
+        ("out", c_void_p), ("out_dtype", c_int32),
+    ]
+
+
+class MatvecArgs(Structure):
+    _fields_ = [
+        ("x", c_void_p), ("x_dtype", c_int32), ("x_rows", c_int64),
+        ("codes", c_void_p), ("code_bits", c_int32),
+        ("scales", c_void_p), ("scales_dtype", c_int32),
+        ("experts", c_int64), ("out_dim", c_int64), ("in_dim", c_int64), ("groups", c_int64),
+        ("codebook", c_void_p), ("codebook_layout", c_int32),
+        ("rhs", c_void_p), ("lhs", c_void_p), ("x_div", c_int32), ("routes", c_int64),
+        ("res_codes", c_void_p), ("res_scales", c_void_p), ("res_scales_dtype", c_int32),
+        ("res_rows", c_int64), ("res_groups", c_int64),
+        ("res_table", c_void_p), ("hot_of_slot", c_void_p),
+        ("out", c_void_p), ("out_dtype", c_int32),
+    ]
+
+
+_SIGNATURES = {
+    "keepvq_abi_version": (c_int, []),
+    "keepvq_status_string": (c_char_p, [c_int]),
+    "keepvq_last_cuda_error": (c_char_p, []),
+    "keepvq_decode_weights": (c_int, [POINTER(DecodeArgs), c_void_p]),
+    "keepvq_routed_matvec": (c_int, [POINTER(MatvecArgs), c_void_p]),
+}
+
+_lock = threading.Lock()
+_lib = None
+
+
+def load() -> ctypes.CDLL:
+    """The loaded library.  Raises if it has not been built (``python -m keep_b200.build``)."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    with _lock:
+        if _lib is None:
+            if not LIBRARY_PATH.exists():
+                raise KeepVQError(
+                    f"{LIBRARY_PATH} is missing: build it with `python -m keep_b200.build` "
+                    "(needs nvcc; there is no CPU fallback)"
+                )
+            lib = ctypes.CDLL(str(LIBRARY_PATH))
+            for name, (restype, argtypes) in _SIGNATURES.items():
+                fn = getattr(lib, name)
+                fn.restype, fn.argtypes = restype, argtypes
+            _lib = lib
+    return _lib
+
+
+def exported_names() -> list[str]:
+    return sorted(_SIGNATURES)
+
+
+def check(status: int, what: str) -> None:
+    if status != 0:
+        lib = load()
+        text = lib.keepvq_status_string(status).decode()
+        detail = lib.keepvq_last_cuda_error().decode() if status == -6 else ""
+        raise KeepVQError(f"{what}: {text} ({status}){': ' + detail if detail else ''}")
+
+
+def dtype_tag(dtype: torch.dtype) -> int:
+    try:
+        return _DTYPE_TAG[dtype]
+    except KeyError:
+        raise ValueError(f"unsupported floating dtype {dtype}") from None
+
+
+def ptr(t: torch.Tensor | None) -> c_void_p:
+    return c_void_p(None if t is None else t.data_ptr())
+
+
+def stream_handle(device: torch.device) -> c_void_p:
+    return c_void_p(torch.cuda.current_stream(device).cuda_stream)
+
+
+def require_cuda(*tensors: torch.Tensor) -> torch.device:
+    """All tensors on one CUDA device; that device is returned.  CPU tensors are refused: the
+    operators never compute on the host."""
+    device = None
+    for t in tensors:
+        if t is None:
+            continue
+        if not t.is_cuda:
+            raise KeepVQError("keep_b200 operators need CUDA tensors; there is no CPU path")
+        if device is None:
+            device = t.device
+        elif t.device != device:
+            raise ValueError(f"tensors on different devices: {device} and {t.device}")
+    if device is None:
+        raise KeepVQError("no CUDA tensor given")
+    return device

@@ -1,0 +1,103 @@
+"""The routed operators (gather_vqmm family) against the oracle and the golden fixtures.
+
+Mirrors tests/test_gather_vqmm.py:40-337 of the reference: gather = per-route qmv; the sorted path
+scatters back to the caller's order; explicit lhs; mixed-expert tile boundaries; traces."""
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import ops
+
+pytestmark = pytest.mark.gpu
+
+
+def f32(t):
+    return t.float().cpu().numpy()
+
+
+def test_golden_reference_outputs(cuda, golden):
+    from keep_b200 import vq_switch
+
+    g = golden("operators")
+    kw = dict(input_dims=128, output_dims=24, group_size=32, code_bits=16)
+    x = torch.from_numpy(g["x"]).to(cuda)
+    for impl in ("cuda", "reference"):
+        got = vq_switch.gather_vqmm(x, g["codes"], g["scales"], None, g["rhs"], implementation=impl, **kw)
+        np.testing.assert_allclose(f32(got), g["token"], rtol=1e-5, atol=1e-5)
+        got = vq_switch.gather_vqmm(x, g["codes"], g["scales"], None, g["flat_rhs"], lhs_indices=g["lhs"], implementation=impl, **kw)
+        np.testing.assert_allclose(f32(got), g["routed"], rtol=1e-5, atol=1e-5)
+        got = vq_switch.vq_switch_qmv(torch.from_numpy(g["xr"]).to(cuda), g["codes"], g["scales"], None, g["rhs"], implementation=impl, **kw)
+        np.testing.assert_allclose(f32(got), g["per_route"], rtol=1e-5, atol=1e-5)
+    got = vq_switch.gather_vqmm(x, g["codes8"], g["scales"], None, g["rhs"], **{**kw, "code_bits": 8})
+    np.testing.assert_allclose(f32(got), g["token8"], rtol=1e-5, atol=1e-5)
+
+
+@pytest.mark.parametrize("strategy", ["direct", "sorted_tiled", "per_route_decoded", "auto"])
+@pytest.mark.parametrize("tokens,top_k", [(4, 3), (50, 6)])
+def test_every_strategy_returns_the_callers_order(cuda, strategy, tokens, top_k):
+    from keep_b200 import vq_switch
+
+    rng = np.random.default_rng(31)
+    experts, out, inp, group = 7, 40, 256, 64
+    codes = rng.integers(0, 1 << 16, (experts, out, inp // 8), dtype=np.uint16)
+    scales = rng.uniform(0.01, 0.2, (experts, out, inp // group)).astype(np.float16)
+    x = rng.normal(size=(tokens, inp)).astype(np.float32)
+    rhs = np.stack([rng.choice(experts, top_k, replace=False) for _ in range(tokens)]).astype(np.int64)
+    want = ops.gather_vqmm(x, codes, scales, None, rhs, code_bits=16)
+    with vq_switch.trace_gather_vqmm_calls() as trace:
+        got = vq_switch.gather_vqmm(torch.from_numpy(x).to(cuda), codes, scales, None, rhs, input_dims=inp, output_dims=out,
+                                    group_size=group, code_bits=16, route_strategy=strategy)
+    np.testing.assert_allclose(f32(got), want, rtol=1e-4, atol=1e-3)
+    assert trace[0]["route_count"] == tokens * top_k
+    if strategy == "auto":
+        assert trace[0]["strategy"] == ("sorted_tiled" if tokens * top_k >= 128 else "direct")
+
+
+def test_sorted_routes_with_explicit_descriptors_and_boundaries(cuda):
+    from keep_b200 import vq_switch
+
+    rng = np.random.default_rng(32)
+    experts, out, inp, group = 5, 24, 128, 32
+    codes = rng.integers(0, 1 << 16, (experts, out, inp // 8), dtype=np.uint16)
+    scales = rng.uniform(0.01, 0.2, (experts, out, inp // group)).astype(np.float16)
+    x = rng.normal(size=(9, inp)).astype(np.float32)
+    sorted_rhs = np.array([0] * 3 + [2] * 37 + [4] * 2, dtype=np.int32)  # expert 1 and 3 unused; 2 spans tiles
+    sorted_lhs = rng.integers(0, 9, sorted_rhs.shape[0]).astype(np.int32)
+    want = ops.gather_vqmm(x, codes, scales, None, sorted_rhs, lhs_indices=sorted_lhs, code_bits=16)
+    xt = torch.from_numpy(x).to(cuda)
+    tiles = vq_switch.expert_block_tile_descriptors(torch.from_numpy(sorted_rhs).to(cuda), num_experts=experts, route_tile=32)
+    te, to, tc = (t.cpu().numpy() for t in tiles)
+    assert te.shape[0] == 2 + experts and tc.sum() == sorted_rhs.shape[0]
+    assert [(int(e), int(o), int(c)) for e, o, c in zip(te, to, tc) if c] == [(0, 0, 3), (2, 3, 32), (2, 35, 5), (4, 40, 2)]
+    got = vq_switch.gather_vqmm_sorted_routes(xt, codes, scales, None, sorted_rhs, sorted_lhs, input_dims=inp, output_dims=out,
+                                              group_size=group, code_bits=16, validate_indices=True, tile_descriptors=tiles)
+    np.testing.assert_allclose(f32(got), want, rtol=1e-4, atol=1e-3)
+    with pytest.raises(ValueError, match="sorted nondecreasing"):
+        vq_switch.gather_vqmm_sorted_routes(xt, codes, scales, None, sorted_rhs[::-1].copy(), sorted_lhs, input_dims=inp,
+                                            output_dims=out, group_size=group, code_bits=16, validate_indices=True)
+    empty = vq_switch.gather_vqmm_sorted_routes(xt, codes, scales, None, sorted_rhs[:0], sorted_lhs[:0], input_dims=inp,
+                                                output_dims=out, group_size=group, code_bits=16)
+    assert tuple(empty.shape) == (0, out)
+
+
+def test_metadata_errors_match_the_reference_messages(cuda):
+    from keep_b200 import vq_switch
+
+    x = torch.zeros((2, 64), device=cuda)
+    codes = torch.zeros((3, 8, 8), dtype=torch.uint16, device=cuda)
+    scales = torch.ones((3, 8, 2), device=cuda)
+    rhs = torch.zeros((2, 2), dtype=torch.int64, device=cuda)
+    kw = dict(input_dims=64, output_dims=8, group_size=32, code_bits=16)
+    with pytest.raises(ValueError, match="route_strategy must be"):
+        vq_switch.gather_vqmm(x, codes, scales, None, rhs, route_strategy="tiled", **kw)
+    with pytest.raises(ValueError, match="rhs_indices token dimension"):
+        vq_switch.gather_vqmm(x, codes, scales, None, rhs[:1], **kw)
+    with pytest.raises(ValueError, match="codes must have shape"):
+        vq_switch.gather_vqmm(x, codes[:, :4], scales, None, rhs, **kw)
+    with pytest.raises(ValueError, match="codes dtype must be uint16"):
+        vq_switch.gather_vqmm(x, codes.to(torch.uint8), scales, None, rhs, **kw)
+    with pytest.raises(ValueError, match=r"indices must be in \[0, 3\)"):
+        vq_switch.gather_vqmm(x, codes, scales, None, rhs + 3, implementation="reference", **kw)
+    with pytest.raises(ValueError, match="same flattened shape"):
+        vq_switch.gather_vqmm(x, codes, scales, None, rhs.reshape(-1), lhs_indices=torch.zeros(3, dtype=torch.int32, device=cuda), **kw)
