@@ -47,13 +47,14 @@ __global__ void __launch_bounds__(256) decode_weights_kernel(keepvq_decode_args 
 
 extern "C" int keepvq_decode_weights(const keepvq_decode_args* args, void* stream) {
   using namespace keepvq;
-  if (!args || !args->codes || !args->codebook || !args->out) return KEEPVQ_ERR_NULL;
+  if (!args) return KEEPVQ_ERR_NULL;
   const keepvq_decode_args& a = *args;
   if (a.code_bits != 8 && a.code_bits != 16) return KEEPVQ_ERR_DTYPE;
   if (!valid_dtype(a.out_dtype) || (a.scales && !valid_dtype(a.scales_dtype))) return KEEPVQ_ERR_DTYPE;
   if (a.rows < 0 || a.codewords < 0 || a.groups <= 0) return KEEPVQ_ERR_SHAPE;
   if (a.codewords % a.groups != 0) return KEEPVQ_ERR_SHAPE;
-  if (a.rows == 0 || a.codewords == 0) return KEEPVQ_OK;
+  if (a.rows == 0 || a.codewords == 0) return KEEPVQ_OK;  // nothing to do; empty tensors carry no pointer
+  if (!a.codes || !a.codebook || !a.out) return KEEPVQ_ERR_NULL;
   if (!aligned_to(a.out, 16)) return KEEPVQ_ERR_ALIGN;
   const int64_t total = a.rows * a.codewords;
   int64_t blocks = (total + 255) / 256;
