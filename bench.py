@@ -1,0 +1,318 @@
+"""Benchmark of the routed E8P MoE layer (decode) on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--batch B] [--impl ours|reference]
+
+A step is one pass of one routed MoE layer (384 experts, hidden 4096, inter 2048, top-6, softmax
+router, uniform-random E8P codes, per-row fp16 scales) over one batch of B decode tokens.  Token
+batches rotate over 64 different seeded batches so that successive steps touch different experts
+of the 2.4 GB pool (larger than L2).  Prints ONE JSON line on rank 0.
+
+``value``      tokens/s with inputs resident in HBM, timed with CUDA events around a CUDA-graph
+               replay of the K steps (no host launch gaps inside the timed region).
+``e2e``        the same metric through ``RoutedMoELayer.decode`` from pinned host buffers: the
+               H2D copy of the tokens and the D2H copy of the layer output are inside the region.
+``roofline``   the dominant kernel (expert projections) timed alone with CUDA events: distinct
+               served experts x code bytes per launch / launch time, against the measured HBM peak.
+``cpu_baseline``  the CPU oracle (a port of the reference's CPU path) timed on the host cores on
+               a bounded sample (one token through its six experts, decode included).
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+import torch
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+EXPERTS, HIDDEN, INTER, TOP_K = 384, 4096, 2048, 6
+CODE_BYTES_PER_PROJECTION = INTER * HIDDEN // 8 * 2          # 2,097,152
+CODE_BYTES_PER_EXPERT = 3 * CODE_BYTES_PER_PROJECTION        # 6,291,456
+ROTATION = 64
+METRIC, UNIT = "routed VQ MoE layer tokens/s", "tokens/s"
+
+
+def measured_peaks() -> tuple[float, str]:
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        return float(json.loads(path.read_text())["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.stop_flag, self.thread = index, [], threading.Event(), None
+
+    def _run(self):
+        while not self.stop_flag.is_set():
+            try:
+                out = subprocess.run(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits"],
+                                     capture_output=True, text=True, timeout=5).stdout.strip()
+                if out:
+                    self.rows.append([c.strip() for c in out.split(",")])
+            except Exception:
+                pass
+            self.stop_flag.wait(0.2)
+
+    def __enter__(self):
+        self.thread = threading.Thread(target=self._run, daemon=True)
+        self.thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self.stop_flag.set()
+        self.thread.join(timeout=6)
+
+    def summary(self) -> dict:
+        sm = [float(r[0]) for r in self.rows if r and r[0].replace(".", "").isdigit()]
+        mx = [float(r[1]) for r in self.rows if len(r) > 1 and r[1].replace(".", "").isdigit()]
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        reasons = sorted({n for r in self.rows for n, v in zip(names, r[2:6]) if v.lower().startswith("active")})
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(self.rows)}
+
+
+def build_layer(device, seed=0):
+    """The benchmark layer with codes drawn on the device (uniform uint16), scales 0.02*U(0.5,1.5)."""
+    from keep_b200 import moe
+
+    gen = torch.Generator(device=device)
+    gen.manual_seed(seed)
+
+    def proj(out, inp):
+        codes = torch.randint(0, 1 << 16, (EXPERTS, out, inp // 8), generator=gen, device=device, dtype=torch.int32).to(torch.uint16)
+        scales = (0.02 * (0.5 + torch.rand((EXPERTS, out, 1), generator=gen, device=device))).to(torch.float16)
+        return moe.Projection(codes, scales)
+
+    router = (0.02 * torch.randn((EXPERTS, HIDDEN), generator=gen, device=device)).to(torch.bfloat16)
+    return moe.RoutedMoELayer(router, proj(INTER, HIDDEN), proj(INTER, HIDDEN), proj(HIDDEN, INTER), top_k=TOP_K)
+
+
+def token_batches(device, batch, count=ROTATION):
+    gen = torch.Generator(device="cpu")
+    gen.manual_seed(1 + batch)
+    return [torch.randn((batch, HIDDEN), generator=gen).to(torch.bfloat16).to(device) for _ in range(count)]
+
+
+def time_graph(fn, steps, warmup):
+    """CUDA-event time of `steps` calls of fn(i) replayed from one CUDA graph, in ms."""
+    stream = torch.cuda.Stream()
+    stream.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(stream):
+        for i in range(max(warmup, 3)):
+            fn(i)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            for i in range(steps):
+                fn(i)
+        graph.replay()  # one untimed replay
+        torch.cuda.synchronize()
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        begin.record(stream)
+        graph.replay()
+        end.record(stream)
+        torch.cuda.synchronize()
+    return begin.elapsed_time(end)
+
+
+def distinct_experts(layer, xs):
+    counts = []
+    for x in xs:
+        _, routing = layer.decode(x)
+        served = routing.served_expert.cpu().numpy()
+        counts.append(len({int(v) for v in served.reshape(-1) if v >= 0}))
+    return counts
+
+
+def projection_roofline(layer, xs, steps, hbm_gbs, peak_kind):
+    """Times the gate projection launch (the dominant kernel, one of three like it per layer) alone."""
+    from keep_b200 import kernels
+
+    routings = []
+    for x in xs:
+        _, r = layer.decode(x)
+        routings.append(r.served_slot.clone())
+    uniq = [len({int(v) for v in r.cpu().numpy().reshape(-1) if v >= 0}) for r in routings]
+    w = layer.w1
+
+    def one(i):
+        j = i % len(xs)
+        kernels.routed_matvec(xs[j], w.codes, w.scales, layer.codebook, routings[j].reshape(-1), x_div=TOP_K, code_bits=16)
+
+    ms = time_graph(one, steps, 3)
+    bytes_per_launch = statistics.fmean(uniq[i % len(xs)] for i in range(steps)) * CODE_BYTES_PER_PROJECTION
+    achieved = bytes_per_launch / (ms / steps * 1e-3) / 1e9
+    return {"bound": "hbm", "achieved": round(achieved, 1), "peak": hbm_gbs, "unit": "GB/s", "frac": round(achieved / hbm_gbs, 4),
+            "traffic": None, "peak_kind": peak_kind, "kernel": "routed_matvec_kernel (gate projection launch)",
+            "algorithmic_bytes_per_launch": int(bytes_per_launch), "us_per_launch": round(ms / steps * 1e3, 2)}
+
+
+def cpu_layer_sample(layer, x_row, threads, experts_per_token=TOP_K):
+    """One token through the CPU oracle: router, decode of its served experts' three projections
+    (grid[codes] * scale, as the reference's CPU path does), the SwiGLU path with the served
+    rounding points.  ``experts_per_token`` < top-k keeps only the strongest picks (a bounded
+    sample).  Returns (seconds, output row)."""
+    from oracle import router as oracle_router
+
+    torch.set_num_threads(threads)
+    begin = time.perf_counter()
+    r = oracle_router.routed_topk(x_row, layer.router_w.cpu(), top_k=TOP_K)
+    slots, weights = r["served_slot"].numpy().copy(), r["served_weight"].numpy()
+    slots[:, experts_per_token:] = -1
+    dense = {}
+    for n in ("w1", "w3", "w2"):
+        p = getattr(layer, n)
+        dense[n] = {int(e): oracle_router.decode_torch(p.codes[int(e)].cpu().numpy(), p.scales[int(e)].cpu().numpy())
+                    for e in slots.reshape(-1) if e >= 0}
+    out = oracle_router.moe_layer(x_row, slots, weights, dense["w1"], dense["w3"], dense["w2"])
+    return time.perf_counter() - begin, out
+
+
+def run_reference(ns):
+    """The reference arm: the CPU path of the layer on the host cores (oracle port), one token per step."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    device = torch.device("cuda", 0) if torch.cuda.is_available() else None
+    if device is None:
+        print(json.dumps({"impl": "reference", "unavailable": "the bench layer is generated on a CUDA device; none present"}))
+        return
+    layer = build_layer(device)
+    xs = token_batches(device, 1, count=max(ns.steps + ns.warmup, 1))
+    threads = os.cpu_count() or 1
+    # a full token costs about 3 s of CPU; keep the whole run within a few minutes
+    per_token = TOP_K if ns.steps <= 48 else max(1, (48 * TOP_K) // ns.steps)
+    for i in range(min(ns.warmup, 1)):
+        cpu_layer_sample(layer, xs[i].cpu(), threads, per_token)
+    times = [cpu_layer_sample(layer, xs[(ns.warmup + i) % len(xs)].cpu(), threads, per_token)[0] for i in range(ns.steps)]
+    total = sum(times)
+    value = ns.steps * (per_token / TOP_K) / total
+    line = {"metric": METRIC, "value": round(value, 4), "unit": UNIT, "n_gpus": ns.gpus, "steps": ns.steps, "warmup": ns.warmup,
+            "ms_per_step": round(total / ns.steps * 1e3, 2), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic", "impl": "reference",
+            "config": {"workload": "decode layer (config 2): 384 experts, hidden 4096, inter 2048, top-6 softmax router; CPU path, one token per step (bounded sample)"},
+            "cpu_baseline": {"value": round(value, 4), "unit": UNIT, "cores": threads, "kind": "port",
+                             "sample": f"per step: router + {per_token} of a token's 6 served experts (decode of 3 projections each + SwiGLU path); value scaled to whole tokens"},
+            "e2e": {"value": round(value, 4), "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line))
+
+
+def run_ours(ns):
+    rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=device)
+    from keep_b200 import _lib
+    _lib.load()
+    hbm_gbs, peak_kind = measured_peaks()
+    layer = build_layer(device, seed=0)
+    batch = ns.batch
+    xs = token_batches(device, batch)
+    uniq = distinct_experts(layer, xs)
+
+    def step(i):
+        layer.decode(xs[i % ROTATION])
+
+    def barrier():
+        if world > 1:
+            import torch.distributed as dist
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    barrier()
+    with ClockSampler(local) as clocks:
+        ms = time_graph(step, ns.steps, ns.warmup)
+        barrier()
+        # end to end: pinned host tokens in, layer output back to the host, every step
+        host_in = [x.cpu().pin_memory() for x in xs]
+        host_out = torch.empty((batch, HIDDEN), dtype=torch.bfloat16).pin_memory()
+        dev_in = torch.empty((batch, HIDDEN), dtype=torch.bfloat16, device=device)
+
+        def e2e_step(i):
+            dev_in.copy_(host_in[i % ROTATION], non_blocking=True)
+            out, _ = layer.decode(dev_in)
+            host_out.copy_(out, non_blocking=True)
+
+        for i in range(max(ns.warmup, 3)):
+            e2e_step(i)
+        torch.cuda.synchronize()
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        begin.record()
+        for i in range(ns.steps):
+            e2e_step(i)
+        end.record()
+        torch.cuda.synchronize()
+        e2e_ms = begin.elapsed_time(end)
+    if world > 1:
+        import torch.distributed as dist
+        t = torch.tensor([ms, e2e_ms], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, e2e_ms = (float(v) for v in t.cpu())
+    tokens = batch * ns.steps * world
+    value = tokens / (ms * 1e-3)
+    e2e_value = tokens / (e2e_ms * 1e-3)
+    if rank != 0:
+        return
+    mean_u = statistics.fmean(uniq[i % ROTATION] for i in range(ns.steps))
+    code_gbs = mean_u * CODE_BYTES_PER_EXPERT / (ms / ns.steps * 1e-3) / 1e9
+    roofline = projection_roofline(layer, xs, ns.steps, hbm_gbs, peak_kind)
+    threads = os.cpu_count() or 1
+    cpu_s, cpu_out = cpu_layer_sample(layer, xs[0][:1].cpu(), threads)
+    gpu_out, _ = layer.decode(xs[0])
+    ref = cpu_out.numpy()
+    parity_gap = float(np.abs(gpu_out[:1].float().cpu().numpy() - ref).max() / np.abs(ref).max())
+    line = {
+        "metric": METRIC, "value": round(value, 1), "unit": UNIT, "n_gpus": world, "steps": ns.steps, "warmup": ns.warmup,
+        "ms_per_step": round(ms / ns.steps, 5), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"decode layer (config 2): 384 experts, hidden 4096, inter 2048, top-6 softmax router, batch {batch}",
+                   "batch": batch, "l2": "inputs larger than L2: 64 rotating token batches over a 2.4 GB expert pool",
+                   "distinct_experts_per_step": round(mean_u, 2)},
+        "layer_code_gbs": round(code_gbs, 1), "layer_code_frac_of_hbm": round(code_gbs / hbm_gbs, 4),
+        "roofline": roofline,
+        "cpu_baseline": {"value": round(1.0 / cpu_s, 4), "unit": UNIT, "cores": threads, "kind": "port",
+                         "sample": "one token: router + decode of 6 experts x 3 projections + SwiGLU path", "parity_gap_vs_gpu": parity_gap},
+        "e2e": {"value": round(e2e_value, 1), "unit": UNIT, "h2d_bytes_per_step": batch * HIDDEN * 2, "d2h_bytes_per_step": batch * HIDDEN * 2},
+        "gpu_launches": 7 * ns.steps,
+        "clocks": clocks.summary(),
+    }
+    print(json.dumps(line))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--batch", type=int, default=64)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ns = ap.parse_args()
+    if ns.impl == "reference":
+        run_reference(ns)
+    else:
+        if not torch.cuda.is_available():
+            raise SystemExit("bench.py needs a CUDA device: the product path has no CPU fallback")
+        run_ours(ns)
+
+
+if __name__ == "__main__":
+    main()

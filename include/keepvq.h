@@ -93,8 +93,9 @@ int keepvq_decode_weights(const keepvq_decode_args* args, void* stream);
  * out[r, n] = sum_k W[rhs[r]][n, k] * x[row(r), k], fp32 accumulation, one rounding to
  * out_dtype.  row(r) = lhs[r] if lhs != NULL else r / x_div.  With a residual,
  * W = base + residual[hot_of_slot[rhs[r]]] for slots whose entry is not KEEPVQ_NO_RESIDUAL;
- * base and residual are accumulated apart and added once in fp32.  With code_bits 8 and no
- * residual block, a route whose rhs is KEEPVQ_NO_RESIDUAL writes zeros.
+ * base and residual are accumulated apart and added once in fp32.  A route whose rhs is
+ * KEEPVQ_NO_RESIDUAL writes zeros (the 8-bit kernels of the reference do the same,
+ * e8_1bit_m1.metal:25-32; here it holds for every code width, so a masked router pick is safe).
  * Indices are not range-checked (vq_switch.py:637,646-648).
  * ------------------------------------------------------------------------------------------ */
 typedef struct keepvq_matvec_args {
@@ -128,6 +129,138 @@ typedef struct keepvq_matvec_args {
 } keepvq_matvec_args;
 
 int keepvq_routed_matvec(const keepvq_matvec_args* args, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Router with routed residency.  Two launches that together stand in for
+ *   Gate.forward           tests/fixtures/v41_reference/model.py:811-829
+ *   gate_masked            scripts/runpod/v41_reap/local_eval.py:69-90
+ *   the fused dual top-k   scripts/v41_build/omlx_lattice.py:77-104,333-338
+ *   the admission test     scripts/v41_build/omlx_routed.py:184-203
+ * ------------------------------------------------------------------------------------------ */
+typedef enum keepvq_score_func {
+  KEEPVQ_SCORE_SOFTMAX = 0,
+  KEEPVQ_SCORE_SIGMOID = 1,
+  KEEPVQ_SCORE_SQRT_SOFTPLUS = 2
+} keepvq_score_func;
+
+/* logits[t, e] = (x[t] . router_w[e]) / gate_temp in fp32. */
+typedef struct keepvq_router_logits_args {
+  const void* x;        /* [tokens, hidden] */
+  int32_t x_dtype;
+  const void* router_w; /* [pool, hidden] */
+  int32_t router_dtype;
+  int64_t tokens;
+  int64_t pool;
+  int64_t hidden;       /* multiple of 8 */
+  float gate_temp;
+  float* logits;        /* [tokens, pool] */
+} keepvq_router_logits_args;
+
+int keepvq_router_logits(const keepvq_router_logits_args* args, void* stream);
+
+/* One router evaluation, two selections.
+ *   scores = f(logits)
+ *   served = top_k(scores + served_bias);  demand = top_k(scores + pool_bias)
+ * served_bias[e] <= -1e29 (or -inf) marks expert e absent: it is never served while a resident
+ * remains, and a pick that lands on one anyway (fewer residents than top_k) gets weight 0 and
+ * slot KEEPVQ_NO_RESIDUAL.  Served weights are raw scores, renormalised over the served picks
+ * when norm_topk_prob != 0, times route_scale.  Demand keeps raw scores.  admit[t, j] is the
+ * demanded expert when it is absent and its demand weight, renormalised over the k demanded
+ * scores and times route_scale, is >= tau; otherwise -1.  Ties go to the lowest expert id;
+ * picks are in descending biased score. */
+typedef struct keepvq_routed_topk_args {
+  const float* logits;       /* [tokens, pool] */
+  int64_t tokens;
+  int64_t pool;
+  int32_t top_k;             /* <= 16 */
+  int32_t score_func;        /* keepvq_score_func */
+  int32_t norm_topk_prob;
+  float route_scale;
+  float tau;
+  const float* served_bias;  /* [pool] or NULL (all resident, zero bias) */
+  const float* pool_bias;    /* [pool] or NULL (zero) */
+  const uint32_t* slot_of;   /* [pool] expert -> slot, or NULL (slot = expert) */
+  float* scores;             /* [tokens, pool] optional output, may be NULL */
+  uint32_t* served_expert;   /* [tokens, top_k] */
+  uint32_t* served_slot;     /* [tokens, top_k] */
+  float* served_weight;      /* [tokens, top_k] */
+  uint32_t* want;            /* [tokens, top_k] */
+  float* want_score;         /* [tokens, top_k] */
+  int32_t* admit;            /* [tokens, top_k] optional, may be NULL */
+} keepvq_routed_topk_args;
+
+int keepvq_routed_topk(const keepvq_routed_topk_args* args, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * One routed MoE layer at decode, as a single launch sequence with no host round trip:
+ * router logits -> dual top-k -> gate/up projections + SwiGLU * gate weight -> down projection
+ * -> fp32 sum over the k served experts.  Stands in for the decode step
+ *   scripts/v41_build/omlx_lattice.py:327-371   (served path, rounding points)
+ *   scripts/runpod/v41_reap/local_eval.py:508-585, tests/fixtures/v41_reference/model.py:843-853
+ *   src/ramp/models/glm4_moe_adapter.py:367-372 (QuantizedVQSwitchGLU) + the weighted sum
+ *
+ * Per token t and served pick j (slot s, weight g):
+ *   G = round(W1[s] x_t), U = round(W3[s] x_t)       rounded to the activation dtype
+ *   h = round(silu(G) * U * g)                        (optional clamp: G <= limit, |U| <= limit)
+ *   y_t += float(round(W2[s] h))                      fp32 sum in pick order
+ *   out_t = round(y_t)
+ * W = base codes (+ the 8-bit residual of slots that hot_of_slot marks, when given).
+ * ------------------------------------------------------------------------------------------ */
+typedef struct keepvq_expert_weights {
+  const uint16_t* codes;    /* [slots, out_dim, in_dim/8] */
+  const void* scales;       /* [slots, out_dim, groups] */
+  int64_t groups;
+  const uint8_t* res_codes; /* [res_rows, out_dim, in_dim/8] or NULL */
+  const void* res_scales;   /* [res_rows, out_dim, res_groups] */
+  int64_t res_groups;
+} keepvq_expert_weights;
+
+typedef struct keepvq_moe_layer_args {
+  const void* x;             /* [tokens, hidden] */
+  int32_t x_dtype;           /* keepvq_dtype; also the dtype of `out` */
+  int64_t tokens;
+  int64_t hidden;
+  int64_t inter;
+  /* router */
+  const void* router_w;      /* [pool, hidden] */
+  int32_t router_dtype;
+  int64_t pool;
+  int32_t top_k;
+  int32_t score_func;
+  int32_t norm_topk_prob;
+  float gate_temp;
+  float route_scale;
+  float tau;
+  const float* served_bias;  /* see keepvq_routed_topk_args */
+  const float* pool_bias;
+  const uint32_t* slot_of;
+  /* experts, indexed by slot */
+  int64_t slots;
+  keepvq_expert_weights w1;  /* gate  [slots, inter, hidden/8]  */
+  keepvq_expert_weights w3;  /* up    [slots, inter, hidden/8]  */
+  keepvq_expert_weights w2;  /* down  [slots, hidden, inter/8]  */
+  int32_t scales_dtype;      /* dtype of every scales / res_scales array */
+  const uint32_t* codebook;  /* E8P packed abs grid */
+  int64_t res_rows;          /* 0 when no residual tier */
+  const uint32_t* res_table; /* KEEPVQ_TABLE_HALF2_PAIRS */
+  const uint32_t* hot_of_slot; /* [slots] */
+  float swiglu_limit;        /* 0 = plain SwiGLU */
+  /* outputs */
+  void* out;                 /* [tokens, hidden] */
+  uint32_t* served_expert;   /* [tokens, top_k] */
+  uint32_t* served_slot;     /* [tokens, top_k] */
+  float* served_weight;      /* [tokens, top_k] */
+  uint32_t* want;            /* [tokens, top_k] */
+  float* want_score;         /* [tokens, top_k] */
+  int32_t* admit;            /* [tokens, top_k] or NULL */
+  /* scratch, at least keepvq_moe_layer_workspace_bytes(), 256-byte aligned */
+  void* workspace;
+  int64_t workspace_bytes;
+} keepvq_moe_layer_args;
+
+/* Bytes of scratch keepvq_moe_decode_layer needs for these sizes (host arithmetic only). */
+int64_t keepvq_moe_layer_workspace_bytes(int64_t tokens, int64_t hidden, int64_t inter, int64_t pool, int32_t top_k);
+int keepvq_moe_decode_layer(const keepvq_moe_layer_args* args, void* stream);
 
 #ifdef __cplusplus
 }

@@ -8,7 +8,7 @@ from __future__ import annotations
 
 import ctypes
 import threading
-from ctypes import POINTER, Structure, c_char_p, c_int, c_int32, c_int64, c_void_p
+from ctypes import POINTER, Structure, c_char_p, c_float, c_int, c_int32, c_int64, c_void_p
 from pathlib import Path
 
 import torch
@@ -51,12 +51,63 @@ class MatvecArgs(Structure):
     ]
 
 
+class RouterLogitsArgs(Structure):
+    _fields_ = [
+        ("x", c_void_p), ("x_dtype", c_int32), ("router_w", c_void_p), ("router_dtype", c_int32),
+        ("tokens", c_int64), ("pool", c_int64), ("hidden", c_int64), ("gate_temp", c_float), ("logits", c_void_p),
+    ]
+
+
+class RoutedTopkArgs(Structure):
+    _fields_ = [
+        ("logits", c_void_p), ("tokens", c_int64), ("pool", c_int64), ("top_k", c_int32), ("score_func", c_int32),
+        ("norm_topk_prob", c_int32), ("route_scale", c_float), ("tau", c_float),
+        ("served_bias", c_void_p), ("pool_bias", c_void_p), ("slot_of", c_void_p), ("scores", c_void_p),
+        ("served_expert", c_void_p), ("served_slot", c_void_p), ("served_weight", c_void_p),
+        ("want", c_void_p), ("want_score", c_void_p), ("admit", c_void_p),
+    ]
+
+
+class ExpertWeights(Structure):
+    _fields_ = [
+        ("codes", c_void_p), ("scales", c_void_p), ("groups", c_int64),
+        ("res_codes", c_void_p), ("res_scales", c_void_p), ("res_groups", c_int64),
+    ]
+
+
+class MoELayerArgs(Structure):
+    _fields_ = [
+        ("x", c_void_p), ("x_dtype", c_int32), ("tokens", c_int64), ("hidden", c_int64), ("inter", c_int64),
+        ("router_w", c_void_p), ("router_dtype", c_int32), ("pool", c_int64), ("top_k", c_int32),
+        ("score_func", c_int32), ("norm_topk_prob", c_int32), ("gate_temp", c_float), ("route_scale", c_float),
+        ("tau", c_float), ("served_bias", c_void_p), ("pool_bias", c_void_p), ("slot_of", c_void_p),
+        ("slots", c_int64), ("w1", ExpertWeights), ("w3", ExpertWeights), ("w2", ExpertWeights),
+        ("scales_dtype", c_int32), ("codebook", c_void_p), ("res_rows", c_int64), ("res_table", c_void_p),
+        ("hot_of_slot", c_void_p), ("swiglu_limit", c_float),
+        ("out", c_void_p), ("served_expert", c_void_p), ("served_slot", c_void_p), ("served_weight", c_void_p),
+        ("want", c_void_p), ("want_score", c_void_p), ("admit", c_void_p),
+        ("workspace", c_void_p), ("workspace_bytes", c_int64),
+    ]
+
+
+SCORE_FUNCS = {"softmax": 0, "sigmoid": 1, "sqrtsoftplus": 2}
+
+#: ctypes mirror of every argument struct in the header, by its C name (the layout test walks this).
+EXTRA_STRUCTS = {
+    "keepvq_router_logits_args": RouterLogitsArgs, "keepvq_routed_topk_args": RoutedTopkArgs,
+    "keepvq_expert_weights": ExpertWeights, "keepvq_moe_layer_args": MoELayerArgs,
+}
+
 _SIGNATURES = {
     "keepvq_abi_version": (c_int, []),
     "keepvq_status_string": (c_char_p, [c_int]),
     "keepvq_last_cuda_error": (c_char_p, []),
     "keepvq_decode_weights": (c_int, [POINTER(DecodeArgs), c_void_p]),
     "keepvq_routed_matvec": (c_int, [POINTER(MatvecArgs), c_void_p]),
+    "keepvq_router_logits": (c_int, [POINTER(RouterLogitsArgs), c_void_p]),
+    "keepvq_routed_topk": (c_int, [POINTER(RoutedTopkArgs), c_void_p]),
+    "keepvq_moe_layer_workspace_bytes": (c_int64, [c_int64, c_int64, c_int64, c_int64, c_int32]),
+    "keepvq_moe_decode_layer": (c_int, [POINTER(MoELayerArgs), c_void_p]),
 }
 
 _lock = threading.Lock()

@@ -65,7 +65,7 @@ __global__ void __launch_bounds__(MV_WARPS * 32) routed_matvec_kernel(keepvq_mat
   const int64_t N = a.out_dim, cw = a.in_dim / 8;
   const int64_t row0 = (static_cast<int64_t>(blockIdx.y) * MV_WARPS + warp) * MV_ROWS;
 
-  if (CODE_BITS == 8 && !NESTED && slot == KEEPVQ_NO_RESIDUAL) {  // uniform over the block
+  if (slot == KEEPVQ_NO_RESIDUAL) {  // a route that is switched off writes zeros; uniform over the block
     if (lane == 0)
       for (int r = 0; r < MV_ROWS && row0 + r < N; ++r) store_from_float(a.out, a.out_dtype, route * N + row0 + r, 0.0f);
     return;

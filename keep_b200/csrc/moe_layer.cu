@@ -1,0 +1,165 @@
+// keepvq_moe_decode_layer: one routed MoE layer at decode as a single launch sequence.
+//
+// Sequence on the caller's stream (no host read anywhere):
+//   1 router logits            router.cu
+//   2 dual top-k + admission   router.cu
+//   3 gate and up projections  routed matvec, token layout, rounded to the activation dtype
+//   4 h = silu(G) * U * g      this file
+//   5 down projection          routed matvec, one row per route
+//   6 fp32 sum over the k picks, one rounding       this file
+// The rounding points are the served path's (scripts/v41_build/omlx_lattice.py:356-371,583-589).
+//
+// Scratch layout (all regions 256-byte aligned):
+//   logits [tokens, pool] f32 | gate [routes, inter] | up [routes, inter] | h [routes, inter]
+//   | down [routes, hidden]     (activation dtype)
+#include <algorithm>
+#include <type_traits>
+
+#include "common.cuh"
+
+namespace keepvq {
+
+template <typename T>
+struct dtype_tag_of {
+  static constexpr int value = sizeof(T) == 4 ? KEEPVQ_F32 : (std::is_same<T, __half>::value ? KEEPVQ_F16 : KEEPVQ_BF16);
+};
+
+static inline int64_t align256(int64_t v) { return (v + 255) / 256 * 256; }
+
+struct LayerScratch {
+  int64_t logits, gate, up, h, down, total;
+};
+
+static LayerScratch plan_scratch(int64_t tokens, int64_t hidden, int64_t inter, int64_t pool, int32_t top_k) {
+  const int64_t routes = tokens * top_k;
+  LayerScratch s;
+  int64_t at = 0;
+  s.logits = at; at += align256(tokens * pool * 4);
+  s.gate = at;   at += align256(routes * inter * 4);  // sized for fp32 activations
+  s.up = at;     at += align256(routes * inter * 4);
+  s.h = at;      at += align256(routes * inter * 4);
+  s.down = at;   at += align256(routes * hidden * 4);
+  s.total = at;
+  return s;
+}
+
+// h[r, n] = round(silu(G) * U * g_r); a switched-off route (weight 0 / no slot) gives zeros.
+template <typename T>
+__global__ void __launch_bounds__(256) swiglu_weight_kernel(const T* __restrict__ gate, const T* __restrict__ up,
+                                                            const float* __restrict__ weight, T* __restrict__ h,
+                                                            int64_t routes, int64_t inter, float limit) {
+  constexpr int tag = dtype_tag_of<T>::value;
+  const int64_t total = routes * inter;
+  for (int64_t i = blockIdx.x * 256ll + threadIdx.x; i < total; i += 256ll * gridDim.x) {
+    const int64_t r = i / inter;
+    float g = load_as_float(gate, tag, i);
+    float u = load_as_float(up, tag, i);
+    if (limit > 0.0f) { g = fminf(g, limit); u = fminf(fmaxf(u, -limit), limit); }
+    const float v = g / (1.0f + expf(-g)) * u * weight[r];
+    store_from_float(h, tag, i, v);
+  }
+}
+
+// out[t, d] = round(sum_j float(down[t*k + j, d])), summed in pick order.
+template <typename T>
+__global__ void __launch_bounds__(256) combine_kernel(const T* __restrict__ down, T* __restrict__ out, int64_t tokens,
+                                                      int64_t hidden, int top_k) {
+  constexpr int tag = dtype_tag_of<T>::value;
+  const int64_t total = tokens * hidden;
+  for (int64_t i = blockIdx.x * 256ll + threadIdx.x; i < total; i += 256ll * gridDim.x) {
+    const int64_t t = i / hidden, d = i - t * hidden;
+    float y = 0.0f;
+    for (int j = 0; j < top_k; ++j) y += load_as_float(down, tag, (t * top_k + j) * hidden + d);
+    store_from_float(out, tag, i, y);
+  }
+}
+
+template <typename T>
+static void launch_elementwise(const keepvq_moe_layer_args& a, const LayerScratch& sc, cudaStream_t s, bool combine) {
+  char* ws = reinterpret_cast<char*>(a.workspace);
+  const int64_t routes = a.tokens * a.top_k;
+  if (!combine) {
+    const int64_t total = routes * a.inter;
+    const unsigned blocks = static_cast<unsigned>(std::min<int64_t>((total + 255) / 256, 148 * 16));
+    swiglu_weight_kernel<T><<<blocks, 256, 0, s>>>(reinterpret_cast<const T*>(ws + sc.gate), reinterpret_cast<const T*>(ws + sc.up),
+                                                   a.served_weight, reinterpret_cast<T*>(ws + sc.h), routes, a.inter, a.swiglu_limit);
+  } else {
+    const int64_t total = a.tokens * a.hidden;
+    const unsigned blocks = static_cast<unsigned>(std::min<int64_t>((total + 255) / 256, 148 * 16));
+    combine_kernel<T><<<blocks, 256, 0, s>>>(reinterpret_cast<const T*>(ws + sc.down), reinterpret_cast<T*>(a.out), a.tokens, a.hidden, a.top_k);
+  }
+}
+
+static int projection(const keepvq_moe_layer_args& a, const keepvq_expert_weights& w, const void* x, int64_t x_rows,
+                      int64_t in_dim, int64_t out_dim, int32_t x_div, void* out, void* stream) {
+  keepvq_matvec_args m = {};
+  m.x = x; m.x_dtype = a.x_dtype; m.x_rows = x_rows;
+  m.codes = w.codes; m.code_bits = 16; m.scales = w.scales; m.scales_dtype = a.scales_dtype;
+  m.experts = a.slots; m.out_dim = out_dim; m.in_dim = in_dim; m.groups = w.groups;
+  m.codebook = a.codebook; m.codebook_layout = KEEPVQ_TABLE_PACKED;
+  m.rhs = a.served_slot; m.lhs = nullptr; m.x_div = x_div; m.routes = a.tokens * a.top_k;
+  if (w.res_codes && a.res_rows > 0) {
+    m.res_codes = w.res_codes; m.res_scales = w.res_scales; m.res_scales_dtype = a.scales_dtype;
+    m.res_rows = a.res_rows; m.res_groups = w.res_groups; m.res_table = a.res_table; m.hot_of_slot = a.hot_of_slot;
+  }
+  m.out = out; m.out_dtype = a.x_dtype;
+  return keepvq_routed_matvec(&m, stream);
+}
+
+}  // namespace keepvq
+
+extern "C" int64_t keepvq_moe_layer_workspace_bytes(int64_t tokens, int64_t hidden, int64_t inter, int64_t pool, int32_t top_k) {
+  if (tokens < 0 || hidden <= 0 || inter <= 0 || pool <= 0 || top_k <= 0) return KEEPVQ_ERR_SHAPE;
+  return keepvq::plan_scratch(tokens, hidden, inter, pool, top_k).total + 256;
+}
+
+extern "C" int keepvq_moe_decode_layer(const keepvq_moe_layer_args* args, void* stream) {
+  using namespace keepvq;
+  if (!args) return KEEPVQ_ERR_NULL;
+  const keepvq_moe_layer_args& a = *args;
+  if (!valid_dtype(a.x_dtype) || !valid_dtype(a.router_dtype) || !valid_dtype(a.scales_dtype)) return KEEPVQ_ERR_DTYPE;
+  if (a.tokens < 0 || a.hidden <= 0 || a.inter <= 0 || a.pool <= 0 || a.slots <= 0 || a.top_k <= 0) return KEEPVQ_ERR_SHAPE;
+  if (a.hidden % 8 || a.inter % 8) return KEEPVQ_ERR_SHAPE;
+  if (a.tokens == 0) return KEEPVQ_OK;
+  if (!a.x || !a.router_w || !a.out || !a.workspace || !a.codebook) return KEEPVQ_ERR_NULL;
+  if (!a.w1.codes || !a.w3.codes || !a.w2.codes || !a.w1.scales || !a.w3.scales || !a.w2.scales) return KEEPVQ_ERR_NULL;
+  if (!a.served_expert || !a.served_slot || !a.served_weight || !a.want || !a.want_score) return KEEPVQ_ERR_NULL;
+  const LayerScratch sc = plan_scratch(a.tokens, a.hidden, a.inter, a.pool, a.top_k);
+  if (!aligned_to(a.workspace, 256)) return KEEPVQ_ERR_ALIGN;
+  if (a.workspace_bytes < sc.total) return KEEPVQ_ERR_CAPACITY;
+  char* ws = reinterpret_cast<char*>(a.workspace);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int64_t routes = a.tokens * a.top_k;
+
+  keepvq_router_logits_args rl = {};
+  rl.x = a.x; rl.x_dtype = a.x_dtype; rl.router_w = a.router_w; rl.router_dtype = a.router_dtype;
+  rl.tokens = a.tokens; rl.pool = a.pool; rl.hidden = a.hidden; rl.gate_temp = a.gate_temp;
+  rl.logits = reinterpret_cast<float*>(ws + sc.logits);
+  int rc = keepvq_router_logits(&rl, stream);
+  if (rc) return rc;
+
+  keepvq_routed_topk_args tk = {};
+  tk.logits = rl.logits; tk.tokens = a.tokens; tk.pool = a.pool; tk.top_k = a.top_k; tk.score_func = a.score_func;
+  tk.norm_topk_prob = a.norm_topk_prob; tk.route_scale = a.route_scale; tk.tau = a.tau;
+  tk.served_bias = a.served_bias; tk.pool_bias = a.pool_bias; tk.slot_of = a.slot_of;
+  tk.served_expert = a.served_expert; tk.served_slot = a.served_slot; tk.served_weight = a.served_weight;
+  tk.want = a.want; tk.want_score = a.want_score; tk.admit = a.admit;
+  rc = keepvq_routed_topk(&tk, stream);
+  if (rc) return rc;
+
+  rc = projection(a, a.w1, a.x, a.tokens, a.hidden, a.inter, a.top_k, ws + sc.gate, stream);
+  if (rc) return rc;
+  rc = projection(a, a.w3, a.x, a.tokens, a.hidden, a.inter, a.top_k, ws + sc.up, stream);
+  if (rc) return rc;
+  if (a.x_dtype == KEEPVQ_F32) launch_elementwise<float>(a, sc, s, false);
+  else if (a.x_dtype == KEEPVQ_F16) launch_elementwise<__half>(a, sc, s, false);
+  else launch_elementwise<__nv_bfloat16>(a, sc, s, false);
+  KEEPVQ_CHECK_LAUNCH();
+  rc = projection(a, a.w2, ws + sc.h, routes, a.inter, a.hidden, 1, ws + sc.down, stream);
+  if (rc) return rc;
+  if (a.x_dtype == KEEPVQ_F32) launch_elementwise<float>(a, sc, s, true);
+  else if (a.x_dtype == KEEPVQ_F16) launch_elementwise<__half>(a, sc, s, true);
+  else launch_elementwise<__nv_bfloat16>(a, sc, s, true);
+  KEEPVQ_CHECK_LAUNCH();
+  return KEEPVQ_OK;
+}

@@ -1,0 +1,205 @@
+// Router for routed residency: logits, score function, and the dual top-k in one launch pair.
+//
+// What it stands in for (reference, jackmaxwil/keep):
+//   - Gate.forward                 tests/fixtures/v41_reference/model.py:811-829
+//   - gate_masked                  scripts/runpod/v41_reap/local_eval.py:69-90
+//   - the fused served/demand top-k  scripts/v41_build/omlx_lattice.py:77-104,333-338
+//   - the admission test (gate >= tau on renormalised demand weights)
+//                                   scripts/v41_build/omlx_routed.py:184-203
+//
+// keepvq_router_logits: logits[t, e] = (x[t] . W[e]) / gate_temp, fp32.  A warp owns one router
+//   row and a tile of 8 tokens; lanes stride the hidden dimension in 16-byte chunks, so each row
+//   of W is read once per token tile.  Products of bf16 values are exact in fp32; the order of
+//   additions is fixed (lane-sequential, then a butterfly), so results are reproducible.
+// keepvq_routed_topk: one warp per token.  Scores = f(logits); served = top-k of
+//   scores + served_bias (absent experts carry -inf or anything <= -1e29); demand = top-k of
+//   scores + pool_bias; ties go to the lowest expert id; picks come out in descending biased
+//   score, the order torch.topk gives.  The bias selects only; weights come from raw scores.
+#include <math.h>
+
+#include "common.cuh"
+
+namespace keepvq {
+
+constexpr int RL_WARPS = 8;    // router rows per block
+constexpr int RL_TOKENS = 8;   // tokens per block
+constexpr float ABSENT_BIAS = -1e29f;  // served_bias at or below this marks an absent expert
+
+template <typename XT, typename WT>
+__global__ void __launch_bounds__(RL_WARPS * 32) router_logits_kernel(keepvq_router_logits_args a) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int64_t e = static_cast<int64_t>(blockIdx.x) * RL_WARPS + warp;
+  const int64_t t0 = static_cast<int64_t>(blockIdx.y) * RL_TOKENS;
+  if (e >= a.pool) return;
+  const WT* w = reinterpret_cast<const WT*>(a.router_w) + e * a.hidden;
+  const XT* x = reinterpret_cast<const XT*>(a.x);
+  float acc[RL_TOKENS];
+#pragma unroll
+  for (int i = 0; i < RL_TOKENS; ++i) acc[i] = 0.0f;
+  for (int64_t k = lane * 8; k < a.hidden; k += 32 * 8) {
+    float wv[8];
+    load8_as_float<WT>(w + k, wv);
+#pragma unroll
+    for (int i = 0; i < RL_TOKENS; ++i) {
+      if (t0 + i < a.tokens) {
+        float xv[8];
+        load8_as_float<XT>(x + (t0 + i) * a.hidden + k, xv);
+#pragma unroll
+        for (int d = 0; d < 8; ++d) acc[i] = fmaf(xv[d], wv[d], acc[i]);
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < RL_TOKENS; ++i) {
+    float v = acc[i];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, o);
+    if (lane == 0 && t0 + i < a.tokens) a.logits[(t0 + i) * a.pool + e] = v / a.gate_temp;
+  }
+}
+
+// (value, index) max with ties to the lower index, across a warp.
+__device__ __forceinline__ void warp_argmax(float& v, int& i) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xFFFFFFFFu, v, o);
+    const int oi = __shfl_xor_sync(0xFFFFFFFFu, i, o);
+    if (ov > v || (ov == v && oi < i)) { v = ov; i = oi; }
+  }
+}
+
+constexpr int TK_WARPS = 4;
+constexpr int TK_MAX_K = 16;
+
+__global__ void __launch_bounds__(TK_WARPS * 32) routed_topk_kernel(keepvq_routed_topk_args a) {
+  extern __shared__ float smem[];  // per warp: scores[pool]
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int64_t t = static_cast<int64_t>(blockIdx.x) * TK_WARPS + warp;
+  if (t >= a.tokens) return;
+  const int P = static_cast<int>(a.pool), K = a.top_k;
+  float* sc = smem + static_cast<size_t>(warp) * P;
+  const float* lg = a.logits + t * P;
+
+  // ---- score function --------------------------------------------------------------------
+  if (a.score_func == KEEPVQ_SCORE_SOFTMAX) {
+    float m = -INFINITY;
+    for (int e = lane; e < P; e += 32) m = fmaxf(m, lg[e]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
+    float s = 0.0f;
+    for (int e = lane; e < P; e += 32) { const float v = expf(lg[e] - m); sc[e] = v; s += v; }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xFFFFFFFFu, s, o);
+    for (int e = lane; e < P; e += 32) sc[e] = sc[e] / s;
+  } else if (a.score_func == KEEPVQ_SCORE_SIGMOID) {
+    for (int e = lane; e < P; e += 32) sc[e] = 1.0f / (1.0f + expf(-lg[e]));
+  } else {  // sqrt(softplus), softplus linear above 20 as torch computes it
+    for (int e = lane; e < P; e += 32) { const float v = lg[e]; sc[e] = sqrtf(v > 20.0f ? v : log1pf(expf(v))); }
+  }
+  __syncwarp();
+  if (a.scores)
+    for (int e = lane; e < P; e += 32) a.scores[t * P + e] = sc[e];
+
+  // ---- two selections over the same scores -------------------------------------------------
+  int picked[TK_MAX_K];
+  for (int pass = 0; pass < 2; ++pass) {
+    const float* bias = pass == 0 ? a.served_bias : a.pool_bias;
+    for (int j = 0; j < K; ++j) {
+      float best = -INFINITY;
+      int besti = 0x7FFFFFFF;
+      for (int e = lane; e < P; e += 32) {
+        bool used = false;
+        for (int q = 0; q < j; ++q) used |= picked[q] == e;
+        if (used) continue;
+        const float key = sc[e] + (bias ? bias[e] : 0.0f);
+        if (key > best || (key == best && e < besti) || besti == 0x7FFFFFFF) { best = key; besti = e; }
+      }
+      warp_argmax(best, besti);
+      picked[j] = besti;
+    }
+    // every lane now holds the same picks; lane j finishes pick j
+    float raw = 0.0f;
+    bool live = false;
+    if (lane < K) {
+      const int e = picked[lane];
+      raw = sc[e];
+      live = pass == 1 || !a.served_bias || a.served_bias[e] > ABSENT_BIAS;
+      if (!live) raw = 0.0f;  // a masked pick carries no weight (local_eval.py:87)
+    }
+    float sum = raw;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xFFFFFFFFu, sum, o);
+    if (lane < K) {
+      const int e = picked[lane];
+      const int64_t o = t * K + lane;
+      if (pass == 0) {
+        float w = raw;
+        if (a.norm_topk_prob && K > 1) w = w / (sum + 1e-20f);
+        w *= a.route_scale;
+        a.served_weight[o] = w;
+        a.served_expert[o] = live ? static_cast<uint32_t>(e) : KEEPVQ_NO_RESIDUAL;
+        a.served_slot[o] = live ? (a.slot_of ? a.slot_of[e] : static_cast<uint32_t>(e)) : KEEPVQ_NO_RESIDUAL;
+      } else {
+        a.want[o] = static_cast<uint32_t>(e);
+        a.want_score[o] = raw;
+        if (a.admit) {
+          // the policy's own normalisation: always over the k demanded scores (omlx_routed.py:186)
+          const float g = raw / (sum + 1e-20f) * a.route_scale;
+          const bool absent = a.served_bias && a.served_bias[e] <= ABSENT_BIAS;
+          a.admit[o] = (absent && g >= a.tau) ? e : -1;
+        }
+      }
+    }
+  }
+}
+
+template <typename XT>
+static void launch_logits(const keepvq_router_logits_args& a, dim3 grid, cudaStream_t s) {
+  if (a.router_dtype == KEEPVQ_F32) router_logits_kernel<XT, float><<<grid, RL_WARPS * 32, 0, s>>>(a);
+  else if (a.router_dtype == KEEPVQ_F16) router_logits_kernel<XT, __half><<<grid, RL_WARPS * 32, 0, s>>>(a);
+  else router_logits_kernel<XT, __nv_bfloat16><<<grid, RL_WARPS * 32, 0, s>>>(a);
+}
+
+}  // namespace keepvq
+
+extern "C" int keepvq_router_logits(const keepvq_router_logits_args* args, void* stream) {
+  using namespace keepvq;
+  if (!args) return KEEPVQ_ERR_NULL;
+  const keepvq_router_logits_args& a = *args;
+  if (!valid_dtype(a.x_dtype) || !valid_dtype(a.router_dtype)) return KEEPVQ_ERR_DTYPE;
+  if (a.tokens < 0 || a.pool <= 0 || a.hidden <= 0 || a.hidden % 8 != 0) return KEEPVQ_ERR_SHAPE;
+  if (!(a.gate_temp > 0.0f)) return KEEPVQ_ERR_SHAPE;
+  if (a.tokens == 0) return KEEPVQ_OK;
+  if (!a.x || !a.router_w || !a.logits) return KEEPVQ_ERR_NULL;
+  if (!aligned_to(a.x, 16) || !aligned_to(a.router_w, 16)) return KEEPVQ_ERR_ALIGN;
+  const int64_t token_tiles = (a.tokens + RL_TOKENS - 1) / RL_TOKENS;
+  if (token_tiles > 65535) return KEEPVQ_ERR_CAPACITY;
+  dim3 grid(static_cast<unsigned>((a.pool + RL_WARPS - 1) / RL_WARPS), static_cast<unsigned>(token_tiles));
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (a.x_dtype == KEEPVQ_F32) launch_logits<float>(a, grid, s);
+  else if (a.x_dtype == KEEPVQ_F16) launch_logits<__half>(a, grid, s);
+  else launch_logits<__nv_bfloat16>(a, grid, s);
+  KEEPVQ_CHECK_LAUNCH();
+  return KEEPVQ_OK;
+}
+
+extern "C" int keepvq_routed_topk(const keepvq_routed_topk_args* args, void* stream) {
+  using namespace keepvq;
+  if (!args) return KEEPVQ_ERR_NULL;
+  const keepvq_routed_topk_args& a = *args;
+  if (a.tokens < 0 || a.pool <= 0 || a.top_k <= 0 || a.top_k > TK_MAX_K || a.top_k > a.pool) return KEEPVQ_ERR_SHAPE;
+  if (a.score_func < KEEPVQ_SCORE_SOFTMAX || a.score_func > KEEPVQ_SCORE_SQRT_SOFTPLUS) return KEEPVQ_ERR_DTYPE;
+  if (a.tokens == 0) return KEEPVQ_OK;
+  if (!a.logits || !a.served_slot || !a.served_expert || !a.served_weight || !a.want || !a.want_score) return KEEPVQ_ERR_NULL;
+  const size_t smem = static_cast<size_t>(TK_WARPS) * a.pool * sizeof(float);
+  if (smem > 200 * 1024) return KEEPVQ_ERR_CAPACITY;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(routed_topk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (e != cudaSuccess) return note_cuda_error(e);
+  }
+  const unsigned blocks = static_cast<unsigned>((a.tokens + TK_WARPS - 1) / TK_WARPS);
+  routed_topk_kernel<<<blocks, TK_WARPS * 32, smem, s>>>(a);
+  KEEPVQ_CHECK_LAUNCH();
+  return KEEPVQ_OK;
+}

@@ -1,0 +1,131 @@
+"""One routed MoE layer over E8P experts: the fused decode step.
+
+``RoutedMoELayer.decode(x)`` is the call a serving loop makes per layer.  It stands in for the
+reference's decode step (``scripts/v41_build/omlx_lattice.py:327-371``: stock gate -> fused top-k
+-> ``e8p_m1`` / ``e8p_nested_m1`` gate, up, down -> sum over the picks) and, without a residency
+mask, for ``QuantizedVQSwitchGLU`` plus the weighted sum
+(``src/ramp/models/glm4_moe_adapter.py:367-372``, ``deepseek_v4_flash_adapter.py:1781-1784``).
+Everything runs in ``keepvq_moe_decode_layer``: one launch sequence, no host read.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+from . import _lib
+from .router import Routing
+from .vq import as_device, table_on
+
+
+@dataclass
+class Projection:
+    """Codes ``[slots, out, in/8]`` uint16 and scales ``[slots, out, groups]`` of one projection,
+    plus the optional 8-bit residual arrays ``[res_rows, out, in/8]`` / ``[res_rows, out, res_groups]``."""
+
+    codes: torch.Tensor
+    scales: torch.Tensor
+    res_codes: torch.Tensor | None = None
+    res_scales: torch.Tensor | None = None
+
+    def struct(self) -> _lib.ExpertWeights:
+        return _lib.ExpertWeights(
+            codes=_lib.ptr(self.codes), scales=_lib.ptr(self.scales), groups=int(self.scales.shape[2]),
+            res_codes=_lib.ptr(self.res_codes), res_scales=_lib.ptr(self.res_scales),
+            res_groups=int(self.res_scales.shape[2]) if self.res_scales is not None else 0)
+
+
+class RoutedMoELayer:
+    """Router + resident experts of one layer.
+
+    ``w1`` (gate), ``w3`` (up): ``[slots, inter, hidden/8]``; ``w2`` (down): ``[slots, hidden, inter/8]``.
+    Residency state is three device arrays the caller may rewrite between calls: ``served_bias``
+    ``[pool]`` (``router.OFF`` on absent experts), ``slot_of`` ``[pool]`` and, with a residual tier,
+    ``hot_of_slot`` ``[slots]``.  With ``served_bias=None`` every expert is resident and
+    ``slot_of`` is the identity.
+    """
+
+    def __init__(self, router_w, w1: Projection, w3: Projection, w2: Projection, *, top_k: int, score_func: str = "softmax",
+                 route_scale: float = 1.0, tau: float = 0.3, gate_temp: float = 1.0, norm_topk_prob: bool = True,
+                 served_bias=None, pool_bias=None, slot_of=None, hot_of_slot=None, res_table=None, codebook=None,
+                 swiglu_limit: float = 0.0):
+        if score_func not in _lib.SCORE_FUNCS:
+            raise ValueError("score_func must be 'softmax', 'sigmoid' or 'sqrtsoftplus'")
+        self.device = _lib.require_cuda(router_w, w1.codes, w3.codes, w2.codes)
+        self.router_w = router_w.contiguous()
+        self.w1, self.w3, self.w2 = w1, w3, w2
+        for p in (w1, w3, w2):
+            if p.codes.dtype != torch.uint16:
+                raise ValueError(f"expert codes must be uint16, found {p.codes.dtype}")
+            if p.scales.dtype != w1.scales.dtype:
+                raise ValueError("all scales must share one dtype")
+        self.slots, self.inter, cw = (int(s) for s in w1.codes.shape)
+        self.hidden, self.pool = cw * 8, int(router_w.shape[0])
+        if tuple(w3.codes.shape) != tuple(w1.codes.shape) or tuple(w2.codes.shape) != (self.slots, self.hidden, self.inter // 8):
+            raise ValueError("w1/w3 must be [slots, inter, hidden/8] and w2 [slots, hidden, inter/8]")
+        if int(router_w.shape[1]) != self.hidden:
+            raise ValueError("router_w must be [pool, hidden]")
+        self.top_k, self.score_func = int(top_k), score_func
+        self.route_scale, self.tau, self.gate_temp = float(route_scale), float(tau), float(gate_temp)
+        self.norm_topk_prob, self.swiglu_limit = bool(norm_topk_prob), float(swiglu_limit)
+        f32 = lambda t: None if t is None else as_device(t, self.device).to(torch.float32).contiguous()  # noqa: E731
+        u32 = lambda t: None if t is None else as_device(t, self.device).contiguous()  # noqa: E731
+        self.served_bias, self.pool_bias = f32(served_bias), f32(pool_bias)
+        self.slot_of, self.hot_of_slot = u32(slot_of), u32(hot_of_slot)
+        if self.served_bias is None and self.slot_of is None and self.slots != self.pool:
+            raise ValueError("with every expert resident, codes must hold one slot per pool expert")
+        self.codebook = table_on(self.device, "e8p") if codebook is None else as_device(codebook, self.device).contiguous()
+        self.res_rows = int(w1.res_codes.shape[0]) if w1.res_codes is not None else 0
+        self.res_table = None
+        if self.res_rows:
+            if self.hot_of_slot is None:
+                raise ValueError("a residual tier needs hot_of_slot")
+            self.res_table = table_on(self.device, "e8_1bit_half2") if res_table is None else as_device(res_table, self.device).contiguous()
+        self._buffers: dict[tuple, dict] = {}
+
+    def _buffers_for(self, tokens: int, dtype: torch.dtype) -> dict:
+        key = (tokens, dtype)
+        if key not in self._buffers:
+            lib = _lib.load()
+            nbytes = int(lib.keepvq_moe_layer_workspace_bytes(tokens, self.hidden, self.inter, self.pool, self.top_k))
+            if nbytes < 0:
+                _lib.check(nbytes, "keepvq_moe_layer_workspace_bytes")
+            dev, k = self.device, self.top_k
+            i32 = lambda: torch.empty((tokens, k), dtype=torch.int32, device=dev)  # noqa: E731
+            f32 = lambda: torch.empty((tokens, k), dtype=torch.float32, device=dev)  # noqa: E731
+            self._buffers[key] = dict(
+                workspace=torch.empty(nbytes, dtype=torch.uint8, device=dev), nbytes=nbytes,
+                out=torch.empty((tokens, self.hidden), dtype=dtype, device=dev),
+                routing=Routing(served_expert=i32(), served_slot=i32(), served_weight=f32(), want=i32(), want_score=f32(), admit=i32()))
+        return self._buffers[key]
+
+    def decode(self, x: torch.Tensor, *, out: torch.Tensor | None = None) -> tuple[torch.Tensor, Routing]:
+        """``x`` [tokens, hidden] -> (``[tokens, hidden]`` in x's dtype, routing outputs).
+
+        Buffers are cached per (tokens, dtype) and reused by the next call of the same shape, so
+        the call is CUDA-graph capturable after one warm-up call; copy results you want to keep.
+        """
+        _lib.require_cuda(x)
+        if x.ndim != 2 or int(x.shape[1]) != self.hidden:
+            raise ValueError(f"x must be [tokens, {self.hidden}], found {tuple(x.shape)}")
+        x = x.contiguous()
+        tokens = int(x.shape[0])
+        buf = self._buffers_for(tokens, x.dtype)
+        r: Routing = buf["routing"]
+        target = buf["out"] if out is None else out
+        args = _lib.MoELayerArgs(
+            x=_lib.ptr(x), x_dtype=_lib.dtype_tag(x.dtype), tokens=tokens, hidden=self.hidden, inter=self.inter,
+            router_w=_lib.ptr(self.router_w), router_dtype=_lib.dtype_tag(self.router_w.dtype), pool=self.pool,
+            top_k=self.top_k, score_func=_lib.SCORE_FUNCS[self.score_func], norm_topk_prob=int(self.norm_topk_prob),
+            gate_temp=self.gate_temp, route_scale=self.route_scale, tau=self.tau,
+            served_bias=_lib.ptr(self.served_bias), pool_bias=_lib.ptr(self.pool_bias), slot_of=_lib.ptr(self.slot_of),
+            slots=self.slots, w1=self.w1.struct(), w3=self.w3.struct(), w2=self.w2.struct(),
+            scales_dtype=_lib.dtype_tag(self.w1.scales.dtype), codebook=_lib.ptr(self.codebook), res_rows=self.res_rows,
+            res_table=_lib.ptr(self.res_table), hot_of_slot=_lib.ptr(self.hot_of_slot), swiglu_limit=self.swiglu_limit,
+            out=_lib.ptr(target), served_expert=_lib.ptr(r.served_expert), served_slot=_lib.ptr(r.served_slot),
+            served_weight=_lib.ptr(r.served_weight), want=_lib.ptr(r.want), want_score=_lib.ptr(r.want_score),
+            admit=_lib.ptr(r.admit), workspace=_lib.ptr(buf["workspace"]), workspace_bytes=buf["nbytes"])
+        with torch.cuda.device(self.device):
+            _lib.check(_lib.load().keepvq_moe_decode_layer(args, _lib.stream_handle(self.device)), "keepvq_moe_decode_layer")
+        return target, r

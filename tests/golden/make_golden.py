@@ -133,6 +133,34 @@ def operator_fixture(checkout: Path) -> None:
     )
 
 
+def router_fixture(checkout: Path) -> None:
+    """Outputs of the reference's ``gate_masked`` (scripts/runpod/v41_reap/local_eval.py:69-90) on
+    seeded inputs, for the three score functions, with and without a residency mask and with
+    fewer allowed experts than top-k."""
+    import types
+
+    import torch
+
+    sys.path.insert(0, str(checkout / "scripts" / "runpod" / "v41_reap"))
+    local_eval = load_by_path("keep_reference_local_eval", checkout / "scripts" / "runpod" / "v41_reap" / "local_eval.py")
+    rng = np.random.default_rng(41)
+    pool, dim, tokens, k = 24, 64, 9, 4
+    weight = rng.normal(scale=0.3, size=(pool, dim)).astype(np.float32)
+    x = rng.normal(size=(tokens, dim)).astype(np.float32)
+    bias = (0.01 * rng.normal(size=pool)).astype(np.float32)
+    allowed = rng.random((tokens, pool)) < 0.5
+    few = np.zeros((tokens, pool), dtype=bool)
+    few[:, [3, 17]] = True
+    out = dict(weight=weight, x=x, bias=bias, allowed=allowed, few=few, top_k=np.int64(k))
+    for func in ("softmax", "sigmoid", "sqrtsoftplus"):
+        gate = types.SimpleNamespace(weight=torch.from_numpy(weight), bias=torch.from_numpy(bias), gate_temp=1.25,
+                                     score_func=func, topk=k, norm_topk_prob=True, route_scale=1.5)
+        for name, mask in (("all", np.ones((tokens, pool), dtype=bool)), ("masked", allowed), ("few", few)):
+            w, i = local_eval.gate_masked(gate, torch.from_numpy(x), torch.from_numpy(mask), torch.nn.functional.linear)
+            out[f"{func}_{name}_weights"], out[f"{func}_{name}_indices"] = w.numpy(), i.numpy()
+    np.savez_compressed(HERE / "router.npz", **out)
+
+
 def main() -> None:
     checkout = Path(sys.argv[1]).resolve()
     sys.path.insert(0, str(checkout / "src"))
@@ -140,6 +168,7 @@ def main() -> None:
 
     codebook_fixture(e8)
     operator_fixture(checkout)
+    router_fixture(checkout)
     for f in sorted(HERE.glob("*.npz")):
         print(f.name, f.stat().st_size, "bytes")
 

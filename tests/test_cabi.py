@@ -10,7 +10,7 @@ def declared_entry_points():
     names = []
     for header in sorted((ROOT / "include").glob("*.h")):
         text = re.sub(r"/\*.*?\*/", "", header.read_text(), flags=re.S)
-        names += re.findall(r"^\s*(?:const\s+char\s*\*|int)\s+(keepvq_\w+)\s*\(", text, flags=re.M)
+        names += re.findall(r"^\s*(?:const\s+char\s*\*|int64_t|int)\s+(keepvq_\w+)\s*\(", text, flags=re.M)
     return names
 
 

@@ -1,0 +1,109 @@
+"""The fused decode layer against the CPU oracle: routing exact, outputs within the stated bf16
+tolerance (max|got - want| / max|want| <= 1e-2), cosine similarity reported."""
+
+import numpy as np
+import pytest
+import torch
+
+import synthetic
+from oracle import e8, router as oracle_router
+
+pytestmark = pytest.mark.gpu
+TOLERANCE = 1e-2  # max relative gap the path promises for bf16 activations
+
+
+def build_layer(cuda, cfg, **kw):
+    from keep_b200 import moe
+
+    def proj(name, res=None):
+        codes, scales = cfg[name]
+        rc, rs = (None, None) if res is None else res[name]
+        dev = lambda a: None if a is None else torch.from_numpy(a).to(cuda)  # noqa: E731
+        return moe.Projection(dev(codes), dev(scales), dev(rc), dev(rs))
+
+    res = kw.pop("res", None)
+    return moe.RoutedMoELayer(cfg["router"].to(cuda), proj("w1", res), proj("w3", res), proj("w2", res), **kw)
+
+
+def check_layer(cfg, x, out, routing, *, top_k, served_bias=None, pool_bias=None, slot_of=None, res=None, hot_of_slot=None,
+                **router_kw):
+    want = oracle_router.routed_topk(x, cfg["router"], served_bias, pool_bias, slot_of, top_k=top_k, **router_kw)
+    assert oracle_router.min_cut_gap(want["served_keys"], top_k) > 0
+    np.testing.assert_array_equal(routing.served_expert.cpu().numpy(), want["served_expert"].numpy())
+    np.testing.assert_array_equal(routing.served_slot.cpu().numpy(), want["served_slot"].numpy())
+    np.testing.assert_array_equal(routing.want.cpu().numpy(), want["want"].numpy())
+    np.testing.assert_array_equal(routing.admit.cpu().numpy(), want["admit"].numpy())
+    np.testing.assert_allclose(routing.served_weight.cpu().numpy(), want["served_weight"].numpy(), rtol=2e-5)
+    slots = want["served_slot"].numpy()
+    dense = {n: oracle_router.dense_slots(*cfg[n], slots, res=None if res is None else res[n], hot_of_slot=hot_of_slot)
+             for n in ("w1", "w3", "w2")}
+    ref = oracle_router.moe_layer(x, slots, want["served_weight"].numpy(), dense["w1"], dense["w3"], dense["w2"])
+    got = out.float().cpu().numpy()
+    gap, cos = e8.relative_gap(got, ref.numpy()), e8.cosine_similarity(got, ref.numpy())
+    print(f"layer output: relative gap {gap:.3e}, cosine {cos:.8f}")
+    assert gap <= TOLERANCE and cos >= 0.9999
+    return gap, cos
+
+
+@pytest.mark.parametrize("tokens", [1, 5])
+def test_small_layer_all_resident(cuda, tokens):
+    cfg = synthetic.layer(seed=2, experts=12, hidden=256, inter=128)
+    x = synthetic.tokens(3 + tokens, tokens, 256)
+    layer = build_layer(cuda, cfg, top_k=3)
+    out, routing = layer.decode(x.to(cuda))
+    assert out.dtype == torch.bfloat16 and tuple(out.shape) == (tokens, 256)
+    check_layer(cfg, x, out, routing, top_k=3)
+
+
+def test_small_layer_grouped_scales_and_fp16(cuda):
+    cfg = synthetic.layer(seed=4, experts=10, hidden=512, inter=256, group_hidden=64, group_inter=128)
+    x = synthetic.tokens(9, 4, 512)
+    layer = build_layer(cuda, cfg, top_k=4, score_func="sqrtsoftplus", route_scale=1.5)
+    out, routing = layer.decode(x.to(cuda))
+    check_layer(cfg, x, out, routing, top_k=4, score_func="sqrtsoftplus", route_scale=1.5)
+
+
+def test_residency_mask_and_nested_residual(cuda):
+    """Half the pool resident, a residual tier on some slots, admissions at tau = 0.3."""
+    rng = np.random.default_rng(8)
+    pool, slots, hidden, inter, k = 16, 8, 256, 128, 3
+    cfg = synthetic.layer(seed=6, experts=pool, hidden=hidden, inter=inter)
+    resident = np.sort(rng.choice(pool, slots, replace=False))
+    slot_of = np.full(pool, 0xFFFFFFFF, dtype=np.uint32)
+    slot_of[resident] = rng.permutation(slots).astype(np.uint32)
+    served_bias = np.full(pool, oracle_router.OFF, dtype=np.float32)
+    served_bias[resident] = 0.0
+    slot_cfg = dict(cfg)  # weight arrays are indexed by slot: slot s holds expert resident-of-slot
+    expert_of_slot = np.empty(slots, dtype=np.int64)
+    expert_of_slot[slot_of[resident].astype(np.int64)] = resident
+    for n in ("w1", "w3", "w2"):
+        slot_cfg[n] = (cfg[n][0][expert_of_slot], cfg[n][1][expert_of_slot])
+    res = synthetic.residual_tier(7, 3, hidden, inter)
+    hot_of_slot = np.full(slots, 0xFFFFFFFF, dtype=np.uint32)
+    hot_of_slot[[1, 4, 6]] = [2, 0, 1]
+    x = synthetic.tokens(10, 6, hidden)
+    layer = build_layer(cuda, slot_cfg, top_k=k, served_bias=served_bias, slot_of=slot_of, hot_of_slot=hot_of_slot, res=res, tau=0.3)
+    out, routing = layer.decode(x.to(cuda))
+    check_layer(slot_cfg, x, out, routing, top_k=k, served_bias=served_bias, slot_of=slot_of, res=res, hot_of_slot=hot_of_slot, tau=0.3)
+    assert (routing.admit.cpu().numpy() >= 0).any(), "seed should produce at least one admission"
+
+
+def test_fewer_residents_than_top_k_leaves_dead_picks_at_zero(cuda):
+    cfg = synthetic.layer(seed=11, experts=6, hidden=128, inter=64)
+    served_bias = np.array([0, oracle_router.OFF, oracle_router.OFF, 0, oracle_router.OFF, oracle_router.OFF], dtype=np.float32)
+    x = synthetic.tokens(12, 3, 128)
+    layer = build_layer(cuda, cfg, top_k=3, served_bias=served_bias, slot_of=np.arange(6, dtype=np.uint32))
+    out, routing = layer.decode(x.to(cuda))
+    assert ((routing.served_slot.cpu().numpy() >= 0).sum(-1) == 2).all()
+    check_layer(cfg, x, out, routing, top_k=3, served_bias=served_bias, slot_of=np.arange(6))
+
+
+@pytest.mark.parametrize("batch", [1, 16])
+def test_config2_shape_decode_layer(cuda, batch):
+    """The benchmark layer shape (hidden 4096, inter 2048, top-6, softmax) on a 48-expert slice of
+    the pool so the CPU oracle finishes in seconds; tokens bf16 N(0,1), seed 1 + batch."""
+    cfg = synthetic.layer(seed=0, experts=48)
+    x = synthetic.tokens(1 + batch, batch, 4096)
+    layer = build_layer(cuda, cfg, top_k=6)
+    out, routing = layer.decode(x.to(cuda))
+    check_layer(cfg, x, out, routing, top_k=6)
