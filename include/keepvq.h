@@ -245,6 +245,8 @@ typedef struct keepvq_moe_layer_args {
   const uint32_t* res_table; /* KEEPVQ_TABLE_HALF2_PAIRS */
   const uint32_t* hot_of_slot; /* [slots] */
   float swiglu_limit;        /* 0 = plain SwiGLU */
+  int32_t codebook_all_odd;  /* caller vouches that every nibble of `codebook` is odd (the E8P table
+                                is); allows the int8 tensor-core kernels.  0 = general kernels */
   /* outputs */
   void* out;                 /* [tokens, hidden] */
   uint32_t* served_expert;   /* [tokens, top_k] */
@@ -261,6 +263,20 @@ typedef struct keepvq_moe_layer_args {
 /* Bytes of scratch keepvq_moe_decode_layer needs for these sizes (host arithmetic only). */
 int64_t keepvq_moe_layer_workspace_bytes(int64_t tokens, int64_t hidden, int64_t inter, int64_t pool, int32_t top_k);
 int keepvq_moe_decode_layer(const keepvq_moe_layer_args* args, void* stream);
+
+/* The same sequence, cut into stages: run the stages named in `stages` (a mask) on the same
+ * arguments and scratch.  A later stage reads what earlier ones left in the outputs and the
+ * scratch, so a profiler or benchmark can replay one stage after a full run.  No counterpart in
+ * the reference; its stages are separate MLX ops (scripts/v41_build/omlx_lattice.py:332-371). */
+typedef enum keepvq_moe_stage {
+  KEEPVQ_STAGE_ROUTER = 1,   /* logits + dual top-k */
+  KEEPVQ_STAGE_PREPARE = 2,  /* route grouping + activation quantisation (tensor-core kernels only) */
+  KEEPVQ_STAGE_GATE_UP = 4,  /* gate, up, SwiGLU * weight */
+  KEEPVQ_STAGE_DOWN = 8,     /* down projection */
+  KEEPVQ_STAGE_COMBINE = 16, /* sum over the k picks */
+  KEEPVQ_STAGE_ALL = 31
+} keepvq_moe_stage;
+int keepvq_moe_decode_stages(const keepvq_moe_layer_args* args, int32_t stages, void* stream);
 
 #ifdef __cplusplus
 }

@@ -83,7 +83,7 @@ class MoELayerArgs(Structure):
         ("tau", c_float), ("served_bias", c_void_p), ("pool_bias", c_void_p), ("slot_of", c_void_p),
         ("slots", c_int64), ("w1", ExpertWeights), ("w3", ExpertWeights), ("w2", ExpertWeights),
         ("scales_dtype", c_int32), ("codebook", c_void_p), ("res_rows", c_int64), ("res_table", c_void_p),
-        ("hot_of_slot", c_void_p), ("swiglu_limit", c_float),
+        ("hot_of_slot", c_void_p), ("swiglu_limit", c_float), ("codebook_all_odd", c_int32),
         ("out", c_void_p), ("served_expert", c_void_p), ("served_slot", c_void_p), ("served_weight", c_void_p),
         ("want", c_void_p), ("want_score", c_void_p), ("admit", c_void_p),
         ("workspace", c_void_p), ("workspace_bytes", c_int64),
@@ -91,6 +91,7 @@ class MoELayerArgs(Structure):
 
 
 SCORE_FUNCS = {"softmax": 0, "sigmoid": 1, "sqrtsoftplus": 2}
+STAGE_ROUTER, STAGE_PREPARE, STAGE_GATE_UP, STAGE_DOWN, STAGE_COMBINE, STAGE_ALL = 1, 2, 4, 8, 16, 31
 
 #: ctypes mirror of every argument struct in the header, by its C name (the layout test walks this).
 EXTRA_STRUCTS = {
@@ -108,6 +109,7 @@ _SIGNATURES = {
     "keepvq_routed_topk": (c_int, [POINTER(RoutedTopkArgs), c_void_p]),
     "keepvq_moe_layer_workspace_bytes": (c_int64, [c_int64, c_int64, c_int64, c_int64, c_int32]),
     "keepvq_moe_decode_layer": (c_int, [POINTER(MoELayerArgs), c_void_p]),
+    "keepvq_moe_decode_stages": (c_int, [POINTER(MoELayerArgs), c_int32, c_void_p]),
 }
 
 _lock = threading.Lock()

@@ -1,0 +1,66 @@
+// Internal interface of the tensor-core decode path (moe_fast.cu), used by moe_layer.cu.
+//
+// The idea.  A 16-bit E8P codeword decodes to eight weights w = s*h/2 + p/4, with h an odd
+// integer from the abs table (|h| in {1,3,5}), s the sign bit and p = +-1 by the parity of the
+// sign byte.  Then 4w = 2q + 1 for the integer q = h ^ (neg ? 0xFE : 0) ^ parity, which is pure
+// bit arithmetic on a byte.  So a row's dot product with integer activations x' is
+//     4 * sum_k w_k x'_k = 2 * sum_k q_k x'_k + sum_k x'_k,
+// an exact int8 tensor-core product plus one per-token constant.  Activations are quantised per
+// row to 16-bit fixed point (power-of-two scale) and fed as a signed high byte and an unsigned
+// low byte, two MMAs per tile.  The only rounding in a projection is that fixed-point step.
+#pragma once
+
+#include "common.cuh"
+
+namespace keepvq {
+namespace fast {
+
+constexpr int MAX_GROUP_ROUTES = 8;  // routes of one expert that share an MMA tile (its 8 columns)
+
+// Quantised activation rows: the B operand of the projections.
+struct QuantRows {
+  uint8_t* q;       // [rows, in_dim/8, 16]: per codeword 4 words: hi(dims 6,4,2,0) hi(7,5,3,1) lo(...) lo(...)
+  float* scale;     // [rows] power of two: x ~= scale * x'
+  int32_t* sums;    // [rows, groups] sum of x' over each scale group
+};
+
+// Routes grouped by the slot they are served from.
+struct RouteGroups {
+  int32_t* count;        // [1] number of groups
+  int32_t* slot;         // [max_groups]
+  int32_t* start;        // [max_groups] first entry in `routes`
+  int32_t* size;         // [max_groups] 1..MAX_GROUP_ROUTES
+  int32_t* routes;       // [routes] route ids ordered by group
+};
+
+struct Projection {
+  const uint16_t* codes;  // [slots, out_dim, in_dim/8]
+  const void* scales;     // [slots, out_dim, groups]
+};
+
+struct FastProjectionArgs {
+  Projection a;           // gate (or down)
+  Projection b;           // up, or {nullptr, nullptr} for a single projection
+  int32_t scales_dtype;
+  int64_t out_dim, in_dim, groups;
+  const uint32_t* codebook;
+  QuantRows x;            // activations
+  int32_t x_div;          // activation row of route r is r / x_div
+  RouteGroups groups_of_routes;
+  const float* route_weight;  // [routes] gate weight (gate/up only)
+  float swiglu_limit;
+  void* out;              // [routes, out_dim]
+  int32_t out_dtype;
+  int64_t max_routes;
+};
+
+// True when the shapes fit the tensor-core path (in_dim % 256 == 0, group size % 256 == 0, ...).
+bool shapes_supported(int64_t out_dim, int64_t in_dim, int64_t groups);
+
+int quantize_rows(const void* x, int32_t x_dtype, int64_t rows, int64_t in_dim, int64_t groups, const QuantRows& out, cudaStream_t s);
+int group_routes(const uint32_t* served_slot, int64_t routes, int64_t slots, const RouteGroups& out, cudaStream_t s);
+int gate_up(const FastProjectionArgs& args, cudaStream_t s);   // h = round(silu(G) * U * weight)
+int down(const FastProjectionArgs& args, cudaStream_t s);      // out = round(W2 h)
+
+}  // namespace fast
+}  // namespace keepvq

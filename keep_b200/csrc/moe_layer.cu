@@ -9,13 +9,21 @@
 //   6 fp32 sum over the k picks, one rounding       this file
 // The rounding points are the served path's (scripts/v41_build/omlx_lattice.py:356-371,583-589).
 //
+// Two sets of kernels serve steps 3-5.  The tensor-core set (moe_fast.cu) groups routes by slot,
+// quantises activations to 16-bit fixed point and runs the projections on the int8 tensor cores,
+// SwiGLU fused into the gate/up epilogue; it needs a table whose entries are all odd half-units
+// (true of the E8P table; the caller vouches with `codebook_all_odd`), input dims and scale groups
+// that are multiples of 256, and no residual tier.  Everything else takes the general kernels.
+//
 // Scratch layout (all regions 256-byte aligned):
 //   logits [tokens, pool] f32 | gate [routes, inter] | up [routes, inter] | h [routes, inter]
 //   | down [routes, hidden]     (activation dtype)
+//   | quantised x, quantised h, their scales and group sums, the route groups   (tensor-core set)
 #include <algorithm>
 #include <type_traits>
 
 #include "common.cuh"
+#include "moe_fast.cuh"
 
 namespace keepvq {
 
@@ -27,7 +35,9 @@ struct dtype_tag_of {
 static inline int64_t align256(int64_t v) { return (v + 255) / 256 * 256; }
 
 struct LayerScratch {
-  int64_t logits, gate, up, h, down, total;
+  int64_t logits, gate, up, h, down;
+  int64_t xq, xscale, xsums, hq, hscale, hsums, gcount, gslot, gstart, gsize, groutes;
+  int64_t total;
 };
 
 static LayerScratch plan_scratch(int64_t tokens, int64_t hidden, int64_t inter, int64_t pool, int32_t top_k) {
@@ -39,6 +49,17 @@ static LayerScratch plan_scratch(int64_t tokens, int64_t hidden, int64_t inter, 
   s.up = at;     at += align256(routes * inter * 4);
   s.h = at;      at += align256(routes * inter * 4);
   s.down = at;   at += align256(routes * hidden * 4);
+  s.xq = at;     at += align256(tokens * hidden * 2);
+  s.xscale = at; at += align256(tokens * 4);
+  s.xsums = at;  at += align256(tokens * (hidden / 8) * 4);  // room for one scale group per codeword
+  s.hq = at;     at += align256(routes * inter * 2);
+  s.hscale = at; at += align256(routes * 4);
+  s.hsums = at;  at += align256(routes * (inter / 8) * 4);
+  s.gcount = at; at += 256;
+  s.gslot = at;  at += align256(routes * 4);
+  s.gstart = at; at += align256(routes * 4);
+  s.gsize = at;  at += align256(routes * 4);
+  s.groutes = at; at += align256(routes * 4);
   s.total = at;
   return s;
 }
@@ -113,7 +134,7 @@ extern "C" int64_t keepvq_moe_layer_workspace_bytes(int64_t tokens, int64_t hidd
   return keepvq::plan_scratch(tokens, hidden, inter, pool, top_k).total + 256;
 }
 
-extern "C" int keepvq_moe_decode_layer(const keepvq_moe_layer_args* args, void* stream) {
+extern "C" int keepvq_moe_decode_stages(const keepvq_moe_layer_args* args, int32_t stages, void* stream) {
   using namespace keepvq;
   if (!args) return KEEPVQ_ERR_NULL;
   const keepvq_moe_layer_args& a = *args;
@@ -124,42 +145,80 @@ extern "C" int keepvq_moe_decode_layer(const keepvq_moe_layer_args* args, void* 
   if (!a.x || !a.router_w || !a.out || !a.workspace || !a.codebook) return KEEPVQ_ERR_NULL;
   if (!a.w1.codes || !a.w3.codes || !a.w2.codes || !a.w1.scales || !a.w3.scales || !a.w2.scales) return KEEPVQ_ERR_NULL;
   if (!a.served_expert || !a.served_slot || !a.served_weight || !a.want || !a.want_score) return KEEPVQ_ERR_NULL;
+  if (a.w1.groups <= 0 || a.w3.groups != a.w1.groups || a.w2.groups <= 0) return KEEPVQ_ERR_SHAPE;
   const LayerScratch sc = plan_scratch(a.tokens, a.hidden, a.inter, a.pool, a.top_k);
   if (!aligned_to(a.workspace, 256)) return KEEPVQ_ERR_ALIGN;
   if (a.workspace_bytes < sc.total) return KEEPVQ_ERR_CAPACITY;
   char* ws = reinterpret_cast<char*>(a.workspace);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int64_t routes = a.tokens * a.top_k;
+  const bool residual = a.res_rows > 0 && (a.w1.res_codes || a.w3.res_codes || a.w2.res_codes);
+  const bool tensor_path = a.codebook_all_odd && !residual && fast::shapes_supported(a.inter, a.hidden, a.w1.groups) &&
+                           fast::shapes_supported(a.hidden, a.inter, a.w2.groups);
+  int rc = KEEPVQ_OK;
 
-  keepvq_router_logits_args rl = {};
-  rl.x = a.x; rl.x_dtype = a.x_dtype; rl.router_w = a.router_w; rl.router_dtype = a.router_dtype;
-  rl.tokens = a.tokens; rl.pool = a.pool; rl.hidden = a.hidden; rl.gate_temp = a.gate_temp;
-  rl.logits = reinterpret_cast<float*>(ws + sc.logits);
-  int rc = keepvq_router_logits(&rl, stream);
-  if (rc) return rc;
+  if (stages & KEEPVQ_STAGE_ROUTER) {
+    keepvq_router_logits_args rl = {};
+    rl.x = a.x; rl.x_dtype = a.x_dtype; rl.router_w = a.router_w; rl.router_dtype = a.router_dtype;
+    rl.tokens = a.tokens; rl.pool = a.pool; rl.hidden = a.hidden; rl.gate_temp = a.gate_temp;
+    rl.logits = reinterpret_cast<float*>(ws + sc.logits);
+    if ((rc = keepvq_router_logits(&rl, stream))) return rc;
+    keepvq_routed_topk_args tk = {};
+    tk.logits = rl.logits; tk.tokens = a.tokens; tk.pool = a.pool; tk.top_k = a.top_k; tk.score_func = a.score_func;
+    tk.norm_topk_prob = a.norm_topk_prob; tk.route_scale = a.route_scale; tk.tau = a.tau;
+    tk.served_bias = a.served_bias; tk.pool_bias = a.pool_bias; tk.slot_of = a.slot_of;
+    tk.served_expert = a.served_expert; tk.served_slot = a.served_slot; tk.served_weight = a.served_weight;
+    tk.want = a.want; tk.want_score = a.want_score; tk.admit = a.admit;
+    if ((rc = keepvq_routed_topk(&tk, stream))) return rc;
+  }
 
-  keepvq_routed_topk_args tk = {};
-  tk.logits = rl.logits; tk.tokens = a.tokens; tk.pool = a.pool; tk.top_k = a.top_k; tk.score_func = a.score_func;
-  tk.norm_topk_prob = a.norm_topk_prob; tk.route_scale = a.route_scale; tk.tau = a.tau;
-  tk.served_bias = a.served_bias; tk.pool_bias = a.pool_bias; tk.slot_of = a.slot_of;
-  tk.served_expert = a.served_expert; tk.served_slot = a.served_slot; tk.served_weight = a.served_weight;
-  tk.want = a.want; tk.want_score = a.want_score; tk.admit = a.admit;
-  rc = keepvq_routed_topk(&tk, stream);
-  if (rc) return rc;
+  if (tensor_path) {
+    fast::RouteGroups groups = {reinterpret_cast<int32_t*>(ws + sc.gcount), reinterpret_cast<int32_t*>(ws + sc.gslot),
+                                reinterpret_cast<int32_t*>(ws + sc.gstart), reinterpret_cast<int32_t*>(ws + sc.gsize),
+                                reinterpret_cast<int32_t*>(ws + sc.groutes)};
+    fast::QuantRows xq = {reinterpret_cast<uint8_t*>(ws + sc.xq), reinterpret_cast<float*>(ws + sc.xscale), reinterpret_cast<int32_t*>(ws + sc.xsums)};
+    fast::QuantRows hq = {reinterpret_cast<uint8_t*>(ws + sc.hq), reinterpret_cast<float*>(ws + sc.hscale), reinterpret_cast<int32_t*>(ws + sc.hsums)};
+    if (stages & KEEPVQ_STAGE_PREPARE) {
+      if ((rc = fast::group_routes(a.served_slot, routes, a.slots, groups, s))) return rc;
+      if ((rc = fast::quantize_rows(a.x, a.x_dtype, a.tokens, a.hidden, a.w1.groups, xq, s))) return rc;
+    }
+    fast::FastProjectionArgs p = {};
+    p.scales_dtype = a.scales_dtype; p.codebook = a.codebook; p.groups_of_routes = groups; p.max_routes = routes;
+    p.out_dtype = a.x_dtype; p.swiglu_limit = a.swiglu_limit; p.route_weight = a.served_weight;
+    if (stages & KEEPVQ_STAGE_GATE_UP) {
+      p.a = {a.w1.codes, a.w1.scales}; p.b = {a.w3.codes, a.w3.scales};
+      p.out_dim = a.inter; p.in_dim = a.hidden; p.groups = a.w1.groups; p.x = xq; p.x_div = a.top_k; p.out = ws + sc.h;
+      if ((rc = fast::gate_up(p, s))) return rc;
+    }
+    if (stages & KEEPVQ_STAGE_DOWN) {
+      if ((rc = fast::quantize_rows(ws + sc.h, a.x_dtype, routes, a.inter, a.w2.groups, hq, s))) return rc;
+      p.a = {a.w2.codes, a.w2.scales}; p.b = {nullptr, nullptr};
+      p.out_dim = a.hidden; p.in_dim = a.inter; p.groups = a.w2.groups; p.x = hq; p.x_div = 1; p.out = ws + sc.down;
+      if ((rc = fast::down(p, s))) return rc;
+    }
+  } else {
+    if (stages & KEEPVQ_STAGE_GATE_UP) {
+      if ((rc = projection(a, a.w1, a.x, a.tokens, a.hidden, a.inter, a.top_k, ws + sc.gate, stream))) return rc;
+      if ((rc = projection(a, a.w3, a.x, a.tokens, a.hidden, a.inter, a.top_k, ws + sc.up, stream))) return rc;
+      if (a.x_dtype == KEEPVQ_F32) launch_elementwise<float>(a, sc, s, false);
+      else if (a.x_dtype == KEEPVQ_F16) launch_elementwise<__half>(a, sc, s, false);
+      else launch_elementwise<__nv_bfloat16>(a, sc, s, false);
+      KEEPVQ_CHECK_LAUNCH();
+    }
+    if (stages & KEEPVQ_STAGE_DOWN) {
+      if ((rc = projection(a, a.w2, ws + sc.h, routes, a.inter, a.hidden, 1, ws + sc.down, stream))) return rc;
+    }
+  }
 
-  rc = projection(a, a.w1, a.x, a.tokens, a.hidden, a.inter, a.top_k, ws + sc.gate, stream);
-  if (rc) return rc;
-  rc = projection(a, a.w3, a.x, a.tokens, a.hidden, a.inter, a.top_k, ws + sc.up, stream);
-  if (rc) return rc;
-  if (a.x_dtype == KEEPVQ_F32) launch_elementwise<float>(a, sc, s, false);
-  else if (a.x_dtype == KEEPVQ_F16) launch_elementwise<__half>(a, sc, s, false);
-  else launch_elementwise<__nv_bfloat16>(a, sc, s, false);
-  KEEPVQ_CHECK_LAUNCH();
-  rc = projection(a, a.w2, ws + sc.h, routes, a.inter, a.hidden, 1, ws + sc.down, stream);
-  if (rc) return rc;
-  if (a.x_dtype == KEEPVQ_F32) launch_elementwise<float>(a, sc, s, true);
-  else if (a.x_dtype == KEEPVQ_F16) launch_elementwise<__half>(a, sc, s, true);
-  else launch_elementwise<__nv_bfloat16>(a, sc, s, true);
-  KEEPVQ_CHECK_LAUNCH();
+  if (stages & KEEPVQ_STAGE_COMBINE) {
+    if (a.x_dtype == KEEPVQ_F32) launch_elementwise<float>(a, sc, s, true);
+    else if (a.x_dtype == KEEPVQ_F16) launch_elementwise<__half>(a, sc, s, true);
+    else launch_elementwise<__nv_bfloat16>(a, sc, s, true);
+    KEEPVQ_CHECK_LAUNCH();
+  }
   return KEEPVQ_OK;
+}
+
+extern "C" int keepvq_moe_decode_layer(const keepvq_moe_layer_args* args, void* stream) {
+  return keepvq_moe_decode_stages(args, KEEPVQ_STAGE_ALL, stream);
 }

@@ -76,6 +76,10 @@ class RoutedMoELayer:
         if self.served_bias is None and self.slot_of is None and self.slots != self.pool:
             raise ValueError("with every expert resident, codes must hold one slot per pool expert")
         self.codebook = table_on(self.device, "e8p") if codebook is None else as_device(codebook, self.device).contiguous()
+        # The int8 tensor-core kernels need every table nibble odd (odd half-unit magnitudes).  The
+        # E8P table is; a custom table is read back once, here, never on the token path.
+        nibbles = (self.codebook.cpu().to(torch.int64) & 0xFFFFFFFF)[:, None] >> (4 * torch.arange(8))[None] & 1
+        self.codebook_all_odd = bool(nibbles.all())
         self.res_rows = int(w1.res_codes.shape[0]) if w1.res_codes is not None else 0
         self.res_table = None
         if self.res_rows:
@@ -84,8 +88,8 @@ class RoutedMoELayer:
             self.res_table = table_on(self.device, "e8_1bit_half2") if res_table is None else as_device(res_table, self.device).contiguous()
         self._buffers: dict[tuple, dict] = {}
 
-    def _buffers_for(self, tokens: int, dtype: torch.dtype) -> dict:
-        key = (tokens, dtype)
+    def _buffers_for(self, tokens: int, dtype: torch.dtype, state: int = 0) -> dict:
+        key = (tokens, dtype, state)
         if key not in self._buffers:
             lib = _lib.load()
             nbytes = int(lib.keepvq_moe_layer_workspace_bytes(tokens, self.hidden, self.inter, self.pool, self.top_k))
@@ -100,18 +104,34 @@ class RoutedMoELayer:
                 routing=Routing(served_expert=i32(), served_slot=i32(), served_weight=f32(), want=i32(), want_score=f32(), admit=i32()))
         return self._buffers[key]
 
-    def decode(self, x: torch.Tensor, *, out: torch.Tensor | None = None) -> tuple[torch.Tensor, Routing]:
+    @property
+    def kernel_path(self) -> str:
+        """``"tensor"`` when calls run on the int8 tensor-core kernels, else ``"general"``."""
+        ok = lambda inp, groups: inp % 256 == 0 and (inp // 256) % groups == 0  # noqa: E731
+        fits = ok(self.hidden, int(self.w1.scales.shape[2])) and ok(self.inter, int(self.w2.scales.shape[2]))
+        return "tensor" if self.codebook_all_odd and not self.res_rows and fits else "general"
+
+    @property
+    def launches_per_call(self) -> int:
+        """Kernel launches one ``decode`` call enqueues."""
+        return 8 if self.kernel_path == "tensor" else 7
+
+    def decode(self, x: torch.Tensor, *, out: torch.Tensor | None = None, stages: int = _lib.STAGE_ALL,
+               state: int = 0) -> tuple[torch.Tensor, Routing]:
         """``x`` [tokens, hidden] -> (``[tokens, hidden]`` in x's dtype, routing outputs).
 
         Buffers are cached per (tokens, dtype) and reused by the next call of the same shape, so
         the call is CUDA-graph capturable after one warm-up call; copy results you want to keep.
+        ``stages`` (a mask of ``_lib.STAGE_*``) replays part of the sequence on the state a full
+        call left behind; profilers and the benchmark use it.  ``state`` picks one of several
+        independent buffer sets (each keeps its own scratch and outputs).
         """
         _lib.require_cuda(x)
         if x.ndim != 2 or int(x.shape[1]) != self.hidden:
             raise ValueError(f"x must be [tokens, {self.hidden}], found {tuple(x.shape)}")
         x = x.contiguous()
         tokens = int(x.shape[0])
-        buf = self._buffers_for(tokens, x.dtype)
+        buf = self._buffers_for(tokens, x.dtype, state)
         r: Routing = buf["routing"]
         target = buf["out"] if out is None else out
         args = _lib.MoELayerArgs(
@@ -123,9 +143,10 @@ class RoutedMoELayer:
             slots=self.slots, w1=self.w1.struct(), w3=self.w3.struct(), w2=self.w2.struct(),
             scales_dtype=_lib.dtype_tag(self.w1.scales.dtype), codebook=_lib.ptr(self.codebook), res_rows=self.res_rows,
             res_table=_lib.ptr(self.res_table), hot_of_slot=_lib.ptr(self.hot_of_slot), swiglu_limit=self.swiglu_limit,
+            codebook_all_odd=int(self.codebook_all_odd),
             out=_lib.ptr(target), served_expert=_lib.ptr(r.served_expert), served_slot=_lib.ptr(r.served_slot),
             served_weight=_lib.ptr(r.served_weight), want=_lib.ptr(r.want), want_score=_lib.ptr(r.want_score),
             admit=_lib.ptr(r.admit), workspace=_lib.ptr(buf["workspace"]), workspace_bytes=buf["nbytes"])
         with torch.cuda.device(self.device):
-            _lib.check(_lib.load().keepvq_moe_decode_layer(args, _lib.stream_handle(self.device)), "keepvq_moe_decode_layer")
+            _lib.check(_lib.load().keepvq_moe_decode_stages(args, int(stages), _lib.stream_handle(self.device)), "keepvq_moe_decode_stages")
         return target, r

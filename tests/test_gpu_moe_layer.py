@@ -98,6 +98,32 @@ def test_fewer_residents_than_top_k_leaves_dead_picks_at_zero(cuda):
     check_layer(cfg, x, out, routing, top_k=3, served_bias=served_bias, slot_of=np.arange(6))
 
 
+@pytest.mark.parametrize("tokens,experts,top_k,group", [(3, 12, 3, None), (20, 4, 3, 256), (9, 6, 2, 256)])
+def test_tensor_core_path_small_shapes(cuda, tokens, experts, top_k, group):
+    """Shapes the int8 tensor-core kernels accept (input dims multiples of 256), with grouped scales
+    and with more than eight routes on one expert (20 tokens x top-3 over 4 experts)."""
+    cfg = synthetic.layer(seed=21, experts=experts, hidden=512, inter=256, group_hidden=group, group_inter=group)
+    x = synthetic.tokens(22 + tokens, tokens, 512)
+    layer = build_layer(cuda, cfg, top_k=top_k)
+    assert layer.kernel_path == "tensor"
+    out, routing = layer.decode(x.to(cuda))
+    check_layer(cfg, x, out, routing, top_k=top_k)
+
+
+def test_tensor_and_general_kernels_agree(cuda):
+    """The same layer through both kernel sets: routing identical, outputs within the tolerance."""
+    cfg = synthetic.layer(seed=23, experts=8, hidden=512, inter=256)
+    x = synthetic.tokens(24, 7, 512).to(cuda)
+    fast = build_layer(cuda, cfg, top_k=4)
+    general = build_layer(cuda, cfg, top_k=4)
+    general.codebook_all_odd = False  # forces the general kernels
+    assert (fast.kernel_path, general.kernel_path) == ("tensor", "general")
+    a, ra = fast.decode(x)
+    b, rb = general.decode(x)
+    assert torch.equal(ra.served_slot, rb.served_slot)
+    assert e8.relative_gap(a.float().cpu().numpy(), b.float().cpu().numpy()) <= TOLERANCE
+
+
 @pytest.mark.parametrize("batch", [1, 16])
 def test_config2_shape_decode_layer(cuda, batch):
     """The benchmark layer shape (hidden 4096, inter 2048, top-6, softmax) on a 48-expert slice of
