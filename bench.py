@@ -229,11 +229,11 @@ def run_ours(ns):
     hbm_gbs, peak_kind = measured_peaks()
     layer = build_layer(device, seed=0)
     batch = ns.batch
-    xs = token_batches(device, batch)
+    xs = token_batches(device, batch, ns.rotation)
     uniq = distinct_experts(layer, xs)
 
     def step(i):
-        layer.decode(xs[i % ROTATION])
+        layer.decode(xs[i % len(xs)])
 
     def barrier():
         if world > 1:
@@ -251,7 +251,7 @@ def run_ours(ns):
         dev_in = torch.empty((batch, HIDDEN), dtype=torch.bfloat16, device=device)
 
         def e2e_step(i):
-            dev_in.copy_(host_in[i % ROTATION], non_blocking=True)
+            dev_in.copy_(host_in[i % len(xs)], non_blocking=True)
             out, _ = layer.decode(dev_in)
             host_out.copy_(out, non_blocking=True)
 
@@ -275,7 +275,7 @@ def run_ours(ns):
     e2e_value = tokens / (e2e_ms * 1e-3)
     if rank != 0:
         return
-    mean_u = statistics.fmean(uniq[i % ROTATION] for i in range(ns.steps))
+    mean_u = statistics.fmean(uniq[i % len(xs)] for i in range(ns.steps))
     code_gbs = mean_u * CODE_BYTES_PER_EXPERT / (ms / ns.steps * 1e-3) / 1e9
     roofline = projection_roofline(layer, xs, ns.steps, hbm_gbs, peak_kind)
     threads = os.cpu_count() or 1
@@ -307,6 +307,7 @@ def main():
     ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--batch", type=int, default=64)
+    ap.add_argument("--rotation", type=int, default=ROTATION, help="distinct token batches to rotate over (profiling runs use fewer)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ns = ap.parse_args()
     if ns.impl == "reference":

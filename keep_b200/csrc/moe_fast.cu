@@ -14,6 +14,8 @@
 //   - the K order inside an MMA is permuted (byte j of the low word is table nibble 3-j, of the
 //     high word nibble 7-j); the activations are stored in that same order by quantize_rows.
 //   - accumulation is exact in int32; one conversion to fp32 per scale group.
+#include <stdlib.h>
+
 #include <algorithm>
 
 #include "moe_fast.cuh"
@@ -25,11 +27,17 @@ namespace fast {
 // Activation quantisation: x -> 16-bit fixed point with a power-of-two scale per row.
 // ------------------------------------------------------------------------------------------
 template <typename XT>
-__global__ void __launch_bounds__(256) quantize_rows_kernel(const XT* __restrict__ x, int64_t in_dim, int64_t groups, QuantRows out) {
+__global__ void __launch_bounds__(256) quantize_rows_kernel(const XT* __restrict__ x, int64_t rows, int64_t in_dim, int64_t groups, QuantRows out) {
   __shared__ float warp_max[8];
   __shared__ float row_scale;
   extern __shared__ int32_t group_sum[];
   const int64_t row = blockIdx.x, cw = in_dim / 8, per_group = cw / groups;
+  if (row == rows) {  // one extra all-zero row: the B operand of MMA columns that carry no route
+    for (int64_t c = threadIdx.x; c < cw; c += 256) reinterpret_cast<uint4*>(out.q)[row * cw + c] = make_uint4(0, 0, 0, 0);
+    for (int64_t g = threadIdx.x; g < groups; g += 256) out.sums[row * groups + g] = 0;
+    if (threadIdx.x == 0) out.scale[row] = 1.0f;
+    return;
+  }
   const XT* xr = x + row * in_dim;
   for (int64_t g = threadIdx.x; g < groups; g += 256) group_sum[g] = 0;
 
@@ -52,6 +60,7 @@ __global__ void __launch_bounds__(256) quantize_rows_kernel(const XT* __restrict
       int ex;
       frexpf(m, &ex);            // m < 2^ex
       s = ldexpf(1.0f, ex - 15);  // |x| / s < 2^15
+      if (m / s > 32639.0f) s *= 2.0f;  // 127 * 256 + 127: the largest value two signed bytes hold
     }
     row_scale = s;
     out.scale[row] = s;
@@ -65,7 +74,7 @@ __global__ void __launch_bounds__(256) quantize_rows_kernel(const XT* __restrict
     int q[8], total = 0;
 #pragma unroll
     for (int d = 0; d < 8; ++d) {
-      q[d] = max(-32767, min(32767, __float2int_rn(v[d] * inv)));
+      q[d] = max(-32639, min(32639, __float2int_rn(v[d] * inv)));
       total += q[d];
     }
     atomicAdd(&group_sum[c / per_group], total);
@@ -73,11 +82,13 @@ __global__ void __launch_bounds__(256) quantize_rows_kernel(const XT* __restrict
     uint32_t hi0 = 0, hi1 = 0, lo0 = 0, lo1 = 0;
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
+      // x' = 256 * hi + lo with both bytes signed, so the two MMAs are the same s8 x s8 kind
       const int e = q[6 - 2 * j], o = q[7 - 2 * j];
-      hi0 |= static_cast<uint32_t>((e >> 8) & 0xFF) << (8 * j);
-      lo0 |= static_cast<uint32_t>(e & 0xFF) << (8 * j);
-      hi1 |= static_cast<uint32_t>((o >> 8) & 0xFF) << (8 * j);
-      lo1 |= static_cast<uint32_t>(o & 0xFF) << (8 * j);
+      const int eh = (e + 128) >> 8, oh = (o + 128) >> 8;
+      hi0 |= static_cast<uint32_t>(eh & 0xFF) << (8 * j);
+      lo0 |= static_cast<uint32_t>((e - 256 * eh) & 0xFF) << (8 * j);
+      hi1 |= static_cast<uint32_t>(oh & 0xFF) << (8 * j);
+      lo1 |= static_cast<uint32_t>((o - 256 * oh) & 0xFF) << (8 * j);
     }
     reinterpret_cast<uint4*>(out.q)[row * cw + c] = make_uint4(hi0, hi1, lo0, lo1);
   }
@@ -86,13 +97,12 @@ __global__ void __launch_bounds__(256) quantize_rows_kernel(const XT* __restrict
 }
 
 int quantize_rows(const void* x, int32_t x_dtype, int64_t rows, int64_t in_dim, int64_t groups, const QuantRows& out, cudaStream_t s) {
-  if (rows == 0) return KEEPVQ_OK;
   const size_t smem = static_cast<size_t>(groups) * sizeof(int32_t);
   if (smem > 40 * 1024) return KEEPVQ_ERR_CAPACITY;
-  const unsigned grid = static_cast<unsigned>(rows);
-  if (x_dtype == KEEPVQ_F32) quantize_rows_kernel<float><<<grid, 256, smem, s>>>(reinterpret_cast<const float*>(x), in_dim, groups, out);
-  else if (x_dtype == KEEPVQ_F16) quantize_rows_kernel<__half><<<grid, 256, smem, s>>>(reinterpret_cast<const __half*>(x), in_dim, groups, out);
-  else quantize_rows_kernel<__nv_bfloat16><<<grid, 256, smem, s>>>(reinterpret_cast<const __nv_bfloat16*>(x), in_dim, groups, out);
+  const unsigned grid = static_cast<unsigned>(rows + 1);  // + the zero row
+  if (x_dtype == KEEPVQ_F32) quantize_rows_kernel<float><<<grid, 256, smem, s>>>(reinterpret_cast<const float*>(x), rows, in_dim, groups, out);
+  else if (x_dtype == KEEPVQ_F16) quantize_rows_kernel<__half><<<grid, 256, smem, s>>>(reinterpret_cast<const __half*>(x), rows, in_dim, groups, out);
+  else quantize_rows_kernel<__nv_bfloat16><<<grid, 256, smem, s>>>(reinterpret_cast<const __nv_bfloat16*>(x), rows, in_dim, groups, out);
   KEEPVQ_CHECK_LAUNCH();
   return KEEPVQ_OK;
 }
@@ -197,18 +207,17 @@ __device__ __forceinline__ void mma_s8s8(int (&c)[4], uint32_t a0, uint32_t a1, 
   asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
       : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
-__device__ __forceinline__ void mma_s8u8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
-  asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.u8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-      : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-
 // One codeword -> two A-fragment words.  `sign` is its low byte, `abs_off` its high byte * 256,
-// `lut_lane` the byte address of this lane's replica.  q = table[abs][parity] ^ (neg ? 0xFE : 0).
-__device__ __forceinline__ void decode_to_fragment(const uint8_t* lut_lane, uint32_t sign, uint32_t abs_off, uint32_t& lo, uint32_t& hi) {
+// `lut_lane` the 32-bit shared-memory address of this lane's replica.
+// q = table[abs][parity] ^ (neg ? 0xFE : 0).
+__device__ __forceinline__ void decode_to_fragment(uint32_t lut_lane, uint32_t sign, uint32_t abs_off, uint32_t& lo, uint32_t& hi) {
   const uint32_t parity_off = (__popc(sign) & 1u) << 7;
-  const uint2 e = *reinterpret_cast<const uint2*>(lut_lane + abs_off + parity_off);
-  lo = e.x ^ (top_bits_to_byte_masks(sign * SPREAD_LO) & 0xFEFEFEFEu);
-  hi = e.y ^ (top_bits_to_byte_masks(sign * SPREAD_HI) & 0xFEFEFEFEu);
+  uint32_t ex, ey;
+  // volatile: keeps the table reads after the code prefetch that precedes them in program order,
+  // so the compiler cannot sink that prefetch to the end of the step to save registers
+  asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(ex), "=r"(ey) : "r"(lut_lane + abs_off + parity_off));
+  lo = ex ^ (top_bits_to_byte_masks(sign * SPREAD_LO) & 0xFEFEFEFEu);
+  hi = ey ^ (top_bits_to_byte_masks(sign * SPREAD_HI) & 0xFEFEFEFEu);
 }
 
 __device__ __forceinline__ void team_barrier(int team) {
@@ -242,7 +251,7 @@ __global__ void __launch_bounds__(CTA_THREADS, 1) projection_kernel(FastProjecti
 
   const int lane = threadIdx.x & 31, warp = (threadIdx.x >> 5) % TEAM_WARPS, team = threadIdx.x / (TEAM_WARPS * 32);
   const int g = lane >> 2, t = lane & 3;
-  const uint8_t* lut_lane = lut + (lane & (LUT_REPLICAS - 1)) * 8;
+  const uint32_t lut_lane = static_cast<uint32_t>(__cvta_generic_to_shared(lut)) + (lane & (LUT_REPLICAS - 1)) * 8;
   float* team_red = red + static_cast<size_t>(team) * TEAM_WARPS * ACCS * 32;
   const int64_t N = p.out_dim, cw = p.in_dim / 8;
   const int n_chunks = static_cast<int>(cw / CHUNK_CODES);
@@ -258,7 +267,7 @@ __global__ void __launch_bounds__(CTA_THREADS, 1) projection_kernel(FastProjecti
     const int gsize = p.groups_of_routes.size[gi], gstart = p.groups_of_routes.start[gi];
     const int64_t row0 = static_cast<int64_t>(rb) * rows_per_item;
     const int my_route = g < gsize ? p.groups_of_routes.routes[gstart + g] : -1;
-    const uint4* bsrc = reinterpret_cast<const uint4*>(p.x.q) + static_cast<int64_t>(my_route < 0 ? 0 : my_route / p.x_div) * cw;
+    const uint4* bsrc = reinterpret_cast<const uint4*>(p.x.q) + (my_route < 0 ? p.x_zero_row : static_cast<int64_t>(my_route / p.x_div)) * cw;
 
     float part[M][TILES][4];
     int acc_h[M][TILES][4], acc_l[M][TILES][4];
@@ -281,8 +290,7 @@ __global__ void __launch_bounds__(CTA_THREADS, 1) projection_kernel(FastProjecti
         }
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
-        uint4 b = make_uint4(0, 0, 0, 0);
-        if (my_route >= 0) b = bsrc[cb + i];
+        const uint4 b = bsrc[cb + i];
 #pragma unroll
         for (int m = 0; m < M; ++m)
 #pragma unroll
@@ -303,7 +311,7 @@ __global__ void __launch_bounds__(CTA_THREADS, 1) projection_kernel(FastProjecti
               decode_to_fragment(lut_lane, sign, abs_off, a[half], a[2 + half]);
             }
             mma_s8s8(acc_h[m][tl], a[0], a[1], a[2], a[3], b.x, b.y);
-            mma_s8u8(acc_l[m][tl], a[0], a[1], a[2], a[3], b.z, b.w);
+            mma_s8s8(acc_l[m][tl], a[0], a[1], a[2], a[3], b.z, b.w);
           }
       }
       // close the scale group when this warp's next chunk belongs to another one
@@ -370,6 +378,276 @@ __global__ void __launch_bounds__(CTA_THREADS, 1) projection_kernel(FastProjecti
   }
 }
 
+// ------------------------------------------------------------------------------------------
+// The same projection for batches with many route groups.  A CTA takes (route group, slab of
+// output rows); its 16 warps each own 16*TILES rows of the slab over the whole input dimension,
+// so there is no split-K reduction.
+//   - Codes stream through a private two-stage cp.async ring per warp (a lane copies and later
+//     reads back its own 16-byte pieces), so the next chunk is always in flight behind the one
+//     being decoded, whatever order the compiler gives the instructions.
+//   - The group's quantised activations (the B operand, up to 64 KB) are staged once per item
+//     into shared memory in MMA-fragment order.
+//   - Two decoders share the work so that neither the integer pipe nor shared-memory bandwidth
+//     is the only limit: the arithmetic one of the team kernel (one table read), and one that
+//     reads a second table indexed by the sign byte, whose entry is the XOR mask the arithmetic
+//     computes (sign flips, the parity bit of every byte, the extra flip of table nibble 0 on
+//     odd parity).  TABLE_STEPS says which steps of a chunk use the second.
+// ------------------------------------------------------------------------------------------
+constexpr int CK_WARPS = 16;
+constexpr int CK_THREADS = CK_WARPS * 32;
+constexpr int CK_MAX_CHUNKS = 16;                                   // in_dim <= 4096
+constexpr int CK_B_BYTES = CK_MAX_CHUNKS * 8 * 32 * 16;             // 64 KB
+constexpr int CK_ABS_BYTES = LUT_BYTES;                             // 64 KB: [abs row][parity][replica]
+constexpr int CK_SIGN_BYTES = 256 * LUT_REPLICAS * 8;               // 32 KB: [sign byte][replica]
+constexpr int CK_STAGES = 2;
+constexpr unsigned TABLE_STEPS = 0xAAu;  // bit i set: step i of a chunk decodes through the sign table
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ uint2 lds64(uint32_t addr) {
+  uint2 v;
+  asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+  return v;
+}
+
+// The int8 MMA has a long dependent-accumulate latency (about 290 cycles measured), so each
+// (matrix, tile, byte) keeps two accumulators, used by alternate steps, to double the number of
+// independent MMA chains in flight.
+// MODE 0 is the product.  The others are measurement aids selected by KEEPVQ_PROJECTION_MODE and
+// their outputs are meaningless: 1 = loads only, 3 = no decode (raw words into the MMA),
+// 4 = no MMA.
+template <int M, int TILES, int MODE>
+__device__ __forceinline__ void decode_chunk(uint32_t abs_lane, uint32_t sign_lane, const uint4 (&codes)[M][2 * TILES], uint32_t b_addr,
+                                             int (&acc_h)[2][M][TILES][4], int (&acc_l)[2][M][TILES][4]) {
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const uint4 b = lds128(b_addr + i * 512);  // (hi k0-3, hi k16-19, lo k0-3, lo k16-19) of step i
+#pragma unroll
+    for (int m = 0; m < M; ++m)
+#pragma unroll
+      for (int tl = 0; tl < TILES; ++tl) {
+        uint32_t a[4];
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {  // rows g and g + 8 of the tile
+          const uint4 v = codes[m][2 * tl + half];
+          const uint32_t word = (i >> 1) == 0 ? v.x : (i >> 1) == 1 ? v.y : (i >> 1) == 2 ? v.z : v.w;
+          uint32_t sign, abs_off;  // sign byte; abs row * 256 (its even-parity entry, 16 replicas of 8 bytes)
+          if (i & 1) {
+            asm("prmt.b32 %0, %1, %2, %3;" : "=r"(sign) : "r"(word), "r"(0u), "r"(0x4442u));
+            asm("prmt.b32 %0, %1, %2, %3;" : "=r"(abs_off) : "r"(word), "r"(0u), "r"(0x4434u));
+          } else {
+            sign = word & 0xFFu;
+            abs_off = word & 0xFF00u;
+          }
+          if (MODE == 3) {
+            a[half] = sign;
+            a[2 + half] = abs_off;
+          } else if ((TABLE_STEPS >> i) & 1u) {
+            const uint2 e = lds64(abs_lane + abs_off), x = lds64(sign_lane + (sign << 7));
+            a[half] = e.x ^ x.x;
+            a[2 + half] = e.y ^ x.y;
+          } else {
+            decode_to_fragment(abs_lane, sign, abs_off, a[half], a[2 + half]);
+          }
+        }
+        if (MODE == 4) {
+#pragma unroll
+          for (int r = 0; r < 4; ++r) acc_h[i & 1][m][tl][r] += a[r] ^ b.x;
+        } else {
+          mma_s8s8(acc_h[i & 1][m][tl], a[0], a[1], a[2], a[3], b.x, b.y);
+          mma_s8s8(acc_l[i & 1][m][tl], a[0], a[1], a[2], a[3], b.z, b.w);
+        }
+      }
+  }
+}
+
+template <int M, int TILES, int MODE>
+__global__ void __launch_bounds__(CK_THREADS, 1) projection_cta_kernel(FastProjectionArgs p) {
+  extern __shared__ __align__(16) uint8_t smem[];
+  // ---- tables -----------------------------------------------------------------------------
+  for (int e = threadIdx.x; e < 768; e += CK_THREADS) {
+    uint32_t lo = 0, hi = 0;
+    if (e < 512) {  // abs entry (row e/2, parity e&1): byte j of the low word is table nibble 3-j, of the high word 7-j
+      const uint32_t word = p.codebook[e >> 1], par = e & 1;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int nl = 3 - j, nh = 7 - j;
+        uint32_t hl = ((word >> (4 * nl)) & 0xFu) - 8u, hh = ((word >> (4 * nh)) & 0xFu) - 8u;
+        if (par) { hl = nl == 0 ? ~hl : hl ^ 1u; hh ^= 1u; }
+        lo |= (hl & 0xFFu) << (8 * j);
+        hi |= (hh & 0xFFu) << (8 * j);
+      }
+    } else {        // sign entry: 0xFE where the sign bit is set, ^1 everywhere (^0xFF on nibble 0) on odd parity
+      const uint32_t sb = e - 512, par = __popc(sb) & 1u;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int nl = 3 - j, nh = 7 - j;
+        uint32_t ml = ((sb >> nl) & 1u) ? 0xFEu : 0u, mh = ((sb >> nh) & 1u) ? 0xFEu : 0u;
+        if (par) { ml ^= nl == 0 ? 0xFFu : 0x01u; mh ^= 0x01u; }
+        lo |= ml << (8 * j);
+        hi |= mh << (8 * j);
+      }
+    }
+    uint2* dst = reinterpret_cast<uint2*>(smem) + e * LUT_REPLICAS;  // abs table, then sign table
+#pragma unroll
+    for (int r = 0; r < LUT_REPLICAS; ++r) dst[r] = make_uint2(lo, hi);
+  }
+
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int g = lane >> 2, t = lane & 3;
+  const uint32_t smem_base = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
+  const uint32_t abs_lane = smem_base + (lane & (LUT_REPLICAS - 1)) * 8;
+  const uint32_t sign_lane = abs_lane + CK_ABS_BYTES;
+  const uint32_t b_base = smem_base + CK_ABS_BYTES + CK_SIGN_BYTES;
+  constexpr int STREAMS = M * 2 * TILES;                 // 16-byte pieces a lane owns per chunk
+  constexpr int STAGE_BYTES = STREAMS * 512;             // per warp
+  const uint32_t ring = b_base + CK_B_BYTES + warp * (CK_STAGES * STAGE_BYTES) + lane * 16;
+  const int64_t N = p.out_dim, cw = p.in_dim / 8;
+  const int n_chunks = static_cast<int>(cw / CHUNK_CODES);
+  const int chunks_per_group = n_chunks / static_cast<int>(p.groups);
+  constexpr int ROWS = 16 * TILES;              // per warp
+  constexpr int SLAB = ROWS * CK_WARPS;         // per CTA item
+  const int slabs = static_cast<int>((N + SLAB - 1) / SLAB);
+  const int items = p.groups_of_routes.count[0] * slabs;
+  const Projection mats[2] = {p.a, p.b};
+
+  for (int item = blockIdx.x; item < items; item += gridDim.x) {
+    const int gi = item / slabs, slab = item - gi * slabs;
+    const int64_t slot = p.groups_of_routes.slot[gi];
+    const int gsize = p.groups_of_routes.size[gi], gstart = p.groups_of_routes.start[gi];
+    const int64_t row0 = static_cast<int64_t>(slab) * SLAB + warp * ROWS;
+    const bool active = row0 < N;
+    const uint16_t* row_ptr[M][2 * TILES];
+#pragma unroll
+    for (int m = 0; m < M; ++m)
+#pragma unroll
+      for (int j = 0; j < 2 * TILES; ++j)
+        row_ptr[m][j] = mats[m].codes + (slot * N + min(row0 + 8 * j + g, N - 1)) * cw + t * 8;
+    auto fetch = [&](int c) {  // chunk c of this lane's row streams -> ring stage c % CK_STAGES
+      if (active && c < n_chunks) {
+        const uint32_t dst = ring + (c % CK_STAGES) * STAGE_BYTES;
+#pragma unroll
+        for (int m = 0; m < M; ++m)
+#pragma unroll
+          for (int j = 0; j < 2 * TILES; ++j) cp_async16(dst + (m * 2 * TILES + j) * 512, row_ptr[m][j] + c * CHUNK_CODES);
+      }
+      cp_async_commit();
+    };
+
+    __syncthreads();  // every warp is done with the previous item's activations (and the tables are built)
+    {                 // stage this group's activations in fragment order: [chunk * 8 + step][lane]
+      const int route = g < gsize ? p.groups_of_routes.routes[gstart + g] : -1;
+      const uint4* src = reinterpret_cast<const uint4*>(p.x.q) + (route < 0 ? p.x_zero_row : static_cast<int64_t>(route / p.x_div)) * cw + t * 8;
+      for (int step = warp; step < n_chunks * 8; step += CK_WARPS)
+        cp_async16(b_base + lane * 16 + step * 512, src + (step >> 3) * CHUNK_CODES + (step & 7));
+      cp_async_commit();
+    }
+    fetch(0);
+    cp_async_wait<1>();  // the activations (the older group) have landed
+    __syncthreads();
+    if (!active) { cp_async_wait<0>(); continue; }
+
+    float part[M][TILES][4];
+    int acc_h[2][M][TILES][4], acc_l[2][M][TILES][4];
+#pragma unroll
+    for (int m = 0; m < M; ++m)
+#pragma unroll
+      for (int tl = 0; tl < TILES; ++tl)
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+          part[m][tl][r] = 0.0f;
+          acc_h[0][m][tl][r] = acc_h[1][m][tl][r] = 0;
+          acc_l[0][m][tl][r] = acc_l[1][m][tl][r] = 0;
+        }
+
+    for (int c = 0; c < n_chunks; ++c) {
+      fetch(c + 1);
+      cp_async_wait<1>();  // chunk c has landed (the younger group may still fly)
+      uint4 cur[M][2 * TILES];
+      const uint32_t src = ring + (c % CK_STAGES) * STAGE_BYTES;
+#pragma unroll
+      for (int m = 0; m < M; ++m)
+#pragma unroll
+        for (int j = 0; j < 2 * TILES; ++j) cur[m][j] = lds128(src + (m * 2 * TILES + j) * 512);
+      if (MODE == 1) {
+#pragma unroll
+        for (int m = 0; m < M; ++m)
+#pragma unroll
+          for (int j = 0; j < 2 * TILES; ++j) acc_h[0][m][j / 2][j & 1] += cur[m][j].x ^ cur[m][j].y ^ cur[m][j].z ^ cur[m][j].w;
+      } else {
+        decode_chunk<M, TILES, MODE>(abs_lane, sign_lane, cur, b_base + lane * 16 + c * 8 * 512, acc_h, acc_l);
+      }
+      const int group = c / chunks_per_group;
+      if (c + 1 == n_chunks || (c + 1) / chunks_per_group != group) {
+#pragma unroll
+        for (int m = 0; m < M; ++m)
+#pragma unroll
+          for (int tl = 0; tl < TILES; ++tl)
+#pragma unroll
+            for (int r = 0; r < 4; ++r) {
+              const int64_t row = min(row0 + 16 * tl + g + (r >= 2 ? 8 : 0), N - 1);
+              const float sc = load_as_float(mats[m].scales, p.scales_dtype, (slot * N + row) * p.groups + group);
+              const int hi = acc_h[0][m][tl][r] + acc_h[1][m][tl][r], lo = acc_l[0][m][tl][r] + acc_l[1][m][tl][r];
+              part[m][tl][r] = fmaf(sc, 256.0f * static_cast<float>(hi) + static_cast<float>(lo), part[m][tl][r]);
+              acc_h[0][m][tl][r] = acc_h[1][m][tl][r] = 0;
+              acc_l[0][m][tl][r] = acc_l[1][m][tl][r] = 0;
+            }
+      }
+    }
+    cp_async_wait<0>();
+
+    // ---- epilogue in registers: lane (g, t) holds rows {g, g+8} of each tile, columns {2t, 2t+1}
+#pragma unroll
+    for (int cc = 0; cc < 2; ++cc) {
+      const int col = 2 * t + cc;
+      if (col >= gsize) continue;
+      const int route = p.groups_of_routes.routes[gstart + col];
+      const int64_t xrow = route / p.x_div;
+      const float xs = p.x.scale[xrow];
+      const float weight = M == 2 ? p.route_weight[route] : 1.0f;
+#pragma unroll
+      for (int tl = 0; tl < TILES; ++tl)
+#pragma unroll
+        for (int rr = 0; rr < 2; ++rr) {
+          const int r = 2 * rr + cc;
+          const int64_t row = row0 + 16 * tl + g + 8 * rr;
+          if (row >= N) continue;
+          float y[M];
+#pragma unroll
+          for (int m = 0; m < M; ++m) {
+            float shift = 0.0f;
+            for (int64_t q = 0; q < p.groups; ++q)
+              shift = fmaf(load_as_float(mats[m].scales, p.scales_dtype, (slot * N + row) * p.groups + q),
+                           static_cast<float>(p.x.sums[xrow * p.groups + q]), shift);
+            y[m] = xs * (0.5f * part[m][tl][r] + 0.25f * shift);
+          }
+          float result;
+          if (M == 2) {
+            float gt = y[0], up = y[M - 1];
+            if (p.out_dtype == KEEPVQ_BF16) { gt = __bfloat162float(__float2bfloat16_rn(gt)); up = __bfloat162float(__float2bfloat16_rn(up)); }
+            else if (p.out_dtype == KEEPVQ_F16) { gt = __half2float(__float2half_rn(gt)); up = __half2float(__float2half_rn(up)); }
+            if (p.swiglu_limit > 0.0f) { gt = fminf(gt, p.swiglu_limit); up = fminf(fmaxf(up, -p.swiglu_limit), p.swiglu_limit); }
+            result = gt / (1.0f + expf(-gt)) * up * weight;
+          } else {
+            result = y[0];
+          }
+          store_from_float(p.out, p.out_dtype, static_cast<int64_t>(route) * N + row, result);
+        }
+    }
+  }
+  cp_async_wait<0>();
+}
+
 bool shapes_supported(int64_t out_dim, int64_t in_dim, int64_t groups) {
   if (in_dim % (8 * CHUNK_CODES) != 0 || groups <= 0) return false;
   const int64_t chunks = in_dim / (8 * CHUNK_CODES);
@@ -401,8 +679,50 @@ static int launch_projection(const FastProjectionArgs& p, cudaStream_t s) {
   return KEEPVQ_OK;
 }
 
-int gate_up(const FastProjectionArgs& p, cudaStream_t s) { return launch_projection<2, 2>(p, s); }
-int down(const FastProjectionArgs& p, cudaStream_t s) { return launch_projection<1, 4>(p, s); }
+template <int M, int TILES, int MODE>
+static int launch_projection_cta_mode(const FastProjectionArgs& p, cudaStream_t s) {
+  constexpr size_t smem = CK_ABS_BYTES + CK_SIGN_BYTES + CK_B_BYTES + CK_WARPS * CK_STAGES * (M * 2 * TILES * 512);
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(projection_cta_kernel<M, TILES, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (e != cudaSuccess) return note_cuda_error(e);
+    configured = true;
+  }
+  projection_cta_kernel<M, TILES, MODE><<<sm_count(), CK_THREADS, smem, s>>>(p);
+  KEEPVQ_CHECK_LAUNCH();
+  return KEEPVQ_OK;
+}
+
+static int diagnostic_mode() {
+  static int mode = -1;
+  if (mode < 0) {
+    const char* v = getenv("KEEPVQ_PROJECTION_MODE");
+    mode = v ? atoi(v) : 0;
+    if (mode < 0 || mode > 4) mode = 0;
+  }
+  return mode;
+}
+
+template <int M, int TILES>
+static int launch_projection_cta(const FastProjectionArgs& p, cudaStream_t s) {
+  switch (diagnostic_mode()) {
+    case 1: return launch_projection_cta_mode<M, TILES, 1>(p, s);
+    case 3: return launch_projection_cta_mode<M, TILES, 3>(p, s);
+    case 4: return launch_projection_cta_mode<M, TILES, 4>(p, s);
+    default: return launch_projection_cta_mode<M, TILES, 0>(p, s);
+  }
+}
+
+// Enough routes to give every CTA of the machine its own (group, slab) items, and activations
+// that fit the shared-memory stage?
+static bool many_items(const FastProjectionArgs& p) { return p.max_routes >= 48 && p.in_dim <= 8 * CHUNK_CODES * CK_MAX_CHUNKS; }
+
+int gate_up(const FastProjectionArgs& p, cudaStream_t s) {
+  return many_items(p) ? launch_projection_cta<2, 1>(p, s) : launch_projection<2, 2>(p, s);
+}
+int down(const FastProjectionArgs& p, cudaStream_t s) {
+  return many_items(p) ? launch_projection_cta<1, 2>(p, s) : launch_projection<1, 4>(p, s);
+}
 
 }  // namespace fast
 }  // namespace keepvq

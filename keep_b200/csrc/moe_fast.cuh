@@ -19,9 +19,9 @@ constexpr int MAX_GROUP_ROUTES = 8;  // routes of one expert that share an MMA t
 
 // Quantised activation rows: the B operand of the projections.
 struct QuantRows {
-  uint8_t* q;       // [rows, in_dim/8, 16]: per codeword 4 words: hi(dims 6,4,2,0) hi(7,5,3,1) lo(...) lo(...)
-  float* scale;     // [rows] power of two: x ~= scale * x'
-  int32_t* sums;    // [rows, groups] sum of x' over each scale group
+  uint8_t* q;       // [rows + 1, in_dim/8, 16] (last row all zero): per codeword 4 words: hi(dims 6,4,2,0) hi(7,5,3,1) lo(...) lo(...)
+  float* scale;     // [rows + 1] power of two: x ~= scale * x'
+  int32_t* sums;    // [rows + 1, groups] sum of x' over each scale group
 };
 
 // Routes grouped by the slot they are served from.
@@ -45,6 +45,7 @@ struct FastProjectionArgs {
   int64_t out_dim, in_dim, groups;
   const uint32_t* codebook;
   QuantRows x;            // activations
+  int64_t x_zero_row;     // index of the all-zero row quantize_rows appends
   int32_t x_div;          // activation row of route r is r / x_div
   RouteGroups groups_of_routes;
   const float* route_weight;  // [routes] gate weight (gate/up only)

@@ -49,12 +49,12 @@ static LayerScratch plan_scratch(int64_t tokens, int64_t hidden, int64_t inter, 
   s.up = at;     at += align256(routes * inter * 4);
   s.h = at;      at += align256(routes * inter * 4);
   s.down = at;   at += align256(routes * hidden * 4);
-  s.xq = at;     at += align256(tokens * hidden * 2);
-  s.xscale = at; at += align256(tokens * 4);
-  s.xsums = at;  at += align256(tokens * (hidden / 8) * 4);  // room for one scale group per codeword
-  s.hq = at;     at += align256(routes * inter * 2);
-  s.hscale = at; at += align256(routes * 4);
-  s.hsums = at;  at += align256(routes * (inter / 8) * 4);
+  s.xq = at;     at += align256((tokens + 1) * hidden * 2);  // + the zero row
+  s.xscale = at; at += align256((tokens + 1) * 4);
+  s.xsums = at;  at += align256((tokens + 1) * (hidden / 8) * 4);  // room for one scale group per codeword
+  s.hq = at;     at += align256((routes + 1) * inter * 2);
+  s.hscale = at; at += align256((routes + 1) * 4);
+  s.hsums = at;  at += align256((routes + 1) * (inter / 8) * 4);
   s.gcount = at; at += 256;
   s.gslot = at;  at += align256(routes * 4);
   s.gstart = at; at += align256(routes * 4);
@@ -187,13 +187,13 @@ extern "C" int keepvq_moe_decode_stages(const keepvq_moe_layer_args* args, int32
     p.out_dtype = a.x_dtype; p.swiglu_limit = a.swiglu_limit; p.route_weight = a.served_weight;
     if (stages & KEEPVQ_STAGE_GATE_UP) {
       p.a = {a.w1.codes, a.w1.scales}; p.b = {a.w3.codes, a.w3.scales};
-      p.out_dim = a.inter; p.in_dim = a.hidden; p.groups = a.w1.groups; p.x = xq; p.x_div = a.top_k; p.out = ws + sc.h;
+      p.out_dim = a.inter; p.in_dim = a.hidden; p.groups = a.w1.groups; p.x = xq; p.x_zero_row = a.tokens; p.x_div = a.top_k; p.out = ws + sc.h;
       if ((rc = fast::gate_up(p, s))) return rc;
     }
     if (stages & KEEPVQ_STAGE_DOWN) {
       if ((rc = fast::quantize_rows(ws + sc.h, a.x_dtype, routes, a.inter, a.w2.groups, hq, s))) return rc;
       p.a = {a.w2.codes, a.w2.scales}; p.b = {nullptr, nullptr};
-      p.out_dim = a.hidden; p.in_dim = a.inter; p.groups = a.w2.groups; p.x = hq; p.x_div = 1; p.out = ws + sc.down;
+      p.out_dim = a.hidden; p.in_dim = a.inter; p.groups = a.w2.groups; p.x = hq; p.x_zero_row = routes; p.x_div = 1; p.out = ws + sc.down;
       if ((rc = fast::down(p, s))) return rc;
     }
   } else {
