@@ -278,6 +278,29 @@ typedef enum keepvq_moe_stage {
 } keepvq_moe_stage;
 int keepvq_moe_decode_stages(const keepvq_moe_layer_args* args, int32_t stages, void* stream);
 
+/* ------------------------------------------------------------------------------------------
+ * keepvq_moe_decode_layer for callers that cannot hand over scratch memory.  It has no
+ * counterpart in the reference.
+ *
+ * Who needs it: a host that gave all device memory to its own pool at start-up and has nothing
+ * left to allocate from, or one that must never stall (cudaMalloc / cudaFree synchronise the
+ * device).  This entry point allocates nothing, on the host or on the device, and neither does
+ * anything it calls.  `workspace` and `workspace_bytes` of the arguments are ignored; the scratch
+ * is a fixed KEEPVQ_STATIC_SCRATCH_BYTES array inside the library that every GPU loading the
+ * library holds until the process exits.  Inputs and outputs are still the caller's.
+ *
+ *  - A request whose scratch need (keepvq_moe_layer_workspace_bytes) exceeds the array returns
+ *    KEEPVQ_ERR_CAPACITY and launches nothing.  8 MiB covers, for example, 16 decode tokens of a
+ *    top-6 layer with hidden 4096 and inter 2048.
+ *  - The first call on a device looks up the array's device address (with that device current).
+ *    Make that first call before any stream capture begins.
+ *  - All calls on a device share the one array, and it keeps the last call's contents.  Calls
+ *    that overlap on the GPU race on it: keep them on one stream or order them with events.
+ *    Nothing in the array needs clearing between calls.
+ * ------------------------------------------------------------------------------------------ */
+#define KEEPVQ_STATIC_SCRATCH_BYTES (8u << 20)
+int keepvq_moe_decode_layer_static(const keepvq_moe_layer_args* args, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

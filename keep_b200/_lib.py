@@ -91,6 +91,7 @@ class MoELayerArgs(Structure):
 
 
 SCORE_FUNCS = {"softmax": 0, "sigmoid": 1, "sqrtsoftplus": 2}
+STATIC_SCRATCH_BYTES = 8 << 20  # KEEPVQ_STATIC_SCRATCH_BYTES
 STAGE_ROUTER, STAGE_PREPARE, STAGE_GATE_UP, STAGE_DOWN, STAGE_COMBINE, STAGE_ALL = 1, 2, 4, 8, 16, 31
 
 #: ctypes mirror of every argument struct in the header, by its C name (the layout test walks this).
@@ -110,6 +111,7 @@ _SIGNATURES = {
     "keepvq_moe_layer_workspace_bytes": (c_int64, [c_int64, c_int64, c_int64, c_int64, c_int32]),
     "keepvq_moe_decode_layer": (c_int, [POINTER(MoELayerArgs), c_void_p]),
     "keepvq_moe_decode_stages": (c_int, [POINTER(MoELayerArgs), c_int32, c_void_p]),
+    "keepvq_moe_decode_layer_static": (c_int, [POINTER(MoELayerArgs), c_void_p]),
 }
 
 _lock = threading.Lock()

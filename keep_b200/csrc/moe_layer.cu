@@ -222,3 +222,56 @@ extern "C" int keepvq_moe_decode_stages(const keepvq_moe_layer_args* args, int32
 extern "C" int keepvq_moe_decode_layer(const keepvq_moe_layer_args* args, void* stream) {
   return keepvq_moe_decode_stages(args, KEEPVQ_STAGE_ALL, stream);
 }
+
+// ------------------------------------------------------------------------------------------
+// The decode layer for callers that have no scratch buffer to give.
+//
+// Some hosts cannot allocate device memory at call time: a serving process that handed every
+// byte of the GPU to its own pool at start-up, or a loop that may not stall (cudaMalloc and
+// cudaFree synchronise the device).  For them the scratch lives in this library's image: a
+// fixed array in device memory that every GPU loading the library holds until the process
+// exits.  All calls on a device share it, so two calls that overlap on the GPU (different
+// streams, or a graph replay racing a direct call) corrupt each other; serialise them.  The
+// array keeps whatever the last call left there.  Nothing in it has to start at zero: every
+// region is written by an earlier stage of the same call before a later stage reads it.
+// ------------------------------------------------------------------------------------------
+namespace keepvq {
+
+static __device__ __align__(256) unsigned char g_layer_scratch[KEEPVQ_STATIC_SCRATCH_BYTES];
+
+// Device address of g_layer_scratch on the current device.  In host code the array's name is
+// only a handle for the runtime, not an address a kernel can use; the runtime translates it,
+// per device.  Looked up once per device, on the first call made with that device current.
+static int layer_scratch_address(void** out) {
+  constexpr int MAX_DEVICES = 64;
+  static void* cached[MAX_DEVICES] = {};
+  int device = 0;
+  cudaError_t e = cudaGetDevice(&device);
+  if (e != cudaSuccess) return note_cuda_error(e);
+  if (device < 0 || device >= MAX_DEVICES) return KEEPVQ_ERR_CAPACITY;
+  if (!cached[device]) {
+    void* address = nullptr;
+    e = cudaGetSymbolAddress(&address, g_layer_scratch);
+    if (e != cudaSuccess) return note_cuda_error(e);
+    cached[device] = address;
+  }
+  *out = cached[device];
+  return KEEPVQ_OK;
+}
+
+}  // namespace keepvq
+
+extern "C" int keepvq_moe_decode_layer_static(const keepvq_moe_layer_args* args, void* stream) {
+  using namespace keepvq;
+  if (!args) return KEEPVQ_ERR_NULL;
+  if (args->tokens < 0 || args->hidden <= 0 || args->inter <= 0 || args->pool <= 0 || args->top_k <= 0) return KEEPVQ_ERR_SHAPE;
+  const int64_t need = plan_scratch(args->tokens, args->hidden, args->inter, args->pool, args->top_k).total;
+  if (need > static_cast<int64_t>(KEEPVQ_STATIC_SCRATCH_BYTES)) return KEEPVQ_ERR_CAPACITY;  // too many tokens for the built-in scratch
+  void* scratch = nullptr;
+  const int rc = layer_scratch_address(&scratch);
+  if (rc) return rc;
+  keepvq_moe_layer_args with_scratch = *args;
+  with_scratch.workspace = scratch;
+  with_scratch.workspace_bytes = static_cast<int64_t>(KEEPVQ_STATIC_SCRATCH_BYTES);
+  return keepvq_moe_decode_stages(&with_scratch, KEEPVQ_STAGE_ALL, stream);
+}

@@ -104,6 +104,22 @@ class RoutedMoELayer:
                 routing=Routing(served_expert=i32(), served_slot=i32(), served_weight=f32(), want=i32(), want_score=f32(), admit=i32()))
         return self._buffers[key]
 
+    def _layer_args(self, x, out, r: Routing, *, workspace, nbytes) -> _lib.MoELayerArgs:
+        """Argument struct for ``decode_without_scratch`` (the caller's tensors, no scratch)."""
+        return _lib.MoELayerArgs(
+            x=_lib.ptr(x), x_dtype=_lib.dtype_tag(x.dtype), tokens=int(x.shape[0]), hidden=self.hidden, inter=self.inter,
+            router_w=_lib.ptr(self.router_w), router_dtype=_lib.dtype_tag(self.router_w.dtype), pool=self.pool,
+            top_k=self.top_k, score_func=_lib.SCORE_FUNCS[self.score_func], norm_topk_prob=int(self.norm_topk_prob),
+            gate_temp=self.gate_temp, route_scale=self.route_scale, tau=self.tau,
+            served_bias=_lib.ptr(self.served_bias), pool_bias=_lib.ptr(self.pool_bias), slot_of=_lib.ptr(self.slot_of),
+            slots=self.slots, w1=self.w1.struct(), w3=self.w3.struct(), w2=self.w2.struct(),
+            scales_dtype=_lib.dtype_tag(self.w1.scales.dtype), codebook=_lib.ptr(self.codebook), res_rows=self.res_rows,
+            res_table=_lib.ptr(self.res_table), hot_of_slot=_lib.ptr(self.hot_of_slot), swiglu_limit=self.swiglu_limit,
+            codebook_all_odd=int(self.codebook_all_odd),
+            out=_lib.ptr(out), served_expert=_lib.ptr(r.served_expert), served_slot=_lib.ptr(r.served_slot),
+            served_weight=_lib.ptr(r.served_weight), want=_lib.ptr(r.want), want_score=_lib.ptr(r.want_score),
+            admit=_lib.ptr(r.admit), workspace=_lib.ptr(workspace), workspace_bytes=nbytes)
+
     @property
     def kernel_path(self) -> str:
         """``"tensor"`` when calls run on the int8 tensor-core kernels, else ``"general"``."""
@@ -115,6 +131,29 @@ class RoutedMoELayer:
     def launches_per_call(self) -> int:
         """Kernel launches one ``decode`` call enqueues."""
         return 8 if self.kernel_path == "tensor" else 7
+
+    def decode_without_scratch(self, x: torch.Tensor, out: torch.Tensor, routing: Routing) -> tuple[torch.Tensor, Routing]:
+        """The same layer through ``keepvq_moe_decode_layer_static``: the caller supplies the
+        output and routing tensors, and the scratch is the fixed array inside the library, so the
+        call allocates nothing anywhere.  For hosts that cannot allocate device memory at call
+        time (all of it already belongs to their own pool) or may not stall on an allocation.
+
+        Limits: the scratch holds ``_lib.STATIC_SCRATCH_BYTES`` (8 MiB; about 16 tokens at hidden
+        4096, inter 2048, top-6) and a larger request raises ``KeepVQError`` (capacity).  Every
+        call on a device shares that one array: calls that overlap on the GPU race on it, so keep
+        them on one stream.  The first call on a device sets the array up and should come before
+        any stream capture.
+        """
+        _lib.require_cuda(x, out)
+        if x.ndim != 2 or int(x.shape[1]) != self.hidden or not x.is_contiguous():
+            raise ValueError(f"x must be a contiguous [tokens, {self.hidden}] tensor, found {tuple(x.shape)}")
+        if tuple(out.shape) != tuple(x.shape) or out.dtype != x.dtype or not out.is_contiguous():
+            raise ValueError("out must be a contiguous tensor of x's shape and dtype")
+        args = self._layer_args(x, out, routing, workspace=None, nbytes=0)
+        with torch.cuda.device(self.device):
+            _lib.check(_lib.load().keepvq_moe_decode_layer_static(args, _lib.stream_handle(self.device)),
+                       "keepvq_moe_decode_layer_static")
+        return out, routing
 
     def decode(self, x: torch.Tensor, *, out: torch.Tensor | None = None, stages: int = _lib.STAGE_ALL,
                state: int = 0) -> tuple[torch.Tensor, Routing]:
