@@ -279,6 +279,75 @@ typedef enum keepvq_moe_stage {
 int keepvq_moe_decode_stages(const keepvq_moe_layer_args* args, int32_t stages, void* stream);
 
 /* ------------------------------------------------------------------------------------------
+ * Residency bookkeeping for one layer, on the device: admission of strongly demanded absent
+ * experts, routing of experts whose bytes have landed, least-recently-strongly-demanded eviction.
+ * Stands in for Cache.begin / harvest / install / evict (scripts/v41_build/omlx_routed.py:167-247),
+ * which the reference runs in host Python; here the router tables (served_bias, slot_of) are
+ * updated in place on the stream, so the next decode call sees them with no host round trip.
+ *
+ * One tick consumes the demand (want, want_score) of call `call` while call `step` is being built
+ * (step - call = the reference's lag):
+ *   g = want_score / (sum over the k picks + 1e-20) * route_scale, in double;  strong = g >= tau
+ *   wanted[e] = max g over strong picks;   stats.resident += demanded picks that are resident
+ *   install: every reading expert whose `landed` flag is set is routed (served_bias <- pool_bias,
+ *            slot_of, slot_expert, last_use[slot] = step)
+ *   wanted and resident -> last_use[slot] = call;  wanted, absent, not reading -> candidate
+ *   cooling slots whose stamp <= call move to the end of the free list, in order
+ *   candidates in descending (g, expert): pop a slot from the END of the free list and start a
+ *            read (action ADMIT), or count no_slot
+ *   evict: while spare - free - cooling > 0, the routed slot with the smallest (last_use, slot)
+ *            whose expert is not wanted is unrouted (served_bias <- -1e30, slot_of <- absent,
+ *            last_use <- +inf, appended to cooling with stamp `step`)
+ * The host's part: set landed[e] when a read finishes, clear it once it sees the ROUTE action;
+ * start a read for every ADMIT action.  Actions are appended to `actions` as (kind, expert, slot).
+ * ------------------------------------------------------------------------------------------ */
+typedef enum keepvq_residency_action {
+  KEEPVQ_ACTION_ROUTE = 1,
+  KEEPVQ_ACTION_UNROUTE = 2,
+  KEEPVQ_ACTION_ADMIT = 3
+} keepvq_residency_action;
+
+typedef enum keepvq_residency_stat {
+  KEEPVQ_STAT_CALLS = 0, KEEPVQ_STAT_TOKENS, KEEPVQ_STAT_DEMAND, KEEPVQ_STAT_RESIDENT, KEEPVQ_STAT_WANTED,
+  KEEPVQ_STAT_ADMITTED, KEEPVQ_STAT_INSTALLED, KEEPVQ_STAT_EVICTED, KEEPVQ_STAT_BYTES, KEEPVQ_STAT_NO_SLOT,
+  KEEPVQ_STAT_COUNT
+} keepvq_residency_stat;
+
+typedef struct keepvq_residency_args {
+  /* state of the layer, owned by the caller, updated in place */
+  int32_t* slot_expert;     /* [slots] expert in the slot, -1 = unrouted */
+  uint32_t* slot_of;        /* [pool]  slot of the expert, KEEPVQ_NO_RESIDUAL = absent */
+  float* served_bias;       /* [pool]  the router's served bias (see keepvq_routed_topk_args) */
+  const float* pool_bias;   /* [pool]  or NULL (zero) */
+  double* last_use;         /* [slots] */
+  int32_t* free_list;       /* [slots] */
+  int32_t* cooling;         /* [slots][2] (slot, stamp) */
+  int32_t* reading;         /* [slots][2] (expert, slot) */
+  int32_t* counts;          /* [3] entries in free_list, cooling, reading */
+  int64_t* stats;           /* [KEEPVQ_STAT_COUNT] */
+  int64_t pool;
+  int64_t slots;
+  /* the demand being harvested */
+  const uint32_t* want;     /* [tokens, top_k] */
+  const float* want_score;  /* [tokens, top_k] */
+  int64_t tokens;
+  int32_t top_k;
+  const uint8_t* landed;    /* [pool] host-written flags */
+  int64_t call;
+  int64_t step;
+  float tau;
+  float route_scale;
+  int32_t spare;
+  int32_t first_layer;      /* non-zero: this layer counts calls and tokens */
+  /* what happened, for the host to act on */
+  int32_t* actions;         /* [max_actions][3] (kind, expert, slot) */
+  int32_t* action_count;    /* [1] running count; the caller resets it */
+  int32_t max_actions;
+} keepvq_residency_args;
+
+int keepvq_residency_tick(const keepvq_residency_args* args, void* stream);
+
+/* ------------------------------------------------------------------------------------------
  * keepvq_moe_decode_layer for callers that cannot hand over scratch memory.  It has no
  * counterpart in the reference.
  *

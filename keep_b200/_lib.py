@@ -90,6 +90,18 @@ class MoELayerArgs(Structure):
     ]
 
 
+class ResidencyArgs(Structure):
+    _fields_ = [
+        ("slot_expert", c_void_p), ("slot_of", c_void_p), ("served_bias", c_void_p), ("pool_bias", c_void_p),
+        ("last_use", c_void_p), ("free_list", c_void_p), ("cooling", c_void_p), ("reading", c_void_p),
+        ("counts", c_void_p), ("stats", c_void_p), ("pool", c_int64), ("slots", c_int64),
+        ("want", c_void_p), ("want_score", c_void_p), ("tokens", c_int64), ("top_k", c_int32),
+        ("landed", c_void_p), ("call", c_int64), ("step", c_int64), ("tau", c_float), ("route_scale", c_float),
+        ("spare", c_int32), ("first_layer", c_int32),
+        ("actions", c_void_p), ("action_count", c_void_p), ("max_actions", c_int32),
+    ]
+
+
 SCORE_FUNCS = {"softmax": 0, "sigmoid": 1, "sqrtsoftplus": 2}
 STATIC_SCRATCH_BYTES = 8 << 20  # KEEPVQ_STATIC_SCRATCH_BYTES
 STAGE_ROUTER, STAGE_PREPARE, STAGE_GATE_UP, STAGE_DOWN, STAGE_COMBINE, STAGE_ALL = 1, 2, 4, 8, 16, 31
@@ -98,6 +110,7 @@ STAGE_ROUTER, STAGE_PREPARE, STAGE_GATE_UP, STAGE_DOWN, STAGE_COMBINE, STAGE_ALL
 EXTRA_STRUCTS = {
     "keepvq_router_logits_args": RouterLogitsArgs, "keepvq_routed_topk_args": RoutedTopkArgs,
     "keepvq_expert_weights": ExpertWeights, "keepvq_moe_layer_args": MoELayerArgs,
+    "keepvq_residency_args": ResidencyArgs,
 }
 
 _SIGNATURES = {
@@ -112,6 +125,7 @@ _SIGNATURES = {
     "keepvq_moe_decode_layer": (c_int, [POINTER(MoELayerArgs), c_void_p]),
     "keepvq_moe_decode_stages": (c_int, [POINTER(MoELayerArgs), c_int32, c_void_p]),
     "keepvq_moe_decode_layer_static": (c_int, [POINTER(MoELayerArgs), c_void_p]),
+    "keepvq_residency_tick": (c_int, [POINTER(ResidencyArgs), c_void_p]),
 }
 
 _lock = threading.Lock()

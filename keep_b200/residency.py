@@ -1,0 +1,86 @@
+"""Routed residency bookkeeping on the device: admit, install, evict, one kernel per layer tick.
+
+The reference keeps this policy in host Python (``Cache.begin / harvest / install / evict``,
+``scripts/v41_build/omlx_routed.py:167-247``) and reads the demand back two calls late.  Here the
+state lives in device arrays and ``keepvq_residency_tick`` updates the router tables in place, so
+a decode call is never followed by a host read.  The host only feeds ``landed`` flags (a read has
+finished) and drains the action log (reads to start, slots that were unrouted).
+"""
+
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+from . import _lib
+from .router import OFF
+
+STAT_NAMES = ("calls", "tokens", "demand", "resident", "wanted", "admitted", "installed", "evicted", "bytes", "no_slot")
+ACTION_NAMES = {1: "route", 2: "unroute", 3: "admit"}
+
+
+class LayerResidency:
+    """Residency state of one layer.
+
+    ``slot_expert`` [slots]: the starting residents (slot -> expert); ``last_use`` [slots]: their
+    starting recency (the reference starts colder experts lower, ``omlx_routed.py:77``).
+    ``served_bias`` and ``slot_of`` are the tensors a ``RoutedMoELayer`` routes with: pass the
+    layer's own so that ticks and decode calls share them.
+    """
+
+    def __init__(self, slot_expert, last_use, pool: int, *, device, pool_bias=None, served_bias=None, slot_of=None,
+                 tau: float = 0.3, spare: int = 4, route_scale: float = 1.0, top_k: int = 6, max_actions: int = 4096):
+        se = np.asarray(slot_expert, dtype=np.int64)
+        self.slots, self.pool, self.device = int(se.shape[0]), int(pool), torch.device(device)
+        self.tau, self.spare, self.route_scale, self.top_k = float(tau), int(spare), float(route_scale), int(top_k)
+        dev = self.device
+        self.slot_expert = torch.from_numpy(se.astype(np.int32)).to(dev)
+        self.last_use = torch.from_numpy(np.asarray(last_use, dtype=np.float64).copy()).to(dev)
+        self.pool_bias = None if pool_bias is None else torch.as_tensor(pool_bias, dtype=torch.float32).to(dev).contiguous()
+        if slot_of is None:
+            table = np.full(self.pool, 0xFFFFFFFF, dtype=np.uint32)
+            table[se[se >= 0]] = np.flatnonzero(se >= 0).astype(np.uint32)
+            slot_of = torch.from_numpy(table).to(dev)
+        if served_bias is None:
+            bias = np.full(self.pool, OFF, dtype=np.float32)
+            bias[se[se >= 0]] = 0.0 if pool_bias is None else np.asarray(pool_bias, dtype=np.float32)[se[se >= 0]]
+            served_bias = torch.from_numpy(bias).to(dev)
+        self.slot_of, self.served_bias = slot_of, served_bias
+        i32 = lambda *shape: torch.zeros(shape, dtype=torch.int32, device=dev)  # noqa: E731
+        self.free_list, self.cooling, self.reading, self.counts = i32(self.slots), i32(self.slots, 2), i32(self.slots, 2), i32(3)
+        self.stats = torch.zeros(len(STAT_NAMES), dtype=torch.int64, device=dev)
+        self.landed = torch.zeros(self.pool, dtype=torch.uint8, device=dev)
+        self.actions, self.action_count, self.max_actions = i32(max_actions, 3), i32(1), int(max_actions)
+
+    def tick(self, want: torch.Tensor, want_score: torch.Tensor, *, call: int, step: int, first_layer: bool = False) -> None:
+        """Harvest the demand of call ``call`` while call ``step`` is being built.  Enqueued on the
+        current stream; reads nothing back."""
+        _lib.require_cuda(want, want_score)
+        tokens = int(want.shape[0])
+        args = _lib.ResidencyArgs(
+            slot_expert=_lib.ptr(self.slot_expert), slot_of=_lib.ptr(self.slot_of), served_bias=_lib.ptr(self.served_bias),
+            pool_bias=_lib.ptr(self.pool_bias), last_use=_lib.ptr(self.last_use), free_list=_lib.ptr(self.free_list),
+            cooling=_lib.ptr(self.cooling), reading=_lib.ptr(self.reading), counts=_lib.ptr(self.counts), stats=_lib.ptr(self.stats),
+            pool=self.pool, slots=self.slots, want=_lib.ptr(want.contiguous()), want_score=_lib.ptr(want_score.contiguous()),
+            tokens=tokens, top_k=self.top_k, landed=_lib.ptr(self.landed), call=int(call), step=int(step), tau=self.tau,
+            route_scale=self.route_scale, spare=self.spare, first_layer=int(first_layer),
+            actions=_lib.ptr(self.actions), action_count=_lib.ptr(self.action_count), max_actions=self.max_actions)
+        with torch.cuda.device(self.device):
+            _lib.check(_lib.load().keepvq_residency_tick(args, _lib.stream_handle(self.device)), "keepvq_residency_tick")
+
+    # ---- host-side helpers (synchronise; for installers, logs and tests, not the token path) ----
+    def drain_actions(self) -> list[tuple[str, int, int]]:
+        n = min(int(self.action_count.item()), self.max_actions)
+        rows = self.actions[:n].cpu().tolist()
+        self.action_count.zero_()
+        return [(ACTION_NAMES[k], e, s) for k, e, s in rows]
+
+    def snapshot(self) -> dict:
+        counts = self.counts.cpu().tolist()
+        last = self.last_use.cpu().numpy()
+        return dict(
+            slot_expert=self.slot_expert.cpu().tolist(),
+            last_use=[None if not np.isfinite(v) else float(v) for v in last],
+            free=self.free_list[: counts[0]].cpu().tolist(), cooling=self.cooling[: counts[1]].cpu().tolist(),
+            reading={str(e): s for e, s in self.reading[: counts[2]].cpu().tolist()},
+            stats=dict(zip(STAT_NAMES, self.stats.cpu().tolist())))

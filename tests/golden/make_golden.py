@@ -161,6 +161,101 @@ def router_fixture(checkout: Path) -> None:
     np.savez_compressed(HERE / "router.npz", **out)
 
 
+def residency_fixture(checkout: Path) -> None:
+    """A step-by-step trace of the reference's ``Cache`` policy (scripts/v41_build/omlx_routed.py:
+    167-247: begin -> harvest -> install / admit / evict) on a seeded demand stream, with reads that
+    land on a scripted schedule.  The reference class runs unmodified; only its storage hooks
+    (``slabs`` / ``route`` / ``unroute``) and its reader pool are stand-ins."""
+    import json
+    import os
+    import types
+
+    sys.path.insert(0, str(checkout / "scripts" / "v41_build"))
+    os.environ.update(OMLX_ROUTED_TAU="0.3", OMLX_ROUTED_SPARE="2", OMLX_ROUTED_LAG="2")
+    omlx_routed = load_by_path("keep_reference_omlx_routed", checkout / "scripts" / "v41_build" / "omlx_routed.py")
+
+    landed: set[int] = set()
+
+    class Future:
+        def __init__(self, expert):
+            self.expert = expert
+
+        def done(self):
+            return self.expert in landed
+
+        def result(self):
+            return 64
+
+    class Pool:
+        def submit(self, fn, expert):
+            return Future(expert)
+
+    class Layer:
+        def __init__(self, index, hot, rank):
+            self.index = index
+            self.slot_expert = np.array(hot, dtype=np.int64)
+            self.slot_of = {e: s for s, e in enumerate(hot)}
+            self.last_use = -1.0 - np.array(rank, dtype=np.float64)
+            self.cooling, self.free, self.reading = [], [], {}
+
+        def views_current(self):
+            return True
+
+    log: list = []
+
+    class Trace(omlx_routed.Cache):
+        def slabs(self, layer, expert, slot):
+            return [(expert,)]
+
+        def route(self, layer, expert, slot):
+            log.append(("route", layer.index, int(expert), int(slot)))
+
+        def unroute(self, layer, expert, slot):
+            log.append(("unroute", layer.index, int(expert), int(slot)))
+
+    pool_size, slots, k, tokens, steps = 24, 10, 3, 4, 14
+    config = types.SimpleNamespace(score_func="sqrtsoftplus", n_activated_experts=k, route_scale=1.5)
+    cache = Trace(config, None)
+    cache.pool = Pool()
+    rng = np.random.default_rng(77)
+    layers = []
+    for index in range(2):
+        hot = rng.permutation(pool_size)[:slots].tolist()
+        layers.append(Layer(index, hot, rank=list(range(slots))))
+    cache.layers = layers
+    init = [dict(slot_expert=l.slot_expert.tolist(), last_use=l.last_use.tolist()) for l in layers]
+
+    trace = []
+    for step in range(1, steps + 1):
+        demand = []
+        for layer in layers:
+            index = np.stack([rng.choice(pool_size, k, replace=False) for _ in range(tokens)]).astype(np.uint32)
+            weight = rng.uniform(0.05, 1.0, size=(tokens, k)).astype(np.float32) ** 2
+            demand.append((index, weight))
+        cache.pending[cache.step + 1] = demand  # what observe() records while call step+1 is built
+        # each outstanding read lands with probability 0.6 before this tick (same flag for both layers)
+        for layer in layers:
+            for expert in list(layer.reading):
+                if rng.random() < 0.6:
+                    landed.add(expert)
+        before = len(log)
+        landed_now = sorted(int(e) for e in landed)  # per layer: expert ids whose bytes are in
+        cache.begin()
+        landed.clear()  # a landed read is consumed by the install of this tick
+        trace.append(dict(
+            step=cache.step, landed=landed_now,
+            demand=[dict(index=i.tolist(), weight=[[float(v) for v in row] for row in w]) for i, w in demand],
+            layers=[dict(slot_expert=l.slot_expert.tolist(),
+                         last_use=[None if not np.isfinite(v) else float(v) for v in l.last_use],
+                         free=[int(s) for s in l.free], cooling=[[int(s), int(c)] for s, c in l.cooling],
+                         reading={str(int(e)): int(s) for e, (s, _) in l.reading.items()}) for l in layers],
+            stats={key: (float(v) if key == "policy_s" else int(v)) for key, v in cache.stats.items() if key != "policy_s"},
+            actions=[list(a) for a in log[before:]]))
+    (HERE / "residency_trace.json").write_text(json.dumps(dict(
+        tau=cache.tau, spare=cache.spare, lag=cache.lag, route_scale=1.5, top_k=k, pool=pool_size, slots=slots,
+        init=init, trace=trace), indent=0))
+
+
 def main() -> None:
     checkout = Path(sys.argv[1]).resolve()
     sys.path.insert(0, str(checkout / "src"))
@@ -169,6 +264,7 @@ def main() -> None:
     codebook_fixture(e8)
     operator_fixture(checkout)
     router_fixture(checkout)
+    residency_fixture(checkout)
     for f in sorted(HERE.glob("*.npz")):
         print(f.name, f.stat().st_size, "bytes")
 
