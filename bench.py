@@ -216,6 +216,123 @@ def run_reference(ns):
     print(json.dumps(line))
 
 
+EP_LAYERS, EP_BATCH = 40, 256
+
+
+def build_ep_stack(device, rank, world, layers):
+    """Config 5: `layers` MoE layers, each with its 384 experts sharded contiguously over the ranks
+    and a replicated router (same seed on every rank)."""
+    from keep_b200 import expert_parallel, moe
+
+    per_rank = EXPERTS // world
+    stack = []
+    for index in range(layers):
+        shard = torch.Generator(device=device)
+        shard.manual_seed(100_000 + 1000 * index + rank)
+
+        def proj(out, inp):
+            codes = torch.randint(0, 1 << 16, (per_rank, out, inp // 8), generator=shard, device=device, dtype=torch.int32).to(torch.uint16)
+            scales = (0.02 * (0.5 + torch.rand((per_rank, out, 1), generator=shard, device=device))).to(torch.float16)
+            return moe.Projection(codes, scales)
+
+        shared = torch.Generator(device=device)
+        shared.manual_seed(100 + index)
+        router = (0.02 * torch.randn((EXPERTS, HIDDEN), generator=shared, device=device)).to(torch.bfloat16)
+        local = moe.RoutedMoELayer(torch.zeros((per_rank, HIDDEN), dtype=torch.bfloat16, device=device),
+                                   proj(INTER, HIDDEN), proj(INTER, HIDDEN), proj(HIDDEN, INTER), top_k=1)
+        stack.append(expert_parallel.ExpertParallelLayer(router, local, experts_per_rank=per_rank, top_k=TOP_K))
+    return stack
+
+
+def run_expert_parallel(ns, rank, world, local, device):
+    """N > 1: the 40-layer expert-parallel stack (config 5).  256 decode tokens in total, split
+    evenly over the ranks; per layer: router, dispatch all-to-all, local experts, combine
+    all-to-all.  The same tokens enter every layer (the layers differ in weights), so the stack
+    is 40 dependent-in-stream layer passes per step."""
+    import torch.distributed as dist
+    from keep_b200 import _lib
+
+    _lib.load()
+    hbm_gbs, peak_kind = measured_peaks()
+    layers = ns.layers
+    stack = build_ep_stack(device, rank, world, layers)
+    tokens_local = EP_BATCH // world
+    gen = torch.Generator(device="cpu")
+    gen.manual_seed(5 + rank)
+    host_in = torch.randn((tokens_local, HIDDEN), generator=gen).to(torch.bfloat16).pin_memory()
+    x = host_in.to(device)
+    outs = [None]
+
+    def step():
+        out = None
+        for layer in stack:
+            out = layer.forward(x)
+        outs[0] = out
+
+    for _ in range(max(ns.warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+    graph = None
+    if not ns.no_graph:
+        try:
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=side):
+                    step()
+            torch.cuda.synchronize()
+            g.replay()
+            torch.cuda.synchronize()
+            graph = g
+        except Exception as exc:  # capture of the collectives refused: fall back to eager launches
+            if rank == 0:
+                print(f"[bench] CUDA graph capture failed ({type(exc).__name__}); timing eager launches", file=sys.stderr)
+            graph = None
+    run = graph.replay if graph is not None else step
+
+    dist.barrier()
+    torch.cuda.synchronize()
+    with ClockSampler(local) as clocks:
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        begin.record()
+        for _ in range(ns.steps):
+            run()
+        end.record()
+        torch.cuda.synchronize()
+        ms = begin.elapsed_time(end)
+        dist.barrier()
+        host_out = torch.empty((tokens_local, HIDDEN), dtype=torch.bfloat16).pin_memory()
+        begin.record()
+        for _ in range(ns.steps):
+            x.copy_(host_in, non_blocking=True)
+            run()
+            host_out.copy_(outs[0], non_blocking=True)
+        end.record()
+        torch.cuda.synchronize()
+        e2e_ms = begin.elapsed_time(end)
+    t = torch.tensor([ms, e2e_ms], device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms, e2e_ms = (float(v) for v in t.cpu())
+    if rank != 0:
+        return
+    tokens = EP_BATCH * ns.steps
+    line = {
+        "metric": METRIC, "value": round(tokens / (ms * 1e-3), 1), "unit": UNIT, "n_gpus": world, "steps": ns.steps, "warmup": ns.warmup,
+        "ms_per_step": round(ms / ns.steps, 4), "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"expert-parallel stack (config 5): {layers} layers x 384 experts sharded {EXPERTS // world} per GPU, top-6, "
+                               f"{EP_BATCH} decode tokens in total ({tokens_local} per GPU), NCCL all-to-all dispatch and combine",
+                   "layers": layers, "batch": EP_BATCH, "l2": f"inputs larger than L2: {layers} layers x {EXPERTS // world * CODE_BYTES_PER_EXPERT / 1e9:.1f} GB of codes per GPU",
+                   "cuda_graph": graph is not None, "note": "value counts each token once per pass through the whole stack"},
+        "roofline": None, "cpu_baseline": None,
+        "layer_us": round(ms / ns.steps / layers * 1e3, 1),
+        "e2e": {"value": round(tokens / (e2e_ms * 1e-3), 1), "unit": UNIT, "h2d_bytes_per_step": EP_BATCH * HIDDEN * 2, "d2h_bytes_per_step": EP_BATCH * HIDDEN * 2},
+        "gpu_launches": 8 * layers * ns.steps * world, "kernel_path": stack[0].local.kernel_path, "clocks": clocks.summary(),
+    }
+    print(json.dumps(line))
+
+
 def run_ours(ns):
     rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -224,6 +341,11 @@ def run_ours(ns):
     if world > 1:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=device)
+        try:
+            run_expert_parallel(ns, rank, world, local, device)
+        finally:
+            dist.destroy_process_group()
+        return
     from keep_b200 import _lib
     _lib.load()
     hbm_gbs, peak_kind = measured_peaks()
@@ -308,6 +430,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--batch", type=int, default=64)
     ap.add_argument("--rotation", type=int, default=ROTATION, help="distinct token batches to rotate over (profiling runs use fewer)")
+    ap.add_argument("--layers", type=int, default=EP_LAYERS, help="layers of the expert-parallel stack (N > 1)")
+    ap.add_argument("--no-graph", action="store_true", help="expert-parallel run: time eager launches instead of a CUDA graph")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ns = ap.parse_args()
     if ns.impl == "reference":
