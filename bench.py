@@ -287,7 +287,7 @@ def run_expert_parallel(ns, rank, world, local, device):
             graph = g
         except Exception as exc:  # capture of the collectives refused: fall back to eager launches
             if rank == 0:
-                print(f"[bench] CUDA graph capture failed ({type(exc).__name__}); timing eager launches", file=sys.stderr)
+                print(f"[bench] CUDA graph capture failed ({type(exc).__name__}: {str(exc)[:300]}); timing eager launches", file=sys.stderr)
             graph = None
     run = graph.replay if graph is not None else step
 

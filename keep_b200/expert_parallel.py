@@ -38,20 +38,23 @@ class RouteExchange:
 
     def plan(self, served_expert: torch.Tensor):
         """served_expert [tokens, k] (global ids, negative = dead pick) -> (position [tokens, k] of
-        each route in the send buffer, or -1; capacity).  Device-side arithmetic only."""
+        each route in the send buffer, with ``world * capacity`` for a dead or overflowing route;
+        capacity).  Fixed-shape device arithmetic only: nothing is read back, so the exchange can
+        sit inside a CUDA graph."""
         tokens, k = served_expert.shape
         routes = tokens * k
         capacity = self.capacity or routes
+        rows = self.world * capacity
         flat = served_expert.reshape(-1).long()
-        live = flat >= 0
-        dest = torch.where(live, flat // self.experts_per_rank, torch.full_like(flat, self.world))  # dead routes sort last
+        dest = torch.where(flat >= 0, flat // self.experts_per_rank, torch.full_like(flat, self.world))  # dead routes sort last
         order = torch.argsort(dest, stable=True)
-        counts = torch.bincount(dest, minlength=self.world + 1)
+        counts = torch.zeros(self.world + 1, dtype=torch.long, device=flat.device).scatter_add_(0, dest, torch.ones_like(dest))
         starts = torch.cumsum(counts, 0) - counts
-        rank_in_bucket = torch.arange(routes, device=flat.device) - starts[dest[order]]
-        position = torch.full((routes,), -1, dtype=torch.long, device=flat.device)
-        ok = (dest[order] < self.world) & (rank_in_bucket < capacity)
-        position[order] = torch.where(ok, dest[order] * capacity + rank_in_bucket, torch.full_like(rank_in_bucket, -1))
+        sorted_dest = dest[order]
+        rank_in_bucket = torch.arange(routes, device=flat.device) - starts[sorted_dest]
+        ok = (sorted_dest < self.world) & (rank_in_bucket < capacity)
+        sorted_pos = torch.where(ok, sorted_dest * capacity + rank_in_bucket, torch.full_like(rank_in_bucket, rows))
+        position = torch.empty_like(sorted_pos).scatter_(0, order, sorted_pos)
         return position.reshape(tokens, k), capacity
 
     def dispatch(self, x: torch.Tensor, served_expert: torch.Tensor, served_weight: torch.Tensor):
@@ -60,28 +63,26 @@ class RouteExchange:
         tokens, k = served_expert.shape
         position, capacity = self.plan(served_expert)
         rows = self.world * capacity
-        flat_pos = position.reshape(-1)
-        live = flat_pos >= 0
-        target = flat_pos[live]
+        flat_pos = position.reshape(-1)  # dead routes point at the spare row `rows`, cut off below
         token_of_route = torch.arange(tokens * k, device=x.device) // k
-        send_x = torch.zeros((rows, x.shape[1]), dtype=x.dtype, device=x.device)
-        send_x[target] = x[token_of_route[live]]
-        send_slot = torch.full((rows,), NO_SLOT, dtype=torch.int32, device=x.device)
-        send_slot[target] = (served_expert.reshape(-1)[live].long() % self.experts_per_rank).to(torch.int32)
-        send_weight = torch.zeros((rows,), dtype=torch.float32, device=x.device)
-        send_weight[target] = served_weight.reshape(-1)[live].float()
-        return self._all_to_all(send_x), self._all_to_all(send_slot), self._all_to_all(send_weight), position
+        send_x = torch.zeros((rows + 1, x.shape[1]), dtype=x.dtype, device=x.device)
+        send_x.index_copy_(0, flat_pos, x[token_of_route])
+        local_slot = (served_expert.reshape(-1).long().clamp(min=0) % self.experts_per_rank).to(torch.int32)
+        send_slot = torch.full((rows + 1,), NO_SLOT, dtype=torch.int32, device=x.device)
+        send_slot.index_copy_(0, flat_pos, local_slot)
+        send_weight = torch.zeros((rows + 1,), dtype=torch.float32, device=x.device)
+        send_weight.index_copy_(0, flat_pos, served_weight.reshape(-1).float())
+        return (self._all_to_all(send_x[:rows]), self._all_to_all(send_slot[:rows]), self._all_to_all(send_weight[:rows]), position)
 
     def combine(self, y_routes: torch.Tensor, position: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
         """y_routes [world * capacity, hidden] (per received route) -> [tokens, hidden]: each token's
         picks summed in fp32 in pick order, one rounding."""
         back = self._all_to_all(y_routes)
+        back = torch.cat([back, torch.zeros((1, back.shape[1]), dtype=back.dtype, device=back.device)])  # row of a dead route
         tokens, k = position.shape
         acc = torch.zeros((tokens, back.shape[1]), dtype=torch.float32, device=back.device)
         for j in range(k):  # pick order, as the single-GPU combine
-            pos = position[:, j]
-            rows = back[pos.clamp(min=0)].float()
-            acc += torch.where((pos >= 0)[:, None], rows, torch.zeros_like(rows))
+            acc += back[position[:, j]].float()
         return acc.to(out_dtype)
 
     def _all_to_all(self, send: torch.Tensor) -> torch.Tensor:

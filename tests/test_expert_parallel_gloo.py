@@ -54,7 +54,8 @@ def worker(rank, port, results):
         results[rank] = float((out - want).abs().max() / want.abs().max())
         # every live route got a distinct position; the dead one none
         pos = position.reshape(-1)
-        assert int((pos < 0).sum()) == 1 and len(set(pos[pos >= 0].tolist())) == TOKENS * TOP_K - 1
+        dump = WORLD * TOKENS * TOP_K
+        assert int((pos == dump).sum()) == 1 and len(set(pos[pos != dump].tolist())) == TOKENS * TOP_K - 1
     finally:
         dist.destroy_process_group()
 
@@ -85,4 +86,4 @@ def test_single_rank_plan_is_dense_and_ordered():
     served = torch.tensor([[3, 0], [1, -1], [2, 2]])
     position, capacity = exchange.plan(served)
     assert capacity == 6
-    assert position.tolist() == [[0, 1], [2, -1], [3, 4]]
+    assert position.tolist() == [[0, 1], [2, 6], [3, 4]]  # 6 = the spare row of a dead pick
