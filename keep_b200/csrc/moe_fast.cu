@@ -113,7 +113,7 @@ int quantize_rows(const void* x, int32_t x_dtype, int64_t rows, int64_t in_dim, 
 // ------------------------------------------------------------------------------------------
 constexpr int GR_THREADS = 1024;
 
-__global__ void __launch_bounds__(GR_THREADS) group_routes_kernel(const uint32_t* __restrict__ served_slot, int routes, int slots, RouteGroups out) {
+__global__ void __launch_bounds__(GR_THREADS) group_routes_kernel(const uint32_t* __restrict__ served_slot, int routes, int slots, int max_group, RouteGroups out) {
   extern __shared__ int32_t sm[];
   int32_t* count = sm;               // [slots] routes per slot, then running cursor
   int32_t* first = sm + slots;       // [slots] first position of the slot in `routes`
@@ -131,7 +131,7 @@ __global__ void __launch_bounds__(GR_THREADS) group_routes_kernel(const uint32_t
   const int per = (slots + GR_THREADS - 1) / GR_THREADS;
   const int lo = min(tid * per, slots), hi = min(lo + per, slots);
   int a = 0, b = 0;
-  for (int s = lo; s < hi; ++s) { a += count[s]; b += (count[s] + MAX_GROUP_ROUTES - 1) / MAX_GROUP_ROUTES; }
+  for (int s = lo; s < hi; ++s) { a += count[s]; b += (count[s] + max_group - 1) / max_group; }
   int ia = a, ib = b;
 #pragma unroll
   for (int o = 1; o < 32; o <<= 1) {
@@ -153,11 +153,11 @@ __global__ void __launch_bounds__(GR_THREADS) group_routes_kernel(const uint32_t
   int base_a = ia - a + (warp ? warp_a[warp - 1] : 0), base_b = ib - b + (warp ? warp_b[warp - 1] : 0);
   for (int s = lo; s < hi; ++s) {
     first[s] = base_a; gfirst[s] = base_b;
-    const int c = count[s], g = (c + MAX_GROUP_ROUTES - 1) / MAX_GROUP_ROUTES;
+    const int c = count[s], g = (c + max_group - 1) / max_group;
     for (int i = 0; i < g; ++i) {
       out.slot[base_b + i] = s;
-      out.start[base_b + i] = base_a + i * MAX_GROUP_ROUTES;
-      out.size[base_b + i] = min(MAX_GROUP_ROUTES, c - i * MAX_GROUP_ROUTES);
+      out.start[base_b + i] = base_a + i * max_group;
+      out.size[base_b + i] = min(max_group, c - i * max_group);
     }
     base_a += c; base_b += g;
   }
@@ -171,14 +171,14 @@ __global__ void __launch_bounds__(GR_THREADS) group_routes_kernel(const uint32_t
   }
 }
 
-int group_routes(const uint32_t* served_slot, int64_t routes, int64_t slots, const RouteGroups& out, cudaStream_t s) {
+int group_routes(const uint32_t* served_slot, int64_t routes, int64_t slots, int max_group, const RouteGroups& out, cudaStream_t s) {
   if (routes > (1 << 20) || slots > 16384) return KEEPVQ_ERR_CAPACITY;
   const size_t smem = static_cast<size_t>(slots) * 3 * sizeof(int32_t);
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(group_routes_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     if (e != cudaSuccess) return note_cuda_error(e);
   }
-  group_routes_kernel<<<1, GR_THREADS, smem, s>>>(served_slot, static_cast<int>(routes), static_cast<int>(slots), out);
+  group_routes_kernel<<<1, GR_THREADS, smem, s>>>(served_slot, static_cast<int>(routes), static_cast<int>(slots), max_group, out);
   KEEPVQ_CHECK_LAUNCH();
   return KEEPVQ_OK;
 }

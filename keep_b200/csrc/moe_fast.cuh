@@ -15,7 +15,8 @@
 namespace keepvq {
 namespace fast {
 
-constexpr int MAX_GROUP_ROUTES = 8;  // routes of one expert that share an MMA tile (its 8 columns)
+constexpr int MAX_GROUP_ROUTES = 8;     // routes of one expert that share an mma.sync tile (its 8 columns)
+constexpr int PREFILL_GROUP_ROUTES = 128;  // routes of one expert per tcgen05 item
 
 // Quantised activation rows: the B operand of the projections.
 struct QuantRows {
@@ -29,7 +30,7 @@ struct RouteGroups {
   int32_t* count;        // [1] number of groups
   int32_t* slot;         // [max_groups]
   int32_t* start;        // [max_groups] first entry in `routes`
-  int32_t* size;         // [max_groups] 1..MAX_GROUP_ROUTES
+  int32_t* size;         // [max_groups] 1..max_group
   int32_t* routes;       // [routes] route ids ordered by group
 };
 
@@ -59,9 +60,15 @@ struct FastProjectionArgs {
 bool shapes_supported(int64_t out_dim, int64_t in_dim, int64_t groups);
 
 int quantize_rows(const void* x, int32_t x_dtype, int64_t rows, int64_t in_dim, int64_t groups, const QuantRows& out, cudaStream_t s);
-int group_routes(const uint32_t* served_slot, int64_t routes, int64_t slots, const RouteGroups& out, cudaStream_t s);
+int group_routes(const uint32_t* served_slot, int64_t routes, int64_t slots, int max_group, const RouteGroups& out, cudaStream_t s);
 int gate_up(const FastProjectionArgs& args, cudaStream_t s);   // h = round(silu(G) * U * weight)
 int down(const FastProjectionArgs& args, cudaStream_t s);      // out = round(W2 h)
+
+// tcgen05 kernels for many routes per expert (prefill_umma.cu).  `status` is a device word that
+// a CTA sets to 1 if one of its bounded waits expires.
+bool prefill_supported(int64_t out_dim, int64_t in_dim, int64_t groups);
+int prefill_gate_up(const FastProjectionArgs& args, int32_t* status, cudaStream_t s);
+int prefill_down(const FastProjectionArgs& args, int32_t* status, cudaStream_t s);
 
 }  // namespace fast
 }  // namespace keepvq

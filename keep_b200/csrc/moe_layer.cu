@@ -34,9 +34,12 @@ struct dtype_tag_of {
 
 static inline int64_t align256(int64_t v) { return (v + 255) / 256 * 256; }
 
+// From this many routes on, experts see enough routes each for the tcgen05 kernels to pay.
+constexpr int64_t PREFILL_MIN_ROUTES = 1024;
+
 struct LayerScratch {
   int64_t logits, gate, up, h, down;
-  int64_t xq, xscale, xsums, hq, hscale, hsums, gcount, gslot, gstart, gsize, groutes;
+  int64_t xq, xscale, xsums, hq, hscale, hsums, gcount, gslot, gstart, gsize, groutes, status;
   int64_t total;
 };
 
@@ -60,6 +63,7 @@ static LayerScratch plan_scratch(int64_t tokens, int64_t hidden, int64_t inter, 
   s.gstart = at; at += align256(routes * 4);
   s.gsize = at;  at += align256(routes * 4);
   s.groutes = at; at += align256(routes * 4);
+  s.status = at; at += 256;
   s.total = at;
   return s;
 }
@@ -178,8 +182,16 @@ extern "C" int keepvq_moe_decode_stages(const keepvq_moe_layer_args* args, int32
                                 reinterpret_cast<int32_t*>(ws + sc.groutes)};
     fast::QuantRows xq = {reinterpret_cast<uint8_t*>(ws + sc.xq), reinterpret_cast<float*>(ws + sc.xscale), reinterpret_cast<int32_t*>(ws + sc.xsums)};
     fast::QuantRows hq = {reinterpret_cast<uint8_t*>(ws + sc.hq), reinterpret_cast<float*>(ws + sc.hscale), reinterpret_cast<int32_t*>(ws + sc.hsums)};
+    // many routes per expert: the tcgen05 kernels, which decode a code once per 128 routes
+    const bool prefill = routes >= PREFILL_MIN_ROUTES && fast::prefill_supported(a.inter, a.hidden, a.w1.groups) &&
+                         fast::prefill_supported(a.hidden, a.inter, a.w2.groups);
+    int32_t* wait_status = reinterpret_cast<int32_t*>(ws + sc.status);
     if (stages & KEEPVQ_STAGE_PREPARE) {
-      if ((rc = fast::group_routes(a.served_slot, routes, a.slots, groups, s))) return rc;
+      if (prefill) {
+        cudaError_t e = cudaMemsetAsync(wait_status, 0, sizeof(int32_t), s);
+        if (e != cudaSuccess) return note_cuda_error(e);
+      }
+      if ((rc = fast::group_routes(a.served_slot, routes, a.slots, prefill ? fast::PREFILL_GROUP_ROUTES : fast::MAX_GROUP_ROUTES, groups, s))) return rc;
       if ((rc = fast::quantize_rows(a.x, a.x_dtype, a.tokens, a.hidden, a.w1.groups, xq, s))) return rc;
     }
     fast::FastProjectionArgs p = {};
@@ -188,13 +200,13 @@ extern "C" int keepvq_moe_decode_stages(const keepvq_moe_layer_args* args, int32
     if (stages & KEEPVQ_STAGE_GATE_UP) {
       p.a = {a.w1.codes, a.w1.scales}; p.b = {a.w3.codes, a.w3.scales};
       p.out_dim = a.inter; p.in_dim = a.hidden; p.groups = a.w1.groups; p.x = xq; p.x_zero_row = a.tokens; p.x_div = a.top_k; p.out = ws + sc.h;
-      if ((rc = fast::gate_up(p, s))) return rc;
+      if ((rc = prefill ? fast::prefill_gate_up(p, wait_status, s) : fast::gate_up(p, s))) return rc;
     }
     if (stages & KEEPVQ_STAGE_DOWN) {
       if ((rc = fast::quantize_rows(ws + sc.h, a.x_dtype, routes, a.inter, a.w2.groups, hq, s))) return rc;
       p.a = {a.w2.codes, a.w2.scales}; p.b = {nullptr, nullptr};
       p.out_dim = a.hidden; p.in_dim = a.inter; p.groups = a.w2.groups; p.x = hq; p.x_zero_row = routes; p.x_div = 1; p.out = ws + sc.down;
-      if ((rc = fast::down(p, s))) return rc;
+      if ((rc = prefill ? fast::prefill_down(p, wait_status, s) : fast::down(p, s))) return rc;
     }
   } else {
     if (stages & KEEPVQ_STAGE_GATE_UP) {

@@ -124,6 +124,21 @@ def test_tensor_and_general_kernels_agree(cuda):
     assert e8.relative_gap(a.float().cpu().numpy(), b.float().cpu().numpy()) <= TOLERANCE
 
 
+@pytest.mark.parametrize("tokens,experts,top_k", [(300, 8, 4), (1100, 5, 1)])
+def test_many_routes_per_expert_take_the_tcgen05_kernels(cuda, tokens, experts, top_k):
+    """From 1024 routes on, the layer runs the tcgen05 (int8, tensor memory) kernels: experts with
+    more routes than one 128-column item, ragged last items, and an expert nobody picks."""
+    cfg = synthetic.layer(seed=41, experts=experts, hidden=512, inter=256)
+    cfg["router"][experts - 1] = -1.0  # bf16 rows of -1: this expert's logits sink, nobody routes to it
+    x = synthetic.tokens(42, tokens, 512).abs()
+    layer = build_layer(cuda, cfg, top_k=top_k)
+    assert layer.kernel_path == "tensor" and tokens * top_k >= 1024
+    out, routing = layer.decode(x.to(cuda))
+    served = routing.served_expert.cpu().numpy()
+    assert (served != experts - 1).all()
+    check_layer(cfg, x, out, routing, top_k=top_k)
+
+
 @pytest.mark.parametrize("batch", [1, 16])
 def test_config2_shape_decode_layer(cuda, batch):
     """The benchmark layer shape (hidden 4096, inter 2048, top-6, softmax) on a 48-expert slice of
