@@ -166,6 +166,46 @@ def projection_roofline(layer, xs, steps, hbm_gbs, peak_kind):
             "us_per_launch": round(ms / steps * 1e3, 2)}
 
 
+PREFILL_TOKENS = 4096
+PREFILL_FLOPS = 2.0 * PREFILL_TOKENS * TOP_K * (INTER * HIDDEN) * 3  # useful FLOPs of the three projections: 1.2369e12
+
+
+def prefill_leg(layer, device, steps=6):
+    """Config 3: 4096 tokens through the same layer (about 64 routes per expert; the skew variant
+    shifts the router logits by a Zipf(1.1) per-expert bias).  Reports the whole layer and the
+    expert projections alone (tcgen05 kernels), as TFLOP/s of useful bf16-equivalent work."""
+    from keep_b200 import _lib
+
+    peaks = json.loads((ROOT / "MEASURED_PEAKS.json").read_text()) if (ROOT / "MEASURED_PEAKS.json").exists() else {}
+    peak = float(peaks.get("bf16_tflops", 1590.0))
+    gen = torch.Generator(device="cpu")
+    gen.manual_seed(2)
+    xs = [torch.randn((PREFILL_TOKENS, HIDDEN), generator=gen).to(torch.bfloat16).to(device) for _ in range(2)]
+    out = {}
+    for name in ("uniform", "zipf"):
+        saved = layer.pool_bias, layer.served_bias
+        if name == "zipf":
+            rank = torch.randperm(EXPERTS, generator=gen).float() + 1.0
+            bias = (-1.1 * torch.log(rank)).to(device)
+            # the bias enters the selection only: scores + bias picks, weights come from raw scores
+            layer.pool_bias = layer.served_bias = bias
+        for j, x in enumerate(xs):
+            _, r = layer.decode(x, state=100 + j)
+        per_expert = torch.bincount(r.served_expert.reshape(-1).long().clamp(min=0), minlength=EXPERTS).cpu()
+        ms_layer = time_graph(lambda i: layer.decode(xs[i % 2], state=100 + i % 2), steps, 3)
+        expert_stages = _lib.STAGE_GATE_UP | _lib.STAGE_DOWN
+        ms_experts = time_graph(lambda i: layer.decode(xs[i % 2], stages=expert_stages, state=100 + i % 2), steps, 3)
+        out[name] = {
+            "layer_ms": round(ms_layer / steps, 4), "layer_tokens_per_s": round(PREFILL_TOKENS / (ms_layer / steps * 1e-3), 1),
+            "experts_ms": round(ms_experts / steps, 4), "experts_tflops": round(PREFILL_FLOPS / (ms_experts / steps * 1e-3) / 1e12, 1),
+            "experts_frac_of_bf16_peak": round(PREFILL_FLOPS / (ms_experts / steps * 1e-3) / 1e12 / peak, 4),
+            "routes_per_expert": {"mean": round(float(per_expert.float().mean()), 1), "max": int(per_expert.max()), "min": int(per_expert.min())}}
+        layer.pool_bias, layer.served_bias = saved
+    out["peak_tflops"], out["useful_flops"] = peak, PREFILL_FLOPS
+    out["kernel"] = "prefill_projection_kernel (tcgen05.mma kind::i8, two int8 MMAs per bf16-equivalent product)"
+    return out
+
+
 def cpu_layer_sample(layer, x_row, threads, experts_per_token=TOP_K):
     """One token through the CPU oracle: router, decode of its served experts' three projections
     (grid[codes] * scale, as the reference's CPU path does), the SwiGLU path with the served
@@ -417,6 +457,7 @@ def run_ours(ns):
         "cpu_baseline": {"value": round(1.0 / cpu_s, 4), "unit": UNIT, "cores": threads, "kind": "port",
                          "sample": "one token: router + decode of 6 experts x 3 projections + SwiGLU path", "parity_gap_vs_gpu": parity_gap},
         "e2e": {"value": round(e2e_value, 1), "unit": UNIT, "h2d_bytes_per_step": batch * HIDDEN * 2, "d2h_bytes_per_step": batch * HIDDEN * 2},
+        "prefill": prefill_leg(layer, device) if not ns.no_prefill else None,
         "gpu_launches": layer.launches_per_call * ns.steps, "kernel_path": layer.kernel_path,
         "clocks": clocks.summary(),
     }
@@ -432,6 +473,7 @@ def main():
     ap.add_argument("--rotation", type=int, default=ROTATION, help="distinct token batches to rotate over (profiling runs use fewer)")
     ap.add_argument("--layers", type=int, default=EP_LAYERS, help="layers of the expert-parallel stack (N > 1)")
     ap.add_argument("--no-graph", action="store_true", help="expert-parallel run: time eager launches instead of a CUDA graph")
+    ap.add_argument("--no-prefill", action="store_true", help="skip the 4096-token prefill leg (config 3)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ns = ap.parse_args()
     if ns.impl == "reference":

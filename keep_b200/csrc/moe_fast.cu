@@ -27,13 +27,21 @@ namespace fast {
 // Activation quantisation: x -> 16-bit fixed point with a power-of-two scale per row.
 // ------------------------------------------------------------------------------------------
 template <typename XT>
-__global__ void __launch_bounds__(256) quantize_rows_kernel(const XT* __restrict__ x, int64_t rows, int64_t in_dim, int64_t groups, QuantRows out) {
+__global__ void __launch_bounds__(256) quantize_rows_kernel(const XT* __restrict__ x, int64_t rows, int64_t in_dim, int64_t groups, QuantRows out, int planes) {
   __shared__ float warp_max[8];
   __shared__ float row_scale;
   extern __shared__ int32_t group_sum[];
   const int64_t row = blockIdx.x, cw = in_dim / 8, per_group = cw / groups;
   if (row == rows) {  // one extra all-zero row: the B operand of MMA columns that carry no route
-    for (int64_t c = threadIdx.x; c < cw; c += 256) reinterpret_cast<uint4*>(out.q)[row * cw + c] = make_uint4(0, 0, 0, 0);
+    // (both layouts: the buffer is (rows + 1) * cw * 16 bytes either way)
+    for (int64_t c = threadIdx.x; c < cw; c += 256) {
+      if (planes) {
+        reinterpret_cast<uint2*>(out.q)[row * cw + c] = make_uint2(0, 0);
+        reinterpret_cast<uint2*>(out.q + (rows + 1) * cw * 8)[row * cw + c] = make_uint2(0, 0);
+      } else {
+        reinterpret_cast<uint4*>(out.q)[row * cw + c] = make_uint4(0, 0, 0, 0);
+      }
+    }
     for (int64_t g = threadIdx.x; g < groups; g += 256) out.sums[row * groups + g] = 0;
     if (threadIdx.x == 0) out.scale[row] = 1.0f;
     return;
@@ -90,19 +98,24 @@ __global__ void __launch_bounds__(256) quantize_rows_kernel(const XT* __restrict
       hi1 |= static_cast<uint32_t>(oh & 0xFF) << (8 * j);
       lo1 |= static_cast<uint32_t>((o - 256 * oh) & 0xFF) << (8 * j);
     }
-    reinterpret_cast<uint4*>(out.q)[row * cw + c] = make_uint4(hi0, hi1, lo0, lo1);
+    if (planes) {  // high bytes of every row first, then the low bytes: what the tcgen05 B tiles copy from
+      reinterpret_cast<uint2*>(out.q)[row * cw + c] = make_uint2(hi0, hi1);
+      reinterpret_cast<uint2*>(out.q + (rows + 1) * cw * 8)[row * cw + c] = make_uint2(lo0, lo1);
+    } else {
+      reinterpret_cast<uint4*>(out.q)[row * cw + c] = make_uint4(hi0, hi1, lo0, lo1);
+    }
   }
   __syncthreads();
   for (int64_t g = threadIdx.x; g < groups; g += 256) out.sums[row * groups + g] = group_sum[g];
 }
 
-int quantize_rows(const void* x, int32_t x_dtype, int64_t rows, int64_t in_dim, int64_t groups, const QuantRows& out, cudaStream_t s) {
+int quantize_rows(const void* x, int32_t x_dtype, int64_t rows, int64_t in_dim, int64_t groups, const QuantRows& out, bool planes, cudaStream_t s) {
   const size_t smem = static_cast<size_t>(groups) * sizeof(int32_t);
   if (smem > 40 * 1024) return KEEPVQ_ERR_CAPACITY;
   const unsigned grid = static_cast<unsigned>(rows + 1);  // + the zero row
-  if (x_dtype == KEEPVQ_F32) quantize_rows_kernel<float><<<grid, 256, smem, s>>>(reinterpret_cast<const float*>(x), rows, in_dim, groups, out);
-  else if (x_dtype == KEEPVQ_F16) quantize_rows_kernel<__half><<<grid, 256, smem, s>>>(reinterpret_cast<const __half*>(x), rows, in_dim, groups, out);
-  else quantize_rows_kernel<__nv_bfloat16><<<grid, 256, smem, s>>>(reinterpret_cast<const __nv_bfloat16*>(x), rows, in_dim, groups, out);
+  if (x_dtype == KEEPVQ_F32) quantize_rows_kernel<float><<<grid, 256, smem, s>>>(reinterpret_cast<const float*>(x), rows, in_dim, groups, out, planes ? 1 : 0);
+  else if (x_dtype == KEEPVQ_F16) quantize_rows_kernel<__half><<<grid, 256, smem, s>>>(reinterpret_cast<const __half*>(x), rows, in_dim, groups, out, planes ? 1 : 0);
+  else quantize_rows_kernel<__nv_bfloat16><<<grid, 256, smem, s>>>(reinterpret_cast<const __nv_bfloat16*>(x), rows, in_dim, groups, out, planes ? 1 : 0);
   KEEPVQ_CHECK_LAUNCH();
   return KEEPVQ_OK;
 }

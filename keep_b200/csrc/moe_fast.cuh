@@ -59,7 +59,9 @@ struct FastProjectionArgs {
 // True when the shapes fit the tensor-core path (in_dim % 256 == 0, group size % 256 == 0, ...).
 bool shapes_supported(int64_t out_dim, int64_t in_dim, int64_t groups);
 
-int quantize_rows(const void* x, int32_t x_dtype, int64_t rows, int64_t in_dim, int64_t groups, const QuantRows& out, cudaStream_t s);
+// planes = false: 16 bytes per codeword (hi 8, lo 8), what the mma.sync kernels read;
+// planes = true: all high bytes [rows + 1, in_dim] then all low bytes, what the tcgen05 kernels copy.
+int quantize_rows(const void* x, int32_t x_dtype, int64_t rows, int64_t in_dim, int64_t groups, const QuantRows& out, bool planes, cudaStream_t s);
 int group_routes(const uint32_t* served_slot, int64_t routes, int64_t slots, int max_group, const RouteGroups& out, cudaStream_t s);
 int gate_up(const FastProjectionArgs& args, cudaStream_t s);   // h = round(silu(G) * U * weight)
 int down(const FastProjectionArgs& args, cudaStream_t s);      // out = round(W2 h)

@@ -83,6 +83,10 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
                : "r"(taddr) : "memory");
 }
 
+__device__ __forceinline__ void cp_async16_pf(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+
 template <int M>
 __global__ void __launch_bounds__(PF_THREADS, 1) prefill_projection_kernel(FastProjectionArgs p, int32_t* status) {
   extern __shared__ uint8_t smem_raw[];
@@ -94,6 +98,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_projection_kernel(FastP
   __shared__ __align__(8) uint64_t bars[2 * PF_STAGES + 2];
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
+  __shared__ int xrow_of[PF_N_MAX];  // activation row of each route of the current item (loader warps)
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const uint32_t smem_base = smem_addr(smem);
   const uint32_t full0 = smem_addr(&bars[0]), empty0 = smem_addr(&bars[PF_STAGES]);
@@ -275,25 +280,42 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_projection_kernel(FastP
       }
     } else {
       // ================= activation (B operand) loaders =======================================
+      // cp.async straight into the swizzled tiles (16 bytes = two codewords of one route), one
+      // K block in flight behind the one being handed to the MMA warp.
       const int loader = tid - (PF_DECODE_WARPS + 1) * 32;  // 0..95
+      for (int n = loader; n < n_pad; n += PF_B_WARPS * 32) {
+        const int route = n < gsize ? p.groups_of_routes.routes[gstart + n] : -1;
+        xrow_of[n] = route < 0 ? static_cast<int>(p.x_zero_row) : route / p.x_div;
+      }
+      asm volatile("bar.sync 1, %0;" ::"n"(PF_B_WARPS * 32) : "memory");  // the loader warps only
+      const uint8_t* plane[2] = {p.x.q, p.x.q + (p.x_zero_row + 1) * cw * 8};
+      const int64_t row_bytes = cw * 8;
       uint32_t it = iter;
-      for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+      bool ok = true;
+      for (int kb = 0; kb < k_blocks && ok; ++kb, ++it) {
         const uint32_t stage = it % PF_STAGES, phase = (it / PF_STAGES) & 1u;
-        if (!mbar_wait(empty0 + 8 * stage, phase ^ 1u, aborted)) break;
-        const uint32_t b_hi = smem_base + stage * STAGE_BYTES + M * PF_TILE_BYTES, b_lo = b_hi + PF_TILE_BYTES;
-        for (int e = loader; e < n_pad * PF_KBLOCK_CODES; e += PF_B_WARPS * 32) {
-          const int n = e >> 4, c = e & 15;
-          const int route = n < gsize ? p.groups_of_routes.routes[gstart + n] : -1;
-          const int64_t xrow = route < 0 ? p.x_zero_row : static_cast<int64_t>(route / p.x_div);
-          const uint4 v = reinterpret_cast<const uint4*>(p.x.q)[xrow * cw + static_cast<int64_t>(kb) * PF_KBLOCK_CODES + c];
-          const uint32_t off = swizzled(n, c >> 1) + (c & 1) * 8;
-          asm volatile("st.shared.v2.u32 [%0], {%1,%2};" ::"r"(b_hi + off), "r"(v.x), "r"(v.y) : "memory");
-          asm volatile("st.shared.v2.u32 [%0], {%1,%2};" ::"r"(b_lo + off), "r"(v.z), "r"(v.w) : "memory");
+        ok = mbar_wait(empty0 + 8 * stage, phase ^ 1u, aborted);
+        if (!ok) break;
+        const uint32_t b_tiles = smem_base + stage * STAGE_BYTES + M * PF_TILE_BYTES;
+        for (int e = loader; e < n_pad * 16; e += PF_B_WARPS * 32) {  // e = (route n, 16-byte chunk c, plane)
+          const int n = e >> 4, c = (e >> 1) & 7, pl = e & 1;
+          cp_async16_pf(b_tiles + pl * PF_TILE_BYTES + swizzled(n, c), plane[pl] + xrow_of[n] * row_bytes + static_cast<int64_t>(kb) * 128 + c * 16);
         }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        if (kb > 0) {  // the previous K block's copies have landed: publish it
+          asm volatile("cp.async.wait_group 1;" ::: "memory");
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          __syncwarp();
+          if (lane == 0) mbar_arrive(full0 + 8 * ((it - 1) % PF_STAGES));
+        }
+      }
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+      if (ok) {
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         __syncwarp();
-        if (lane == 0) mbar_arrive(full0 + 8 * stage);
+        if (lane == 0) mbar_arrive(full0 + 8 * ((it - 1) % PF_STAGES));
       }
+      asm volatile("bar.sync 1, %0;" ::"n"(PF_B_WARPS * 32) : "memory");  // xrow_of is rewritten for the next item
     }
     iter += k_blocks;
   }
