@@ -16,7 +16,7 @@ namespace keepvq {
 namespace fast {
 
 constexpr int MAX_GROUP_ROUTES = 8;     // routes of one expert that share an mma.sync tile (its 8 columns)
-constexpr int PREFILL_GROUP_ROUTES = 128;  // routes of one expert per tcgen05 item
+constexpr int PREFILL_GROUP_ROUTES = 96;   // routes of one expert per tcgen05 item
 
 // Quantised activation rows: the B operand of the projections.
 struct QuantRows {

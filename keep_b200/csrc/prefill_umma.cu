@@ -8,35 +8,43 @@
 //
 // Arithmetic: the same exact-integer form as the decode kernels (moe_fast.cuh).  A codeword
 // becomes eight int8 values q with 4w = 2q + 1; activations are 16-bit fixed point split in a
-// signed high and a signed low byte.  Per (expert, 128 output rows, up to 128 routes):
+// signed high and a signed low byte.  Per (expert, 128 output rows, up to 64 routes):
 //   D_hi[128 x N] += Q[128 x K] * Xhi[N x K]^T,   D_lo likewise   (int32, exact, in TMEM)
 //   y = scale_row * scale_x * (0.5 * (256 D_hi + D_lo) + 0.25 * sum(x'))
 // The weights are the M operand (128 rows per tile) and the routes the N operand, so a ragged
-// expert group costs at most 15 padded columns, and a code is decoded once per 128 routes.
+// expert group costs at most 15 padded columns, and a code is decoded once per 64 routes.
 //
-// Pipeline per CTA (persistent, one per SM, 12 warps):
-//   warps 0-7   decode: a thread owns half a row of the K block (8 codewords per matrix): one
-//               16-byte global load, two table reads and two XORs per codeword, 16-byte stores
-//               into a K-major SWIZZLE_128B tile.  After the last K block the same warps read
-//               the accumulators back (tcgen05.ld) and run the epilogue.
-//   warp  8     issues the MMAs (one thread), commits stages back to the producers.
-//   warps 9-11  copy the routes' quantised activations into the B tiles (high and low bytes).
-// Two shared-memory stages, mbarrier full/empty pairs.  Every wait is bounded: on expiry the CTA
+// Pipeline per CTA (persistent, one per SM, 16 warps), item = (expert, 128 rows, <= 64 routes):
+//   warps 0-7    decode: a thread owns half a row of the K block (8 codewords per matrix); codes
+//                arrive through a private cp.async ring; two table reads and two XORs per
+//                codeword, 16-byte stores into a K-major SWIZZLE_128B tile (2 stages).
+//   warp  8      issues the MMAs (one thread) into one of two accumulator buffers in tensor
+//                memory, commits stages back to the producers.
+//   warps 9-11   cp.async the routes' quantised activations into the B tiles (4 stages).
+//   warps 12-15  epilogue: tcgen05.ld of the finished buffer while the next item's MMAs fill the
+//                other one.
+// mbarrier full/empty pairs carry every dependency.  Every wait is bounded: on expiry the CTA
 // raises a flag in `status`, stops issuing work, frees its tensor memory and returns.
+#include <stdlib.h>
+
 #include "moe_fast.cuh"
 
 namespace keepvq {
 namespace fast {
 
-constexpr int PF_THREADS = 384;
 constexpr int PF_DECODE_WARPS = 8;
 constexpr int PF_B_WARPS = 3;
-constexpr int PF_STAGES = 2;
-constexpr int PF_N_MAX = 128;                   // routes per item
+constexpr int PF_EPI_WARPS = 4;
+constexpr int PF_THREADS = (PF_DECODE_WARPS + 1 + PF_B_WARPS + PF_EPI_WARPS) * 32;  // 512
+constexpr int PF_A_STAGES = 2;
+constexpr int PF_B_STAGES = 4;
+constexpr int PF_N_MAX = PREFILL_GROUP_ROUTES;  // routes per item
 constexpr int PF_ROWS = 128;                    // output rows per item
 constexpr int PF_KBLOCK_CODES = 16;             // codewords of a row per K block = 128 bytes of int8
-constexpr int PF_TILE_BYTES = PF_ROWS * 128;    // 16 KB
-constexpr int PF_TABLE_BYTES = 2 * 256 * 16 * 8;  // abs + sign tables, 16 replicas of 8 bytes
+constexpr int PF_TILE_BYTES = PF_ROWS * 128;    // 16 KB: one A tile
+constexpr int PF_B_STAGE_BYTES = 2 * PF_N_MAX * 128;  // high-byte rows of the routes, then their low-byte rows
+constexpr int PF_TABLE_BYTES = 256 * 16 * 8;     // abs table, 16 replicas of 8 bytes
+constexpr int PF_CODE_RING_BYTES = 24 * 1024;    // per-thread code prefetch ring of the decode warps
 constexpr uint32_t PF_SPIN_LIMIT = 1u << 24;
 
 __device__ __forceinline__ uint32_t smem_addr(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
@@ -58,6 +66,16 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   }
   *abort_flag = 1;
   return false;
+}
+
+// sign * PF_SPREAD_LO puts sign bits 3,2,1,0 on bits 7,15,23,31; PF_SPREAD_HI does so for bits 7,6,5,4
+// (the shifted copies of an 8-bit value never overlap).  sign_masks then fills each byte with its top bit.
+constexpr uint32_t PF_SPREAD_LO = (1u << 4) | (1u << 13) | (1u << 22) | (1u << 31);
+constexpr uint32_t PF_SPREAD_HI = 1u | (1u << 9) | (1u << 18) | (1u << 27);
+__device__ __forceinline__ uint32_t sign_masks(uint32_t v) {
+  uint32_t m;
+  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(m) : "r"(v), "r"(0u), "r"(0xBA98u));
+  return m;
 }
 
 // K-major SWIZZLE_128B operand tile: rows of 128 bytes, 8-row groups 1024 bytes apart.
@@ -88,43 +106,39 @@ __device__ __forceinline__ void cp_async16_pf(uint32_t dst, const void* src) {
 }
 
 template <int M>
-__global__ void __launch_bounds__(PF_THREADS, 1) prefill_projection_kernel(FastProjectionArgs p, int32_t* status) {
+__global__ void __launch_bounds__(PF_THREADS, 1) prefill_projection_kernel(FastProjectionArgs p, int32_t* status, int diag) {
   extern __shared__ uint8_t smem_raw[];
   // SWIZZLE_128B tiles want 1024-byte alignment; the launch reserves the slack
   uint8_t* smem = smem_raw + ((1024u - (smem_addr(smem_raw) & 1023u)) & 1023u);
-  // layout: [stage][A tiles M x 16 KB | B_hi 16 KB | B_lo 16 KB] ... tables
-  constexpr int STAGE_BYTES = (M + 2) * PF_TILE_BYTES;
-  uint8_t* tables = smem + PF_STAGES * STAGE_BYTES;
-  __shared__ __align__(8) uint64_t bars[2 * PF_STAGES + 2];
+  // layout: A stages [2][M x 16 KB] | B stages [4][hi rows | lo rows] | abs table 32 KB | code ring
+  constexpr int A_STAGE_BYTES = M * PF_TILE_BYTES;
+  constexpr int A_BYTES = PF_A_STAGES * A_STAGE_BYTES, B_BYTES = PF_B_STAGES * PF_B_STAGE_BYTES;
+  uint8_t* tables = smem + A_BYTES + B_BYTES;
+  enum { A_FULL = 0, A_EMPTY = A_FULL + PF_A_STAGES, B_FULL = A_EMPTY + PF_A_STAGES, B_EMPTY = B_FULL + PF_B_STAGES,
+         ACC_FULL = B_EMPTY + PF_B_STAGES, ACC_EMPTY = ACC_FULL + 2, N_BARS = ACC_EMPTY + 2 };
+  __shared__ __align__(8) uint64_t bars[N_BARS];
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
-  __shared__ int xrow_of[PF_N_MAX];  // activation row of each route of the current item (loader warps)
+  // per-warp copies, so that a role needs no barrier of its own (every cross-warp wait is an mbarrier with a limit)
+  __shared__ int xrow_all[PF_B_WARPS][PF_N_MAX];   // loader warps: activation row of each route of the current item
+  __shared__ int4 epi_all[PF_EPI_WARPS][PF_N_MAX];  // epilogue warps: route, x scale, x sum / 4, gate weight
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const uint32_t smem_base = smem_addr(smem);
-  const uint32_t full0 = smem_addr(&bars[0]), empty0 = smem_addr(&bars[PF_STAGES]);
-  const uint32_t accum_full = smem_addr(&bars[2 * PF_STAGES]), accum_empty = smem_addr(&bars[2 * PF_STAGES + 1]);
-  constexpr uint32_t TMEM_COLS = M == 2 ? 512 : 256;
+  const uint32_t bar0 = smem_addr(&bars[0]);
+  auto bar = [&](int which, int index) { return bar0 + 8u * static_cast<uint32_t>(which + index); };
+  constexpr uint32_t ACC_COLS = 2 * M * PF_N_MAX;   // one accumulator buffer: per matrix the high-byte then the low-byte columns
+  constexpr int ACC_BUFS = (2 * ACC_COLS <= 512) ? 2 : 1;  // a second buffer lets the epilogue overlap the next item
+  constexpr uint32_t TMEM_COLS = 512;
 
   // ---- set-up: tables, barriers, tensor memory ------------------------------------------------
-  for (int e = tid; e < 512; e += PF_THREADS) {
+  for (int e = tid; e < 256; e += PF_THREADS) {
+    // abs entry: byte j of the low word is table nibble 3-j, of the high word 7-j, each as h = nibble - 8
+    const uint32_t word = p.codebook[e];
     uint32_t lo = 0, hi = 0;
-    if (e < 256) {  // abs entry: byte j of the low word is table nibble 3-j, of the high word 7-j
-      const uint32_t word = p.codebook[e];
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        lo |= ((((word >> (4 * (3 - j))) & 0xFu) - 8u) & 0xFFu) << (8 * j);
-        hi |= ((((word >> (4 * (7 - j))) & 0xFu) - 8u) & 0xFFu) << (8 * j);
-      }
-    } else {        // sign entry: 0xFE where the sign bit is set; on odd parity ^1 everywhere, ^0xFF on nibble 0
-      const uint32_t sb = e - 256, par = __popc(sb) & 1u;
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const int nl = 3 - j, nh = 7 - j;
-        uint32_t ml = ((sb >> nl) & 1u) ? 0xFEu : 0u, mh = ((sb >> nh) & 1u) ? 0xFEu : 0u;
-        if (par) { ml ^= nl == 0 ? 0xFFu : 0x01u; mh ^= 0x01u; }
-        lo |= ml << (8 * j);
-        hi |= mh << (8 * j);
-      }
+    for (int j = 0; j < 4; ++j) {
+      lo |= ((((word >> (4 * (3 - j))) & 0xFu) - 8u) & 0xFFu) << (8 * j);
+      hi |= ((((word >> (4 * (7 - j))) & 0xFu) - 8u) & 0xFFu) << (8 * j);
     }
     uint2* dst = reinterpret_cast<uint2*>(tables) + e * 16;
 #pragma unroll
@@ -132,9 +146,9 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_projection_kernel(FastP
   }
   if (tid == 0) {
     abort_flag = 0;
-    for (int s = 0; s < PF_STAGES; ++s) { mbar_init(full0 + 8 * s, PF_DECODE_WARPS + PF_B_WARPS); mbar_init(empty0 + 8 * s, 1); }
-    mbar_init(accum_full, 1);
-    mbar_init(accum_empty, PF_DECODE_WARPS);
+    for (int s = 0; s < PF_A_STAGES; ++s) { mbar_init(bar(A_FULL, s), PF_DECODE_WARPS); mbar_init(bar(A_EMPTY, s), 1); }
+    for (int s = 0; s < PF_B_STAGES; ++s) { mbar_init(bar(B_FULL, s), PF_B_WARPS); mbar_init(bar(B_EMPTY, s), 1); }
+    for (int s = 0; s < 2; ++s) { mbar_init(bar(ACC_FULL, s), 1); mbar_init(bar(ACC_EMPTY, s), PF_EPI_WARPS); }  // ACC_BUFS of them in use
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == PF_DECODE_WARPS) {
@@ -151,87 +165,186 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_projection_kernel(FastP
   const int row_tiles = static_cast<int>((N_out + PF_ROWS - 1) / PF_ROWS);
   const int items = p.groups_of_routes.count[0] * row_tiles;
   const Projection mats[2] = {p.a, p.b};
-  const uint32_t abs_lane = smem_addr(tables) + (lane & 15) * 8, sign_lane = abs_lane + 256 * 16 * 8;
   volatile int* aborted = &abort_flag;
 
-  uint32_t iter = 0;  // K blocks handled so far by this CTA: picks the stage and its phase
+  // Every role walks the same item list on its own clock; barriers carry the dependencies.
+  uint32_t iter = 0;  // K blocks since the start: picks stages and phases
   int n_item = 0;
-  for (int item = blockIdx.x; item < items && !*aborted; item += gridDim.x, ++n_item) {
+  for (int item = blockIdx.x; item < items && !*aborted; item += gridDim.x, ++n_item, iter += k_blocks) {
     const int gi = item / row_tiles, tile = item - gi * row_tiles;
     const int64_t slot = p.groups_of_routes.slot[gi];
     const int gsize = p.groups_of_routes.size[gi], gstart = p.groups_of_routes.start[gi];
     const int n_pad = (gsize + 15) & ~15;  // the N of the MMA
     const int64_t row0 = static_cast<int64_t>(tile) * PF_ROWS;
+    const int acc_buf = n_item % ACC_BUFS;
+    const uint32_t acc_phase = (n_item / ACC_BUFS) & 1u;
 
     if (warp < PF_DECODE_WARPS) {
-      // ================= decode producers, then epilogue ======================================
+      // ================= decode producers =====================================================
+      const uint32_t abs_lane = smem_addr(tables) + (lane & 15) * 8;
       const int row = tid >> 1, half = tid & 1;  // half a row of the K block: 8 codewords
       const int64_t grow = min(row0 + row, N_out - 1);
       const uint16_t* src[M];
 #pragma unroll
       for (int m = 0; m < M; ++m) src[m] = mats[m].codes + (slot * N_out + grow) * cw + half * 8;
-      uint4 next[M];
+      // codes arrive through a private cp.async ring, RING - 1 K blocks ahead of the decode
+      constexpr int RING = PF_CODE_RING_BYTES / (M * 256 * 16);
+      const uint32_t ring = smem_base + A_BYTES + B_BYTES + PF_TABLE_BYTES + tid * 16;
+      auto fetch = [&](int kb) {
+        if (kb < k_blocks) {
 #pragma unroll
-      for (int m = 0; m < M; ++m) next[m] = ld_stream_u4(src[m]);
+          for (int m = 0; m < M; ++m) cp_async16_pf(ring + ((kb % RING) * M + m) * (256 * 16), src[m] + kb * PF_KBLOCK_CODES);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+      };
+#pragma unroll
+      for (int kb = 0; kb < RING - 1; ++kb) fetch(kb);
       uint32_t it = iter;
       for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+        fetch(kb + RING - 1);
+        asm volatile("cp.async.wait_group %0;" ::"n"(RING - 1) : "memory");
         uint4 cur[M];
 #pragma unroll
-        for (int m = 0; m < M; ++m) cur[m] = next[m];
-        if (kb + 1 < k_blocks) {
+        for (int m = 0; m < M; ++m)
+          asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(cur[m].x), "=r"(cur[m].y), "=r"(cur[m].z), "=r"(cur[m].w)
+                       : "r"(ring + ((kb % RING) * M + m) * (256 * 16)));
+        const uint32_t stage = it % PF_A_STAGES, phase = (it / PF_A_STAGES) & 1u;
+        if (!mbar_wait(bar(A_EMPTY, stage), phase ^ 1u, aborted)) break;
+        const uint32_t stage_base = smem_base + stage * A_STAGE_BYTES;
 #pragma unroll
-          for (int m = 0; m < M; ++m) next[m] = ld_stream_u4(src[m] + (kb + 1) * PF_KBLOCK_CODES);
-        }
-        const uint32_t stage = it % PF_STAGES, phase = (it / PF_STAGES) & 1u;
-        if (!mbar_wait(empty0 + 8 * stage, phase ^ 1u, aborted)) break;
-        const uint32_t stage_base = smem_base + stage * STAGE_BYTES;
-#pragma unroll
-        for (int m = 0; m < M; ++m) {
+        for (int m = 0; m < M && diag != 2; ++m) {
           const uint32_t words[4] = {cur[m].x, cur[m].y, cur[m].z, cur[m].w};
 #pragma unroll
           for (int pair = 0; pair < 4; ++pair) {  // two codewords = one 16-byte chunk of the row
             const uint32_t w = words[pair];
-            uint32_t e0x, e0y, s0x, s0y, e1x, e1y, s1x, s1y;
-            asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(e0x), "=r"(e0y) : "r"(abs_lane + ((w >> 1) & 0x7F80u)));
-            asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(s0x), "=r"(s0y) : "r"(sign_lane + ((w << 7) & 0x7F80u)));
-            asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(e1x), "=r"(e1y) : "r"(abs_lane + ((w >> 17) & 0x7F80u)));
-            asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(s1x), "=r"(s1y) : "r"(sign_lane + ((w >> 9) & 0x7F80u)));
+            uint32_t q[4];
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+              // q = h ^ (sign bit ? 0xFE : 0); on odd parity of the sign byte ^1 everywhere and ^0xFF on nibble 0
+              const uint32_t sign = (w >> (16 * c)) & 0xFFu, odd = 0u - (__popc(sign) & 1u);
+              uint32_t ex, ey;
+              asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(ex), "=r"(ey) : "r"(abs_lane + ((c ? (w >> 17) : (w >> 1)) & 0x7F80u)));
+              q[2 * c] = ex ^ (sign_masks(sign * PF_SPREAD_LO) & 0xFEFEFEFEu) ^ (odd & 0xFF010101u);
+              q[2 * c + 1] = ey ^ (sign_masks(sign * PF_SPREAD_HI) & 0xFEFEFEFEu) ^ (odd & 0x01010101u);
+            }
             const uint32_t dst = stage_base + m * PF_TILE_BYTES + swizzled(row, half * 4 + pair);
-            asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst), "r"(e0x ^ s0x), "r"(e0y ^ s0y), "r"(e1x ^ s1x), "r"(e1y ^ s1y) : "memory");
+            asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst), "r"(q[0]), "r"(q[1]), "r"(q[2]), "r"(q[3]) : "memory");
           }
         }
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         __syncwarp();
-        if (lane == 0) mbar_arrive(full0 + 8 * stage);
+        if (lane == 0) mbar_arrive(bar(A_FULL, stage));
       }
-      // ---- epilogue: accumulators -> y -> (SwiGLU) -> out -----------------------------------
-      if (!*aborted && mbar_wait(accum_full, n_item & 1, aborted)) {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+    } else if (warp == PF_DECODE_WARPS) {
+      // ================= MMA issuer ============================================================
+      if (lane == 0) {
+        // N = 2 * n_pad: the high-byte rows and the low-byte rows of the routes are one B operand
+        const uint32_t idesc = (2u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(n_pad >> 2) << 17) | ((PF_ROWS >> 4) << 24);
+        bool ok = mbar_wait(bar(ACC_EMPTY, acc_buf), acc_phase ^ 1u, aborted);  // the epilogue has drained this buffer
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const int quarter = warp & 3, col_half = warp >> 2;
-        const int64_t erow = row0 + quarter * 32 + lane;
-        float scale[M];
+        const uint32_t acc = tmem + acc_buf * ACC_COLS;
+        uint32_t it = iter;
+        for (int kb = 0; kb < k_blocks && ok; ++kb, ++it) {
+          const uint32_t sa = it % PF_A_STAGES, sb = it % PF_B_STAGES;
+          ok = mbar_wait(bar(A_FULL, sa), (it / PF_A_STAGES) & 1u, aborted) && mbar_wait(bar(B_FULL, sb), (it / PF_B_STAGES) & 1u, aborted);
+          if (!ok) break;
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint32_t a_base = smem_base + sa * A_STAGE_BYTES, b_base = smem_base + A_BYTES + sb * PF_B_STAGE_BYTES;
 #pragma unroll
-        for (int m = 0; m < M; ++m) scale[m] = load_as_float(mats[m].scales, p.scales_dtype, slot * N_out + min(erow, N_out - 1));
-        for (int c0 = col_half * 16; c0 < n_pad; c0 += 32) {  // the two warpgroups interleave 16-column chunks
+          const uint64_t b_desc = umma_desc(b_base);
+#pragma unroll
+          for (int m = 0; m < M; ++m) {
+            const uint64_t a_desc = umma_desc(a_base + m * PF_TILE_BYTES);
+#pragma unroll
+            for (int k = 0; k < 4 && diag != 4; ++k)  // 32 bytes of K per instruction: advance both start addresses by 2 x 16 B
+              umma_i8(acc + m * (2 * PF_N_MAX), a_desc + 2 * k, b_desc + 2 * k, idesc, (kb | k) != 0);
+          }
+          umma_commit(bar(A_EMPTY, sa));  // the stages may be refilled once these MMAs have read them
+          umma_commit(bar(B_EMPTY, sb));
+        }
+        if (ok) umma_commit(bar(ACC_FULL, acc_buf));
+      }
+    } else if (warp < PF_DECODE_WARPS + 1 + PF_B_WARPS) {
+      // ================= activation (B operand) loaders =======================================
+      // cp.async straight into the swizzled tiles (16 bytes = two codewords of one route); a K
+      // block is published when its copies have landed, up to three later ones already in flight.
+      const int loader = tid - (PF_DECODE_WARPS + 1) * 32;  // 0..95
+      int* xrow_of = xrow_all[warp - (PF_DECODE_WARPS + 1)];
+      __syncwarp();
+      for (int n = lane; n < n_pad; n += 32) {
+        const int route = n < gsize ? p.groups_of_routes.routes[gstart + n] : -1;
+        xrow_of[n] = route < 0 ? static_cast<int>(p.x_zero_row) : route / p.x_div;
+      }
+      __syncwarp();
+      const uint8_t* plane[2] = {p.x.q, p.x.q + (p.x_zero_row + 1) * cw * 8};
+      const int64_t row_bytes = cw * 8;
+      uint32_t it = iter;
+      bool ok = true;
+      auto publish = [&](uint32_t which) {
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(B_FULL, which % PF_B_STAGES));
+      };
+      for (int kb = 0; kb < k_blocks && ok; ++kb, ++it) {
+        const uint32_t stage = it % PF_B_STAGES, phase = (it / PF_B_STAGES) & 1u;
+        ok = mbar_wait(bar(B_EMPTY, stage), phase ^ 1u, aborted);
+        if (!ok) break;
+        const uint32_t b_stage = smem_base + A_BYTES + stage * PF_B_STAGE_BYTES;
+        for (int e = loader; e < n_pad * 16 && diag != 3; e += PF_B_WARPS * 32) {  // e = (route n, 16-byte chunk c, plane)
+          const int n = e >> 4, c = (e >> 1) & 7, pl = e & 1;
+          cp_async16_pf(b_stage + swizzled(pl * n_pad + n, c), plane[pl] + xrow_of[n] * row_bytes + static_cast<int64_t>(kb) * 128 + c * 16);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        if (kb >= PF_B_STAGES - 1) {  // K block kb - 3 has landed
+          asm volatile("cp.async.wait_group %0;" ::"n"(PF_B_STAGES - 1) : "memory");
+          publish(it - (PF_B_STAGES - 1));
+        }
+      }
+      if (ok) {  // drain: publish the last K blocks in order
+        const int tail = k_blocks < PF_B_STAGES - 1 ? k_blocks : PF_B_STAGES - 1;
+        if (tail >= 3) { asm volatile("cp.async.wait_group 2;" ::: "memory"); publish(it - 3); }
+        if (tail >= 2) { asm volatile("cp.async.wait_group 1;" ::: "memory"); publish(it - 2); }
+        if (tail >= 1) { asm volatile("cp.async.wait_group 0;" ::: "memory"); publish(it - 1); }
+      }
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+    } else {
+      // ================= epilogue: accumulators -> y -> (SwiGLU) -> out =======================
+      const int quarter = warp - (PF_DECODE_WARPS + 1 + PF_B_WARPS);
+      int4* per_route = epi_all[quarter];
+      __syncwarp();
+      for (int n = lane; n < n_pad; n += 32) {
+        const int route = n < gsize ? p.groups_of_routes.routes[gstart + n] : -1;
+        const int64_t xrow = route < 0 ? p.x_zero_row : static_cast<int64_t>(route / p.x_div);
+        const float weight = (M == 2 && route >= 0) ? p.route_weight[route] : 1.0f;
+        per_route[n] = make_int4(route, __float_as_int(p.x.scale[xrow]), __float_as_int(0.25f * static_cast<float>(p.x.sums[xrow])), __float_as_int(weight));
+      }
+      __syncwarp();
+      const int64_t erow = row0 + quarter * 32 + lane;
+      float scale[M];
+#pragma unroll
+      for (int m = 0; m < M; ++m) scale[m] = load_as_float(mats[m].scales, p.scales_dtype, slot * N_out + min(erow, N_out - 1));
+      if (mbar_wait(bar(ACC_FULL, acc_buf), acc_phase, aborted)) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t acc_base = tmem + acc_buf * ACC_COLS + (static_cast<uint32_t>(quarter * 32) << 16);
+        for (int c0 = 0; c0 < n_pad && diag != 1; c0 += 16) {
           uint32_t acc[M][2][16];
 #pragma unroll
           for (int m = 0; m < M; ++m)
 #pragma unroll
-            for (int piece = 0; piece < 2; ++piece)
-              tmem_ld16(tmem + (static_cast<uint32_t>(quarter * 32) << 16) + (m * 2 + piece) * PF_N_MAX + c0, acc[m][piece]);
+            for (int piece = 0; piece < 2; ++piece) tmem_ld16(acc_base + m * (2 * PF_N_MAX) + piece * n_pad + c0, acc[m][piece]);
           asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
-            const int col = c0 + j;
-            if (col >= gsize || erow >= N_out) continue;
-            const int route = p.groups_of_routes.routes[gstart + col];
-            const int64_t xrow = route / p.x_div;
-            const float xs = p.x.scale[xrow], xsum = static_cast<float>(p.x.sums[xrow]);
+            const int4 pr = per_route[c0 + j];
+            const int route = pr.x;
+            if (route < 0 || erow >= N_out) continue;
+            const float x_scale = __int_as_float(pr.y), x_sum4 = __int_as_float(pr.z);
             float y[M];
 #pragma unroll
             for (int m = 0; m < M; ++m) {
               const float dot = 256.0f * static_cast<float>(static_cast<int>(acc[m][0][j])) + static_cast<float>(static_cast<int>(acc[m][1][j]));
-              y[m] = scale[m] * xs * (0.5f * dot + 0.25f * xsum);
+              y[m] = scale[m] * x_scale * (0.5f * dot + x_sum4);
             }
             float result;
             if (M == 2) {
@@ -239,7 +352,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_projection_kernel(FastP
               if (p.out_dtype == KEEPVQ_BF16) { gt = __bfloat162float(__float2bfloat16_rn(gt)); up = __bfloat162float(__float2bfloat16_rn(up)); }
               else if (p.out_dtype == KEEPVQ_F16) { gt = __half2float(__float2half_rn(gt)); up = __half2float(__float2half_rn(up)); }
               if (p.swiglu_limit > 0.0f) { gt = fminf(gt, p.swiglu_limit); up = fminf(fmaxf(up, -p.swiglu_limit), p.swiglu_limit); }
-              result = gt / (1.0f + expf(-gt)) * up * p.route_weight[route];
+              result = gt / (1.0f + expf(-gt)) * up * __int_as_float(pr.w);
             } else {
               result = y[0];
             }
@@ -248,76 +361,9 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_projection_kernel(FastP
         }
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
         __syncwarp();
-        if (lane == 0) mbar_arrive(accum_empty);
+        if (lane == 0) mbar_arrive(bar(ACC_EMPTY, acc_buf));
       }
-    } else if (warp == PF_DECODE_WARPS) {
-      // ================= MMA issuer ============================================================
-      if (lane == 0) {
-        const uint32_t idesc = (2u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(n_pad >> 3) << 17) | ((PF_ROWS >> 4) << 24);
-        bool ok = mbar_wait(accum_empty, (n_item & 1) ^ 1u, aborted);  // the epilogue has drained the accumulators
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        uint32_t it = iter;
-        for (int kb = 0; kb < k_blocks && ok; ++kb, ++it) {
-          const uint32_t stage = it % PF_STAGES, phase = (it / PF_STAGES) & 1u;
-          ok = mbar_wait(full0 + 8 * stage, phase, aborted);
-          if (!ok) break;
-          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          const uint32_t stage_base = smem_base + stage * STAGE_BYTES;
-#pragma unroll
-          for (int m = 0; m < M; ++m) {
-            const uint64_t a_desc = umma_desc(stage_base + m * PF_TILE_BYTES);
-#pragma unroll
-            for (int piece = 0; piece < 2; ++piece) {
-              const uint64_t b_desc = umma_desc(stage_base + (M + piece) * PF_TILE_BYTES);
-#pragma unroll
-              for (int k = 0; k < 4; ++k)  // 32 bytes of K per instruction: advance both start addresses by 2 x 16 B
-                umma_i8(tmem + (m * 2 + piece) * PF_N_MAX, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb | k) != 0);
-            }
-          }
-          umma_commit(empty0 + 8 * stage);  // the stage may be refilled once these MMAs have read it
-        }
-        if (ok) umma_commit(accum_full);
-      }
-    } else {
-      // ================= activation (B operand) loaders =======================================
-      // cp.async straight into the swizzled tiles (16 bytes = two codewords of one route), one
-      // K block in flight behind the one being handed to the MMA warp.
-      const int loader = tid - (PF_DECODE_WARPS + 1) * 32;  // 0..95
-      for (int n = loader; n < n_pad; n += PF_B_WARPS * 32) {
-        const int route = n < gsize ? p.groups_of_routes.routes[gstart + n] : -1;
-        xrow_of[n] = route < 0 ? static_cast<int>(p.x_zero_row) : route / p.x_div;
-      }
-      asm volatile("bar.sync 1, %0;" ::"n"(PF_B_WARPS * 32) : "memory");  // the loader warps only
-      const uint8_t* plane[2] = {p.x.q, p.x.q + (p.x_zero_row + 1) * cw * 8};
-      const int64_t row_bytes = cw * 8;
-      uint32_t it = iter;
-      bool ok = true;
-      for (int kb = 0; kb < k_blocks && ok; ++kb, ++it) {
-        const uint32_t stage = it % PF_STAGES, phase = (it / PF_STAGES) & 1u;
-        ok = mbar_wait(empty0 + 8 * stage, phase ^ 1u, aborted);
-        if (!ok) break;
-        const uint32_t b_tiles = smem_base + stage * STAGE_BYTES + M * PF_TILE_BYTES;
-        for (int e = loader; e < n_pad * 16; e += PF_B_WARPS * 32) {  // e = (route n, 16-byte chunk c, plane)
-          const int n = e >> 4, c = (e >> 1) & 7, pl = e & 1;
-          cp_async16_pf(b_tiles + pl * PF_TILE_BYTES + swizzled(n, c), plane[pl] + xrow_of[n] * row_bytes + static_cast<int64_t>(kb) * 128 + c * 16);
-        }
-        asm volatile("cp.async.commit_group;" ::: "memory");
-        if (kb > 0) {  // the previous K block's copies have landed: publish it
-          asm volatile("cp.async.wait_group 1;" ::: "memory");
-          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-          __syncwarp();
-          if (lane == 0) mbar_arrive(full0 + 8 * ((it - 1) % PF_STAGES));
-        }
-      }
-      asm volatile("cp.async.wait_group 0;" ::: "memory");
-      if (ok) {
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        __syncwarp();
-        if (lane == 0) mbar_arrive(full0 + 8 * ((it - 1) % PF_STAGES));
-      }
-      asm volatile("bar.sync 1, %0;" ::"n"(PF_B_WARPS * 32) : "memory");  // xrow_of is rewritten for the next item
     }
-    iter += k_blocks;
   }
 
   // ---- teardown ------------------------------------------------------------------------------
@@ -333,7 +379,7 @@ bool prefill_supported(int64_t out_dim, int64_t in_dim, int64_t groups) {
 
 template <int M>
 static int launch_prefill(const FastProjectionArgs& p, int32_t* status, cudaStream_t s) {
-  constexpr size_t smem = PF_STAGES * (M + 2) * PF_TILE_BYTES + PF_TABLE_BYTES + 1024;
+  constexpr size_t smem = PF_A_STAGES * M * PF_TILE_BYTES + PF_B_STAGES * PF_B_STAGE_BYTES + PF_TABLE_BYTES + PF_CODE_RING_BYTES + 1024;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(prefill_projection_kernel<M>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
@@ -343,7 +389,9 @@ static int launch_prefill(const FastProjectionArgs& p, int32_t* status, cudaStre
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  prefill_projection_kernel<M><<<sms, PF_THREADS, smem, s>>>(p, status);
+  static int diag = -1;  // measurement aid: KEEPVQ_PREFILL_DIAG = 1 no epilogue, 2 no decode, 3 no activation copies, 4 no MMAs (outputs meaningless)
+  if (diag < 0) { const char* v = getenv("KEEPVQ_PREFILL_DIAG"); diag = v ? atoi(v) : 0; }
+  prefill_projection_kernel<M><<<sms, PF_THREADS, smem, s>>>(p, status, diag);
   KEEPVQ_CHECK_LAUNCH();
   return KEEPVQ_OK;
 }
