@@ -120,7 +120,6 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_projection_kernel(FastP
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
   // per-warp copies, so that a role needs no barrier of its own (every cross-warp wait is an mbarrier with a limit)
-  __shared__ int xrow_all[PF_B_WARPS][PF_N_MAX];   // loader warps: activation row of each route of the current item
   __shared__ int4 epi_all[PF_EPI_WARPS][PF_N_MAX];  // epilogue warps: route, x scale, x sum / 4, gate weight
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const uint32_t smem_base = smem_addr(smem);
@@ -269,16 +268,23 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_projection_kernel(FastP
       // ================= activation (B operand) loaders =======================================
       // cp.async straight into the swizzled tiles (16 bytes = two codewords of one route); a K
       // block is published when its copies have landed, up to three later ones already in flight.
+      // A thread keeps one (chunk, plane) and every sixth route: sources and destinations are
+      // worked out once per item, a K block then costs an add and a copy per route.
       const int loader = tid - (PF_DECODE_WARPS + 1) * 32;  // 0..95
-      int* xrow_of = xrow_all[warp - (PF_DECODE_WARPS + 1)];
-      __syncwarp();
-      for (int n = lane; n < n_pad; n += 32) {
-        const int route = n < gsize ? p.groups_of_routes.routes[gstart + n] : -1;
-        xrow_of[n] = route < 0 ? static_cast<int>(p.x_zero_row) : route / p.x_div;
-      }
-      __syncwarp();
-      const uint8_t* plane[2] = {p.x.q, p.x.q + (p.x_zero_row + 1) * cw * 8};
+      constexpr int SLOTS = PF_N_MAX * 16 / (PF_B_WARPS * 32);  // routes per thread
+      static_assert(SLOTS * PF_B_WARPS * 32 == PF_N_MAX * 16 && (PF_B_WARPS * 32) % 16 == 0, "loader split");
+      const int c = (loader >> 1) & 7, pl = loader & 1, n0 = loader >> 4;
       const int64_t row_bytes = cw * 8;
+      const uint8_t* plane = p.x.q + (pl ? (p.x_zero_row + 1) * row_bytes : 0) + c * 16;
+      const uint8_t* src[SLOTS];
+      uint32_t dst[SLOTS];
+#pragma unroll
+      for (int i = 0; i < SLOTS; ++i) {
+        const int n = n0 + i * (PF_B_WARPS * 2);
+        const int route = n < gsize ? p.groups_of_routes.routes[gstart + n] : -1;
+        src[i] = plane + (route < 0 ? p.x_zero_row : static_cast<int64_t>(route / p.x_div)) * row_bytes;
+        dst[i] = swizzled(pl * n_pad + n, c);
+      }
       uint32_t it = iter;
       bool ok = true;
       auto publish = [&](uint32_t which) {
@@ -291,10 +297,9 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_projection_kernel(FastP
         ok = mbar_wait(bar(B_EMPTY, stage), phase ^ 1u, aborted);
         if (!ok) break;
         const uint32_t b_stage = smem_base + A_BYTES + stage * PF_B_STAGE_BYTES;
-        for (int e = loader; e < n_pad * 16 && diag != 3; e += PF_B_WARPS * 32) {  // e = (route n, 16-byte chunk c, plane)
-          const int n = e >> 4, c = (e >> 1) & 7, pl = e & 1;
-          cp_async16_pf(b_stage + swizzled(pl * n_pad + n, c), plane[pl] + xrow_of[n] * row_bytes + static_cast<int64_t>(kb) * 128 + c * 16);
-        }
+#pragma unroll
+        for (int i = 0; i < SLOTS; ++i)
+          if (n0 + i * (PF_B_WARPS * 2) < n_pad && diag != 3) cp_async16_pf(b_stage + dst[i], src[i] + kb * 128);
         asm volatile("cp.async.commit_group;" ::: "memory");
         if (kb >= PF_B_STAGES - 1) {  // K block kb - 3 has landed
           asm volatile("cp.async.wait_group %0;" ::"n"(PF_B_STAGES - 1) : "memory");
@@ -311,6 +316,17 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_projection_kernel(FastP
     } else {
       // ================= epilogue: accumulators -> y -> (SwiGLU) -> out =======================
       const int quarter = warp - (PF_DECODE_WARPS + 1 + PF_B_WARPS);
+      {  // pull the code rows of this CTA's next item into L2 while the current one is being multiplied
+        const int next = item + gridDim.x;
+        if (next < items) {
+          const int ngi = next / row_tiles, ntile = next - ngi * row_tiles;
+          const int64_t nrow = min(static_cast<int64_t>(ntile) * PF_ROWS + quarter * 32 + lane, N_out - 1);
+          const int64_t nslot = p.groups_of_routes.slot[ngi];
+#pragma unroll
+          for (int m = 0; m < M; ++m)
+            asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(mats[m].codes + (nslot * N_out + nrow) * cw), "r"(static_cast<uint32_t>(cw * 2)) : "memory");
+        }
+      }
       int4* per_route = epi_all[quarter];
       __syncwarp();
       for (int n = lane; n < n_pad; n += 32) {
