@@ -200,6 +200,11 @@ def prefill_leg(layer, device, steps=6):
             "experts_ms": round(ms_experts / steps, 4), "experts_tflops": round(PREFILL_FLOPS / (ms_experts / steps * 1e-3) / 1e12, 1),
             "experts_frac_of_bf16_peak": round(PREFILL_FLOPS / (ms_experts / steps * 1e-3) / 1e12 / peak, 4),
             "routes_per_expert": {"mean": round(float(per_expert.float().mean()), 1), "max": int(per_expert.max()), "min": int(per_expert.min())}}
+        if name == "uniform":  # where the layer's time goes, stage by stage
+            names = {"router": _lib.STAGE_ROUTER, "prepare": _lib.STAGE_PREPARE, "gate_up": _lib.STAGE_GATE_UP,
+                     "down": _lib.STAGE_DOWN, "combine": _lib.STAGE_COMBINE}
+            out[name]["stage_ms"] = {k: round(time_graph(lambda i, m=m: layer.decode(xs[i % 2], stages=m, state=100 + i % 2), steps, 3) / steps, 4)
+                                     for k, m in names.items()}
         layer.pool_bias, layer.served_bias = saved
     out["peak_tflops"], out["useful_flops"] = peak, PREFILL_FLOPS
     out["kernel"] = "prefill_projection_kernel (tcgen05.mma kind::i8, two int8 MMAs per bf16-equivalent product)"

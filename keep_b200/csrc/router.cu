@@ -11,6 +11,7 @@
 //   row and a tile of 8 tokens; lanes stride the hidden dimension in 16-byte chunks, so each row
 //   of W is read once per token tile.  Products of bf16 values are exact in fp32; the order of
 //   additions is fixed (lane-sequential, then a butterfly), so results are reproducible.
+//   From 64 tokens on a shared-memory tiled kernel takes over (one FMA chain per logit, k ascending).
 // keepvq_routed_topk: one warp per token.  Scores = f(logits); served = top-k of
 //   scores + served_bias (absent experts carry -inf or anything <= -1e29); demand = top-k of
 //   scores + pool_bias; ties go to the lowest expert id; picks come out in descending biased
@@ -56,6 +57,58 @@ __global__ void __launch_bounds__(RL_WARPS * 32) router_logits_kernel(keepvq_rou
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, o);
     if (lane == 0 && t0 + i < a.tokens) a.logits[(t0 + i) * a.pool + e] = v / a.gate_temp;
   }
+}
+
+// Many tokens: a 64 x 64 tile of logits per block, K staged through shared memory 32 at a time,
+// 4 x 4 outputs per thread.  Each output is one chain of fp32 FMAs over k ascending, so it is
+// reproducible and independent of the tiling.
+constexpr int RT_TILE = 64, RT_K = 32, RT_THREADS = 256, RT_LD = RT_TILE + 4;
+
+template <typename XT, typename WT>
+__global__ void __launch_bounds__(RT_THREADS) router_logits_tiled_kernel(keepvq_router_logits_args a) {
+  __shared__ __align__(16) float xs[RT_K][RT_LD], ws[RT_K][RT_LD];
+  const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+  const int64_t t0 = static_cast<int64_t>(blockIdx.y) * RT_TILE, e0 = static_cast<int64_t>(blockIdx.x) * RT_TILE;
+  const XT* x = reinterpret_cast<const XT*>(a.x);
+  const WT* w = reinterpret_cast<const WT*>(a.router_w);
+  const int lrow = tid >> 2, lk = (tid & 3) * 8;  // staging: 64 rows x 4 pieces of 8 values
+  const int64_t xt = min(t0 + lrow, a.tokens - 1), we = min(e0 + lrow, a.pool - 1);
+  float acc[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[i][j] = 0.0f;
+  for (int64_t k0 = 0; k0 < a.hidden; k0 += RT_K) {
+    float xv[8], wv[8];
+    if (k0 + lk < a.hidden) {
+      load8_as_float<XT>(x + xt * a.hidden + k0 + lk, xv);
+      load8_as_float<WT>(w + we * a.hidden + k0 + lk, wv);
+    } else {
+#pragma unroll
+      for (int d = 0; d < 8; ++d) xv[d] = wv[d] = 0.0f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int d = 0; d < 8; ++d) { xs[lk + d][lrow] = xv[d]; ws[lk + d][lrow] = wv[d]; }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < RT_K; ++k) {
+      const float4 xa = *reinterpret_cast<const float4*>(&xs[k][ty * 4]);
+      const float4 wb = *reinterpret_cast<const float4*>(&ws[k][tx * 4]);
+      const float xr[4] = {xa.x, xa.y, xa.z, xa.w}, wr[4] = {wb.x, wb.y, wb.z, wb.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(xr[i], wr[j], acc[i][j]);
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int64_t t = t0 + ty * 4 + i, e = e0 + tx * 4 + j;
+      if (t < a.tokens && e < a.pool) a.logits[t * a.pool + e] = acc[i][j] / a.gate_temp;
+    }
 }
 
 // (value, index) max with ties to the lower index, across a warp.
@@ -154,6 +207,13 @@ __global__ void __launch_bounds__(TK_WARPS * 32) routed_topk_kernel(keepvq_route
 }
 
 template <typename XT>
+static void launch_logits_tiled(const keepvq_router_logits_args& a, dim3 grid, cudaStream_t s) {
+  if (a.router_dtype == KEEPVQ_F32) router_logits_tiled_kernel<XT, float><<<grid, RT_THREADS, 0, s>>>(a);
+  else if (a.router_dtype == KEEPVQ_F16) router_logits_tiled_kernel<XT, __half><<<grid, RT_THREADS, 0, s>>>(a);
+  else router_logits_tiled_kernel<XT, __nv_bfloat16><<<grid, RT_THREADS, 0, s>>>(a);
+}
+
+template <typename XT>
 static void launch_logits(const keepvq_router_logits_args& a, dim3 grid, cudaStream_t s) {
   if (a.router_dtype == KEEPVQ_F32) router_logits_kernel<XT, float><<<grid, RL_WARPS * 32, 0, s>>>(a);
   else if (a.router_dtype == KEEPVQ_F16) router_logits_kernel<XT, __half><<<grid, RL_WARPS * 32, 0, s>>>(a);
@@ -172,10 +232,20 @@ extern "C" int keepvq_router_logits(const keepvq_router_logits_args* args, void*
   if (a.tokens == 0) return KEEPVQ_OK;
   if (!a.x || !a.router_w || !a.logits) return KEEPVQ_ERR_NULL;
   if (!aligned_to(a.x, 16) || !aligned_to(a.router_w, 16)) return KEEPVQ_ERR_ALIGN;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (a.tokens >= RT_TILE) {  // many tokens: the tiled kernel
+    const int64_t tiles = (a.tokens + RT_TILE - 1) / RT_TILE;
+    if (tiles > 65535) return KEEPVQ_ERR_CAPACITY;
+    dim3 grid(static_cast<unsigned>((a.pool + RT_TILE - 1) / RT_TILE), static_cast<unsigned>(tiles));
+    if (a.x_dtype == KEEPVQ_F32) launch_logits_tiled<float>(a, grid, s);
+    else if (a.x_dtype == KEEPVQ_F16) launch_logits_tiled<__half>(a, grid, s);
+    else launch_logits_tiled<__nv_bfloat16>(a, grid, s);
+    KEEPVQ_CHECK_LAUNCH();
+    return KEEPVQ_OK;
+  }
   const int64_t token_tiles = (a.tokens + RL_TOKENS - 1) / RL_TOKENS;
   if (token_tiles > 65535) return KEEPVQ_ERR_CAPACITY;
   dim3 grid(static_cast<unsigned>((a.pool + RL_WARPS - 1) / RL_WARPS), static_cast<unsigned>(token_tiles));
-  cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (a.x_dtype == KEEPVQ_F32) launch_logits<float>(a, grid, s);
   else if (a.x_dtype == KEEPVQ_F16) launch_logits<__half>(a, grid, s);
   else launch_logits<__nv_bfloat16>(a, grid, s);
