@@ -159,12 +159,19 @@ def projection_roofline(layer, xs, steps, hbm_gbs, peak_kind):
     launches = 1 if tensor else 3  # general kernels: gate, up and the SwiGLU pass
     bytes_per_stage = statistics.fmean(uniq[i % len(xs)] for i in range(steps)) * 2 * CODE_BYTES_PER_PROJECTION
     achieved = bytes_per_stage / (ms / steps * 1e-3) / 1e9
+    # DRAM bytes per launch from the ncu capture summarised in profiles/projection_cta_kernel_decode_b64_ncu.md:
+    # 995.4 MB read + written for 1025.4 MB of distinct code bytes at batch 64; traffic grows with the
+    # number of distinct experts a launch touches, so other batches scale it by their code bytes.
+    traffic = int(NCU_TRAFFIC_PER_CODE_BYTE * bytes_per_stage) if tensor else None
     return {"bound": "hbm", "achieved": round(achieved, 1), "peak": hbm_gbs, "unit": "GB/s", "frac": round(achieved / hbm_gbs, 4),
-            "traffic": None, "peak_kind": peak_kind,
-            "kernel": "projection_kernel<2,2> (gate+up+SwiGLU, int8 tensor cores)" if tensor else "routed_matvec_kernel x2 + swiglu",
+            "traffic": traffic, "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch, scaled by code bytes" if tensor else None,
+            "peak_kind": peak_kind,
+            "kernel": "projection_cta_kernel<2,1> (gate+up+SwiGLU, int8 tensor cores)" if tensor else "routed_matvec_kernel x2 + swiglu",
             "launches_per_stage": launches, "algorithmic_bytes_per_launch": int(bytes_per_stage),
             "us_per_launch": round(ms / steps * 1e3, 2)}
 
+
+NCU_TRAFFIC_PER_CODE_BYTE = 995.4 / 1025.4
 
 PREFILL_TOKENS = 4096
 PREFILL_FLOPS = 2.0 * PREFILL_TOKENS * TOP_K * (INTER * HIDDEN) * 3  # useful FLOPs of the three projections: 1.2369e12

@@ -11,7 +11,7 @@
 //   row and a tile of 8 tokens; lanes stride the hidden dimension in 16-byte chunks, so each row
 //   of W is read once per token tile.  Products of bf16 values are exact in fp32; the order of
 //   additions is fixed (lane-sequential, then a butterfly), so results are reproducible.
-//   From 64 tokens on a shared-memory tiled kernel takes over (one FMA chain per logit, k ascending).
+//   From 256 tokens on a shared-memory tiled kernel takes over (one FMA chain per logit, k ascending).
 // keepvq_routed_topk: one warp per token.  Scores = f(logits); served = top-k of
 //   scores + served_bias (absent experts carry -inf or anything <= -1e29); demand = top-k of
 //   scores + pool_bias; ties go to the lowest expert id; picks come out in descending biased
@@ -63,6 +63,7 @@ __global__ void __launch_bounds__(RL_WARPS * 32) router_logits_kernel(keepvq_rou
 // 4 x 4 outputs per thread.  Each output is one chain of fp32 FMAs over k ascending, so it is
 // reproducible and independent of the tiling.
 constexpr int RT_TILE = 64, RT_K = 32, RT_THREADS = 256, RT_LD = RT_TILE + 4;
+constexpr int RT_MIN_TOKENS = 256;  // below this the tile grid is too small to fill the GPU
 
 template <typename XT, typename WT>
 __global__ void __launch_bounds__(RT_THREADS) router_logits_tiled_kernel(keepvq_router_logits_args a) {
@@ -233,7 +234,7 @@ extern "C" int keepvq_router_logits(const keepvq_router_logits_args* args, void*
   if (!a.x || !a.router_w || !a.logits) return KEEPVQ_ERR_NULL;
   if (!aligned_to(a.x, 16) || !aligned_to(a.router_w, 16)) return KEEPVQ_ERR_ALIGN;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (a.tokens >= RT_TILE) {  // many tokens: the tiled kernel
+  if (a.tokens >= RT_MIN_TOKENS) {  // many tokens: the tiled kernel
     const int64_t tiles = (a.tokens + RT_TILE - 1) / RT_TILE;
     if (tiles > 65535) return KEEPVQ_ERR_CAPACITY;
     dim3 grid(static_cast<unsigned>((a.pool + RT_TILE - 1) / RT_TILE), static_cast<unsigned>(tiles));
