@@ -348,6 +348,59 @@ typedef struct keepvq_residency_args {
 int keepvq_residency_tick(const keepvq_residency_args* args, void* stream);
 
 /* ------------------------------------------------------------------------------------------
+ * Expert parallelism: packing routes for the dispatch all-to-all and summing them after the
+ * combine all-to-all.
+ *
+ * The reference's only expert-parallel form replicates every token on every rank, runs the
+ * rank's slice of the experts and all-reduces the outputs
+ * (tests/fixtures/v41_reference/model.py:869-872,891-906).  Here a token's hidden state visits
+ * only the ranks that own its experts; the sum over its k picks is the same.
+ *
+ * Every (source, destination) pair owns a fixed block of `capacity` rows in the exchange
+ * buffers, so the all-to-all has constant split sizes and no routing fact reaches the host.
+ * Rank w owns experts [w * experts_per_rank, (w + 1) * experts_per_rank).
+ *
+ * keepvq_ep_pack    for route r (token r / top_k, pick r % top_k) with a live expert e:
+ *                   dest = e / experts_per_rank, pos = number of earlier live routes with the same
+ *                   dest (stable); position[r] = dest * capacity + pos; x's row is copied to
+ *                   send_x[position[r]] and send_meta[position[r]] = (e % experts_per_rank, bits of
+ *                   the route's weight).  Dead routes (expert 0xFFFFFFFF), routes whose expert is
+ *                   out of range and routes beyond a block's capacity get position = world *
+ *                   capacity.  Unused rows of send_x are zero, of send_meta (-1, 0).
+ * keepvq_ep_combine out[t] = sum over picks j, in pick order, of back[position[t, j]] in fp32,
+ *                   rounded once to the row dtype; positions >= rows add nothing.
+ * ------------------------------------------------------------------------------------------ */
+typedef struct keepvq_ep_pack_args {
+  const void* x;                  /* [tokens, row_bytes] this rank's token rows */
+  int64_t row_bytes;              /* multiple of 16 */
+  const uint32_t* served_expert;  /* [tokens, top_k] global expert ids, 0xFFFFFFFF = dead pick */
+  const float* served_weight;     /* [tokens, top_k] */
+  int64_t tokens;
+  int32_t top_k;
+  int32_t world;                  /* 1..64 ranks */
+  int32_t experts_per_rank;
+  int64_t capacity;               /* rows per (source, destination) block */
+  void* send_x;                   /* [world * capacity, row_bytes] */
+  int32_t* send_meta;             /* [world * capacity, 2] */
+  int32_t* position;              /* [tokens, top_k] */
+} keepvq_ep_pack_args;
+
+int keepvq_ep_pack(const keepvq_ep_pack_args* args, void* stream);
+
+typedef struct keepvq_ep_combine_args {
+  const void* back;               /* [rows, hidden] expert outputs, returned to their send positions */
+  int32_t dtype;                  /* keepvq_dtype of back and out */
+  int64_t rows;
+  int64_t hidden;                 /* multiple of 8 */
+  const int32_t* position;        /* [tokens, top_k] */
+  int64_t tokens;
+  int32_t top_k;
+  void* out;                      /* [tokens, hidden] */
+} keepvq_ep_combine_args;
+
+int keepvq_ep_combine(const keepvq_ep_combine_args* args, void* stream);
+
+/* ------------------------------------------------------------------------------------------
  * keepvq_moe_decode_layer for callers that cannot hand over scratch memory.  It has no
  * counterpart in the reference.
  *

@@ -102,6 +102,21 @@ class ResidencyArgs(Structure):
     ]
 
 
+class EpPackArgs(Structure):
+    _fields_ = [
+        ("x", c_void_p), ("row_bytes", c_int64), ("served_expert", c_void_p), ("served_weight", c_void_p),
+        ("tokens", c_int64), ("top_k", c_int32), ("world", c_int32), ("experts_per_rank", c_int32), ("capacity", c_int64),
+        ("send_x", c_void_p), ("send_meta", c_void_p), ("position", c_void_p),
+    ]
+
+
+class EpCombineArgs(Structure):
+    _fields_ = [
+        ("back", c_void_p), ("dtype", c_int32), ("rows", c_int64), ("hidden", c_int64), ("position", c_void_p),
+        ("tokens", c_int64), ("top_k", c_int32), ("out", c_void_p),
+    ]
+
+
 SCORE_FUNCS = {"softmax": 0, "sigmoid": 1, "sqrtsoftplus": 2}
 STATIC_SCRATCH_BYTES = 8 << 20  # KEEPVQ_STATIC_SCRATCH_BYTES
 STAGE_ROUTER, STAGE_PREPARE, STAGE_GATE_UP, STAGE_DOWN, STAGE_COMBINE, STAGE_ALL = 1, 2, 4, 8, 16, 31
@@ -110,7 +125,7 @@ STAGE_ROUTER, STAGE_PREPARE, STAGE_GATE_UP, STAGE_DOWN, STAGE_COMBINE, STAGE_ALL
 EXTRA_STRUCTS = {
     "keepvq_router_logits_args": RouterLogitsArgs, "keepvq_routed_topk_args": RoutedTopkArgs,
     "keepvq_expert_weights": ExpertWeights, "keepvq_moe_layer_args": MoELayerArgs,
-    "keepvq_residency_args": ResidencyArgs,
+    "keepvq_residency_args": ResidencyArgs, "keepvq_ep_pack_args": EpPackArgs, "keepvq_ep_combine_args": EpCombineArgs,
 }
 
 _SIGNATURES = {
@@ -126,6 +141,8 @@ _SIGNATURES = {
     "keepvq_moe_decode_stages": (c_int, [POINTER(MoELayerArgs), c_int32, c_void_p]),
     "keepvq_moe_decode_layer_static": (c_int, [POINTER(MoELayerArgs), c_void_p]),
     "keepvq_residency_tick": (c_int, [POINTER(ResidencyArgs), c_void_p]),
+    "keepvq_ep_pack": (c_int, [POINTER(EpPackArgs), c_void_p]),
+    "keepvq_ep_combine": (c_int, [POINTER(EpCombineArgs), c_void_p]),
 }
 
 _lock = threading.Lock()

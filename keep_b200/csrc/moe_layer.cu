@@ -34,8 +34,13 @@ struct dtype_tag_of {
 
 static inline int64_t align256(int64_t v) { return (v + 255) / 256 * 256; }
 
-// From this many routes on, experts see enough routes each for the tcgen05 kernels to pay.
+// The tcgen05 kernels decode a code once per 96 routes of an expert but cost the same for one
+// route as for 96; the mma.sync kernels stream an expert's codes once per 8 routes.  Which one
+// pays depends on routes per expert, and the host only knows its upper bound routes / slots
+// (reading the routing back would stall the stream): from 24 on, three passes of the decode
+// kernels cost more than the one pass of the tcgen05 kernels.
 constexpr int64_t PREFILL_MIN_ROUTES = 1024;
+constexpr int64_t PREFILL_MIN_ROUTES_PER_SLOT = 24;
 
 struct LayerScratch {
   int64_t logits, gate, up, h, down;
@@ -183,7 +188,7 @@ extern "C" int keepvq_moe_decode_stages(const keepvq_moe_layer_args* args, int32
     fast::QuantRows xq = {reinterpret_cast<uint8_t*>(ws + sc.xq), reinterpret_cast<float*>(ws + sc.xscale), reinterpret_cast<int32_t*>(ws + sc.xsums)};
     fast::QuantRows hq = {reinterpret_cast<uint8_t*>(ws + sc.hq), reinterpret_cast<float*>(ws + sc.hscale), reinterpret_cast<int32_t*>(ws + sc.hsums)};
     // many routes per expert: the tcgen05 kernels, which decode a code once per 128 routes
-    const bool prefill = routes >= PREFILL_MIN_ROUTES && fast::prefill_supported(a.inter, a.hidden, a.w1.groups) &&
+    const bool prefill = routes >= PREFILL_MIN_ROUTES && routes >= PREFILL_MIN_ROUTES_PER_SLOT * a.slots && fast::prefill_supported(a.inter, a.hidden, a.w1.groups) &&
                          fast::prefill_supported(a.hidden, a.inter, a.w2.groups);
     int32_t* wait_status = reinterpret_cast<int32_t*>(ws + sc.status);
     if (stages & KEEPVQ_STAGE_PREPARE) {

@@ -13,8 +13,11 @@ host before NCCL could be called.  Instead every (source, destination) pair owns
 carry slot id ``NO_SLOT`` and the expert kernels skip them.  At decode sizes the padding is a
 few MB per layer on NVLink and the whole step stays capturable in a CUDA graph.
 
-``RouteExchange`` is plain ``torch`` + ``torch.distributed`` and runs on CPU ranks (gloo) as well,
-which is how its index arithmetic is tested without GPUs.
+On CUDA tensors the packing and the pick summation are the library's own kernels
+(``keepvq_ep_pack``, ``keepvq_ep_combine``: a memset and three launches per layer besides the
+all-to-alls).  On CPU tensors ``RouteExchange`` is plain ``torch`` + ``torch.distributed`` with
+the same positions, which is how the index arithmetic is tested on gloo ranks without GPUs; it
+is the checker of the CUDA kernels, not a serving path.
 """
 
 from __future__ import annotations
@@ -35,6 +38,7 @@ class RouteExchange:
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
         self.experts_per_rank = int(experts_per_rank)
         self.capacity = capacity
+        self._cuda_buffers: dict = {}
 
     def plan(self, served_expert: torch.Tensor):
         """served_expert [tokens, k] (global ids, negative = dead pick) -> (position [tokens, k] of
@@ -60,6 +64,14 @@ class RouteExchange:
     def dispatch(self, x: torch.Tensor, served_expert: torch.Tensor, served_weight: torch.Tensor):
         """-> (recv_x [world * capacity, hidden], recv_slot [..] local expert or NO_SLOT,
         recv_weight [..], position [tokens, k])."""
+        if x.is_cuda:
+            return self._dispatch_cuda(x, served_expert, served_weight)
+        send_x, send_slot, send_weight, position = self.pack_torch(x, served_expert, served_weight)
+        return self._all_to_all(send_x), self._all_to_all(send_slot), self._all_to_all(send_weight), position
+
+    def pack_torch(self, x: torch.Tensor, served_expert: torch.Tensor, served_weight: torch.Tensor):
+        """The send buffers in plain torch: (send_x [rows, hidden], send_slot [rows], send_weight
+        [rows], position [tokens, k])."""
         tokens, k = served_expert.shape
         position, capacity = self.plan(served_expert)
         rows = self.world * capacity
@@ -72,12 +84,67 @@ class RouteExchange:
         send_slot.index_copy_(0, flat_pos, local_slot)
         send_weight = torch.zeros((rows + 1,), dtype=torch.float32, device=x.device)
         send_weight.index_copy_(0, flat_pos, served_weight.reshape(-1).float())
-        return (self._all_to_all(send_x[:rows]), self._all_to_all(send_slot[:rows]), self._all_to_all(send_weight[:rows]), position)
+        return send_x[:rows], send_slot[:rows], send_weight[:rows], position
+
+    def _dispatch_cuda(self, x: torch.Tensor, served_expert: torch.Tensor, served_weight: torch.Tensor):
+        """The CUDA form of ``dispatch``: one library call packs rows, slots and weights; two
+        all-to-alls carry them.  Buffers are cached per shape so the step can be graph-captured."""
+        send_x, send_meta, position = self.pack_cuda(x, served_expert, served_weight)
+        if self.world == 1:
+            recv_x, recv_meta = send_x, send_meta
+        else:
+            buf = self._cuda_buffers[(tuple(served_expert.shape), int(x.shape[1]), x.dtype)]
+            recv_x, recv_meta = buf["recv_x"], buf["recv_meta"]
+            dist.all_to_all_single(recv_x, send_x, group=self.group)
+            dist.all_to_all_single(recv_meta, send_meta, group=self.group)
+        return recv_x, recv_meta[:, 0], recv_meta[:, 1].view(torch.float32), position
+
+    def pack_cuda(self, x: torch.Tensor, served_expert: torch.Tensor, served_weight: torch.Tensor):
+        """``keepvq_ep_pack``: (send_x [rows, hidden], send_meta [rows, 2] = (local slot, weight
+        bits), position [tokens, k] int32).  The tensors are cached per shape and overwritten by the
+        next call."""
+        from . import _lib
+
+        tokens, k = served_expert.shape
+        capacity = self.capacity or tokens * k
+        rows = self.world * capacity
+        x = x.contiguous()
+        row_bytes = int(x.shape[1]) * x.element_size()
+        key = ((tokens, k), int(x.shape[1]), x.dtype)
+        buf = self._cuda_buffers.get(key)
+        if buf is None:
+            dev = x.device
+            buf = self._cuda_buffers[key] = dict(
+                send_x=torch.empty((rows, x.shape[1]), dtype=x.dtype, device=dev), recv_x=torch.empty((rows, x.shape[1]), dtype=x.dtype, device=dev),
+                send_meta=torch.empty((rows, 2), dtype=torch.int32, device=dev), recv_meta=torch.empty((rows, 2), dtype=torch.int32, device=dev),
+                position=torch.empty((tokens, k), dtype=torch.int32, device=dev))
+        experts = served_expert.to(torch.int32).contiguous()
+        weights = served_weight.contiguous().float()
+        args = _lib.EpPackArgs(x=_lib.ptr(x), row_bytes=row_bytes, served_expert=_lib.ptr(experts), served_weight=_lib.ptr(weights),
+                               tokens=tokens, top_k=k, world=self.world, experts_per_rank=self.experts_per_rank, capacity=capacity,
+                               send_x=_lib.ptr(buf["send_x"]), send_meta=_lib.ptr(buf["send_meta"]), position=_lib.ptr(buf["position"]))
+        with torch.cuda.device(x.device):
+            _lib.check(_lib.load().keepvq_ep_pack(args, _lib.stream_handle(x.device)), "keepvq_ep_pack")
+        return buf["send_x"], buf["send_meta"], buf["position"]
+
+    def _combine_cuda(self, back: torch.Tensor, position: torch.Tensor) -> torch.Tensor:
+        from . import _lib
+
+        tokens, k = position.shape
+        back = back.contiguous()
+        out = torch.empty((tokens, back.shape[1]), dtype=back.dtype, device=back.device)
+        args = _lib.EpCombineArgs(back=_lib.ptr(back), dtype=_lib.dtype_tag(back.dtype), rows=int(back.shape[0]), hidden=int(back.shape[1]),
+                                  position=_lib.ptr(position), tokens=tokens, top_k=k, out=_lib.ptr(out))
+        with torch.cuda.device(back.device):
+            _lib.check(_lib.load().keepvq_ep_combine(args, _lib.stream_handle(back.device)), "keepvq_ep_combine")
+        return out
 
     def combine(self, y_routes: torch.Tensor, position: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
         """y_routes [world * capacity, hidden] (per received route) -> [tokens, hidden]: each token's
         picks summed in fp32 in pick order, one rounding."""
         back = self._all_to_all(y_routes)
+        if back.is_cuda and back.dtype == out_dtype:
+            return self._combine_cuda(back, position)
         back = torch.cat([back, torch.zeros((1, back.shape[1]), dtype=back.dtype, device=back.device)])  # row of a dead route
         tokens, k = position.shape
         acc = torch.zeros((tokens, back.shape[1]), dtype=torch.float32, device=back.device)

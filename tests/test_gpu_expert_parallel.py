@@ -66,3 +66,33 @@ def test_two_gpu_expert_parallel_matches_one_gpu():
         assert p.exitcode == 0
     # the same kernels on the same routes: only the bf16 rounding of the final fp32 sum can differ
     assert len(results) == 2 and all(gap <= 1e-2 for gap in results.values()), dict(results)
+
+
+@pytest.mark.parametrize("tokens,k,world,per_rank,capacity", [(6, 3, 2, 4, None), (256, 6, 8, 48, None), (300, 6, 4, 96, 200), (1, 1, 1, 8, None)])
+def test_pack_and_combine_kernels_match_the_torch_exchange(cuda, tokens, k, world, per_rank, capacity):
+    """One GPU, no communication: the packing kernel builds the same send buffers and positions
+    as the plain-torch exchange (stable order inside each destination's block, dead and
+    overflowing routes dropped), and the pick summation gives the same rows."""
+    from keep_b200 import expert_parallel
+
+    gen = torch.Generator().manual_seed(tokens * 31 + world)
+    experts = torch.randint(0, world * per_rank, (tokens, k), generator=gen, dtype=torch.int32)
+    experts[torch.rand((tokens, k), generator=gen) < 0.15] = -1                       # dead picks
+    weights = torch.rand((tokens, k), generator=gen)
+    x = torch.randn((tokens, 512), generator=gen).to(torch.bfloat16)
+    ex = expert_parallel.RouteExchange(per_rank, capacity=capacity)
+    ex.world = world                                                                   # no process group: pack only
+    want_x, want_slot, want_weight, want_pos = ex.pack_torch(x, experts, weights)
+    got_x, got_meta, got_pos = ex.pack_cuda(x.to(cuda), experts.to(cuda), weights.to(cuda))
+    np.testing.assert_array_equal(got_pos.cpu().numpy(), want_pos.numpy())
+    np.testing.assert_array_equal(got_meta[:, 0].cpu().numpy(), want_slot.numpy())
+    np.testing.assert_array_equal(got_meta[:, 1].contiguous().view(torch.float32).cpu().numpy(), want_weight.numpy())
+    assert torch.equal(got_x.cpu(), want_x)
+    if capacity is not None:
+        assert int((want_pos == world * capacity).sum()) > int((experts < 0).sum())     # the small capacity did overflow
+
+    back = torch.randn((int(want_x.shape[0]), 512), generator=gen).to(torch.bfloat16)   # stands for the returned expert outputs
+    ex.world = 1                                                                       # combine without an all-to-all
+    want = ex.combine(back, want_pos, torch.bfloat16)
+    got = ex.combine(back.to(cuda), got_pos, torch.bfloat16)
+    assert torch.equal(got.cpu(), want)

@@ -139,6 +139,17 @@ def test_many_routes_per_expert_take_the_tcgen05_kernels(cuda, tokens, experts, 
     check_layer(cfg, x, out, routing, top_k=top_k)
 
 
+def test_many_routes_spread_over_many_experts_stay_on_the_decode_kernels(cuda):
+    """1200 routes over 64 experts (under 24 per expert on average): the mma.sync kernels, with
+    several 8-route groups per expert."""
+    cfg = synthetic.layer(seed=43, experts=64, hidden=512, inter=256)
+    x = synthetic.tokens(44, 400, 512)
+    layer = build_layer(cuda, cfg, top_k=3)
+    assert layer.kernel_path == "tensor"
+    out, routing = layer.decode(x.to(cuda))
+    check_layer(cfg, x, out, routing, top_k=3)
+
+
 @pytest.mark.parametrize("batch", [1, 16])
 def test_config2_shape_decode_layer(cuda, batch):
     """The benchmark layer shape (hidden 4096, inter 2048, top-6, softmax) on a 48-expert slice of
