@@ -368,7 +368,14 @@ def run_expert_parallel(ns, rank, world, local, device):
     ms, e2e_ms = (float(v) for v in t.cpu())
     if rank != 0:
         return
-    tokens = EP_BATCH * ns.steps
+    # the unit is a token through one routed layer, as at N = 1: a step pushes EP_BATCH tokens through `layers` of them
+    tokens = EP_BATCH * layers * ns.steps
+    layer_s = ms * 1e-3 / ns.steps / layers
+    peaks = json.loads((ROOT / "MEASURED_PEAKS.json").read_text()) if (ROOT / "MEASURED_PEAKS.json").exists() else {}
+    hbm_gbs = float(peaks.get("hbm_gbs", 6650.0))
+    local_experts = EXPERTS // world
+    touched = local_experts * (1.0 - (1.0 - 1.0 / EXPERTS) ** (EP_BATCH * TOP_K))  # expected distinct local experts per layer
+    achieved = touched * CODE_BYTES_PER_EXPERT / layer_s / 1e9
     line = {
         "metric": METRIC, "value": round(tokens / (ms * 1e-3), 1), "unit": UNIT, "n_gpus": world, "steps": ns.steps, "warmup": ns.warmup,
         "ms_per_step": round(ms / ns.steps, 4), "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
@@ -376,11 +383,15 @@ def run_expert_parallel(ns, rank, world, local, device):
         "config": {"workload": f"expert-parallel stack (config 5): {layers} layers x 384 experts sharded {EXPERTS // world} per GPU, top-6, "
                                f"{EP_BATCH} decode tokens in total ({tokens_local} per GPU), NCCL all-to-all dispatch and combine",
                    "layers": layers, "batch": EP_BATCH, "l2": f"inputs larger than L2: {layers} layers x {EXPERTS // world * CODE_BYTES_PER_EXPERT / 1e9:.1f} GB of codes per GPU",
-                   "cuda_graph": graph is not None, "note": "value counts each token once per pass through the whole stack"},
-        "roofline": None, "cpu_baseline": None,
+                   "cuda_graph": graph is not None,
+                   "note": "value = tokens x layers / time: a token through one routed layer is the unit, the same as the one-GPU line"},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": hbm_gbs, "unit": "GB/s", "frac": round(achieved / hbm_gbs, 4), "traffic": None,
+                     "peak_kind": "measured" if "hbm_gbs" in peaks else "fallback", "per": "GPU, whole layer (router, exchange and experts)",
+                     "algorithmic_bytes_per_layer": int(touched * CODE_BYTES_PER_EXPERT)},
+        "stack_tokens_per_s": round(EP_BATCH * ns.steps / (ms * 1e-3), 1), "cpu_baseline": None,
         "layer_us": round(ms / ns.steps / layers * 1e3, 1),
         "e2e": {"value": round(tokens / (e2e_ms * 1e-3), 1), "unit": UNIT, "h2d_bytes_per_step": EP_BATCH * HIDDEN * 2, "d2h_bytes_per_step": EP_BATCH * HIDDEN * 2},
-        "gpu_launches": 8 * layers * ns.steps * world, "kernel_path": stack[0].local.kernel_path, "clocks": clocks.summary(),
+        "gpu_launches": 11 * layers * ns.steps * world, "kernel_path": stack[0].local.kernel_path, "clocks": clocks.summary(),
     }
     print(json.dumps(line))
 

@@ -258,6 +258,10 @@ typedef struct keepvq_moe_layer_args {
   /* scratch, at least keepvq_moe_layer_workspace_bytes(), 256-byte aligned */
   void* workspace;
   int64_t workspace_bytes;
+  /* Live routes the caller expects among tokens * top_k, or 0 for "all of them".  A caller whose
+     rows are mostly dead (the fixed-capacity blocks of an expert-parallel exchange) says so here;
+     it only picks between kernel families (few or many routes per expert), never the result. */
+  int64_t expected_routes;
 } keepvq_moe_layer_args;
 
 /* Bytes of scratch keepvq_moe_decode_layer needs for these sizes (host arithmetic only). */

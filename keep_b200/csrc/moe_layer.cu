@@ -188,7 +188,8 @@ extern "C" int keepvq_moe_decode_stages(const keepvq_moe_layer_args* args, int32
     fast::QuantRows xq = {reinterpret_cast<uint8_t*>(ws + sc.xq), reinterpret_cast<float*>(ws + sc.xscale), reinterpret_cast<int32_t*>(ws + sc.xsums)};
     fast::QuantRows hq = {reinterpret_cast<uint8_t*>(ws + sc.hq), reinterpret_cast<float*>(ws + sc.hscale), reinterpret_cast<int32_t*>(ws + sc.hsums)};
     // many routes per expert: the tcgen05 kernels, which decode a code once per 128 routes
-    const bool prefill = routes >= PREFILL_MIN_ROUTES && routes >= PREFILL_MIN_ROUTES_PER_SLOT * a.slots && fast::prefill_supported(a.inter, a.hidden, a.w1.groups) &&
+    const int64_t live = a.expected_routes > 0 && a.expected_routes < routes ? a.expected_routes : routes;
+    const bool prefill = live >= PREFILL_MIN_ROUTES && live >= PREFILL_MIN_ROUTES_PER_SLOT * a.slots && fast::prefill_supported(a.inter, a.hidden, a.w1.groups) &&
                          fast::prefill_supported(a.hidden, a.inter, a.w2.groups);
     int32_t* wait_status = reinterpret_cast<int32_t*>(ws + sc.status);
     if (stages & KEEPVQ_STAGE_PREPARE) {

@@ -184,5 +184,6 @@ class ExpertParallelLayer:
         r = buf["routing"]
         r.served_slot.copy_(recv_slot.reshape(-1, 1))
         r.served_weight.copy_(recv_weight.reshape(-1, 1))
-        y, _ = self.local.decode(recv_x, stages=_lib.STAGE_ALL & ~_lib.STAGE_ROUTER)
+        # by symmetry a rank receives about as many live routes as it sends; the rest of its rows are padding
+        y, _ = self.local.decode(recv_x, stages=_lib.STAGE_ALL & ~_lib.STAGE_ROUTER, expected_routes=int(x.shape[0]) * self.top_k)
         return self.exchange.combine(y, position, x.dtype)

@@ -118,7 +118,7 @@ class RoutedMoELayer:
             codebook_all_odd=int(self.codebook_all_odd),
             out=_lib.ptr(out), served_expert=_lib.ptr(r.served_expert), served_slot=_lib.ptr(r.served_slot),
             served_weight=_lib.ptr(r.served_weight), want=_lib.ptr(r.want), want_score=_lib.ptr(r.want_score),
-            admit=_lib.ptr(r.admit), workspace=_lib.ptr(workspace), workspace_bytes=nbytes)
+            admit=_lib.ptr(r.admit), workspace=_lib.ptr(workspace), workspace_bytes=nbytes, expected_routes=0)
 
     @property
     def kernel_path(self) -> str:
@@ -156,14 +156,16 @@ class RoutedMoELayer:
         return out, routing
 
     def decode(self, x: torch.Tensor, *, out: torch.Tensor | None = None, stages: int = _lib.STAGE_ALL,
-               state: int = 0) -> tuple[torch.Tensor, Routing]:
+               state: int = 0, expected_routes: int = 0) -> tuple[torch.Tensor, Routing]:
         """``x`` [tokens, hidden] -> (``[tokens, hidden]`` in x's dtype, routing outputs).
 
         Buffers are cached per (tokens, dtype) and reused by the next call of the same shape, so
         the call is CUDA-graph capturable after one warm-up call; copy results you want to keep.
         ``stages`` (a mask of ``_lib.STAGE_*``) replays part of the sequence on the state a full
         call left behind; profilers and the benchmark use it.  ``state`` picks one of several
-        independent buffer sets (each keeps its own scratch and outputs).
+        independent buffer sets (each keeps its own scratch and outputs).  ``expected_routes`` (0 =
+        all) tells the library how many of the ``tokens * top_k`` routes the caller expects to be
+        live, which only picks the kernel family.
         """
         _lib.require_cuda(x)
         if x.ndim != 2 or int(x.shape[1]) != self.hidden:
@@ -185,7 +187,7 @@ class RoutedMoELayer:
             codebook_all_odd=int(self.codebook_all_odd),
             out=_lib.ptr(target), served_expert=_lib.ptr(r.served_expert), served_slot=_lib.ptr(r.served_slot),
             served_weight=_lib.ptr(r.served_weight), want=_lib.ptr(r.want), want_score=_lib.ptr(r.want_score),
-            admit=_lib.ptr(r.admit), workspace=_lib.ptr(buf["workspace"]), workspace_bytes=buf["nbytes"])
+            admit=_lib.ptr(r.admit), workspace=_lib.ptr(buf["workspace"]), workspace_bytes=buf["nbytes"], expected_routes=int(expected_routes))
         with torch.cuda.device(self.device):
             _lib.check(_lib.load().keepvq_moe_decode_stages(args, int(stages), _lib.stream_handle(self.device)), "keepvq_moe_decode_stages")
         return target, r
