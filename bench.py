@@ -173,6 +173,17 @@ def projection_roofline(layer, xs, steps, hbm_gbs, peak_kind):
 
 NCU_TRAFFIC_PER_CODE_BYTE = 995.4 / 1025.4
 
+
+def stage_times(layer, xs, steps):
+    """Microseconds per stage of the layer call, each stage replayed alone on the state the full
+    calls of `projection_roofline` left behind (same rotation of token batches)."""
+    from keep_b200 import _lib
+
+    names = {"router": _lib.STAGE_ROUTER, "prepare": _lib.STAGE_PREPARE, "gate_up": _lib.STAGE_GATE_UP,
+             "down": _lib.STAGE_DOWN, "combine": _lib.STAGE_COMBINE}
+    return {k: round(time_graph(lambda i, m=m: layer.decode(xs[i % len(xs)], stages=m, state=1 + i % len(xs)), steps, 3) / steps * 1e3, 1)
+            for k, m in names.items()}
+
 PREFILL_TOKENS = 4096
 PREFILL_FLOPS = 2.0 * PREFILL_TOKENS * TOP_K * (INTER * HIDDEN) * 3  # useful FLOPs of the three projections: 1.2369e12
 
@@ -476,7 +487,7 @@ def run_ours(ns):
                    "batch": batch, "l2": "inputs larger than L2: 64 rotating token batches over a 2.4 GB expert pool",
                    "distinct_experts_per_step": round(mean_u, 2)},
         "layer_code_gbs": round(code_gbs, 1), "layer_code_frac_of_hbm": round(code_gbs / hbm_gbs, 4),
-        "roofline": roofline,
+        "roofline": roofline, "stage_us": stage_times(layer, xs, ns.steps),
         "cpu_baseline": {"value": round(1.0 / cpu_s, 4), "unit": UNIT, "cores": threads, "kind": "port",
                          "sample": "one token: router + decode of 6 experts x 3 projections + SwiGLU path", "parity_gap_vs_gpu": parity_gap},
         "e2e": {"value": round(e2e_value, 1), "unit": UNIT, "h2d_bytes_per_step": batch * HIDDEN * 2, "d2h_bytes_per_step": batch * HIDDEN * 2},

@@ -267,6 +267,12 @@ typedef struct keepvq_moe_layer_args {
 /* Bytes of scratch keepvq_moe_decode_layer needs for these sizes (host arithmetic only). */
 int64_t keepvq_moe_layer_workspace_bytes(int64_t tokens, int64_t hidden, int64_t inter, int64_t pool, int32_t top_k);
 int keepvq_moe_decode_layer(const keepvq_moe_layer_args* args, void* stream);
+/* Byte offset, inside the scratch, of an int32 the tcgen05 kernels set to 1 when one of their
+ * bounded waits expires (they then stop, free their tensor memory and return; the call's outputs
+ * are invalid).  The library clears it at the start of a call that can set it and never reads it
+ * back itself: a host that wants to know copies the word out after the call.  No counterpart in
+ * the reference. */
+int64_t keepvq_moe_layer_status_offset(int64_t tokens, int64_t hidden, int64_t inter, int64_t pool, int32_t top_k);
 
 /* The same sequence, cut into stages: run the stages named in `stages` (a mask) on the same
  * arguments and scratch.  A later stage reads what earlier ones left in the outputs and the

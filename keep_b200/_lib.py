@@ -137,6 +137,7 @@ _SIGNATURES = {
     "keepvq_router_logits": (c_int, [POINTER(RouterLogitsArgs), c_void_p]),
     "keepvq_routed_topk": (c_int, [POINTER(RoutedTopkArgs), c_void_p]),
     "keepvq_moe_layer_workspace_bytes": (c_int64, [c_int64, c_int64, c_int64, c_int64, c_int32]),
+    "keepvq_moe_layer_status_offset": (c_int64, [c_int64, c_int64, c_int64, c_int64, c_int32]),
     "keepvq_moe_decode_layer": (c_int, [POINTER(MoELayerArgs), c_void_p]),
     "keepvq_moe_decode_stages": (c_int, [POINTER(MoELayerArgs), c_int32, c_void_p]),
     "keepvq_moe_decode_layer_static": (c_int, [POINTER(MoELayerArgs), c_void_p]),

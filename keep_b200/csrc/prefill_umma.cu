@@ -250,7 +250,6 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_projection_kernel(FastP
           if (!ok) break;
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           const uint32_t a_base = smem_base + sa * A_STAGE_BYTES, b_base = smem_base + A_BYTES + sb * PF_B_STAGE_BYTES;
-#pragma unroll
           const uint64_t b_desc = umma_desc(b_base);
 #pragma unroll
           for (int m = 0; m < M; ++m) {

@@ -7,12 +7,13 @@
 //   - the admission test (gate >= tau on renormalised demand weights)
 //                                   scripts/v41_build/omlx_routed.py:184-203
 //
-// keepvq_router_logits: logits[t, e] = (x[t] . W[e]) / gate_temp, fp32.  A warp owns one router
-//   row and a tile of 8 tokens; lanes stride the hidden dimension in 16-byte chunks, so each row
-//   of W is read once per token tile.  Products of bf16 values are exact in fp32; the order of
-//   additions is fixed (lane-sequential, then a butterfly), so results are reproducible.
+// keepvq_router_logits: logits[t, e] = (x[t] . W[e]) / gate_temp, fp32.  A block owns 4 router
+//   rows and a tile of 8 tokens, its warps split the hidden dimension.  Products of bf16 values
+//   are exact in fp32; the order of additions is fixed (lane-sequential, a butterfly over lanes,
+//   then over warps), so results are reproducible.
 //   From 256 tokens on a shared-memory tiled kernel takes over (one FMA chain per logit, k ascending).
-// keepvq_routed_topk: one warp per token.  Scores = f(logits); served = top-k of
+// keepvq_routed_topk: one warp per token (pool in registers up to 1024 experts, in shared memory
+//   beyond).  Scores = f(logits); served = top-k of
 //   scores + served_bias (absent experts carry -inf or anything <= -1e29); demand = top-k of
 //   scores + pool_bias; ties go to the lowest expert id; picks come out in descending biased
 //   score, the order torch.topk gives.  The bias selects only; weights come from raw scores.
@@ -22,40 +23,60 @@
 
 namespace keepvq {
 
-constexpr int RL_WARPS = 8;    // router rows per block
+constexpr int RL_WARPS = 8;    // warps per block; they split the hidden dimension
+constexpr int RL_ROWS = 4;     // router rows per block
 constexpr int RL_TOKENS = 8;   // tokens per block
 constexpr float ABSENT_BIAS = -1e29f;  // served_bias at or below this marks an absent expert
 
+// Few tokens: latency is what counts, so a block's 8 warps split the hidden dimension (every load
+// of a lane is independent of the others) and a block covers 4 router rows x 8 tokens.  A logit is
+// summed lane-sequentially, then by a butterfly over the lanes, then over the warps in order.
 template <typename XT, typename WT>
 __global__ void __launch_bounds__(RL_WARPS * 32) router_logits_kernel(keepvq_router_logits_args a) {
+  __shared__ float part[RL_WARPS][RL_ROWS * RL_TOKENS];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int64_t e = static_cast<int64_t>(blockIdx.x) * RL_WARPS + warp;
-  const int64_t t0 = static_cast<int64_t>(blockIdx.y) * RL_TOKENS;
-  if (e >= a.pool) return;
-  const WT* w = reinterpret_cast<const WT*>(a.router_w) + e * a.hidden;
+  const int64_t e0 = static_cast<int64_t>(blockIdx.x) * RL_ROWS, t0 = static_cast<int64_t>(blockIdx.y) * RL_TOKENS;
+  const WT* w = reinterpret_cast<const WT*>(a.router_w);
   const XT* x = reinterpret_cast<const XT*>(a.x);
-  float acc[RL_TOKENS];
+  float acc[RL_ROWS][RL_TOKENS];
 #pragma unroll
-  for (int i = 0; i < RL_TOKENS; ++i) acc[i] = 0.0f;
-  for (int64_t k = lane * 8; k < a.hidden; k += 32 * 8) {
-    float wv[8];
-    load8_as_float<WT>(w + k, wv);
+  for (int r = 0; r < RL_ROWS; ++r)
+#pragma unroll
+    for (int i = 0; i < RL_TOKENS; ++i) acc[r][i] = 0.0f;
+  const int64_t chunks = a.hidden / 8;
+#pragma unroll 2
+  for (int64_t c = warp * 32 + lane; c < chunks; c += RL_WARPS * 32) {
+    float wv[RL_ROWS][8];
+#pragma unroll
+    for (int r = 0; r < RL_ROWS; ++r) load8_as_float<WT>(w + min(e0 + r, a.pool - 1) * a.hidden + c * 8, wv[r]);
 #pragma unroll
     for (int i = 0; i < RL_TOKENS; ++i) {
       if (t0 + i < a.tokens) {
         float xv[8];
-        load8_as_float<XT>(x + (t0 + i) * a.hidden + k, xv);
+        load8_as_float<XT>(x + (t0 + i) * a.hidden + c * 8, xv);
 #pragma unroll
-        for (int d = 0; d < 8; ++d) acc[i] = fmaf(xv[d], wv[d], acc[i]);
+        for (int r = 0; r < RL_ROWS; ++r)
+#pragma unroll
+          for (int d = 0; d < 8; ++d) acc[r][i] = fmaf(xv[d], wv[r][d], acc[r][i]);
       }
     }
   }
 #pragma unroll
-  for (int i = 0; i < RL_TOKENS; ++i) {
-    float v = acc[i];
+  for (int r = 0; r < RL_ROWS; ++r)
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, o);
-    if (lane == 0 && t0 + i < a.tokens) a.logits[(t0 + i) * a.pool + e] = v / a.gate_temp;
+    for (int i = 0; i < RL_TOKENS; ++i) {
+      float v = acc[r][i];
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, o);
+      if (lane == 0) part[warp][r * RL_TOKENS + i] = v;
+    }
+  __syncthreads();
+  if (threadIdx.x < RL_ROWS * RL_TOKENS) {
+    float v = 0.0f;
+#pragma unroll
+    for (int q = 0; q < RL_WARPS; ++q) v += part[q][threadIdx.x];
+    const int64_t e = e0 + threadIdx.x / RL_TOKENS, t = t0 + threadIdx.x % RL_TOKENS;
+    if (e < a.pool && t < a.tokens) a.logits[t * a.pool + e] = v / a.gate_temp;
   }
 }
 
@@ -124,6 +145,113 @@ __device__ __forceinline__ void warp_argmax(float& v, int& i) {
 
 constexpr int TK_WARPS = 4;
 constexpr int TK_MAX_K = 16;
+
+// Floats as unsigned keys of the same order (-inf lowest of the real values); 0 is below all of them.
+__device__ __forceinline__ uint32_t ordered_key(float v) {
+  const uint32_t u = __float_as_uint(v);
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+
+// One warp per token with the pool in registers (NPL experts per lane, expert e = lane + 32 i).
+// A pick is a register scan, one warp max and one warp min (redux.sync); no shared memory and no
+// loads inside the selection loops.  Same arithmetic and the same results as routed_topk_kernel.
+template <int NPL>
+__global__ void __launch_bounds__(TK_WARPS * 32) routed_topk_reg_kernel(keepvq_routed_topk_args a) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int64_t t = static_cast<int64_t>(blockIdx.x) * TK_WARPS + warp;
+  if (t >= a.tokens) return;
+  const int P = static_cast<int>(a.pool), K = a.top_k;
+  const float* lg = a.logits + t * P;
+  float sc[NPL];
+#pragma unroll
+  for (int i = 0; i < NPL; ++i) { const int e = lane + 32 * i; sc[i] = e < P ? lg[e] : -INFINITY; }
+
+  // ---- score function --------------------------------------------------------------------
+  if (a.score_func == KEEPVQ_SCORE_SOFTMAX) {
+    float m = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < NPL; ++i) m = fmaxf(m, sc[i]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
+    float s = 0.0f;
+#pragma unroll
+    for (int i = 0; i < NPL; ++i)
+      if (lane + 32 * i < P) { sc[i] = expf(sc[i] - m); s += sc[i]; }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xFFFFFFFFu, s, o);
+#pragma unroll
+    for (int i = 0; i < NPL; ++i) sc[i] = sc[i] / s;
+  } else if (a.score_func == KEEPVQ_SCORE_SIGMOID) {
+#pragma unroll
+    for (int i = 0; i < NPL; ++i) sc[i] = 1.0f / (1.0f + expf(-sc[i]));
+  } else {
+#pragma unroll
+    for (int i = 0; i < NPL; ++i) { const float v = sc[i]; sc[i] = sqrtf(v > 20.0f ? v : log1pf(expf(v))); }
+  }
+  if (a.scores) {
+#pragma unroll
+    for (int i = 0; i < NPL; ++i)
+      if (lane + 32 * i < P) a.scores[t * P + lane + 32 * i] = sc[i];
+  }
+
+  // ---- two selections over the same scores -------------------------------------------------
+  for (int pass = 0; pass < 2; ++pass) {
+    const float* bias = pass == 0 ? a.served_bias : a.pool_bias;
+    uint32_t key[NPL];
+#pragma unroll
+    for (int i = 0; i < NPL; ++i) {
+      const int e = lane + 32 * i;
+      key[i] = e < P ? max(ordered_key(sc[i] + (bias ? bias[e] : 0.0f)), 1u) : 0u;
+    }
+    int my_e = 0;       // lane j keeps pick j
+    float my_raw = 0.0f;
+    for (int j = 0; j < K; ++j) {
+      uint32_t bu = 0u, bi = 0xFFFFFFFFu;
+#pragma unroll
+      for (int i = 0; i < NPL; ++i)
+        if (key[i] > bu) { bu = key[i]; bi = lane + 32 * i; }
+      const uint32_t top = __reduce_max_sync(0xFFFFFFFFu, bu);
+      const uint32_t win = __reduce_min_sync(0xFFFFFFFFu, bu == top ? bi : 0xFFFFFFFFu);  // ties: the lowest expert id
+      float raw = 0.0f;
+#pragma unroll
+      for (int i = 0; i < NPL; ++i)
+        if (static_cast<uint32_t>(lane + 32 * i) == win) { raw = sc[i]; key[i] = 0u; }
+      raw = __shfl_sync(0xFFFFFFFFu, raw, win & 31u);
+      if (lane == j) { my_e = static_cast<int>(win); my_raw = raw; }
+    }
+    float raw = 0.0f;
+    bool live = false;
+    if (lane < K) {
+      raw = my_raw;
+      live = pass == 1 || !a.served_bias || a.served_bias[my_e] > ABSENT_BIAS;
+      if (!live) raw = 0.0f;  // a masked pick carries no weight (local_eval.py:87)
+    }
+    float sum = raw;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xFFFFFFFFu, sum, o);
+    if (lane < K) {
+      const int e = my_e;
+      const int64_t o = t * K + lane;
+      if (pass == 0) {
+        float w = raw;
+        if (a.norm_topk_prob && K > 1) w = w / (sum + 1e-20f);
+        w *= a.route_scale;
+        a.served_weight[o] = w;
+        a.served_expert[o] = live ? static_cast<uint32_t>(e) : KEEPVQ_NO_RESIDUAL;
+        a.served_slot[o] = live ? (a.slot_of ? a.slot_of[e] : static_cast<uint32_t>(e)) : KEEPVQ_NO_RESIDUAL;
+      } else {
+        a.want[o] = static_cast<uint32_t>(e);
+        a.want_score[o] = raw;
+        if (a.admit) {
+          // the policy's own normalisation: always over the k demanded scores (omlx_routed.py:186)
+          const float g = raw / (sum + 1e-20f) * a.route_scale;
+          const bool absent = a.served_bias && a.served_bias[e] <= ABSENT_BIAS;
+          a.admit[o] = (absent && g >= a.tau) ? e : -1;
+        }
+      }
+    }
+  }
+}
 
 __global__ void __launch_bounds__(TK_WARPS * 32) routed_topk_kernel(keepvq_routed_topk_args a) {
   extern __shared__ float smem[];  // per warp: scores[pool]
@@ -246,7 +374,7 @@ extern "C" int keepvq_router_logits(const keepvq_router_logits_args* args, void*
   }
   const int64_t token_tiles = (a.tokens + RL_TOKENS - 1) / RL_TOKENS;
   if (token_tiles > 65535) return KEEPVQ_ERR_CAPACITY;
-  dim3 grid(static_cast<unsigned>((a.pool + RL_WARPS - 1) / RL_WARPS), static_cast<unsigned>(token_tiles));
+  dim3 grid(static_cast<unsigned>((a.pool + RL_ROWS - 1) / RL_ROWS), static_cast<unsigned>(token_tiles));
   if (a.x_dtype == KEEPVQ_F32) launch_logits<float>(a, grid, s);
   else if (a.x_dtype == KEEPVQ_F16) launch_logits<__half>(a, grid, s);
   else launch_logits<__nv_bfloat16>(a, grid, s);
@@ -262,14 +390,21 @@ extern "C" int keepvq_routed_topk(const keepvq_routed_topk_args* args, void* str
   if (a.score_func < KEEPVQ_SCORE_SOFTMAX || a.score_func > KEEPVQ_SCORE_SQRT_SOFTPLUS) return KEEPVQ_ERR_DTYPE;
   if (a.tokens == 0) return KEEPVQ_OK;
   if (!a.logits || !a.served_slot || !a.served_expert || !a.served_weight || !a.want || !a.want_score) return KEEPVQ_ERR_NULL;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const unsigned blocks = static_cast<unsigned>((a.tokens + TK_WARPS - 1) / TK_WARPS);
+  if (a.pool <= 1024) {  // the pool fits the registers of a warp
+    if (a.pool <= 128) routed_topk_reg_kernel<4><<<blocks, TK_WARPS * 32, 0, s>>>(a);
+    else if (a.pool <= 384) routed_topk_reg_kernel<12><<<blocks, TK_WARPS * 32, 0, s>>>(a);
+    else routed_topk_reg_kernel<32><<<blocks, TK_WARPS * 32, 0, s>>>(a);
+    KEEPVQ_CHECK_LAUNCH();
+    return KEEPVQ_OK;
+  }
   const size_t smem = static_cast<size_t>(TK_WARPS) * a.pool * sizeof(float);
   if (smem > 200 * 1024) return KEEPVQ_ERR_CAPACITY;
-  cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(routed_topk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     if (e != cudaSuccess) return note_cuda_error(e);
   }
-  const unsigned blocks = static_cast<unsigned>((a.tokens + TK_WARPS - 1) / TK_WARPS);
   routed_topk_kernel<<<blocks, TK_WARPS * 32, smem, s>>>(a);
   KEEPVQ_CHECK_LAUNCH();
   return KEEPVQ_OK;

@@ -120,6 +120,16 @@ class RoutedMoELayer:
             served_weight=_lib.ptr(r.served_weight), want=_lib.ptr(r.want), want_score=_lib.ptr(r.want_score),
             admit=_lib.ptr(r.admit), workspace=_lib.ptr(workspace), workspace_bytes=nbytes, expected_routes=0)
 
+    def wait_expired(self, tokens: int, dtype: torch.dtype, state: int = 0) -> bool:
+        """True when a bounded wait of the tcgen05 kernels expired during the last call of this
+        shape (its outputs are then invalid).  Reads one word back: synchronises the stream."""
+        buf = self._buffers_for(tokens, dtype, state)
+        offset = int(_lib.load().keepvq_moe_layer_status_offset(tokens, self.hidden, self.inter, self.pool, self.top_k))
+        if offset < 0:
+            _lib.check(offset, "keepvq_moe_layer_status_offset")
+        base = (-buf["workspace"].data_ptr()) % 256  # the library aligns the scratch to 256 bytes
+        return bool(buf["workspace"][base + offset: base + offset + 4].view(torch.int32).item())
+
     @property
     def kernel_path(self) -> str:
         """``"tensor"`` when calls run on the int8 tensor-core kernels, else ``"general"``."""

@@ -136,6 +136,7 @@ def test_many_routes_per_expert_take_the_tcgen05_kernels(cuda, tokens, experts, 
     out, routing = layer.decode(x.to(cuda))
     served = routing.served_expert.cpu().numpy()
     assert (served != experts - 1).all()
+    assert not layer.wait_expired(tokens, x.dtype)  # no bounded wait of the tcgen05 kernels gave up
     check_layer(cfg, x, out, routing, top_k=top_k)
 
 
