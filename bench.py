@@ -174,6 +174,19 @@ def projection_roofline(layer, xs, steps, hbm_gbs, peak_kind):
 NCU_TRAFFIC_PER_CODE_BYTE = 995.4 / 1025.4
 
 
+def batch_sweep(layer, device, rotation, steps, hbm_gbs, batches=(1, 4, 16)):
+    """The other decode batch sizes of config 2: layer tokens/s and the gate/up kernel's fraction
+    of the HBM peak, measured the same way as the headline batch."""
+    out = {}
+    for b in batches:
+        xs = token_batches(device, b, rotation)
+        ms = time_graph(lambda i: layer.decode(xs[i % len(xs)]), steps, 3)
+        roof = projection_roofline(layer, xs, steps, hbm_gbs, "")
+        out[str(b)] = {"tokens_per_s": round(b * steps / (ms * 1e-3), 1), "layer_us": round(ms / steps * 1e3, 1),
+                       "gate_up_us": roof["us_per_launch"], "gate_up_frac_of_hbm": roof["frac"]}
+    return out
+
+
 def stage_times(layer, xs, steps):
     """Microseconds per stage of the layer call, each stage replayed alone on the state the full
     calls of `projection_roofline` left behind (same rotation of token batches)."""
@@ -491,6 +504,7 @@ def run_ours(ns):
         "cpu_baseline": {"value": round(1.0 / cpu_s, 4), "unit": UNIT, "cores": threads, "kind": "port",
                          "sample": "one token: router + decode of 6 experts x 3 projections + SwiGLU path", "parity_gap_vs_gpu": parity_gap},
         "e2e": {"value": round(e2e_value, 1), "unit": UNIT, "h2d_bytes_per_step": batch * HIDDEN * 2, "d2h_bytes_per_step": batch * HIDDEN * 2},
+        "batch_sweep": batch_sweep(layer, device, ns.rotation, ns.steps, hbm_gbs) if not ns.no_prefill else None,
         "prefill": prefill_leg(layer, device) if not ns.no_prefill else None,
         "gpu_launches": layer.launches_per_call * ns.steps, "kernel_path": layer.kernel_path,
         "clocks": clocks.summary(),
@@ -507,7 +521,7 @@ def main():
     ap.add_argument("--rotation", type=int, default=ROTATION, help="distinct token batches to rotate over (profiling runs use fewer)")
     ap.add_argument("--layers", type=int, default=EP_LAYERS, help="layers of the expert-parallel stack (N > 1)")
     ap.add_argument("--no-graph", action="store_true", help="expert-parallel run: time eager launches instead of a CUDA graph")
-    ap.add_argument("--no-prefill", action="store_true", help="skip the 4096-token prefill leg (config 3)")
+    ap.add_argument("--no-prefill", action="store_true", help="skip the 4096-token prefill leg (config 3) and the batch sweep")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ns = ap.parse_args()
     if ns.impl == "reference":
