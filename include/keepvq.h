@@ -358,6 +358,40 @@ typedef struct keepvq_residency_args {
 int keepvq_residency_tick(const keepvq_residency_args* args, void* stream);
 
 /* ------------------------------------------------------------------------------------------
+ * keepvq_grouped_projection: out[r] = W[rhs[r]] @ x[r], one activation row per route, on the
+ * int8 tensor-core kernels.  What gather_vqmm_sorted_routes reaches in the reference for prefill
+ * (src/ramp/ops/vq_switch.py:620-913 -> src/ramp/kernels/gather_vqmm.py:597-928 and the native
+ * nax_e8p_fp16_sorted_matmul_steel, src/ramp/kernels/nax.py:330-366).  Routes are grouped by
+ * expert on the device, so they need not arrive sorted; rhs 0xFFFFFFFF gives a zero row.
+ * Returns KEEPVQ_ERR_UNSUPPORTED when the shapes or the table do not fit these kernels (16-bit
+ * codes, in_dim % 256 == 0, whole scale groups per 256 inputs, every table nibble odd): the
+ * caller then uses keepvq_routed_matvec.  Activations are rounded to 16-bit fixed point per row
+ * (relative 2^-15 of the row maximum); everything else is exact integer arithmetic.
+ * The scratch also holds, at keepvq_grouped_projection_status_offset, the int32 the tcgen05
+ * kernel sets when a bounded wait expires (see keepvq_moe_layer_status_offset).
+ * ------------------------------------------------------------------------------------------ */
+typedef struct keepvq_grouped_projection_args {
+  const void* x;             /* [routes, in_dim] */
+  int32_t x_dtype;
+  int64_t routes;
+  const uint32_t* rhs;       /* [routes] expert (slot) of each route */
+  const uint16_t* codes;     /* [slots, out_dim, in_dim/8] */
+  const void* scales;        /* [slots, out_dim, groups] */
+  int32_t scales_dtype;
+  int64_t slots, out_dim, in_dim, groups;
+  const uint32_t* codebook;  /* E8P packed abs grid */
+  int32_t codebook_all_odd;  /* as in keepvq_moe_layer_args */
+  void* out;                 /* [routes, out_dim] */
+  int32_t out_dtype;
+  void* workspace;           /* keepvq_grouped_projection_workspace_bytes(), 256-byte aligned */
+  int64_t workspace_bytes;
+} keepvq_grouped_projection_args;
+
+int64_t keepvq_grouped_projection_workspace_bytes(int64_t routes, int64_t in_dim);
+int64_t keepvq_grouped_projection_status_offset(int64_t routes, int64_t in_dim);
+int keepvq_grouped_projection(const keepvq_grouped_projection_args* args, void* stream);
+
+/* ------------------------------------------------------------------------------------------
  * Expert parallelism: packing routes for the dispatch all-to-all and summing them after the
  * combine all-to-all.
  *

@@ -102,6 +102,15 @@ class ResidencyArgs(Structure):
     ]
 
 
+class GroupedProjectionArgs(Structure):
+    _fields_ = [
+        ("x", c_void_p), ("x_dtype", c_int32), ("routes", c_int64), ("rhs", c_void_p), ("codes", c_void_p), ("scales", c_void_p),
+        ("scales_dtype", c_int32), ("slots", c_int64), ("out_dim", c_int64), ("in_dim", c_int64), ("groups", c_int64),
+        ("codebook", c_void_p), ("codebook_all_odd", c_int32), ("out", c_void_p), ("out_dtype", c_int32),
+        ("workspace", c_void_p), ("workspace_bytes", c_int64),
+    ]
+
+
 class EpPackArgs(Structure):
     _fields_ = [
         ("x", c_void_p), ("row_bytes", c_int64), ("served_expert", c_void_p), ("served_weight", c_void_p),
@@ -125,7 +134,7 @@ STAGE_ROUTER, STAGE_PREPARE, STAGE_GATE_UP, STAGE_DOWN, STAGE_COMBINE, STAGE_ALL
 EXTRA_STRUCTS = {
     "keepvq_router_logits_args": RouterLogitsArgs, "keepvq_routed_topk_args": RoutedTopkArgs,
     "keepvq_expert_weights": ExpertWeights, "keepvq_moe_layer_args": MoELayerArgs,
-    "keepvq_residency_args": ResidencyArgs, "keepvq_ep_pack_args": EpPackArgs, "keepvq_ep_combine_args": EpCombineArgs,
+    "keepvq_residency_args": ResidencyArgs, "keepvq_grouped_projection_args": GroupedProjectionArgs, "keepvq_ep_pack_args": EpPackArgs, "keepvq_ep_combine_args": EpCombineArgs,
 }
 
 _SIGNATURES = {
@@ -142,6 +151,9 @@ _SIGNATURES = {
     "keepvq_moe_decode_stages": (c_int, [POINTER(MoELayerArgs), c_int32, c_void_p]),
     "keepvq_moe_decode_layer_static": (c_int, [POINTER(MoELayerArgs), c_void_p]),
     "keepvq_residency_tick": (c_int, [POINTER(ResidencyArgs), c_void_p]),
+    "keepvq_grouped_projection_workspace_bytes": (c_int64, [c_int64, c_int64]),
+    "keepvq_grouped_projection_status_offset": (c_int64, [c_int64, c_int64]),
+    "keepvq_grouped_projection": (c_int, [POINTER(GroupedProjectionArgs), c_void_p]),
     "keepvq_ep_pack": (c_int, [POINTER(EpPackArgs), c_void_p]),
     "keepvq_ep_combine": (c_int, [POINTER(EpCombineArgs), c_void_p]),
 }

@@ -1,0 +1,81 @@
+// One expert-grouped projection over routes, on the int8 tensor-core kernels: the operator-level
+// counterpart of the reference's sorted-route prefill kernels
+// (src/ramp/kernels/gather_vqmm.py:597-928, native/vq_nax_ext/kernels/nax_fp16_matmul.metal:904-1062).
+//
+// out[r] = W[rhs[r]] @ x[r] for r < routes; x holds one activation row per route (the caller
+// gathers them, as the reference does before its kernels, src/ramp/ops/vq_switch.py:758-761).
+// The sequence is the down projection of the layer call: quantise the rows, group the routes by
+// expert on the device, then the tcgen05 kernel (24 or more routes per expert on average) or the
+// mma.sync one.  Routes need not be sorted; a route with expert 0xFFFFFFFF gives a zero row.
+#include "moe_fast.cuh"
+
+namespace keepvq {
+
+struct GroupedScratch {
+  int64_t xq, xscale, xsums, gcount, gslot, gstart, gsize, groutes, status, total;
+};
+
+static inline int64_t up256(int64_t v) { return (v + 255) / 256 * 256; }
+
+static GroupedScratch plan_grouped(int64_t routes, int64_t in_dim) {
+  GroupedScratch s;
+  int64_t at = 0;
+  s.xq = at;      at += up256((routes + 1) * in_dim * 2);
+  s.xscale = at;  at += up256((routes + 1) * 4);
+  s.xsums = at;   at += up256((routes + 1) * (in_dim / 8) * 4);
+  s.gcount = at;  at += 256;
+  s.gslot = at;   at += up256(routes * 4);
+  s.gstart = at;  at += up256(routes * 4);
+  s.gsize = at;   at += up256(routes * 4);
+  s.groutes = at; at += up256(routes * 4);
+  s.status = at;  at += 256;
+  s.total = at;
+  return s;
+}
+
+}  // namespace keepvq
+
+extern "C" int64_t keepvq_grouped_projection_workspace_bytes(int64_t routes, int64_t in_dim) {
+  if (routes < 0 || in_dim <= 0 || in_dim % 8) return KEEPVQ_ERR_SHAPE;
+  return keepvq::plan_grouped(routes, in_dim).total;
+}
+
+extern "C" int64_t keepvq_grouped_projection_status_offset(int64_t routes, int64_t in_dim) {
+  if (routes < 0 || in_dim <= 0 || in_dim % 8) return KEEPVQ_ERR_SHAPE;
+  return keepvq::plan_grouped(routes, in_dim).status;
+}
+
+extern "C" int keepvq_grouped_projection(const keepvq_grouped_projection_args* args, void* stream) {
+  using namespace keepvq;
+  if (!args) return KEEPVQ_ERR_NULL;
+  const keepvq_grouped_projection_args& a = *args;
+  if (!valid_dtype(a.x_dtype) || !valid_dtype(a.scales_dtype)) return KEEPVQ_ERR_DTYPE;
+  if (a.routes < 0 || a.slots <= 0 || a.out_dim <= 0 || a.in_dim <= 0 || a.in_dim % 8 || a.groups <= 0) return KEEPVQ_ERR_SHAPE;
+  if (a.routes == 0) return KEEPVQ_OK;
+  if (!a.x || !a.rhs || !a.codes || !a.scales || !a.codebook || !a.out || !a.workspace) return KEEPVQ_ERR_NULL;
+  if (!a.codebook_all_odd || !fast::shapes_supported(a.out_dim, a.in_dim, a.groups)) return KEEPVQ_ERR_UNSUPPORTED;
+  if (!aligned_to(a.x, 16) || !aligned_to(a.codes, 16) || !aligned_to(a.workspace, 256)) return KEEPVQ_ERR_ALIGN;
+  const GroupedScratch sc = plan_grouped(a.routes, a.in_dim);
+  if (a.workspace_bytes < sc.total) return KEEPVQ_ERR_CAPACITY;
+  char* ws = reinterpret_cast<char*>(a.workspace);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  fast::RouteGroups groups = {reinterpret_cast<int32_t*>(ws + sc.gcount), reinterpret_cast<int32_t*>(ws + sc.gslot),
+                              reinterpret_cast<int32_t*>(ws + sc.gstart), reinterpret_cast<int32_t*>(ws + sc.gsize),
+                              reinterpret_cast<int32_t*>(ws + sc.groutes)};
+  fast::QuantRows xq = {reinterpret_cast<uint8_t*>(ws + sc.xq), reinterpret_cast<float*>(ws + sc.xscale), reinterpret_cast<int32_t*>(ws + sc.xsums)};
+  const bool many = a.routes >= 1024 && a.routes >= 24 * a.slots && fast::prefill_supported(a.out_dim, a.in_dim, a.groups);
+  int32_t* wait_status = reinterpret_cast<int32_t*>(ws + sc.status);
+  int rc;
+  if (many) {
+    cudaError_t e = cudaMemsetAsync(wait_status, 0, sizeof(int32_t), s);
+    if (e != cudaSuccess) return note_cuda_error(e);
+  }
+  if ((rc = fast::group_routes(a.rhs, a.routes, a.slots, many ? fast::PREFILL_GROUP_ROUTES : fast::MAX_GROUP_ROUTES, groups, s))) return rc;
+  if ((rc = fast::quantize_rows(a.x, a.x_dtype, a.routes, a.in_dim, a.groups, xq, many, s))) return rc;
+  fast::FastProjectionArgs p = {};
+  p.a = {a.codes, a.scales}; p.b = {nullptr, nullptr};
+  p.scales_dtype = a.scales_dtype; p.codebook = a.codebook; p.groups_of_routes = groups; p.max_routes = a.routes;
+  p.out_dim = a.out_dim; p.in_dim = a.in_dim; p.groups = a.groups; p.x = xq; p.x_zero_row = a.routes; p.x_div = 1;
+  p.out = a.out; p.out_dtype = a.out_dtype; p.swiglu_limit = 0.0f; p.route_weight = nullptr;
+  return many ? fast::prefill_down(p, wait_status, s) : fast::down(p, s);
+}

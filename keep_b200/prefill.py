@@ -3,18 +3,72 @@
 Stands in for the reference's sorted-route kernels: ``gather_vqmm_tiled_down`` /
 ``gather_vqmm_mma*_blocks`` (``src/ramp/kernels/gather_vqmm.py:597-928``) and the native
 ``nax_e8p_fp16_sorted_matmul_steel[_m32n64]`` (``src/ramp/kernels/nax.py:330-366,3601-3632``).
+
+16-bit E8P codes whose shapes fit go to ``keepvq_grouped_projection`` (int8 tensor cores: the
+tcgen05 kernel from 24 routes per expert on, the mma.sync one below); everything else (8-bit
+codes, odd shapes, custom tables with even nibbles) to the general routed kernel.
 """
 
 from __future__ import annotations
 
 import torch
 
-from .kernels import routed_matvec
+from . import _lib
+from .kernels import qmv_output_dtype, routed_matvec
+
+_UNSUPPORTED = -5  # KEEPVQ_ERR_UNSUPPORTED
+_all_odd: dict = {}     # table data_ptr -> every nibble odd (read back once per table, never per call)
+_workspaces: dict = {}  # (device, routes, in_dim) -> scratch tensor
+
+
+def _table_all_odd(table: torch.Tensor) -> bool:
+    key = (table.data_ptr(), str(table.device))
+    if key not in _all_odd:
+        nibbles = (table.cpu().to(torch.int64) & 0xFFFFFFFF)[:, None] >> (4 * torch.arange(8))[None] & 1
+        _all_odd[key] = bool(nibbles.all())
+    return _all_odd[key]
+
+
+def tensor_core_projection(rows, codes, scales, table, rhs):
+    """``keepvq_grouped_projection`` on one activation row per route, or None when the library
+    says these shapes are not for the tensor-core kernels."""
+    routes, in_dim = int(rows.shape[0]), int(rows.shape[1])
+    slots, out_dim, groups = int(codes.shape[0]), int(codes.shape[1]), int(scales.shape[2])
+    if codes.dtype != torch.uint16 or in_dim % 256 or rows.dtype not in (torch.float32, torch.float16, torch.bfloat16):
+        return None
+    lib = _lib.load()
+    device = rows.device
+    key = (str(device), routes, in_dim)
+    if key not in _workspaces:
+        nbytes = int(lib.keepvq_grouped_projection_workspace_bytes(routes, in_dim))
+        if nbytes < 0:
+            _lib.check(nbytes, "keepvq_grouped_projection_workspace_bytes")
+        _workspaces[key] = torch.empty(nbytes, dtype=torch.uint8, device=device)
+    ws = _workspaces[key]
+    out_dtype = qmv_output_dtype(rows.dtype)
+    out = torch.empty((routes, out_dim), dtype=out_dtype, device=device)
+    rows, rhs = rows.contiguous(), rhs.to(torch.int32).contiguous()
+    args = _lib.GroupedProjectionArgs(
+        x=_lib.ptr(rows), x_dtype=_lib.dtype_tag(rows.dtype), routes=routes, rhs=_lib.ptr(rhs), codes=_lib.ptr(codes), scales=_lib.ptr(scales),
+        scales_dtype=_lib.dtype_tag(scales.dtype), slots=slots, out_dim=out_dim, in_dim=in_dim, groups=groups, codebook=_lib.ptr(table),
+        codebook_all_odd=int(_table_all_odd(table)), out=_lib.ptr(out), out_dtype=_lib.dtype_tag(out_dtype),
+        workspace=_lib.ptr(ws), workspace_bytes=int(ws.numel()))
+    with torch.cuda.device(device):
+        status = lib.keepvq_grouped_projection(args, _lib.stream_handle(device))
+    if status == _UNSUPPORTED:
+        return None
+    _lib.check(status, "keepvq_grouped_projection")
+    return out
 
 
 def grouped_matmul_sorted(x, codes, scales, table, sorted_rhs, sorted_lhs, *, code_bits: int, tile_descriptors=None):
     """``out[r] = W[sorted_rhs[r]] @ x[sorted_lhs[r]]`` (``x[r]`` when ``sorted_lhs`` is None),
     ``[routes, out]`` in the given order.  ``tile_descriptors`` is accepted for callers that
-    pre-build it; the CUDA kernels derive their own tiling from ``sorted_rhs``."""
+    pre-build it; the CUDA kernels derive their own grouping from ``sorted_rhs``."""
     del tile_descriptors
+    if code_bits == 16 and scales.is_floating_point() and scales.dtype in (torch.float32, torch.float16, torch.bfloat16):
+        rows = x if sorted_lhs is None else x[sorted_lhs.long()]  # the gather the reference does before its kernels
+        out = tensor_core_projection(rows, codes, scales, table, sorted_rhs)
+        if out is not None:
+            return out
     return routed_matvec(x, codes, scales, table, sorted_rhs, lhs=sorted_lhs, x_div=1, code_bits=code_bits)

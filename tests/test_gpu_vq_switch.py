@@ -101,3 +101,31 @@ def test_metadata_errors_match_the_reference_messages(cuda):
         vq_switch.gather_vqmm(x, codes, scales, None, rhs + 3, implementation="reference", **kw)
     with pytest.raises(ValueError, match="same flattened shape"):
         vq_switch.gather_vqmm(x, codes, scales, None, rhs.reshape(-1), lhs_indices=torch.zeros(3, dtype=torch.int32, device=cuda), **kw)
+
+
+@pytest.mark.parametrize("routes,experts", [(300, 6), (1500, 6), (1200, 40)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_sorted_routes_on_the_tensor_core_kernels(cuda, routes, experts, dtype):
+    """Prefill-shaped sorted calls (16-bit codes, in_dim % 256 == 0, one scale group per row) run
+    keepvq_grouped_projection: the mma.sync kernel for 300 routes, the tcgen05 kernel for 1500
+    routes over 6 experts, the mma.sync one again for 1200 routes spread over 40 experts.  The
+    only rounding is the 16-bit fixed-point step on the activations."""
+    from keep_b200 import prefill, vq, vq_switch
+
+    rng = np.random.default_rng(90 + routes)
+    out, inp, tokens = 136, 512, 64
+    codes = rng.integers(0, 1 << 16, (experts, out, inp // 8), dtype=np.uint16)
+    scales = (0.02 * rng.uniform(0.5, 1.5, (experts, out, 1))).astype(np.float16)
+    x = torch.from_numpy(rng.normal(size=(tokens, inp)).astype(np.float32)).to(dtype)
+    rhs = np.sort(rng.integers(0, experts - 1, routes)).astype(np.int64)  # the last expert gets no route
+    lhs = rng.integers(0, tokens, routes).astype(np.int64)
+    want = ops.gather_vqmm(x.float().numpy(), codes, scales, None, rhs, lhs_indices=lhs, code_bits=16)
+    got = vq_switch.gather_vqmm_sorted_routes(x.to(cuda), codes, scales, None, rhs, lhs, input_dims=inp, output_dims=out,
+                                              group_size=inp, code_bits=16, validate_indices=True)
+    assert got.dtype == dtype and tuple(got.shape) == (routes, out)
+    tol = dict(rtol=1e-4, atol=3e-4) if dtype == torch.float32 else dict(rtol=1e-2, atol=1e-2)
+    np.testing.assert_allclose(f32(got), want, **tol)
+    rows = x.to(cuda)[torch.from_numpy(lhs).to(cuda)]
+    direct = prefill.tensor_core_projection(rows, torch.from_numpy(codes).to(cuda), torch.from_numpy(scales).to(cuda),
+                                            vq.table_on(cuda, "e8p"), torch.from_numpy(rhs).to(cuda))
+    assert direct is not None and torch.equal(direct, got)  # the operator did take this entry point
