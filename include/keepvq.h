@@ -444,6 +444,39 @@ typedef struct keepvq_ep_combine_args {
 
 int keepvq_ep_combine(const keepvq_ep_combine_args* args, void* stream);
 
+/* The same exchange without a collective library in the data path: ranks write rows straight into
+ * each other's buffers over NVLink (peer-mapped memory the caller sets up once and describes
+ * here), and a flag barrier with a bounded wait orders the phases.  One process per GPU; every
+ * rank makes the same sequence of calls.
+ *
+ * keepvq_ep_dispatch_peer  the plan of keepvq_ep_pack, with rows, slots and weights stored
+ *                          directly at row (rank * capacity + pos) of the destination rank's
+ *                          recv_x / recv_meta, then a barrier: when the call's work is done on
+ *                          this rank's stream, every rank's rows for it have landed.
+ * keepvq_ep_return_peer    row r of y (a live route received from rank r / capacity) goes to row
+ *                          (rank * capacity + r % capacity) of that rank's `back`, then a barrier;
+ *                          keepvq_ep_combine then runs on the local `back` with the positions
+ *                          keepvq_ep_dispatch_peer wrote.
+ *
+ * One set of buffers is enough for back-to-back layers: a rank leaves the second barrier of a
+ * layer only after every rank has finished reading what the first phase wrote.  A wait that
+ * expires (a peer that never arrives) sets *status to 1 and the kernel returns; nothing traps. */
+typedef struct keepvq_ep_peer_args {
+  int32_t world, rank;
+  int64_t capacity;             /* rows per (source, destination) block */
+  int64_t row_bytes;            /* multiple of 16 */
+  void* const* recv_x;          /* device array [world]: each rank's [world * capacity, row_bytes] */
+  int32_t* const* recv_meta;    /* device array [world]: each rank's [world * capacity, 2] */
+  void* const* back;            /* device array [world]: each rank's [world * capacity, row_bytes] */
+  int32_t* const* flags;        /* device array [world]: each rank's [world] arrival words, zero at start */
+  int32_t* epoch;               /* [1] this rank's barrier count, zero at start */
+  int32_t* status;              /* [1] */
+  uint32_t wait_spins;          /* polls (about a microsecond each) before a barrier gives up; 0 = 4,194,304 */
+} keepvq_ep_peer_args;
+
+int keepvq_ep_dispatch_peer(const keepvq_ep_pack_args* pack, const keepvq_ep_peer_args* peer, void* stream);
+int keepvq_ep_return_peer(const void* y, const keepvq_ep_peer_args* peer, void* stream);
+
 /* ------------------------------------------------------------------------------------------
  * keepvq_moe_decode_layer for callers that cannot hand over scratch memory.  It has no
  * counterpart in the reference.

@@ -119,6 +119,14 @@ class EpPackArgs(Structure):
     ]
 
 
+class EpPeerArgs(Structure):
+    _fields_ = [
+        ("world", c_int32), ("rank", c_int32), ("capacity", c_int64), ("row_bytes", c_int64),
+        ("recv_x", c_void_p), ("recv_meta", c_void_p), ("back", c_void_p), ("flags", c_void_p), ("epoch", c_void_p), ("status", c_void_p),
+        ("wait_spins", ctypes.c_uint32),
+    ]
+
+
 class EpCombineArgs(Structure):
     _fields_ = [
         ("back", c_void_p), ("dtype", c_int32), ("rows", c_int64), ("hidden", c_int64), ("position", c_void_p),
@@ -134,7 +142,7 @@ STAGE_ROUTER, STAGE_PREPARE, STAGE_GATE_UP, STAGE_DOWN, STAGE_COMBINE, STAGE_ALL
 EXTRA_STRUCTS = {
     "keepvq_router_logits_args": RouterLogitsArgs, "keepvq_routed_topk_args": RoutedTopkArgs,
     "keepvq_expert_weights": ExpertWeights, "keepvq_moe_layer_args": MoELayerArgs,
-    "keepvq_residency_args": ResidencyArgs, "keepvq_grouped_projection_args": GroupedProjectionArgs, "keepvq_ep_pack_args": EpPackArgs, "keepvq_ep_combine_args": EpCombineArgs,
+    "keepvq_residency_args": ResidencyArgs, "keepvq_grouped_projection_args": GroupedProjectionArgs, "keepvq_ep_pack_args": EpPackArgs, "keepvq_ep_peer_args": EpPeerArgs, "keepvq_ep_combine_args": EpCombineArgs,
 }
 
 _SIGNATURES = {
@@ -156,6 +164,8 @@ _SIGNATURES = {
     "keepvq_grouped_projection": (c_int, [POINTER(GroupedProjectionArgs), c_void_p]),
     "keepvq_ep_pack": (c_int, [POINTER(EpPackArgs), c_void_p]),
     "keepvq_ep_combine": (c_int, [POINTER(EpCombineArgs), c_void_p]),
+    "keepvq_ep_dispatch_peer": (c_int, [POINTER(EpPackArgs), POINTER(EpPeerArgs), c_void_p]),
+    "keepvq_ep_return_peer": (c_int, [c_void_p, POINTER(EpPeerArgs), c_void_p]),
 }
 
 _lock = threading.Lock()

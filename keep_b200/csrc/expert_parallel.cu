@@ -61,6 +61,103 @@ __global__ void __launch_bounds__(EP_PLAN_THREADS) ep_plan_kernel(keepvq_ep_pack
   }
 }
 
+// ---- the exchange over peer-mapped memory --------------------------------------------------
+// The same plan, with each destination's slots and weights stored in that rank's recv_meta.
+__global__ void __launch_bounds__(EP_PLAN_THREADS) ep_plan_peer_kernel(keepvq_ep_pack_args a, keepvq_ep_peer_args peer) {
+  __shared__ int warp_count[32][EP_MAX_WORLD];
+  __shared__ int base[EP_MAX_WORLD];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int64_t rows = static_cast<int64_t>(a.world) * a.capacity, routes = a.tokens * a.top_k;
+  for (int64_t i = tid; i < rows; i += EP_PLAN_THREADS) {  // my block in every rank's table: empty
+    int32_t* meta = peer.recv_meta[i / a.capacity] + 2 * (static_cast<int64_t>(peer.rank) * a.capacity + i % a.capacity);
+    meta[0] = -1;
+    meta[1] = 0;
+  }
+  if (tid < a.world) base[tid] = 0;
+  __threadfence_system();
+  __syncthreads();
+  for (int64_t chunk = 0; chunk < routes; chunk += EP_PLAN_THREADS) {
+    const int64_t r = chunk + tid;
+    const uint32_t e = r < routes ? a.served_expert[r] : EP_DEAD;
+    int dest = -1;
+    if (e != EP_DEAD && e / static_cast<uint32_t>(a.experts_per_rank) < static_cast<uint32_t>(a.world)) dest = static_cast<int>(e / a.experts_per_rank);
+    int before = 0;
+    for (int w = 0; w < a.world; ++w) {
+      const unsigned votes = __ballot_sync(0xFFFFFFFFu, dest == w);
+      if (lane == 0) warp_count[warp][w] = __popc(votes);
+      if (dest == w) before = __popc(votes & ((1u << lane) - 1u));
+    }
+    __syncthreads();
+    if (r < routes) {
+      int64_t pos = rows;
+      if (dest >= 0) {
+        int slot = base[dest] + before;
+        for (int i = 0; i < warp; ++i) slot += warp_count[i][dest];
+        if (slot < a.capacity) {
+          pos = static_cast<int64_t>(dest) * a.capacity + slot;
+          int32_t* meta = peer.recv_meta[dest] + 2 * (static_cast<int64_t>(peer.rank) * a.capacity + slot);
+          meta[0] = static_cast<int32_t>(e % a.experts_per_rank);
+          meta[1] = __float_as_int(a.served_weight[r]);
+        }
+      }
+      a.position[r] = static_cast<int32_t>(pos);
+    }
+    __syncthreads();
+    if (tid < a.world) {
+      int total = 0;
+      for (int i = 0; i < 32; ++i) total += warp_count[i][tid];
+      base[tid] += total;
+    }
+    __syncthreads();
+  }
+}
+
+__global__ void __launch_bounds__(256) ep_copy_peer_kernel(keepvq_ep_pack_args a, keepvq_ep_peer_args peer) {
+  const int64_t r = blockIdx.x, rows = static_cast<int64_t>(a.world) * a.capacity;
+  const int64_t pos = a.position[r];
+  if (pos >= rows) return;
+  const int64_t dest = pos / a.capacity, slot = pos % a.capacity;
+  const uint4* src = reinterpret_cast<const uint4*>(static_cast<const uint8_t*>(a.x) + (r / a.top_k) * a.row_bytes);
+  uint4* dst = reinterpret_cast<uint4*>(static_cast<uint8_t*>(peer.recv_x[dest]) + (static_cast<int64_t>(peer.rank) * a.capacity + slot) * a.row_bytes);
+  for (int64_t i = threadIdx.x; i < a.row_bytes / 16; i += blockDim.x) dst[i] = src[i];
+}
+
+// Row r of y, if it is a live route, back to the rank it came from.
+__global__ void __launch_bounds__(256) ep_return_peer_kernel(const uint8_t* __restrict__ y, keepvq_ep_peer_args peer) {
+  const int64_t r = blockIdx.x;
+  if (peer.recv_meta[peer.rank][2 * r] < 0) return;
+  const int64_t src_rank = r / peer.capacity, slot = r % peer.capacity;
+  const uint4* src = reinterpret_cast<const uint4*>(y + r * peer.row_bytes);
+  uint4* dst = reinterpret_cast<uint4*>(static_cast<uint8_t*>(peer.back[src_rank]) + (static_cast<int64_t>(peer.rank) * peer.capacity + slot) * peer.row_bytes);
+  for (int64_t i = threadIdx.x; i < peer.row_bytes / 16; i += blockDim.x) dst[i] = src[i];
+}
+
+// Flag barrier over the ranks.  Thread w tells rank w "I have arrived at barrier number e" and
+// waits for rank w's word in this rank's flags.  The work before the barrier ran in earlier
+// kernels of this stream; the system-scope fences order it before the flag stores and order the
+// peers' work before what follows the barrier here.  The wait is bounded (a few seconds by default).
+constexpr uint32_t EP_WAIT_LIMIT = 1u << 22;
+
+__global__ void __launch_bounds__(EP_MAX_WORLD) ep_barrier_kernel(keepvq_ep_peer_args peer) {
+  const int w = threadIdx.x;
+  const int32_t e = *peer.epoch + 1;
+  __threadfence_system();
+  if (w < peer.world) {
+    volatile int32_t* theirs = peer.flags[w] + peer.rank;
+    *theirs = e;
+    volatile int32_t* mine = peer.flags[peer.rank] + w;
+    const uint32_t limit = peer.wait_spins ? peer.wait_spins : EP_WAIT_LIMIT;
+    uint32_t spin = 0;
+    while (static_cast<int32_t>(*mine - e) < 0) {
+      if (++spin >= limit) { atomicExch(peer.status, 1); break; }
+      __nanosleep(100);
+    }
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (w == 0) *peer.epoch = e;
+}
+
 __global__ void __launch_bounds__(256) ep_copy_kernel(keepvq_ep_pack_args a) {
   const int64_t r = blockIdx.x, rows = static_cast<int64_t>(a.world) * a.capacity;
   const int64_t pos = a.position[r];
@@ -129,6 +226,52 @@ extern "C" int keepvq_ep_combine(const keepvq_ep_combine_args* args, void* strea
   if (a.dtype == KEEPVQ_F32) ep_combine_kernel<float><<<grid, 256, 0, s>>>(a);
   else if (a.dtype == KEEPVQ_F16) ep_combine_kernel<__half><<<grid, 256, 0, s>>>(a);
   else ep_combine_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(a);
+  KEEPVQ_CHECK_LAUNCH();
+  return KEEPVQ_OK;
+}
+
+static int check_peer(const keepvq_ep_peer_args& p) {
+  if (p.world <= 0 || p.world > keepvq::EP_MAX_WORLD || p.rank < 0 || p.rank >= p.world || p.capacity <= 0) return KEEPVQ_ERR_SHAPE;
+  if (p.row_bytes <= 0 || p.row_bytes % 16 != 0) return KEEPVQ_ERR_SHAPE;
+  if (!p.recv_x || !p.recv_meta || !p.back || !p.flags || !p.epoch || !p.status) return KEEPVQ_ERR_NULL;
+  if (static_cast<int64_t>(p.world) * p.capacity >= (1ll << 31)) return KEEPVQ_ERR_CAPACITY;
+  return KEEPVQ_OK;
+}
+
+extern "C" int keepvq_ep_dispatch_peer(const keepvq_ep_pack_args* pack, const keepvq_ep_peer_args* peer, void* stream) {
+  using namespace keepvq;
+  if (!pack || !peer) return KEEPVQ_ERR_NULL;
+  const keepvq_ep_pack_args& a = *pack;
+  const keepvq_ep_peer_args& p = *peer;
+  if (int rc = check_peer(p)) return rc;
+  if (a.tokens < 0 || a.top_k <= 0 || a.experts_per_rank <= 0) return KEEPVQ_ERR_SHAPE;
+  if (a.world != p.world || a.capacity != p.capacity || a.row_bytes != p.row_bytes) return KEEPVQ_ERR_SHAPE;
+  const int64_t routes = a.tokens * a.top_k;
+  if (routes >= (1ll << 31)) return KEEPVQ_ERR_CAPACITY;
+  if (routes > 0 && (!a.x || !a.served_expert || !a.served_weight || !a.position)) return KEEPVQ_ERR_NULL;
+  if (!aligned_to(a.x, 16)) return KEEPVQ_ERR_ALIGN;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  ep_plan_peer_kernel<<<1, EP_PLAN_THREADS, 0, s>>>(a, p);
+  KEEPVQ_CHECK_LAUNCH();
+  if (routes > 0) {
+    ep_copy_peer_kernel<<<static_cast<unsigned>(routes), 256, 0, s>>>(a, p);
+    KEEPVQ_CHECK_LAUNCH();
+  }
+  ep_barrier_kernel<<<1, EP_MAX_WORLD, 0, s>>>(p);
+  KEEPVQ_CHECK_LAUNCH();
+  return KEEPVQ_OK;
+}
+
+extern "C" int keepvq_ep_return_peer(const void* y, const keepvq_ep_peer_args* peer, void* stream) {
+  using namespace keepvq;
+  if (!y || !peer) return KEEPVQ_ERR_NULL;
+  const keepvq_ep_peer_args& p = *peer;
+  if (int rc = check_peer(p)) return rc;
+  if (!aligned_to(y, 16)) return KEEPVQ_ERR_ALIGN;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  ep_return_peer_kernel<<<static_cast<unsigned>(p.world * p.capacity), 256, 0, s>>>(static_cast<const uint8_t*>(y), p);
+  KEEPVQ_CHECK_LAUNCH();
+  ep_barrier_kernel<<<1, EP_MAX_WORLD, 0, s>>>(p);
   KEEPVQ_CHECK_LAUNCH();
   return KEEPVQ_OK;
 }

@@ -13,7 +13,8 @@ host before NCCL could be called.  Instead every (source, destination) pair owns
 carry slot id ``NO_SLOT`` and the expert kernels skip them.  At decode sizes the padding is a
 few MB per layer on NVLink and the whole step stays capturable in a CUDA graph.
 
-On CUDA tensors the packing and the pick summation are the library's own kernels
+``PeerExchange`` is the NVLink form: rows go straight into the peers' buffers, no collective in the
+data path.  ``RouteExchange`` is the NCCL form.  On CUDA tensors its packing and pick summation are the library's own kernels
 (``keepvq_ep_pack``, ``keepvq_ep_combine``: a memset and three launches per layer besides the
 all-to-alls).  On CPU tensors ``RouteExchange`` is plain ``torch`` + ``torch.distributed`` with
 the same positions, which is how the index arithmetic is tested on gloo ranks without GPUs; it
@@ -160,6 +161,90 @@ class RouteExchange:
         return recv
 
 
+class PeerExchange:
+    """The same dispatch / combine without a collective in the data path: every rank writes its
+    routes straight into the destination ranks' buffers over NVLink and a flag barrier with a
+    bounded wait orders the phases (``keepvq_ep_dispatch_peer``, ``keepvq_ep_return_peer``).
+
+    The buffers are ``torch.distributed._symmetric_memory`` allocations of a fixed shape
+    (``tokens`` x ``top_k`` routes per rank, rows of ``hidden`` values of ``dtype``), made once;
+    every rank must construct the exchange and call it in the same order.  One exchange serves
+    any number of layers run back to back.  CUDA only, one process per GPU.
+    """
+
+    def __init__(self, experts_per_rank: int, *, tokens: int, top_k: int, hidden: int, dtype: torch.dtype, device: torch.device,
+                 group=None, capacity: int | None = None, wait_spins: int = 0):
+        import torch.distributed._symmetric_memory as symm_mem
+
+        from . import _lib
+
+        self.group = group if group is not None else dist.group.WORLD
+        self.world, self.rank = dist.get_world_size(self.group), dist.get_rank(self.group)
+        self.experts_per_rank, self.tokens, self.top_k, self.hidden, self.dtype = int(experts_per_rank), int(tokens), int(top_k), int(hidden), dtype
+        self.capacity = int(capacity or tokens * top_k)
+        rows = self.world * self.capacity
+        self.row_bytes = hidden * torch.empty((), dtype=dtype).element_size()
+
+        def shared(shape, dt):
+            t = symm_mem.empty(*shape, dtype=dt, device=device)
+            t.zero_()
+            handle = symm_mem.rendezvous(t, self.group)
+            return t, handle
+
+        self.recv_x, hx = shared((rows, hidden), dtype)
+        self.recv_meta, hm = shared((rows, 2), torch.int32)
+        self.back, hb = shared((rows, hidden), dtype)
+        self.flags, hf = shared((max(self.world, 32),), torch.int32)
+        self._handles = (hx, hm, hb, hf)  # keep the mappings alive
+        table = lambda h: torch.tensor([int(p) for p in h.buffer_ptrs], dtype=torch.int64, device=device)  # noqa: E731
+        self._tables = tuple(table(h) for h in self._handles)
+        self.epoch = torch.zeros(1, dtype=torch.int32, device=device)
+        self.status = torch.zeros(1, dtype=torch.int32, device=device)
+        self.position = torch.empty((tokens, top_k), dtype=torch.int32, device=device)
+        self._peer = _lib.EpPeerArgs(world=self.world, rank=self.rank, capacity=self.capacity, row_bytes=self.row_bytes,
+                                     recv_x=_lib.ptr(self._tables[0]), recv_meta=_lib.ptr(self._tables[1]), back=_lib.ptr(self._tables[2]),
+                                     flags=_lib.ptr(self._tables[3]), epoch=_lib.ptr(self.epoch), status=_lib.ptr(self.status),
+                                     wait_spins=int(wait_spins))
+        torch.cuda.synchronize(device)
+        dist.barrier(self.group)  # every rank's buffers are zeroed and mapped before anyone writes
+
+    def dispatch(self, x: torch.Tensor, served_expert: torch.Tensor, served_weight: torch.Tensor):
+        """-> (recv_x, recv_slot, recv_weight, position), as ``RouteExchange.dispatch``."""
+        from . import _lib
+
+        if tuple(served_expert.shape) != (self.tokens, self.top_k) or tuple(x.shape) != (self.tokens, self.hidden) or x.dtype != self.dtype:
+            raise ValueError("this exchange was built for another shape or dtype")
+        x = x.contiguous()
+        experts = served_expert.to(torch.int32).contiguous()
+        weights = served_weight.contiguous().float()
+        args = _lib.EpPackArgs(x=_lib.ptr(x), row_bytes=self.row_bytes, served_expert=_lib.ptr(experts), served_weight=_lib.ptr(weights),
+                               tokens=self.tokens, top_k=self.top_k, world=self.world, experts_per_rank=self.experts_per_rank,
+                               capacity=self.capacity, send_x=None, send_meta=None, position=_lib.ptr(self.position))
+        with torch.cuda.device(x.device):
+            _lib.check(_lib.load().keepvq_ep_dispatch_peer(args, self._peer, _lib.stream_handle(x.device)), "keepvq_ep_dispatch_peer")
+        return self.recv_x, self.recv_meta[:, 0], self.recv_meta[:, 1].view(torch.float32), self.position
+
+    def combine(self, y_routes: torch.Tensor, position: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+        from . import _lib
+
+        y = y_routes.contiguous()
+        if y.dtype != self.dtype or out_dtype != self.dtype or tuple(y.shape) != tuple(self.recv_x.shape):
+            raise ValueError("this exchange was built for another shape or dtype")
+        with torch.cuda.device(y.device):
+            _lib.check(_lib.load().keepvq_ep_return_peer(_lib.ptr(y), self._peer, _lib.stream_handle(y.device)), "keepvq_ep_return_peer")
+        out = torch.empty((self.tokens, self.hidden), dtype=self.dtype, device=y.device)
+        args = _lib.EpCombineArgs(back=_lib.ptr(self.back), dtype=_lib.dtype_tag(self.dtype), rows=int(self.back.shape[0]), hidden=self.hidden,
+                                  position=_lib.ptr(position), tokens=self.tokens, top_k=self.top_k, out=_lib.ptr(out))
+        with torch.cuda.device(y.device):
+            _lib.check(_lib.load().keepvq_ep_combine(args, _lib.stream_handle(y.device)), "keepvq_ep_combine")
+        return out
+
+    def wait_expired(self) -> bool:
+        """True when a barrier gave up waiting for a peer (results since then are invalid).  Reads
+        one word back: synchronises the stream."""
+        return bool(self.status.item())
+
+
 class ExpertParallelLayer:
     """One routed MoE layer whose experts are sharded over the ranks of ``group``.
 
@@ -168,10 +253,11 @@ class ExpertParallelLayer:
     """
 
     def __init__(self, router_w: torch.Tensor, local, *, experts_per_rank: int, top_k: int, group=None, score_func: str = "softmax",
-                 route_scale: float = 1.0, norm_topk_prob: bool = True, capacity: int | None = None):
+                 route_scale: float = 1.0, norm_topk_prob: bool = True, capacity: int | None = None, exchange=None):
         self.router_w, self.local = router_w.contiguous(), local
         self.top_k, self.score_func, self.route_scale, self.norm_topk_prob = top_k, score_func, route_scale, norm_topk_prob
-        self.exchange = RouteExchange(experts_per_rank, group=group, capacity=capacity)
+        # `exchange`: a PeerExchange shared by the layers of a stack, or None for NCCL all-to-alls
+        self.exchange = exchange if exchange is not None else RouteExchange(experts_per_rank, group=group, capacity=capacity)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         from . import _lib

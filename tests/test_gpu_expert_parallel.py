@@ -14,10 +14,11 @@ pytestmark = pytest.mark.gpu
 EXPERTS, HIDDEN, INTER, TOP_K, TOKENS = 8, 512, 256, 3, 6
 
 
-def worker(rank, world, port, results):
+def worker(rank, world, port, results, kind="nccl"):
     import torch.distributed as dist
 
-    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    # no NVLink multicast objects anywhere: plain peer mappings and plain NCCL rings
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0", TORCH_SYMM_MEM_DISABLE_MULTICAST="1")
     torch.cuda.set_device(rank)
     device = torch.device("cuda", rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=device)
@@ -37,18 +38,27 @@ def worker(rank, world, port, results):
         shard = slice(lo, lo + per_rank)
         local = moe.RoutedMoELayer(torch.zeros((per_rank, HIDDEN), dtype=torch.bfloat16, device=device),
                                    proj("w1", shard), proj("w3", shard), proj("w2", shard), top_k=1)
-        layer = expert_parallel.ExpertParallelLayer(cfg["router"].to(device), local, experts_per_rank=per_rank, top_k=TOP_K)
-        x = synthetic.tokens(60 + rank, TOKENS, HIDDEN).to(device)
-        got = layer.forward(x)
-        want, _ = full.decode(x)
-        torch.cuda.synchronize()
-        ref = want.float().cpu().numpy()
-        results[rank] = float(np.abs(got.float().cpu().numpy() - ref).max() / np.abs(ref).max())
+        exchange = None
+        if kind == "peer":
+            exchange = expert_parallel.PeerExchange(per_rank, tokens=TOKENS, top_k=TOP_K, hidden=HIDDEN, dtype=torch.bfloat16, device=device)
+        layer = expert_parallel.ExpertParallelLayer(cfg["router"].to(device), local, experts_per_rank=per_rank, top_k=TOP_K, exchange=exchange)
+        worst = 0.0
+        for call in range(3):  # the buffers and barrier counts are reused from call to call
+            x = synthetic.tokens(60 + rank + 10 * call, TOKENS, HIDDEN).to(device)
+            got = layer.forward(x)
+            want, _ = full.decode(x)
+            torch.cuda.synchronize()
+            ref = want.float().cpu().numpy()
+            worst = max(worst, float(np.abs(got.float().cpu().numpy() - ref).max() / np.abs(ref).max()))
+        if exchange is not None:
+            assert not exchange.wait_expired()
+        results[rank] = worst
     finally:
         dist.destroy_process_group()
 
 
-def test_two_gpu_expert_parallel_matches_one_gpu():
+@pytest.mark.parametrize("kind", ["nccl", "peer"])
+def test_two_gpu_expert_parallel_matches_one_gpu(kind):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     import torch.multiprocessing as mp
@@ -58,7 +68,7 @@ def test_two_gpu_expert_parallel_matches_one_gpu():
         port = s.getsockname()[1]
     ctx = mp.get_context("spawn")
     results = ctx.Manager().dict()
-    procs = [ctx.Process(target=worker, args=(rank, 2, port, results)) for rank in range(2)]
+    procs = [ctx.Process(target=worker, args=(rank, 2, port, results, kind)) for rank in range(2)]
     for p in procs:
         p.start()
     for p in procs:
@@ -96,3 +106,37 @@ def test_pack_and_combine_kernels_match_the_torch_exchange(cuda, tokens, k, worl
     want = ex.combine(back, want_pos, torch.bfloat16)
     got = ex.combine(back.to(cuda), got_pos, torch.bfloat16)
     assert torch.equal(got.cpu(), want)
+
+
+def test_peer_barrier_gives_up_when_a_peer_never_arrives(cuda):
+    """Failure detection without a fault: one GPU plays rank 0 of two, the buffers of "rank 1" are
+    plain local tensors whose arrival word nothing ever sets.  The barrier polls 2000 times, sets
+    the status word and returns; the context stays usable and the rows still landed."""
+    from keep_b200 import _lib
+
+    tokens, k, hidden, per_rank, world = 4, 2, 64, 3, 2
+    capacity, rows = tokens * k, world * tokens * k
+    gen = torch.Generator().manual_seed(5)
+    x = torch.randn((tokens, hidden), generator=gen).to(torch.bfloat16).to(cuda)
+    experts = torch.randint(0, world * per_rank, (tokens, k), generator=gen, dtype=torch.int32).to(cuda)
+    weights = torch.rand((tokens, k), generator=gen).to(cuda)
+    make = lambda shape, dt: [torch.zeros(shape, dtype=dt, device=cuda) for _ in range(world)]  # noqa: E731
+    recv_x, recv_meta, back, flags = make((rows, hidden), torch.bfloat16), make((rows, 2), torch.int32), make((rows, hidden), torch.bfloat16), make((32,), torch.int32)
+    table = lambda ts: torch.tensor([t.data_ptr() for t in ts], dtype=torch.int64, device=cuda)  # noqa: E731
+    tables = [table(ts) for ts in (recv_x, recv_meta, back, flags)]
+    epoch, status = torch.zeros(1, dtype=torch.int32, device=cuda), torch.zeros(1, dtype=torch.int32, device=cuda)
+    position = torch.empty((tokens, k), dtype=torch.int32, device=cuda)
+    peer = _lib.EpPeerArgs(world=world, rank=0, capacity=capacity, row_bytes=hidden * 2, recv_x=_lib.ptr(tables[0]), recv_meta=_lib.ptr(tables[1]),
+                           back=_lib.ptr(tables[2]), flags=_lib.ptr(tables[3]), epoch=_lib.ptr(epoch), status=_lib.ptr(status), wait_spins=2000)
+    pack = _lib.EpPackArgs(x=_lib.ptr(x), row_bytes=hidden * 2, served_expert=_lib.ptr(experts), served_weight=_lib.ptr(weights), tokens=tokens,
+                           top_k=k, world=world, experts_per_rank=per_rank, capacity=capacity, send_x=None, send_meta=None, position=_lib.ptr(position))
+    _lib.check(_lib.load().keepvq_ep_dispatch_peer(pack, peer, _lib.stream_handle(cuda)), "keepvq_ep_dispatch_peer")
+    torch.cuda.synchronize()
+    assert int(status.item()) == 1 and int(epoch.item()) == 1            # gave up on rank 1, and said so
+    assert int(flags[1][0].item()) == 1 and int(flags[0][0].item()) == 1  # its own arrival was announced to both
+    pos = position.cpu().reshape(-1)
+    for r in range(tokens * k):                                          # the rows did land where the plan says
+        dest, slot = divmod(int(pos[r]), capacity)
+        assert torch.equal(recv_x[dest][slot].cpu(), x[r // k].cpu())    # rank 0's block is the first of each table
+        assert int(recv_meta[dest][slot][0]) == int(experts.reshape(-1)[r]) % per_rank
+    assert torch.equal((x.float() * 2).cpu(), x.float().cpu() * 2)        # the context still answers
