@@ -295,13 +295,16 @@ def run_reference(ns):
 EP_LAYERS, EP_BATCH = 40, 256
 
 
-def build_ep_stack(device, rank, world, layers):
+def build_ep_stack(device, rank, world, layers, exchange_kind="peer"):
     """Config 5: `layers` MoE layers, each with its 384 experts sharded contiguously over the ranks
     and a replicated router (same seed on every rank)."""
     from keep_b200 import expert_parallel, moe
 
     per_rank = EXPERTS // world
     stack = []
+    exchange = None
+    if exchange_kind == "peer":  # one set of peer-mapped buffers serves every layer of the stack
+        exchange = expert_parallel.PeerExchange(per_rank, tokens=EP_BATCH // world, top_k=TOP_K, hidden=HIDDEN, dtype=torch.bfloat16, device=device)
     for index in range(layers):
         shard = torch.Generator(device=device)
         shard.manual_seed(100_000 + 1000 * index + rank)
@@ -316,7 +319,7 @@ def build_ep_stack(device, rank, world, layers):
         router = (0.02 * torch.randn((EXPERTS, HIDDEN), generator=shared, device=device)).to(torch.bfloat16)
         local = moe.RoutedMoELayer(torch.zeros((per_rank, HIDDEN), dtype=torch.bfloat16, device=device),
                                    proj(INTER, HIDDEN), proj(INTER, HIDDEN), proj(HIDDEN, INTER), top_k=1)
-        stack.append(expert_parallel.ExpertParallelLayer(router, local, experts_per_rank=per_rank, top_k=TOP_K))
+        stack.append(expert_parallel.ExpertParallelLayer(router, local, experts_per_rank=per_rank, top_k=TOP_K, exchange=exchange))
     return stack
 
 
@@ -331,7 +334,7 @@ def run_expert_parallel(ns, rank, world, local, device):
     _lib.load()
     hbm_gbs, peak_kind = measured_peaks()
     layers = ns.layers
-    stack = build_ep_stack(device, rank, world, layers)
+    stack = build_ep_stack(device, rank, world, layers, ns.exchange)
     tokens_local = EP_BATCH // world
     gen = torch.Generator(device="cpu")
     gen.manual_seed(5 + rank)
@@ -387,9 +390,12 @@ def run_expert_parallel(ns, rank, world, local, device):
         end.record()
         torch.cuda.synchronize()
         e2e_ms = begin.elapsed_time(end)
-    t = torch.tensor([ms, e2e_ms], device=device)
+    expired = float(stack[0].exchange.wait_expired()) if ns.exchange == "peer" else 0.0
+    t = torch.tensor([ms, e2e_ms, expired], device=device)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms, e2e_ms = (float(v) for v in t.cpu())
+    ms, e2e_ms, expired = (float(v) for v in t.cpu())
+    if expired:
+        raise RuntimeError("a barrier of the peer exchange gave up waiting for a rank: the timing is invalid")
     if rank != 0:
         return
     # the unit is a token through one routed layer, as at N = 1: a step pushes EP_BATCH tokens through `layers` of them
@@ -405,9 +411,9 @@ def run_expert_parallel(ns, rank, world, local, device):
         "ms_per_step": round(ms / ns.steps, 4), "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic",
         "config": {"workload": f"expert-parallel stack (config 5): {layers} layers x 384 experts sharded {EXPERTS // world} per GPU, top-6, "
-                               f"{EP_BATCH} decode tokens in total ({tokens_local} per GPU), NCCL all-to-all dispatch and combine",
+                               f"{EP_BATCH} decode tokens in total ({tokens_local} per GPU), " + ("dispatch and combine by peer stores over NVLink with flag barriers" if ns.exchange == "peer" else "NCCL all-to-all dispatch and combine"),
                    "layers": layers, "batch": EP_BATCH, "l2": f"inputs larger than L2: {layers} layers x {EXPERTS // world * CODE_BYTES_PER_EXPERT / 1e9:.1f} GB of codes per GPU",
-                   "cuda_graph": graph is not None,
+                   "cuda_graph": graph is not None, "exchange": ns.exchange,
                    "note": "value = tokens x layers / time: a token through one routed layer is the unit, the same as the one-GPU line"},
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": hbm_gbs, "unit": "GB/s", "frac": round(achieved / hbm_gbs, 4), "traffic": None,
                      "peak_kind": "measured" if "hbm_gbs" in peaks else "fallback", "per": "GPU, whole layer (router, exchange and experts)",
@@ -427,6 +433,7 @@ def run_ours(ns):
     device = torch.device("cuda", local)
     if world > 1:
         import torch.distributed as dist
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")  # plain peer mappings: the exchange uses no multicast
         dist.init_process_group("nccl", device_id=device)
         try:
             run_expert_parallel(ns, rank, world, local, device)
@@ -520,6 +527,7 @@ def main():
     ap.add_argument("--batch", type=int, default=64)
     ap.add_argument("--rotation", type=int, default=ROTATION, help="distinct token batches to rotate over (profiling runs use fewer)")
     ap.add_argument("--layers", type=int, default=EP_LAYERS, help="layers of the expert-parallel stack (N > 1)")
+    ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"], help="expert-parallel run: how routes travel between the GPUs")
     ap.add_argument("--no-graph", action="store_true", help="expert-parallel run: time eager launches instead of a CUDA graph")
     ap.add_argument("--no-prefill", action="store_true", help="skip the 4096-token prefill leg (config 3) and the batch sweep")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])

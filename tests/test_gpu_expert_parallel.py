@@ -11,10 +11,10 @@ import torch
 import synthetic
 
 pytestmark = pytest.mark.gpu
-EXPERTS, HIDDEN, INTER, TOP_K, TOKENS = 8, 512, 256, 3, 6
+EXPERTS, HIDDEN, INTER, TOP_K = 8, 512, 256, 3
 
 
-def worker(rank, world, port, results, kind="nccl"):
+def worker(rank, world, port, results, kind="nccl", tokens=6):
     import torch.distributed as dist
 
     # no NVLink multicast objects anywhere: plain peer mappings and plain NCCL rings
@@ -40,11 +40,11 @@ def worker(rank, world, port, results, kind="nccl"):
                                    proj("w1", shard), proj("w3", shard), proj("w2", shard), top_k=1)
         exchange = None
         if kind == "peer":
-            exchange = expert_parallel.PeerExchange(per_rank, tokens=TOKENS, top_k=TOP_K, hidden=HIDDEN, dtype=torch.bfloat16, device=device)
+            exchange = expert_parallel.PeerExchange(per_rank, tokens=tokens, top_k=TOP_K, hidden=HIDDEN, dtype=torch.bfloat16, device=device)
         layer = expert_parallel.ExpertParallelLayer(cfg["router"].to(device), local, experts_per_rank=per_rank, top_k=TOP_K, exchange=exchange)
         worst = 0.0
         for call in range(3):  # the buffers and barrier counts are reused from call to call
-            x = synthetic.tokens(60 + rank + 10 * call, TOKENS, HIDDEN).to(device)
+            x = synthetic.tokens(60 + rank + 10 * call, tokens, HIDDEN).to(device)
             got = layer.forward(x)
             want, _ = full.decode(x)
             torch.cuda.synchronize()
@@ -57,8 +57,8 @@ def worker(rank, world, port, results, kind="nccl"):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("kind", ["nccl", "peer"])
-def test_two_gpu_expert_parallel_matches_one_gpu(kind):
+@pytest.mark.parametrize("kind,tokens", [("nccl", 6), ("peer", 6), ("peer", 200)])
+def test_two_gpu_expert_parallel_matches_one_gpu(kind, tokens):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     import torch.multiprocessing as mp
@@ -68,7 +68,7 @@ def test_two_gpu_expert_parallel_matches_one_gpu(kind):
         port = s.getsockname()[1]
     ctx = mp.get_context("spawn")
     results = ctx.Manager().dict()
-    procs = [ctx.Process(target=worker, args=(rank, 2, port, results, kind)) for rank in range(2)]
+    procs = [ctx.Process(target=worker, args=(rank, 2, port, results, kind, tokens)) for rank in range(2)]
     for p in procs:
         p.start()
     for p in procs:
