@@ -187,6 +187,54 @@ def batch_sweep(layer, device, rotation, steps, hbm_gbs, batches=(1, 4, 16)):
     return out
 
 
+def residency_leg(layer, device, rotation, steps, hbm_gbs, batch=16, resident=192, hot=32):
+    """Config 4: routed residency at batch 16.  Half the pool resident (seed 3), absent experts
+    masked out of the served selection, the 32 resident experts a 4096-token warm-up routing
+    selects most carry the nested 8-bit residual (scale 0.005), admissions at tau = 0.3.  Reports
+    layer tokens/s and the GB/s of code bytes the served routes touch (base + residual)."""
+    from keep_b200 import moe, router as router_ops
+
+    cpu = torch.Generator().manual_seed(3)
+    residents = torch.randperm(EXPERTS, generator=cpu)[:resident].sort().values
+    slot_of = torch.full((EXPERTS,), 0xFFFFFFFF, dtype=torch.int64)
+    slot_of[residents] = torch.arange(resident)
+    served_bias = torch.full((EXPERTS,), -1e30)
+    served_bias[residents] = 0.0
+    gen = torch.Generator(device="cpu").manual_seed(4)
+    warm = torch.randn((PREFILL_TOKENS, HIDDEN), generator=gen).to(torch.bfloat16).to(device)
+    routed = router_ops.routed_topk(warm, layer.router_w, served_bias.numpy(), None, slot_of.numpy().astype(np.uint32), top_k=TOP_K)
+    picks = routed.served_slot.reshape(-1).long()
+    counts = torch.bincount(picks[picks < resident], minlength=resident)
+    hot_slots = counts.topk(hot).indices.cpu()
+    hot_of_slot = torch.full((resident,), 0xFFFFFFFF, dtype=torch.int64)
+    hot_of_slot[hot_slots] = torch.arange(hot)
+    dgen = torch.Generator(device=device).manual_seed(7)
+
+    def with_residual(p, out, inp):
+        res_codes = torch.randint(0, 256, (hot, out, inp // 8), generator=dgen, device=device, dtype=torch.int32).to(torch.uint8)
+        res_scales = torch.full((hot, out, 1), 0.005, dtype=torch.float16, device=device)
+        return moe.Projection(p.codes[:resident], p.scales[:resident], res_codes, res_scales)
+
+    tiered = moe.RoutedMoELayer(layer.router_w, with_residual(layer.w1, INTER, HIDDEN), with_residual(layer.w3, INTER, HIDDEN),
+                                with_residual(layer.w2, HIDDEN, INTER), top_k=TOP_K, tau=0.3, served_bias=served_bias.numpy(),
+                                slot_of=slot_of.numpy().astype(np.uint32), hot_of_slot=hot_of_slot.numpy().astype(np.uint32))
+    xs = token_batches(device, batch, rotation)
+    base_u, hot_u, admitted = [], [], []
+    for j, x in enumerate(xs):
+        _, r = tiered.decode(x, state=1 + j)
+        slots = {int(v) for v in r.served_slot.cpu().numpy().astype("int64").reshape(-1) if 0 <= v < resident}
+        base_u.append(len(slots))
+        hot_u.append(sum(1 for v in slots if int(hot_of_slot[v]) < hot))
+        admitted.append(int((r.admit >= 0).sum()))
+    ms = time_graph(lambda i: tiered.decode(xs[i % len(xs)]), steps, 3)
+    code_bytes = statistics.fmean(base_u) * CODE_BYTES_PER_EXPERT + statistics.fmean(hot_u) * CODE_BYTES_PER_EXPERT / 2
+    gbs = code_bytes / (ms / steps * 1e-3) / 1e9
+    return {"batch": batch, "resident": resident, "hot": hot, "tokens_per_s": round(batch * steps / (ms * 1e-3), 1), "layer_us": round(ms / steps * 1e3, 1),
+            "distinct_base_experts": round(statistics.fmean(base_u), 1), "distinct_hot_experts": round(statistics.fmean(hot_u), 1),
+            "admissions_per_step": round(statistics.fmean(admitted), 1), "code_gbs": round(gbs, 1), "code_frac_of_hbm": round(gbs / hbm_gbs, 4),
+            "kernel_path": tiered.kernel_path}
+
+
 def stage_times(layer, xs, steps):
     """Microseconds per stage of the layer call, each stage replayed alone on the state the full
     calls of `projection_roofline` left behind (same rotation of token batches)."""
@@ -361,6 +409,7 @@ def run_expert_parallel(ns, rank, world, local, device):
                 with torch.cuda.graph(g, stream=side):
                     step()
             torch.cuda.synchronize()
+            dist.barrier()  # the ranks finish capturing at different times; the first replay meets on the device
             g.replay()
             torch.cuda.synchronize()
             graph = g
@@ -512,6 +561,7 @@ def run_ours(ns):
                          "sample": "one token: router + decode of 6 experts x 3 projections + SwiGLU path", "parity_gap_vs_gpu": parity_gap},
         "e2e": {"value": round(e2e_value, 1), "unit": UNIT, "h2d_bytes_per_step": batch * HIDDEN * 2, "d2h_bytes_per_step": batch * HIDDEN * 2},
         "batch_sweep": batch_sweep(layer, device, ns.rotation, ns.steps, hbm_gbs) if not ns.no_prefill else None,
+        "residency": residency_leg(layer, device, ns.rotation, ns.steps, hbm_gbs) if not ns.no_prefill else None,
         "prefill": prefill_leg(layer, device) if not ns.no_prefill else None,
         "gpu_launches": layer.launches_per_call * ns.steps, "kernel_path": layer.kernel_path,
         "clocks": clocks.summary(),

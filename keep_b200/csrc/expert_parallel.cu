@@ -136,7 +136,7 @@ __global__ void __launch_bounds__(256) ep_return_peer_kernel(const uint8_t* __re
 // waits for rank w's word in this rank's flags.  The work before the barrier ran in earlier
 // kernels of this stream; the system-scope fences order it before the flag stores and order the
 // peers' work before what follows the barrier here.  The wait is bounded (a few seconds by default).
-constexpr uint32_t EP_WAIT_LIMIT = 1u << 22;
+constexpr uint32_t EP_WAIT_LIMIT = 1u << 23;
 
 __global__ void __launch_bounds__(EP_MAX_WORLD) ep_barrier_kernel(keepvq_ep_peer_args peer) {
   const int w = threadIdx.x;

@@ -73,7 +73,7 @@ extern "C" int keepvq_grouped_projection(const keepvq_grouped_projection_args* a
   if ((rc = fast::group_routes(a.rhs, a.routes, a.slots, many ? fast::PREFILL_GROUP_ROUTES : fast::MAX_GROUP_ROUTES, groups, s))) return rc;
   if ((rc = fast::quantize_rows(a.x, a.x_dtype, a.routes, a.in_dim, a.groups, xq, many, s))) return rc;
   fast::FastProjectionArgs p = {};
-  p.a = {a.codes, a.scales}; p.b = {nullptr, nullptr};
+  p.a = {a.codes, a.scales, nullptr, nullptr}; p.b = {nullptr, nullptr, nullptr, nullptr};
   p.scales_dtype = a.scales_dtype; p.codebook = a.codebook; p.groups_of_routes = groups; p.max_routes = a.routes;
   p.out_dim = a.out_dim; p.in_dim = a.in_dim; p.groups = a.groups; p.x = xq; p.x_zero_row = a.routes; p.x_div = 1;
   p.out = a.out; p.out_dtype = a.out_dtype; p.swiglu_limit = 0.0f; p.route_weight = nullptr;

@@ -439,7 +439,7 @@ __device__ __forceinline__ uint2 lds64(uint32_t addr) {
 // MODE 0 is the product.  The others are measurement aids selected by KEEPVQ_PROJECTION_MODE and
 // their outputs are meaningless: 1 = loads only, 3 = no decode (raw words into the MMA),
 // 4 = no MMA.
-template <int M, int TILES, int MODE>
+template <int M, int TILES, int MODE, bool USE_SIGN_TABLE>
 __device__ __forceinline__ void decode_chunk(uint32_t abs_lane, uint32_t sign_lane, const uint4 (&codes)[M][2 * TILES], uint32_t b_addr,
                                              int (&acc_h)[2][M][TILES][4], int (&acc_l)[2][M][TILES][4]) {
 #pragma unroll
@@ -465,7 +465,7 @@ __device__ __forceinline__ void decode_chunk(uint32_t abs_lane, uint32_t sign_la
           if (MODE == 3) {
             a[half] = sign;
             a[2 + half] = abs_off;
-          } else if ((TABLE_STEPS >> i) & 1u) {
+          } else if (USE_SIGN_TABLE && ((TABLE_STEPS >> i) & 1u)) {
             const uint2 e = lds64(abs_lane + abs_off), x = lds64(sign_lane + (sign << 7));
             a[half] = e.x ^ x.x;
             a[2 + half] = e.y ^ x.y;
@@ -484,13 +484,25 @@ __device__ __forceinline__ void decode_chunk(uint32_t abs_lane, uint32_t sign_la
   }
 }
 
-template <int M, int TILES, int MODE>
+// NESTED: the layer has a residual tier.  The second table then holds the residual codebook
+// instead of the sign masks (the base decode does its signs on the integer pipe in every step),
+// and an item whose slot is hot runs a second pass over the residual's 8-bit codes: one table
+// read per codeword gives the int8 operand 2v directly (no signs, no parity, no offset term).
+template <int M, int TILES, int MODE, bool NESTED>
 __global__ void __launch_bounds__(CK_THREADS, 1) projection_cta_kernel(FastProjectionArgs p) {
   extern __shared__ __align__(16) uint8_t smem[];
   // ---- tables -----------------------------------------------------------------------------
   for (int e = threadIdx.x; e < 768; e += CK_THREADS) {
     uint32_t lo = 0, hi = 0;
-    if (e < 512) {  // abs entry (row e/2, parity e&1): byte j of the low word is table nibble 3-j, of the high word 7-j
+    if (e >= 512 && NESTED) {  // residual entry: byte j of the low word is 2 * v[6 - 2j], of the high word 2 * v[7 - 2j]
+      const uint32_t* row = p.res_table + (e - 512) * 4;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const __half2 pair = *reinterpret_cast<const __half2*>(&row[3 - j]);  // dims 6 - 2j, 7 - 2j
+        lo |= (static_cast<uint32_t>(__float2int_rn(2.0f * __low2float(pair))) & 0xFFu) << (8 * j);
+        hi |= (static_cast<uint32_t>(__float2int_rn(2.0f * __high2float(pair))) & 0xFFu) << (8 * j);
+      }
+    } else if (e < 512) {  // abs entry (row e/2, parity e&1): byte j of the low word is table nibble 3-j, of the high word 7-j
       const uint32_t word = p.codebook[e >> 1], par = e & 1;
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
@@ -598,7 +610,7 @@ __global__ void __launch_bounds__(CK_THREADS, 1) projection_cta_kernel(FastProje
 #pragma unroll
           for (int j = 0; j < 2 * TILES; ++j) acc_h[0][m][j / 2][j & 1] += cur[m][j].x ^ cur[m][j].y ^ cur[m][j].z ^ cur[m][j].w;
       } else {
-        decode_chunk<M, TILES, MODE>(abs_lane, sign_lane, cur, b_base + lane * 16 + c * 8 * 512, acc_h, acc_l);
+        decode_chunk<M, TILES, MODE, !NESTED>(abs_lane, sign_lane, cur, b_base + lane * 16 + c * 8 * 512, acc_h, acc_l);
       }
       const int group = c / chunks_per_group;
       if (c + 1 == n_chunks || (c + 1) / chunks_per_group != group) {
@@ -618,6 +630,87 @@ __global__ void __launch_bounds__(CK_THREADS, 1) projection_cta_kernel(FastProje
       }
     }
     cp_async_wait<0>();
+
+    // ---- the residual of a hot slot: a second pass over its 8-bit codes ---------------------
+    float rpart[M][TILES][4];
+#pragma unroll
+    for (int m = 0; m < M; ++m)
+#pragma unroll
+      for (int tl = 0; tl < TILES; ++tl)
+#pragma unroll
+        for (int r = 0; r < 4; ++r) rpart[m][tl][r] = 0.0f;
+    if (NESTED) {
+      const uint32_t hot = p.hot_of_slot[slot];
+      if (hot != 0xFFFFFFFFu) {
+        const int chunks_per_res_group = n_chunks / static_cast<int>(p.res_groups);
+        const uint8_t* res_ptr[M][2 * TILES];
+#pragma unroll
+        for (int m = 0; m < M; ++m)
+#pragma unroll
+          for (int j = 0; j < 2 * TILES; ++j)
+            res_ptr[m][j] = mats[m].res_codes + (static_cast<int64_t>(hot) * N + min(row0 + 8 * j + g, N - 1)) * cw + t * 8;
+        auto fetch_res = [&](int c) {  // 8 codes of 8 bits per row stream
+          if (c < n_chunks) {
+            const uint32_t dst = ring + (c % CK_STAGES) * STAGE_BYTES;
+#pragma unroll
+            for (int m = 0; m < M; ++m)
+#pragma unroll
+              for (int j = 0; j < 2 * TILES; ++j)
+                asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(dst + (m * 2 * TILES + j) * 512), "l"(res_ptr[m][j] + c * CHUNK_CODES) : "memory");
+          }
+          cp_async_commit();
+        };
+        fetch_res(0);
+        for (int c = 0; c < n_chunks; ++c) {
+          fetch_res(c + 1);
+          cp_async_wait<1>();
+          uint2 cur[M][2 * TILES];
+          const uint32_t src = ring + (c % CK_STAGES) * STAGE_BYTES;
+#pragma unroll
+          for (int m = 0; m < M; ++m)
+#pragma unroll
+            for (int j = 0; j < 2 * TILES; ++j) cur[m][j] = lds64(src + (m * 2 * TILES + j) * 512);
+          const uint32_t b_addr = b_base + lane * 16 + c * 8 * 512;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const uint4 b = lds128(b_addr + i * 512);
+#pragma unroll
+            for (int m = 0; m < M; ++m)
+#pragma unroll
+              for (int tl = 0; tl < TILES; ++tl) {
+                uint32_t a[4];
+#pragma unroll
+                for (int half = 0; half < 2; ++half) {
+                  const uint2 v = cur[m][2 * tl + half];
+                  const uint32_t code = ((i < 4 ? v.x : v.y) >> (8 * (i & 3))) & 0xFFu;
+                  const uint2 e = lds64(sign_lane + (code << 7));  // the second table is the residual codebook here
+                  a[half] = e.x;
+                  a[2 + half] = e.y;
+                }
+                mma_s8s8(acc_h[i & 1][m][tl], a[0], a[1], a[2], a[3], b.x, b.y);
+                mma_s8s8(acc_l[i & 1][m][tl], a[0], a[1], a[2], a[3], b.z, b.w);
+              }
+          }
+          const int group = c / chunks_per_res_group;
+          if (c + 1 == n_chunks || (c + 1) / chunks_per_res_group != group) {
+#pragma unroll
+            for (int m = 0; m < M; ++m)
+#pragma unroll
+              for (int tl = 0; tl < TILES; ++tl)
+#pragma unroll
+                for (int r = 0; r < 4; ++r) {
+                  const int64_t row = min(row0 + 16 * tl + g + (r >= 2 ? 8 : 0), N - 1);
+                  const float sc = load_as_float(mats[m].res_scales, p.scales_dtype, (static_cast<int64_t>(hot) * N + row) * p.res_groups + group);
+                  const int hi = acc_h[0][m][tl][r] + acc_h[1][m][tl][r], lo = acc_l[0][m][tl][r] + acc_l[1][m][tl][r];
+                  rpart[m][tl][r] = fmaf(sc, 256.0f * static_cast<float>(hi) + static_cast<float>(lo), rpart[m][tl][r]);
+                  acc_h[0][m][tl][r] = acc_h[1][m][tl][r] = 0;
+                  acc_l[0][m][tl][r] = acc_l[1][m][tl][r] = 0;
+                }
+          }
+        }
+        cp_async_wait<0>();
+      }
+    }
 
     // ---- epilogue in registers: lane (g, t) holds rows {g, g+8} of each tile, columns {2t, 2t+1}
 #pragma unroll
@@ -642,7 +735,7 @@ __global__ void __launch_bounds__(CK_THREADS, 1) projection_cta_kernel(FastProje
             for (int64_t q = 0; q < p.groups; ++q)
               shift = fmaf(load_as_float(mats[m].scales, p.scales_dtype, (slot * N + row) * p.groups + q),
                            static_cast<float>(p.x.sums[xrow * p.groups + q]), shift);
-            y[m] = xs * (0.5f * part[m][tl][r] + 0.25f * shift);
+            y[m] = xs * (0.5f * (part[m][tl][r] + rpart[m][tl][r]) + 0.25f * shift);  // a residual weight is q / 2 with no offset
           }
           float result;
           if (M == 2) {
@@ -692,16 +785,16 @@ static int launch_projection(const FastProjectionArgs& p, cudaStream_t s) {
   return KEEPVQ_OK;
 }
 
-template <int M, int TILES, int MODE>
+template <int M, int TILES, int MODE, bool NESTED = false>
 static int launch_projection_cta_mode(const FastProjectionArgs& p, cudaStream_t s) {
   constexpr size_t smem = CK_ABS_BYTES + CK_SIGN_BYTES + CK_B_BYTES + CK_WARPS * CK_STAGES * (M * 2 * TILES * 512);
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(projection_cta_kernel<M, TILES, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    cudaError_t e = cudaFuncSetAttribute(projection_cta_kernel<M, TILES, MODE, NESTED>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     if (e != cudaSuccess) return note_cuda_error(e);
     configured = true;
   }
-  projection_cta_kernel<M, TILES, MODE><<<sm_count(), CK_THREADS, smem, s>>>(p);
+  projection_cta_kernel<M, TILES, MODE, NESTED><<<sm_count(), CK_THREADS, smem, s>>>(p);
   KEEPVQ_CHECK_LAUNCH();
   return KEEPVQ_OK;
 }
@@ -718,6 +811,7 @@ static int diagnostic_mode() {
 
 template <int M, int TILES>
 static int launch_projection_cta(const FastProjectionArgs& p, cudaStream_t s) {
+  if (p.res_table) return launch_projection_cta_mode<M, TILES, 0, true>(p, s);
   switch (diagnostic_mode()) {
     case 1: return launch_projection_cta_mode<M, TILES, 1>(p, s);
     case 3: return launch_projection_cta_mode<M, TILES, 3>(p, s);
@@ -730,10 +824,19 @@ static int launch_projection_cta(const FastProjectionArgs& p, cudaStream_t s) {
 // that fit the shared-memory stage?
 static bool many_items(const FastProjectionArgs& p) { return p.max_routes >= 48 && p.in_dim <= 8 * CHUNK_CODES * CK_MAX_CHUNKS; }
 
+// The residual pass lives in the CTA kernel only: a layer with a residual tier needs enough routes
+// for that kernel and residual scale groups that close on chunk boundaries.
+bool residual_supported(int64_t routes, int64_t in_dim, int64_t res_groups) {
+  if (routes < 48 || in_dim > 8 * CHUNK_CODES * CK_MAX_CHUNKS || in_dim % (8 * CHUNK_CODES) != 0 || res_groups <= 0) return false;
+  return (in_dim / (8 * CHUNK_CODES)) % res_groups == 0;
+}
+
 int gate_up(const FastProjectionArgs& p, cudaStream_t s) {
+  if (p.res_table && !many_items(p)) return KEEPVQ_ERR_UNSUPPORTED;
   return many_items(p) ? launch_projection_cta<2, 1>(p, s) : launch_projection<2, 2>(p, s);
 }
 int down(const FastProjectionArgs& p, cudaStream_t s) {
+  if (p.res_table && !many_items(p)) return KEEPVQ_ERR_UNSUPPORTED;
   return many_items(p) ? launch_projection_cta<1, 2>(p, s) : launch_projection<1, 4>(p, s);
 }
 

@@ -37,6 +37,8 @@ struct RouteGroups {
 struct Projection {
   const uint16_t* codes;  // [slots, out_dim, in_dim/8]
   const void* scales;     // [slots, out_dim, groups]
+  const uint8_t* res_codes;  // [hot rows, out_dim, in_dim/8] 8-bit residual codes, or nullptr
+  const void* res_scales;    // [hot rows, out_dim, res_groups]
 };
 
 struct FastProjectionArgs {
@@ -54,10 +56,17 @@ struct FastProjectionArgs {
   void* out;              // [routes, out_dim]
   int32_t out_dtype;
   int64_t max_routes;
+  // nested residual tier (all null / 0 when the layer has none): slot s adds the 8-bit residual of
+  // row hot_of_slot[s] unless that is 0xFFFFFFFF.  res_table is [256][4] fp16 pairs (dims 2k, 2k+1).
+  int64_t res_groups;
+  const uint32_t* hot_of_slot;
+  const uint32_t* res_table;
 };
 
 // True when the shapes fit the tensor-core path (in_dim % 256 == 0, group size % 256 == 0, ...).
 bool shapes_supported(int64_t out_dim, int64_t in_dim, int64_t groups);
+// True when gate_up / down can also add a nested residual with these scale groups to `routes` routes.
+bool residual_supported(int64_t routes, int64_t in_dim, int64_t res_groups);
 
 // planes = false: 16 bytes per codeword (hi 8, lo 8), what the mma.sync kernels read;
 // planes = true: all high bytes [rows + 1, in_dim] then all low bytes, what the tcgen05 kernels copy.

@@ -167,7 +167,12 @@ extern "C" int keepvq_moe_decode_stages(const keepvq_moe_layer_args* args, int32
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int64_t routes = a.tokens * a.top_k;
   const bool residual = a.res_rows > 0 && (a.w1.res_codes || a.w3.res_codes || a.w2.res_codes);
-  const bool tensor_path = a.codebook_all_odd && !residual && fast::shapes_supported(a.inter, a.hidden, a.w1.groups) &&
+  // a residual tier stays on the tensor-core kernels when all three projections carry it and the
+  // call has enough routes for the kernel that holds the residual pass
+  const bool residual_fits = !residual || (a.w1.res_codes && a.w3.res_codes && a.w2.res_codes && a.res_table && a.hot_of_slot &&
+                                           a.w3.res_groups == a.w1.res_groups && fast::residual_supported(routes, a.hidden, a.w1.res_groups) &&
+                                           fast::residual_supported(routes, a.inter, a.w2.res_groups));
+  const bool tensor_path = a.codebook_all_odd && residual_fits && fast::shapes_supported(a.inter, a.hidden, a.w1.groups) &&
                            fast::shapes_supported(a.hidden, a.inter, a.w2.groups);
   int rc = KEEPVQ_OK;
 
@@ -194,7 +199,7 @@ extern "C" int keepvq_moe_decode_stages(const keepvq_moe_layer_args* args, int32
     fast::QuantRows hq = {reinterpret_cast<uint8_t*>(ws + sc.hq), reinterpret_cast<float*>(ws + sc.hscale), reinterpret_cast<int32_t*>(ws + sc.hsums)};
     // many routes per expert: the tcgen05 kernels, which decode a code once per 128 routes
     const int64_t live = a.expected_routes > 0 && a.expected_routes < routes ? a.expected_routes : routes;
-    const bool prefill = live >= PREFILL_MIN_ROUTES && live >= PREFILL_MIN_ROUTES_PER_SLOT * a.slots && fast::prefill_supported(a.inter, a.hidden, a.w1.groups) &&
+    const bool prefill = !residual && live >= PREFILL_MIN_ROUTES && live >= PREFILL_MIN_ROUTES_PER_SLOT * a.slots && fast::prefill_supported(a.inter, a.hidden, a.w1.groups) &&
                          fast::prefill_supported(a.hidden, a.inter, a.w2.groups);
     int32_t* wait_status = reinterpret_cast<int32_t*>(ws + sc.status);
     if (stages & KEEPVQ_STAGE_PREPARE) {
@@ -209,13 +214,15 @@ extern "C" int keepvq_moe_decode_stages(const keepvq_moe_layer_args* args, int32
     p.scales_dtype = a.scales_dtype; p.codebook = a.codebook; p.groups_of_routes = groups; p.max_routes = routes;
     p.out_dtype = a.x_dtype; p.swiglu_limit = a.swiglu_limit; p.route_weight = a.served_weight;
     if (stages & KEEPVQ_STAGE_GATE_UP) {
-      p.a = {a.w1.codes, a.w1.scales}; p.b = {a.w3.codes, a.w3.scales};
+      p.a = {a.w1.codes, a.w1.scales, a.w1.res_codes, a.w1.res_scales}; p.b = {a.w3.codes, a.w3.scales, a.w3.res_codes, a.w3.res_scales};
+      if (residual) { p.res_groups = a.w1.res_groups; p.hot_of_slot = a.hot_of_slot; p.res_table = a.res_table; }
       p.out_dim = a.inter; p.in_dim = a.hidden; p.groups = a.w1.groups; p.x = xq; p.x_zero_row = a.tokens; p.x_div = a.top_k; p.out = ws + sc.h;
       if ((rc = prefill ? fast::prefill_gate_up(p, wait_status, s) : fast::gate_up(p, s))) return rc;
     }
     if (stages & KEEPVQ_STAGE_DOWN) {
       if ((rc = fast::quantize_rows(ws + sc.h, a.x_dtype, routes, a.inter, a.w2.groups, hq, prefill, s))) return rc;
-      p.a = {a.w2.codes, a.w2.scales}; p.b = {nullptr, nullptr};
+      p.a = {a.w2.codes, a.w2.scales, a.w2.res_codes, a.w2.res_scales}; p.b = {nullptr, nullptr, nullptr, nullptr};
+      if (residual) { p.res_groups = a.w2.res_groups; p.hot_of_slot = a.hot_of_slot; p.res_table = a.res_table; }
       p.out_dim = a.hidden; p.in_dim = a.inter; p.groups = a.w2.groups; p.x = hq; p.x_zero_row = routes; p.x_div = 1; p.out = ws + sc.down;
       if ((rc = prefill ? fast::prefill_down(p, wait_status, s) : fast::down(p, s))) return rc;
     }

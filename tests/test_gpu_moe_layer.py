@@ -88,6 +88,36 @@ def test_residency_mask_and_nested_residual(cuda):
     assert (routing.admit.cpu().numpy() >= 0).any(), "seed should produce at least one admission"
 
 
+@pytest.mark.parametrize("tokens", [20, 6])  # 60 routes: the tensor-core kernels with the residual pass; 18 routes: the general kernels
+def test_nested_residual_at_tensor_core_shapes(cuda, tokens):
+    """Half the pool resident, three hot slots with the 8-bit residual, shapes the int8 kernels take."""
+    rng = np.random.default_rng(18)
+    pool, slots, hidden, inter, k = 16, 8, 512, 256, 3
+    cfg = synthetic.layer(seed=16, experts=pool, hidden=hidden, inter=inter)
+    resident = np.sort(rng.choice(pool, slots, replace=False))
+    slot_of = np.full(pool, 0xFFFFFFFF, dtype=np.uint32)
+    slot_of[resident] = rng.permutation(slots).astype(np.uint32)
+    served_bias = np.full(pool, oracle_router.OFF, dtype=np.float32)
+    served_bias[resident] = 0.0
+    expert_of_slot = np.empty(slots, dtype=np.int64)
+    expert_of_slot[slot_of[resident].astype(np.int64)] = resident
+    slot_cfg = dict(cfg)
+    for n in ("w1", "w3", "w2"):
+        slot_cfg[n] = (cfg[n][0][expert_of_slot], cfg[n][1][expert_of_slot])
+    res = synthetic.residual_tier(17, 3, hidden, inter)
+    hot_of_slot = np.full(slots, 0xFFFFFFFF, dtype=np.uint32)
+    hot_of_slot[[0, 3, 7]] = [1, 2, 0]
+    x = synthetic.tokens(19 + tokens, tokens, hidden)
+    layer = build_layer(cuda, slot_cfg, top_k=k, served_bias=served_bias, slot_of=slot_of, hot_of_slot=hot_of_slot, res=res, tau=0.3)
+    assert layer.kernel_path == "tensor"
+    out, routing = layer.decode(x.to(cuda))
+    check_layer(slot_cfg, x, out, routing, top_k=k, served_bias=served_bias, slot_of=slot_of, res=res, hot_of_slot=hot_of_slot, tau=0.3)
+    # the residual does change the answer: without it the same call misses the oracle
+    plain = build_layer(cuda, slot_cfg, top_k=k, served_bias=served_bias, slot_of=slot_of, tau=0.3)
+    base_only, _ = plain.decode(x.to(cuda))
+    assert not torch.equal(base_only, out)
+
+
 def test_fewer_residents_than_top_k_leaves_dead_picks_at_zero(cuda):
     cfg = synthetic.layer(seed=11, experts=6, hidden=128, inter=64)
     served_bias = np.array([0, oracle_router.OFF, oracle_router.OFF, 0, oracle_router.OFF, oracle_router.OFF], dtype=np.float32)
