@@ -594,6 +594,20 @@ __global__ void __launch_bounds__(CK_THREADS, 1) projection_cta_kernel(FastProje
           acc_h[0][m][tl][r] = acc_h[1][m][tl][r] = 0;
           acc_l[0][m][tl][r] = acc_l[1][m][tl][r] = 0;
         }
+    // what the epilogue needs of this lane's two routes (columns 2t, 2t + 1), asked for now so
+    // that the loads fly behind the main loop instead of in front of the stores
+    int ep_route[2];
+    float ep_xs[2], ep_weight[2], ep_sum[2];
+#pragma unroll
+    for (int cc = 0; cc < 2; ++cc) {
+      const int col = 2 * t + cc;
+      ep_route[cc] = col < gsize ? p.groups_of_routes.routes[gstart + col] : -1;
+      const int64_t xrow = ep_route[cc] < 0 ? p.x_zero_row : static_cast<int64_t>(ep_route[cc] / p.x_div);
+      ep_xs[cc] = p.x.scale[xrow];
+      ep_weight[cc] = (M == 2 && ep_route[cc] >= 0) ? p.route_weight[ep_route[cc]] : 1.0f;
+      ep_sum[cc] = static_cast<float>(p.x.sums[xrow * p.groups]);  // the only group when the rows have one scale
+    }
+    float row_scale[M][TILES][4];  // the last scale group's scale of each accumulator row
 
     for (int c = 0; c < n_chunks; ++c) {
       fetch(c + 1);
@@ -624,6 +638,7 @@ __global__ void __launch_bounds__(CK_THREADS, 1) projection_cta_kernel(FastProje
               const float sc = load_as_float(mats[m].scales, p.scales_dtype, (slot * N + row) * p.groups + group);
               const int hi = acc_h[0][m][tl][r] + acc_h[1][m][tl][r], lo = acc_l[0][m][tl][r] + acc_l[1][m][tl][r];
               part[m][tl][r] = fmaf(sc, 256.0f * static_cast<float>(hi) + static_cast<float>(lo), part[m][tl][r]);
+              row_scale[m][tl][r] = sc;
               acc_h[0][m][tl][r] = acc_h[1][m][tl][r] = 0;
               acc_l[0][m][tl][r] = acc_l[1][m][tl][r] = 0;
             }
@@ -715,12 +730,11 @@ __global__ void __launch_bounds__(CK_THREADS, 1) projection_cta_kernel(FastProje
     // ---- epilogue in registers: lane (g, t) holds rows {g, g+8} of each tile, columns {2t, 2t+1}
 #pragma unroll
     for (int cc = 0; cc < 2; ++cc) {
-      const int col = 2 * t + cc;
-      if (col >= gsize) continue;
-      const int route = p.groups_of_routes.routes[gstart + col];
+      const int route = ep_route[cc];
+      if (route < 0) continue;
       const int64_t xrow = route / p.x_div;
-      const float xs = p.x.scale[xrow];
-      const float weight = M == 2 ? p.route_weight[route] : 1.0f;
+      const float xs = ep_xs[cc];
+      const float weight = ep_weight[cc];
 #pragma unroll
       for (int tl = 0; tl < TILES; ++tl)
 #pragma unroll
@@ -731,10 +745,14 @@ __global__ void __launch_bounds__(CK_THREADS, 1) projection_cta_kernel(FastProje
           float y[M];
 #pragma unroll
           for (int m = 0; m < M; ++m) {
-            float shift = 0.0f;
-            for (int64_t q = 0; q < p.groups; ++q)
-              shift = fmaf(load_as_float(mats[m].scales, p.scales_dtype, (slot * N + row) * p.groups + q),
-                           static_cast<float>(p.x.sums[xrow * p.groups + q]), shift);
+            float shift = 0.0f;  // the +-1/4 of every weight, folded into sum(x') per scale group
+            if (p.groups == 1) {
+              shift = row_scale[m][tl][r] * ep_sum[cc];
+            } else {
+              for (int64_t q = 0; q < p.groups; ++q)
+                shift = fmaf(load_as_float(mats[m].scales, p.scales_dtype, (slot * N + row) * p.groups + q),
+                             static_cast<float>(p.x.sums[xrow * p.groups + q]), shift);
+            }
             y[m] = xs * (0.5f * (part[m][tl][r] + rpart[m][tl][r]) + 0.25f * shift);  // a residual weight is q / 2 with no offset
           }
           float result;
