@@ -546,7 +546,12 @@ __global__ void __launch_bounds__(CK_THREADS, 1) projection_cta_kernel(FastProje
   const int items = p.groups_of_routes.count[0] * slabs;
   const Projection mats[2] = {p.a, p.b};
 
-  for (int item = blockIdx.x; item < items; item += gridDim.x) {
+  // A CTA takes a contiguous run of items, so consecutive items mostly belong to one route group
+  // and its activations are staged once for all of them.
+  const int per_cta = (items + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x);
+  const int first_item = blockIdx.x * per_cta, last_item = min(items, first_item + per_cta);
+  int staged_group = -1;
+  for (int item = first_item; item < last_item; ++item) {
     const int gi = item / slabs, slab = item - gi * slabs;
     const int64_t slot = p.groups_of_routes.slot[gi];
     const int gsize = p.groups_of_routes.size[gi], gstart = p.groups_of_routes.start[gi];
@@ -569,17 +574,22 @@ __global__ void __launch_bounds__(CK_THREADS, 1) projection_cta_kernel(FastProje
       cp_async_commit();
     };
 
-    __syncthreads();  // every warp is done with the previous item's activations (and the tables are built)
-    {                 // stage this group's activations in fragment order: [chunk * 8 + step][lane]
-      const int route = g < gsize ? p.groups_of_routes.routes[gstart + g] : -1;
-      const uint4* src = reinterpret_cast<const uint4*>(p.x.q) + (route < 0 ? p.x_zero_row : static_cast<int64_t>(route / p.x_div)) * cw + t * 8;
-      for (int step = warp; step < n_chunks * 8; step += CK_WARPS)
-        cp_async16(b_base + lane * 16 + step * 512, src + (step >> 3) * CHUNK_CODES + (step & 7));
-      cp_async_commit();
+    if (gi != staged_group) {
+      __syncthreads();  // every warp is done with the previous group's activations (and the tables are built)
+      {                 // stage this group's activations in fragment order: [chunk * 8 + step][lane]
+        const int route = g < gsize ? p.groups_of_routes.routes[gstart + g] : -1;
+        const uint4* src = reinterpret_cast<const uint4*>(p.x.q) + (route < 0 ? p.x_zero_row : static_cast<int64_t>(route / p.x_div)) * cw + t * 8;
+        for (int step = warp; step < n_chunks * 8; step += CK_WARPS)
+          cp_async16(b_base + lane * 16 + step * 512, src + (step >> 3) * CHUNK_CODES + (step & 7));
+        cp_async_commit();
+      }
+      fetch(0);
+      cp_async_wait<1>();  // the activations (the older group) have landed
+      __syncthreads();
+      staged_group = gi;
+    } else {
+      fetch(0);
     }
-    fetch(0);
-    cp_async_wait<1>();  // the activations (the older group) have landed
-    __syncthreads();
     if (!active) { cp_async_wait<0>(); continue; }
 
     float part[M][TILES][4];
