@@ -413,7 +413,7 @@ constexpr int CK_B_BYTES = CK_MAX_CHUNKS * 8 * 32 * 16;             // 64 KB
 constexpr int CK_ABS_BYTES = LUT_BYTES;                             // 64 KB: [abs row][parity][replica]
 constexpr int CK_SIGN_BYTES = 256 * LUT_REPLICAS * 8;               // 32 KB: [sign byte][replica]
 constexpr int CK_STAGES = 2;
-constexpr unsigned TABLE_STEPS = 0xAAu;  // bit i set: step i of a chunk decodes through the sign table
+constexpr unsigned TABLE_STEPS = 0xEEu;  // bit i set: step i of a chunk decodes through the sign table
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
