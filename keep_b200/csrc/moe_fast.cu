@@ -548,10 +548,14 @@ __global__ void __launch_bounds__(CK_THREADS, 1) projection_cta_kernel(FastProje
 
   // A CTA takes a contiguous run of items, so consecutive items mostly belong to one route group
   // and its activations are staged once for all of them.
+  // (With a residual tier the items of a hot slot cost half as much again, and a run of them on
+  // one CTA would unbalance the grid: those layers deal the items out round-robin instead.)
   const int per_cta = (items + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x);
-  const int first_item = blockIdx.x * per_cta, last_item = min(items, first_item + per_cta);
+  const int first_item = NESTED ? static_cast<int>(blockIdx.x) : static_cast<int>(blockIdx.x) * per_cta;
+  const int last_item = NESTED ? items : min(items, first_item + per_cta);
+  const int item_step = NESTED ? static_cast<int>(gridDim.x) : 1;
   int staged_group = -1;
-  for (int item = first_item; item < last_item; ++item) {
+  for (int item = first_item; item < last_item; item += item_step) {
     const int gi = item / slabs, slab = item - gi * slabs;
     const int64_t slot = p.groups_of_routes.slot[gi];
     const int gsize = p.groups_of_routes.size[gi], gstart = p.groups_of_routes.start[gi];
