@@ -342,7 +342,8 @@ typedef struct keepvq_residency_args {
   const float* want_score;  /* [tokens, top_k] */
   int64_t tokens;
   int32_t top_k;
-  const uint8_t* landed;    /* [pool] host-written flags */
+  uint8_t* landed;          /* [pool] flags the installer raises when an expert's bytes are in its slot; the
+                               tick that routes the expert clears its flag */
   int64_t call;
   int64_t step;
   float tau;

@@ -58,6 +58,7 @@ __global__ void __launch_bounds__(RT_THREADS) residency_tick_kernel(keepvq_resid
       a.slot_expert[slot] = e;
       a.last_use[slot] = static_cast<double>(a.step);
       a.stats[KEEPVQ_STAT_INSTALLED] += 1;
+      a.landed[e] = 0;  // consumed: a later read of the same expert raises it again
       log_action(a, KEEPVQ_ACTION_ROUTE, e, slot);
     } else {
       a.reading[2 * kept] = e; a.reading[2 * kept + 1] = slot; ++kept;

@@ -84,3 +84,62 @@ class LayerResidency:
             free=self.free_list[: counts[0]].cpu().tolist(), cooling=self.cooling[: counts[1]].cpu().tolist(),
             reading={str(e): s for e, s in self.reading[: counts[2]].cpu().tolist()},
             stats=dict(zip(STAT_NAMES, self.stats.cpu().tolist())))
+
+
+class SlotInstaller:
+    """Carries out the reads the policy admits: an expert's stored bytes go from pinned host
+    memory into its slot's rows of the layer's weight tensors, on a copy stream of their own.
+
+    The reference reads with ``preadv`` into unified memory from reader threads and checks the
+    bytes afterwards (``scripts/v41_build/omlx_routed.py:114-145,218-229``).  Here a read is a
+    handful of ``cudaMemcpyAsync`` calls (one per tensor of the slot) followed, on the same copy
+    stream, by a one-byte store into the policy's ``landed`` flags.  The next policy tick that sees
+    the flag routes the expert, so by stream order its bytes are in place before any kernel can be
+    routed to the slot, and nobody waits for a copy: not the host, not the token path.  Slots are
+    only ever written while unrouted and cooled (the policy hands out free slots, and frees an
+    evicted slot only after the calls that could still read it).
+
+    ``store`` maps a tensor name (``w1_codes``, ``w1_scales``, ... ``w2_scales``) to a pinned host
+    tensor ``[pool, ...]``; ``weights`` maps the same names to the layer's device tensors
+    ``[slots, ...]``.
+    """
+
+    NAMES = tuple(f"{p}_{f}" for p in ("w1", "w3", "w2") for f in ("codes", "scales"))
+
+    def __init__(self, residency: LayerResidency, store: dict, weights: dict):
+        self.residency, self.store, self.weights = residency, store, weights
+        for name in self.NAMES:
+            host, dev = store[name], weights[name]
+            if not host.is_pinned():
+                raise ValueError(f"store[{name!r}] must be pinned host memory")
+            if tuple(host.shape[1:]) != tuple(dev.shape[1:]) or host.dtype != dev.dtype:
+                raise ValueError(f"store[{name!r}] rows do not match the layer's {name}")
+        self.stream = torch.cuda.Stream(device=residency.device)
+        self._one = torch.ones(1, dtype=torch.uint8).pin_memory()
+        self.bytes_copied = 0
+
+    def execute(self, actions) -> int:
+        """Start the read of every ``("admit", expert, slot)`` in ``actions`` (what
+        ``LayerResidency.drain_actions`` returns).  Returns the number of reads started."""
+        started = 0
+        # the reads may only start once the tick that admitted them (and the kernels before it) has run
+        self.stream.wait_stream(torch.cuda.current_stream(self.residency.device))
+        with torch.cuda.stream(self.stream):
+            for kind, expert, slot in actions:
+                if kind != "admit":
+                    continue
+                for name in self.NAMES:
+                    self.weights[name][slot].copy_(self.store[name][expert], non_blocking=True)
+                    self.bytes_copied += self.store[name][expert].numel() * self.store[name].element_size()
+                self.residency.landed[expert : expert + 1].copy_(self._one, non_blocking=True)
+                started += 1
+        return started
+
+    def differing(self, slot: int) -> int:
+        """Tensors of a routed slot whose bytes differ from its expert's stored bytes
+        (``omlx_routed.py:138-145``).  Synchronises; for checks, not the token path."""
+        expert = int(self.residency.slot_expert[slot].item())
+        if expert < 0:
+            return 0
+        self.stream.synchronize()
+        return sum(not torch.equal(self.weights[name][slot].cpu(), self.store[name][expert]) for name in self.NAMES)

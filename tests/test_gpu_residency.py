@@ -63,3 +63,63 @@ def test_tau_infinity_keeps_the_starting_set(cuda):
     snap = state.snapshot()
     assert snap["slot_expert"] == list(range(6)) and not snap["reading"] and not snap["cooling"]
     assert snap["stats"]["admitted"] == 0 and snap["stats"]["evicted"] == 0 and snap["stats"]["calls"] == 3
+
+
+def test_decode_loop_with_admissions_and_installs(cuda):
+    """The whole routed-residency cycle on one layer: decode calls serve the resident half of the
+    pool, the policy kernel admits strongly demanded absent experts, the installer copies their
+    bytes from pinned host memory into free slots on its own stream and raises the landed flag,
+    a later tick routes them, and later calls serve them.  Every call's output must equal the
+    oracle's for the experts that call actually served, every routed slot must hold its expert's
+    stored bytes, and nothing but the action drain reads the device."""
+    import synthetic
+    from keep_b200 import moe, residency
+    from keep_b200.router import OFF
+    from oracle import e8, router as oracle_router
+
+    pool, slots, hidden, inter, k, tokens = 16, 10, 512, 256, 2, 4
+    cfg = synthetic.layer(seed=90, experts=pool, hidden=hidden, inter=inter)
+    start = list(range(6))                                 # experts 0..5 resident in slots 0..5, slots 6..9 free
+    names = residency.SlotInstaller.NAMES
+    full = {f"{p}_{f}": torch.from_numpy(cfg[p][i]) for p in ("w1", "w3", "w2") for i, f in enumerate(("codes", "scales"))}
+    store = {n: full[n].pin_memory() for n in names}
+    weights = {n: torch.zeros((slots,) + tuple(full[n].shape[1:]), dtype=full[n].dtype, device=cuda) for n in names}
+    for n in names:
+        weights[n][: len(start)] = full[n][start].to(cuda)
+    state = residency.LayerResidency(start + [-1] * (slots - len(start)), [-1.0 - r for r in range(slots)], pool, device=cuda,
+                                     tau=0.3, spare=1, top_k=k)
+    # the starting free list: slots 6..9
+    state.free_list[: slots - len(start)] = torch.arange(len(start), slots, dtype=torch.int32, device=cuda)
+    state.counts[0] = slots - len(start)
+    layer = moe.RoutedMoELayer(cfg["router"].to(cuda), moe.Projection(weights["w1_codes"], weights["w1_scales"]),
+                               moe.Projection(weights["w3_codes"], weights["w3_scales"]),
+                               moe.Projection(weights["w2_codes"], weights["w2_scales"]), top_k=k, tau=0.3,
+                               served_bias=state.served_bias, slot_of=state.slot_of)
+    layer.served_bias, layer.slot_of = state.served_bias, state.slot_of  # the very tensors the policy updates
+    installer = residency.SlotInstaller(state, store, weights)
+    dense = {p: oracle_router.dense_slots(*cfg[p], range(pool)) for p in ("w1", "w3", "w2")}  # every expert, by expert id
+
+    served_after_install, installed = 0, set()
+    for step in range(1, 15):
+        x = synthetic.tokens(900 + step, tokens, hidden)
+        out, routing = layer.decode(x.to(cuda))
+        served_expert = routing.served_expert.cpu().numpy().astype(np.int64)
+        served_slot = routing.served_slot.cpu().numpy().astype(np.int64)
+        weight = routing.served_weight.cpu().numpy()
+        slot_expert = state.slot_expert.cpu().numpy()
+        live = served_expert >= 0
+        assert (slot_expert[served_slot[live]] == served_expert[live]).all()        # routed where the policy says
+        served_after_install += int(np.isin(served_expert[live], list(installed)).sum())
+        ref = oracle_router.moe_layer(x, np.where(live, served_expert, -1), weight, dense["w1"], dense["w3"], dense["w2"])
+        assert e8.relative_gap(out.float().cpu().numpy(), ref.numpy()) <= 1e-2
+        state.tick(routing.want, routing.want_score, call=step, step=step + 1, first_layer=True)
+        actions = state.drain_actions()
+        installed |= {e for kind, e, _ in actions if kind == "route"}
+        installer.execute(actions)
+        for slot in range(slots):                                                  # the reference's byte check
+            assert installer.differing(slot) == 0
+    snap = state.snapshot()
+    assert snap["stats"]["admitted"] >= 2 and snap["stats"]["installed"] >= 2, snap["stats"]
+    assert served_after_install > 0, "no installed expert was served afterwards"
+    absent = np.setdiff1d(np.arange(pool), [e for e in snap["slot_expert"] if e >= 0])
+    assert (state.served_bias.cpu().numpy()[absent] == np.float32(OFF)).all()
