@@ -452,7 +452,7 @@ int keepvq_ep_combine(const keepvq_ep_combine_args* args, void* stream);
  *
  * keepvq_ep_dispatch_peer  the plan of keepvq_ep_pack, with rows, slots and weights stored
  *                          directly at row (rank * capacity + pos) of the destination rank's
- *                          recv_x / recv_meta, then a barrier: when the call's work is done on
+ *                          recv_x / recv_meta (slot and weight planes), then a barrier: when the call's work is done on
  *                          this rank's stream, every rank's rows for it have landed.
  * keepvq_ep_return_peer    row r of y (a live route received from rank r / capacity) goes to row
  *                          (rank * capacity + r % capacity) of that rank's `back`, then a barrier;
@@ -467,7 +467,9 @@ typedef struct keepvq_ep_peer_args {
   int64_t capacity;             /* rows per (source, destination) block */
   int64_t row_bytes;            /* multiple of 16 */
   void* const* recv_x;          /* device array [world]: each rank's [world * capacity, row_bytes] */
-  int32_t* const* recv_meta;    /* device array [world]: each rank's [world * capacity, 2] */
+  int32_t* const* recv_meta;    /* device array [world]: each rank's [2, world * capacity]: local slots (-1 = no
+                                   route), then the bits of the routes' weights; the two planes can be handed to
+                                   keepvq_moe_decode_stages as served_slot and served_weight as they are */
   void* const* back;            /* device array [world]: each rank's [world * capacity, row_bytes] */
   int32_t* const* flags;        /* device array [world]: each rank's [world] arrival words, zero at start */
   int32_t* epoch;               /* [1] this rank's barrier count, zero at start */

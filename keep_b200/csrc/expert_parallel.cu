@@ -69,9 +69,9 @@ __global__ void __launch_bounds__(EP_PLAN_THREADS) ep_plan_peer_kernel(keepvq_ep
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int64_t rows = static_cast<int64_t>(a.world) * a.capacity, routes = a.tokens * a.top_k;
   for (int64_t i = tid; i < rows; i += EP_PLAN_THREADS) {  // my block in every rank's table: empty
-    int32_t* meta = peer.recv_meta[i / a.capacity] + 2 * (static_cast<int64_t>(peer.rank) * a.capacity + i % a.capacity);
-    meta[0] = -1;
-    meta[1] = 0;
+    int32_t* meta = peer.recv_meta[i / a.capacity] + static_cast<int64_t>(peer.rank) * a.capacity + i % a.capacity;
+    meta[0] = -1;   // slot plane
+    meta[rows] = 0; // weight plane
   }
   if (tid < a.world) base[tid] = 0;
   __threadfence_system();
@@ -95,9 +95,9 @@ __global__ void __launch_bounds__(EP_PLAN_THREADS) ep_plan_peer_kernel(keepvq_ep
         for (int i = 0; i < warp; ++i) slot += warp_count[i][dest];
         if (slot < a.capacity) {
           pos = static_cast<int64_t>(dest) * a.capacity + slot;
-          int32_t* meta = peer.recv_meta[dest] + 2 * (static_cast<int64_t>(peer.rank) * a.capacity + slot);
+          int32_t* meta = peer.recv_meta[dest] + static_cast<int64_t>(peer.rank) * a.capacity + slot;
           meta[0] = static_cast<int32_t>(e % a.experts_per_rank);
-          meta[1] = __float_as_int(a.served_weight[r]);
+          meta[rows] = __float_as_int(a.served_weight[r]);
         }
       }
       a.position[r] = static_cast<int32_t>(pos);
@@ -125,7 +125,7 @@ __global__ void __launch_bounds__(256) ep_copy_peer_kernel(keepvq_ep_pack_args a
 // Row r of y, if it is a live route, back to the rank it came from.
 __global__ void __launch_bounds__(256) ep_return_peer_kernel(const uint8_t* __restrict__ y, keepvq_ep_peer_args peer) {
   const int64_t r = blockIdx.x;
-  if (peer.recv_meta[peer.rank][2 * r] < 0) return;
+  if (peer.recv_meta[peer.rank][r] < 0) return;
   const int64_t src_rank = r / peer.capacity, slot = r % peer.capacity;
   const uint4* src = reinterpret_cast<const uint4*>(y + r * peer.row_bytes);
   uint4* dst = reinterpret_cast<uint4*>(static_cast<uint8_t*>(peer.back[src_rank]) + (static_cast<int64_t>(peer.rank) * peer.capacity + slot) * peer.row_bytes);

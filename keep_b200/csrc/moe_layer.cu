@@ -90,16 +90,18 @@ __global__ void __launch_bounds__(256) swiglu_weight_kernel(const T* __restrict_
   }
 }
 
-// out[t, d] = round(sum_j float(down[t*k + j, d])), summed in pick order.
+// out[t, d] = round(sum_j float(down[t*k + j, d])), summed in pick order.  A pick without a slot
+// adds nothing (the grouped kernels never touch its row of `down`).
 template <typename T>
-__global__ void __launch_bounds__(256) combine_kernel(const T* __restrict__ down, T* __restrict__ out, int64_t tokens,
-                                                      int64_t hidden, int top_k) {
+__global__ void __launch_bounds__(256) combine_kernel(const T* __restrict__ down, const uint32_t* __restrict__ served_slot, int64_t slots,
+                                                      T* __restrict__ out, int64_t tokens, int64_t hidden, int top_k) {
   constexpr int tag = dtype_tag_of<T>::value;
   const int64_t total = tokens * hidden;
   for (int64_t i = blockIdx.x * 256ll + threadIdx.x; i < total; i += 256ll * gridDim.x) {
     const int64_t t = i / hidden, d = i - t * hidden;
     float y = 0.0f;
-    for (int j = 0; j < top_k; ++j) y += load_as_float(down, tag, (t * top_k + j) * hidden + d);
+    for (int j = 0; j < top_k; ++j)
+      if (served_slot[t * top_k + j] < static_cast<uint64_t>(slots)) y += load_as_float(down, tag, (t * top_k + j) * hidden + d);
     store_from_float(out, tag, i, y);
   }
 }
@@ -116,7 +118,7 @@ static void launch_elementwise(const keepvq_moe_layer_args& a, const LayerScratc
   } else {
     const int64_t total = a.tokens * a.hidden;
     const unsigned blocks = static_cast<unsigned>(std::min<int64_t>((total + 255) / 256, 148 * 16));
-    combine_kernel<T><<<blocks, 256, 0, s>>>(reinterpret_cast<const T*>(ws + sc.down), reinterpret_cast<T*>(a.out), a.tokens, a.hidden, a.top_k);
+    combine_kernel<T><<<blocks, 256, 0, s>>>(reinterpret_cast<const T*>(ws + sc.down), a.served_slot, a.slots, reinterpret_cast<T*>(a.out), a.tokens, a.hidden, a.top_k);
   }
 }
 

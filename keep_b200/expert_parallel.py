@@ -192,7 +192,7 @@ class PeerExchange:
             return t, handle
 
         self.recv_x, hx = shared((rows, hidden), dtype)
-        self.recv_meta, hm = shared((rows, 2), torch.int32)
+        self.recv_meta, hm = shared((2, rows), torch.int32)  # slot plane, weight plane
         self.back, hb = shared((rows, hidden), dtype)
         self.flags, hf = shared((max(self.world, 32),), torch.int32)
         self._handles = (hx, hm, hb, hf)  # keep the mappings alive
@@ -222,7 +222,7 @@ class PeerExchange:
                                capacity=self.capacity, send_x=None, send_meta=None, position=_lib.ptr(self.position))
         with torch.cuda.device(x.device):
             _lib.check(_lib.load().keepvq_ep_dispatch_peer(args, self._peer, _lib.stream_handle(x.device)), "keepvq_ep_dispatch_peer")
-        return self.recv_x, self.recv_meta[:, 0], self.recv_meta[:, 1].view(torch.float32), self.position
+        return self.recv_x, self.recv_meta[0], self.recv_meta[1].view(torch.float32), self.position
 
     def combine(self, y_routes: torch.Tensor, position: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
         from . import _lib
@@ -268,8 +268,11 @@ class ExpertParallelLayer:
         recv_x, recv_slot, recv_weight, position = self.exchange.dispatch(x, routing.served_expert, routing.served_weight)
         buf = self.local._buffers_for(int(recv_x.shape[0]), recv_x.dtype)
         r = buf["routing"]
-        r.served_slot.copy_(recv_slot.reshape(-1, 1))
-        r.served_weight.copy_(recv_weight.reshape(-1, 1))
+        if recv_slot.is_contiguous() and recv_weight.is_contiguous():  # the peer exchange: the local layer reads the planes in place
+            r.served_slot, r.served_weight = recv_slot.reshape(-1, 1), recv_weight.reshape(-1, 1)
+        else:
+            r.served_slot.copy_(recv_slot.reshape(-1, 1))
+            r.served_weight.copy_(recv_weight.reshape(-1, 1))
         # by symmetry a rank receives about as many live routes as it sends; the rest of its rows are padding
         y, _ = self.local.decode(recv_x, stages=_lib.STAGE_ALL & ~_lib.STAGE_ROUTER, expected_routes=int(x.shape[0]) * self.top_k)
         return self.exchange.combine(y, position, x.dtype)

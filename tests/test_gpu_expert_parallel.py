@@ -121,7 +121,7 @@ def test_peer_barrier_gives_up_when_a_peer_never_arrives(cuda):
     experts = torch.randint(0, world * per_rank, (tokens, k), generator=gen, dtype=torch.int32).to(cuda)
     weights = torch.rand((tokens, k), generator=gen).to(cuda)
     make = lambda shape, dt: [torch.zeros(shape, dtype=dt, device=cuda) for _ in range(world)]  # noqa: E731
-    recv_x, recv_meta, back, flags = make((rows, hidden), torch.bfloat16), make((rows, 2), torch.int32), make((rows, hidden), torch.bfloat16), make((32,), torch.int32)
+    recv_x, recv_meta, back, flags = make((rows, hidden), torch.bfloat16), make((2, rows), torch.int32), make((rows, hidden), torch.bfloat16), make((32,), torch.int32)
     table = lambda ts: torch.tensor([t.data_ptr() for t in ts], dtype=torch.int64, device=cuda)  # noqa: E731
     tables = [table(ts) for ts in (recv_x, recv_meta, back, flags)]
     epoch, status = torch.zeros(1, dtype=torch.int32, device=cuda), torch.zeros(1, dtype=torch.int32, device=cuda)
@@ -138,5 +138,5 @@ def test_peer_barrier_gives_up_when_a_peer_never_arrives(cuda):
     for r in range(tokens * k):                                          # the rows did land where the plan says
         dest, slot = divmod(int(pos[r]), capacity)
         assert torch.equal(recv_x[dest][slot].cpu(), x[r // k].cpu())    # rank 0's block is the first of each table
-        assert int(recv_meta[dest][slot][0]) == int(experts.reshape(-1)[r]) % per_rank
+        assert int(recv_meta[dest][0][slot]) == int(experts.reshape(-1)[r]) % per_rank
     assert torch.equal((x.float() * 2).cpu(), x.float().cpu() * 2)        # the context still answers

@@ -128,6 +128,24 @@ def test_fewer_residents_than_top_k_leaves_dead_picks_at_zero(cuda):
     check_layer(cfg, x, out, routing, top_k=3, served_bias=served_bias, slot_of=np.arange(6))
 
 
+@pytest.mark.parametrize("tokens", [3, 30, 400])  # the small-batch kernel, the CTA kernel, the tcgen05 kernel
+def test_dead_picks_at_tensor_core_shapes(cuda, tokens):
+    """Two residents, top-3: every token has a pick without a slot, which must add nothing,
+    whichever of the grouped kernels runs (they never touch the rows of such routes)."""
+    cfg = synthetic.layer(seed=13, experts=6, hidden=512, inter=256)
+    served_bias = np.array([0, oracle_router.OFF, oracle_router.OFF, 0, oracle_router.OFF, oracle_router.OFF], dtype=np.float32)
+    x = synthetic.tokens(14 + tokens, tokens, 512)
+    layer = build_layer(cuda, cfg, top_k=3, served_bias=served_bias, slot_of=np.arange(6, dtype=np.uint32))
+    assert layer.kernel_path == "tensor"
+    # poison the scratch so that an untouched row cannot pass as zeros by luck
+    layer.decode(x.to(cuda))
+    for buf in layer._buffers.values():
+        buf["workspace"].fill_(0x7F)
+    out, routing = layer.decode(x.to(cuda))
+    assert ((routing.served_slot.cpu().numpy() >= 0).sum(-1) == 2).all()
+    check_layer(cfg, x, out, routing, top_k=3, served_bias=served_bias, slot_of=np.arange(6))
+
+
 @pytest.mark.parametrize("tokens,experts,top_k,group", [(3, 12, 3, None), (20, 4, 3, 256), (9, 6, 2, 256)])
 def test_tensor_core_path_small_shapes(cuda, tokens, experts, top_k, group):
     """Shapes the int8 tensor-core kernels accept (input dims multiples of 256), with grouped scales
