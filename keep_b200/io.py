@@ -1,0 +1,103 @@
+"""Readers for the layer files the routed path is served from.
+
+The reference writes one ``layer-NN.npz`` per MoE layer: an uncompressed zip of
+``{w1,w2,w3}_codes`` (uint16 ``[E, out, in/8]``, uint8 for 1-bit codes), ``{w1,w2,w3}_scales``
+(fp16 ``[E, out, in/g]``) and ``code_bits`` (``scripts/runpod/v41_reap/keep_quant.py:16-19,131-133``),
+and serves from it with positional reads of one expert's slab at a time
+(``scripts/v41_build/omlx_lattice.py:115-150``).
+
+``LayerFile`` finds each array inside the zip once and then hands out experts as views of a memory
+map (no decompression, no whole-file read): the bytes an installer copies into a slot are the
+file's own bytes.  ``store`` materialises the whole layer in (pinned) host memory for
+``residency.SlotInstaller``; ``projection`` builds the device tensors of the resident slots.
+"""
+
+from __future__ import annotations
+
+import io
+import struct
+import zipfile
+from pathlib import Path
+
+import numpy as np
+import torch
+
+TENSOR_NAMES = tuple(f"{p}_{f}" for p in ("w1", "w3", "w2") for f in ("codes", "scales"))
+
+
+class LayerFile:
+    """One ``layer-NN.npz``.  ``members[name] = (byte offset of the array data, shape, dtype)``."""
+
+    def __init__(self, path):
+        self.path = Path(path)
+        self.members: dict[str, tuple[int, tuple, np.dtype]] = {}
+        with zipfile.ZipFile(self.path) as archive, open(self.path, "rb") as raw:
+            for info in archive.infolist():
+                if info.compress_type != zipfile.ZIP_STORED:
+                    raise ValueError(f"{self.path}: member {info.filename} is compressed; the serving path needs stored arrays (np.savez)")
+                # local file header: 30 fixed bytes, then the name and the extra field
+                raw.seek(info.header_offset)
+                fixed = raw.read(30)
+                if fixed[:4] != b"PK\x03\x04":
+                    raise ValueError(f"{self.path}: bad local header for {info.filename}")
+                name_len, extra_len = struct.unpack("<HH", fixed[26:30])
+                data_start = info.header_offset + 30 + name_len + extra_len
+                raw.seek(data_start)
+                head = io.BytesIO(raw.read(min(info.file_size, 4096)))
+                version = np.lib.format.read_magic(head)
+                reader = np.lib.format.read_array_header_1_0 if version[0] == 1 else np.lib.format.read_array_header_2_0
+                shape, fortran, dtype = reader(head)
+                if fortran:
+                    raise ValueError(f"{self.path}: {info.filename} is stored in Fortran order")
+                self.members[info.filename.removesuffix(".npy")] = (data_start + head.tell(), tuple(shape), np.dtype(dtype))
+        missing = [n for n in TENSOR_NAMES if n not in self.members]
+        if missing:
+            raise ValueError(f"{self.path}: missing arrays {missing}")
+        self.code_bits = int(self.array("code_bits")) if "code_bits" in self.members else (16 if self.members["w1_codes"][2] == np.uint16 else 8)
+        self.experts = int(self.members["w1_codes"][1][0])
+
+    def array(self, name: str) -> np.ndarray:
+        """The whole array as a read-only memory map of the file."""
+        offset, shape, dtype = self.members[name]
+        if not shape:
+            return np.fromfile(self.path, dtype=dtype, count=1, offset=offset)[0]
+        return np.memmap(self.path, dtype=dtype, mode="r", offset=offset, shape=shape)
+
+    def slab(self, name: str, expert: int) -> tuple[int, int]:
+        """(byte offset in the file, byte count) of one expert's rows of ``name``."""
+        offset, shape, dtype = self.members[name]
+        if not 0 <= expert < shape[0]:
+            raise IndexError(f"expert {expert} outside 0..{shape[0] - 1}")
+        size = int(np.prod(shape[1:], dtype=np.int64)) * dtype.itemsize
+        return offset + expert * size, size
+
+    def read(self, name: str, experts) -> np.ndarray:
+        """``[len(experts), ...]``: the named array's rows of those experts, copied out of the map."""
+        view = self.array(name)
+        return np.stack([np.asarray(view[int(e)]) for e in experts]) if len(experts) else np.empty((0,) + view.shape[1:], view.dtype)
+
+
+def _torch_dtype(dtype: np.dtype) -> torch.dtype:
+    return {np.dtype(np.uint16): torch.uint16, np.dtype(np.uint8): torch.uint8, np.dtype(np.float16): torch.float16,
+            np.dtype(np.float32): torch.float32}[np.dtype(dtype)]
+
+
+def store(layer: LayerFile, *, pin: bool = True) -> dict[str, torch.Tensor]:
+    """Every expert of the layer in host memory, by tensor name: what ``SlotInstaller`` copies
+    from.  ``pin=True`` (needs a CUDA runtime) makes the copies asynchronous."""
+    out = {}
+    for name in TENSOR_NAMES:
+        view = layer.array(name)
+        host = torch.empty(tuple(view.shape), dtype=_torch_dtype(view.dtype), pin_memory=pin)
+        host.numpy()[...] = view
+        out[name] = host
+    return out
+
+
+def projection(layer: LayerFile, which: str, experts, device):
+    """``moe.Projection`` holding the given experts' rows of ``w1`` / ``w3`` / ``w2`` in slot order."""
+    from .moe import Projection
+
+    codes = torch.from_numpy(layer.read(f"{which}_codes", experts)).to(device)
+    scales = torch.from_numpy(layer.read(f"{which}_scales", experts)).to(device)
+    return Projection(codes, scales)

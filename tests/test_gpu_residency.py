@@ -123,3 +123,44 @@ def test_decode_loop_with_admissions_and_installs(cuda):
     assert served_after_install > 0, "no installed expert was served afterwards"
     absent = np.setdiff1d(np.arange(pool), [e for e in snap["slot_expert"] if e >= 0])
     assert (state.served_bias.cpu().numpy()[absent] == np.float32(OFF)).all()
+
+
+def test_layer_served_from_a_layer_file(cuda, tmp_path):
+    """layer-NN.npz -> resident slots on the device and a pinned store for the installer: a decode
+    call over tensors loaded that way equals the oracle on the file's arrays, and an install copies
+    exactly the file's bytes of that expert."""
+    import synthetic
+    from keep_b200 import io as layer_io, moe, residency
+    from oracle import e8, router as oracle_router
+
+    pool, hidden, inter, k = 8, 512, 256, 2
+    cfg = synthetic.layer(seed=95, experts=pool, hidden=hidden, inter=inter)
+    path = tmp_path / "layer-00.npz"
+    np.savez(path, code_bits=np.asarray(16), **{f"{p}_{f}": cfg[p][i] for p in ("w1", "w3", "w2") for i, f in enumerate(("codes", "scales"))})
+    layer_file = layer_io.LayerFile(path)
+    residents = [5, 2, 7, 0]                                    # slot s holds expert residents[s]; two more slots stay free
+    slots = len(residents) + 2
+    weights = {}
+    for p in ("w1", "w3", "w2"):
+        proj = layer_io.projection(layer_file, p, residents, cuda)
+        for f, t in (("codes", proj.codes), ("scales", proj.scales)):
+            weights[f"{p}_{f}"] = torch.cat([t, torch.zeros((2,) + tuple(t.shape[1:]), dtype=t.dtype, device=cuda)])
+    state = residency.LayerResidency(residents + [-1, -1], [-1.0] * slots, pool, device=cuda, top_k=k)
+    layer = moe.RoutedMoELayer(cfg["router"].to(cuda), *(moe.Projection(weights[f"{p}_codes"], weights[f"{p}_scales"]) for p in ("w1", "w3", "w2")),
+                               top_k=k, served_bias=state.served_bias, slot_of=state.slot_of)
+    x = synthetic.tokens(96, 5, hidden)
+    out, routing = layer.decode(x.to(cuda))
+    experts = routing.served_expert.cpu().numpy().astype(np.int64)
+    assert np.isin(experts, residents).all()
+    dense = {p: oracle_router.dense_slots(*cfg[p], range(pool)) for p in ("w1", "w3", "w2")}
+    ref = oracle_router.moe_layer(x, experts, routing.served_weight.cpu().numpy(), dense["w1"], dense["w3"], dense["w2"])
+    assert e8.relative_gap(out.float().cpu().numpy(), ref.numpy()) <= 1e-2
+    installer = residency.SlotInstaller(state, layer_io.store(layer_file), weights)
+    assert installer.execute([("admit", 3, 4)]) == 1
+    installer.stream.synchronize()
+    assert int(state.landed[3].item()) == 1
+    for name in residency.SlotInstaller.NAMES:
+        offset, size = layer_file.slab(name, 3)
+        with open(path, "rb") as f:
+            f.seek(offset)
+            assert weights[name][4].cpu().numpy().tobytes() == f.read(size)

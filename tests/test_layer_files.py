@@ -1,0 +1,52 @@
+"""Layer files (layer-NN.npz): members found inside the stored zip, slabs at the right bytes,
+compressed files refused.  CPU only."""
+
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from keep_b200 import io as layer_io
+
+
+def write_layer(path, experts=5, out=6, inp=64, code_bits=16, compressed=False):
+    rng = np.random.default_rng(3)
+    arrays = {"code_bits": np.asarray(code_bits)}
+    for p, (o, i) in (("w1", (out, inp)), ("w3", (out, inp)), ("w2", (inp, out * 8))):
+        arrays[f"{p}_codes"] = rng.integers(0, 1 << code_bits, (experts, o, i // 8)).astype(np.uint16 if code_bits == 16 else np.uint8)
+        arrays[f"{p}_scales"] = rng.uniform(0.01, 0.05, (experts, o, 1)).astype(np.float16)
+    (np.savez_compressed if compressed else np.savez)(path, **arrays)
+    return arrays
+
+
+@pytest.mark.parametrize("code_bits", [16, 8])
+def test_members_slabs_and_reads(tmp_path, code_bits):
+    path = tmp_path / "layer-03.npz"
+    arrays = write_layer(path, code_bits=code_bits)
+    layer = layer_io.LayerFile(path)
+    assert layer.code_bits == code_bits and layer.experts == 5
+    fd = os.open(path, os.O_RDONLY)
+    try:
+        for name in layer_io.TENSOR_NAMES:
+            np.testing.assert_array_equal(np.asarray(layer.array(name)), arrays[name])
+            for expert in (0, 3, 4):  # a positional read of the slab gives exactly that expert's bytes
+                offset, size = layer.slab(name, expert)
+                assert os.pread(fd, size, offset) == arrays[name][expert].tobytes()
+            np.testing.assert_array_equal(layer.read(name, [4, 1]), arrays[name][[4, 1]])
+    finally:
+        os.close(fd)
+    with pytest.raises(IndexError):
+        layer.slab("w1_codes", 5)
+    host = layer_io.store(layer, pin=False)
+    assert set(host) == set(layer_io.TENSOR_NAMES) and host["w2_codes"].dtype == (torch.uint16 if code_bits == 16 else torch.uint8)
+    np.testing.assert_array_equal(host["w3_scales"].numpy(), arrays["w3_scales"])
+
+
+def test_compressed_and_incomplete_files_are_refused(tmp_path):
+    write_layer(tmp_path / "c.npz", compressed=True)
+    with pytest.raises(ValueError, match="compressed"):
+        layer_io.LayerFile(tmp_path / "c.npz")
+    np.savez(tmp_path / "m.npz", w1_codes=np.zeros((2, 2, 2), np.uint16))
+    with pytest.raises(ValueError, match="missing arrays"):
+        layer_io.LayerFile(tmp_path / "m.npz")
