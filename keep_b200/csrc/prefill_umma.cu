@@ -38,6 +38,7 @@ constexpr int PF_EPI_WARPS = 4;
 constexpr int PF_THREADS = (PF_DECODE_WARPS + 1 + PF_B_WARPS + PF_EPI_WARPS) * 32;  // 512
 constexpr int PF_A_STAGES = 2;
 constexpr int PF_B_STAGES = 4;
+constexpr int PF_B_LAG = 2;                     // K blocks of activation copies in flight behind the one being published
 constexpr int PF_N_MAX = PREFILL_GROUP_ROUTES;  // routes per item
 constexpr int PF_ROWS = 128;                    // output rows per item
 constexpr int PF_KBLOCK_CODES = 16;             // codewords of a row per K block = 128 bytes of int8
@@ -190,7 +191,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_projection_kernel(FastP
       constexpr int RING = PF_CODE_RING_BYTES / (M * 256 * 16);
       const uint32_t ring = smem_base + A_BYTES + B_BYTES + PF_TABLE_BYTES + tid * 16;
       auto fetch = [&](int kb) {
-        if (kb < k_blocks) {
+        if (kb < k_blocks && diag != 5) {
 #pragma unroll
           for (int m = 0; m < M; ++m) cp_async16_pf(ring + ((kb % RING) * M + m) * (256 * 16), src[m] + kb * PF_KBLOCK_CODES);
         }
@@ -266,7 +267,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_projection_kernel(FastP
     } else if (warp < PF_DECODE_WARPS + 1 + PF_B_WARPS) {
       // ================= activation (B operand) loaders =======================================
       // cp.async straight into the swizzled tiles (16 bytes = two codewords of one route); a K
-      // block is published when its copies have landed, up to three later ones already in flight.
+      // block is published when its copies have landed, two later ones already in flight.
       // A thread keeps one (chunk, plane) and every sixth route: sources and destinations are
       // worked out once per item, a K block then costs an add and a copy per route.
       const int loader = tid - (PF_DECODE_WARPS + 1) * 32;  // 0..95
@@ -300,14 +301,17 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_projection_kernel(FastP
         for (int i = 0; i < SLOTS; ++i)
           if (n0 + i * (PF_B_WARPS * 2) < n_pad && diag != 3) cp_async16_pf(b_stage + dst[i], src[i] + kb * 128);
         asm volatile("cp.async.commit_group;" ::: "memory");
-        if (kb >= PF_B_STAGES - 1) {  // K block kb - 3 has landed
-          asm volatile("cp.async.wait_group %0;" ::"n"(PF_B_STAGES - 1) : "memory");
-          publish(it - (PF_B_STAGES - 1));
+        // Publish K block kb - 2 once its copies have landed.  Two blocks of lag, not three: the
+        // copies of kb reuse the stage of kb - 4, so publishing kb - 2 waits on nothing newer than
+        // the MMAs of kb - 4; with three blocks of lag every publication would wait for the MMAs
+        // just before it and the pipeline would run in lock step.
+        if (kb >= PF_B_LAG) {
+          asm volatile("cp.async.wait_group %0;" ::"n"(PF_B_LAG) : "memory");
+          publish(it - PF_B_LAG);
         }
       }
       if (ok) {  // drain: publish the last K blocks in order
-        const int tail = k_blocks < PF_B_STAGES - 1 ? k_blocks : PF_B_STAGES - 1;
-        if (tail >= 3) { asm volatile("cp.async.wait_group 2;" ::: "memory"); publish(it - 3); }
+        const int tail = k_blocks < PF_B_LAG ? k_blocks : PF_B_LAG;
         if (tail >= 2) { asm volatile("cp.async.wait_group 1;" ::: "memory"); publish(it - 2); }
         if (tail >= 1) { asm volatile("cp.async.wait_group 0;" ::: "memory"); publish(it - 1); }
       }
