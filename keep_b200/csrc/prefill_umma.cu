@@ -346,38 +346,47 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_projection_kernel(FastP
       if (mbar_wait(bar(ACC_FULL, acc_buf), acc_phase, aborted)) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t acc_base = tmem + acc_buf * ACC_COLS + (static_cast<uint32_t>(quarter * 32) << 16);
-        for (int c0 = 0; c0 < n_pad && diag != 1; c0 += 16) {
-          uint32_t acc[M][2][16];
+        // One instantiation per output dtype, and no branch inside the column loop except the
+        // predicated store: the sixteen columns of a chunk are independent chains the compiler
+        // can interleave, which is what hides the latencies of a single warp.
+        const float limit = p.swiglu_limit > 0.0f ? p.swiglu_limit : INFINITY;
+        const bool row_ok = erow < N_out;
+        auto drain = [&](auto round_out, auto store_out) {
+          for (int c0 = 0; c0 < n_pad && diag != 1; c0 += 16) {
+            uint32_t acc[M][2][16];
 #pragma unroll
-          for (int m = 0; m < M; ++m)
+            for (int m = 0; m < M; ++m)
 #pragma unroll
-            for (int piece = 0; piece < 2; ++piece) tmem_ld16(acc_base + m * (2 * PF_N_MAX) + piece * n_pad + c0, acc[m][piece]);
-          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+              for (int piece = 0; piece < 2; ++piece) tmem_ld16(acc_base + m * (2 * PF_N_MAX) + piece * n_pad + c0, acc[m][piece]);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const int4 pr = per_route[c0 + j];
-            const int route = pr.x;
-            if (route < 0 || erow >= N_out) continue;
-            const float x_scale = __int_as_float(pr.y), x_sum4 = __int_as_float(pr.z);
-            float y[M];
+            for (int j = 0; j < 16; ++j) {
+              const int4 pr = per_route[c0 + j];
+              const float x_scale = __int_as_float(pr.y), x_sum4 = __int_as_float(pr.z);
+              float y[M];
 #pragma unroll
-            for (int m = 0; m < M; ++m) {
-              const float dot = 256.0f * static_cast<float>(static_cast<int>(acc[m][0][j])) + static_cast<float>(static_cast<int>(acc[m][1][j]));
-              y[m] = scale[m] * x_scale * (0.5f * dot + x_sum4);
+              for (int m = 0; m < M; ++m) {
+                const float dot = 256.0f * static_cast<float>(static_cast<int>(acc[m][0][j])) + static_cast<float>(static_cast<int>(acc[m][1][j]));
+                y[m] = scale[m] * x_scale * (0.5f * dot + x_sum4);
+              }
+              float result = y[0];
+              if (M == 2) {  // round G and U to the activation dtype first, as the separate kernels of the reference do
+                const float gt = fminf(round_out(y[0]), limit);
+                const float up = fminf(fmaxf(round_out(y[M - 1]), -limit), limit);
+                result = gt / (1.0f + expf(-gt)) * up * __int_as_float(pr.w);
+              }
+              if (pr.x >= 0 && row_ok) store_out(static_cast<int64_t>(pr.x) * N_out + erow, result);
             }
-            float result;
-            if (M == 2) {
-              float gt = y[0], up = y[M - 1];
-              if (p.out_dtype == KEEPVQ_BF16) { gt = __bfloat162float(__float2bfloat16_rn(gt)); up = __bfloat162float(__float2bfloat16_rn(up)); }
-              else if (p.out_dtype == KEEPVQ_F16) { gt = __half2float(__float2half_rn(gt)); up = __half2float(__float2half_rn(up)); }
-              if (p.swiglu_limit > 0.0f) { gt = fminf(gt, p.swiglu_limit); up = fminf(fmaxf(up, -p.swiglu_limit), p.swiglu_limit); }
-              result = gt / (1.0f + expf(-gt)) * up * __int_as_float(pr.w);
-            } else {
-              result = y[0];
-            }
-            store_from_float(p.out, p.out_dtype, static_cast<int64_t>(route) * N_out + erow, result);
           }
-        }
+        };
+        if (p.out_dtype == KEEPVQ_BF16)
+          drain([](float v) { return __bfloat162float(__float2bfloat16_rn(v)); },
+                [&](int64_t i, float v) { static_cast<__nv_bfloat16*>(p.out)[i] = __float2bfloat16_rn(v); });
+        else if (p.out_dtype == KEEPVQ_F16)
+          drain([](float v) { return __half2float(__float2half_rn(v)); },
+                [&](int64_t i, float v) { static_cast<__half*>(p.out)[i] = __float2half_rn(v); });
+        else
+          drain([](float v) { return v; }, [&](int64_t i, float v) { static_cast<float*>(p.out)[i] = v; });
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
         __syncwarp();
         if (lane == 0) mbar_arrive(bar(ACC_EMPTY, acc_buf));
