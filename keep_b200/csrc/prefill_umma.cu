@@ -14,15 +14,16 @@
 // The weights are the M operand (128 rows per tile) and the routes the N operand, so a ragged
 // expert group costs at most 15 padded columns, and a code is decoded once per 64 routes.
 //
-// Pipeline per CTA (persistent, one per SM, 16 warps), item = (expert, 128 rows, <= 64 routes):
+// Pipeline per CTA (persistent, one per SM, 20 warps), item = (expert, 128 rows, <= 64 routes):
 //   warps 0-7    decode: a thread owns half a row of the K block (8 codewords per matrix); codes
 //                arrive through a private cp.async ring; two table reads and two XORs per
 //                codeword, 16-byte stores into a K-major SWIZZLE_128B tile (2 stages).
 //   warp  8      issues the MMAs (one thread) into one of two accumulator buffers in tensor
 //                memory, commits stages back to the producers.
 //   warps 9-11   cp.async the routes' quantised activations into the B tiles (4 stages).
-//   warps 12-15  epilogue: tcgen05.ld of the finished buffer while the next item's MMAs fill the
-//                other one.
+//   warps 12-19  epilogue, two warps per quarter of the rows taking alternate 16-column chunks:
+//                tcgen05.ld of the finished buffer while (down projection) the next item's MMAs
+//                fill the other one.
 // mbarrier full/empty pairs carry every dependency.  Every wait is bounded: on expiry the CTA
 // raises a flag in `status`, stops issuing work, frees its tensor memory and returns.
 #include <stdlib.h>
@@ -34,8 +35,8 @@ namespace fast {
 
 constexpr int PF_DECODE_WARPS = 8;
 constexpr int PF_B_WARPS = 3;
-constexpr int PF_EPI_WARPS = 4;
-constexpr int PF_THREADS = (PF_DECODE_WARPS + 1 + PF_B_WARPS + PF_EPI_WARPS) * 32;  // 512
+constexpr int PF_EPI_WARPS = 8;                 // two per quarter of the rows, alternating 16-column chunks
+constexpr int PF_THREADS = (PF_DECODE_WARPS + 1 + PF_B_WARPS + PF_EPI_WARPS) * 32;  // 640
 constexpr int PF_A_STAGES = 2;
 constexpr int PF_B_STAGES = 4;
 constexpr int PF_B_LAG = 2;                     // K blocks of activation copies in flight behind the one being published
@@ -121,7 +122,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_projection_kernel(FastP
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
   // per-warp copies, so that a role needs no barrier of its own (every cross-warp wait is an mbarrier with a limit)
-  __shared__ int4 epi_all[PF_EPI_WARPS][PF_N_MAX];  // epilogue warps: route, x scale, x sum / 4, gate weight
+  __shared__ int4 epi_all[4][PF_N_MAX];  // per row quarter: route, x scale, x sum / 4, gate weight (each epilogue warp fills and reads its own chunks)
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const uint32_t smem_base = smem_addr(smem);
   const uint32_t bar0 = smem_addr(&bars[0]);
@@ -318,8 +319,8 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_projection_kernel(FastP
       asm volatile("cp.async.wait_group 0;" ::: "memory");
     } else {
       // ================= epilogue: accumulators -> y -> (SwiGLU) -> out =======================
-      const int quarter = warp - (PF_DECODE_WARPS + 1 + PF_B_WARPS);
-      {  // pull the code rows of this CTA's next item into L2 while the current one is being multiplied
+      const int epi = warp - (PF_DECODE_WARPS + 1 + PF_B_WARPS), quarter = epi & 3, half = epi >> 2;  // quarter = warp % 4: its TMEM lanes
+      if (half == 0) {  // pull the code rows of this CTA's next item into L2 while the current one is being multiplied
         const int next = item + gridDim.x;
         if (next < items) {
           const int ngi = next / row_tiles, ntile = next - ngi * row_tiles;
@@ -332,7 +333,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_projection_kernel(FastP
       }
       int4* per_route = epi_all[quarter];
       __syncwarp();
-      for (int n = lane; n < n_pad; n += 32) {
+      for (int n = half * 16 + (lane & 15) + (lane >> 4) * 32; n < n_pad; n += 64) {  // the columns of this warp's chunks
         const int route = n < gsize ? p.groups_of_routes.routes[gstart + n] : -1;
         const int64_t xrow = route < 0 ? p.x_zero_row : static_cast<int64_t>(route / p.x_div);
         const float weight = (M == 2 && route >= 0) ? p.route_weight[route] : 1.0f;
@@ -352,7 +353,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_projection_kernel(FastP
         const float limit = p.swiglu_limit > 0.0f ? p.swiglu_limit : INFINITY;
         const bool row_ok = erow < N_out;
         auto drain = [&](auto round_out, auto store_out) {
-          for (int c0 = 0; c0 < n_pad && diag != 1; c0 += 16) {
+          for (int c0 = half * 16; c0 < n_pad && diag != 1; c0 += 32) {
             uint32_t acc[M][2][16];
 #pragma unroll
             for (int m = 0; m < M; ++m)
