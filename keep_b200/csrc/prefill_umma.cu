@@ -107,8 +107,12 @@ __device__ __forceinline__ void cp_async16_pf(uint32_t dst, const void* src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
 }
 
-template <int M>
+// GLU: the M = 2 A tiles are the gate and the up matrix over the same 128 rows, fused by SwiGLU.
+// !GLU: the M tiles are consecutive 128-row tiles of one matrix, so an item covers 128 * M rows
+// and its activation (B) stages serve all of them (the copies are what bounds a single projection).
+template <int M, bool GLU>
 __global__ void __launch_bounds__(PF_THREADS, 1) prefill_projection_kernel(FastProjectionArgs p, int32_t* status, int diag) {
+  constexpr int ITEM_ROWS = GLU ? PF_ROWS : PF_ROWS * M;
   extern __shared__ uint8_t smem_raw[];
   // SWIZZLE_128B tiles want 1024-byte alignment; the launch reserves the slack
   uint8_t* smem = smem_raw + ((1024u - (smem_addr(smem_raw) & 1023u)) & 1023u);
@@ -163,9 +167,10 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_projection_kernel(FastP
 
   const int64_t N_out = p.out_dim, cw = p.in_dim / 8;
   const int k_blocks = static_cast<int>(cw / PF_KBLOCK_CODES);
-  const int row_tiles = static_cast<int>((N_out + PF_ROWS - 1) / PF_ROWS);
+  const int row_tiles = static_cast<int>((N_out + ITEM_ROWS - 1) / ITEM_ROWS);
   const int items = p.groups_of_routes.count[0] * row_tiles;
-  const Projection mats[2] = {p.a, p.b};
+  const Projection mats[2] = {p.a, GLU ? p.b : p.a};
+  constexpr int TILE_STEP = GLU ? 0 : PF_ROWS;  // rows between the A tiles of an item
   volatile int* aborted = &abort_flag;
 
   // Every role walks the same item list on its own clock; barriers carry the dependencies.
@@ -176,7 +181,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_projection_kernel(FastP
     const int64_t slot = p.groups_of_routes.slot[gi];
     const int gsize = p.groups_of_routes.size[gi], gstart = p.groups_of_routes.start[gi];
     const int n_pad = (gsize + 15) & ~15;  // the N of the MMA
-    const int64_t row0 = static_cast<int64_t>(tile) * PF_ROWS;
+    const int64_t row0 = static_cast<int64_t>(tile) * ITEM_ROWS;
     const int acc_buf = n_item % ACC_BUFS;
     const uint32_t acc_phase = (n_item / ACC_BUFS) & 1u;
 
@@ -184,10 +189,9 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_projection_kernel(FastP
       // ================= decode producers =====================================================
       const uint32_t abs_lane = smem_addr(tables) + (lane & 15) * 8;
       const int row = tid >> 1, half = tid & 1;  // half a row of the K block: 8 codewords
-      const int64_t grow = min(row0 + row, N_out - 1);
       const uint16_t* src[M];
 #pragma unroll
-      for (int m = 0; m < M; ++m) src[m] = mats[m].codes + (slot * N_out + grow) * cw + half * 8;
+      for (int m = 0; m < M; ++m) src[m] = mats[m].codes + (slot * N_out + min(row0 + m * TILE_STEP + row, N_out - 1)) * cw + half * 8;
       // codes arrive through a private cp.async ring, RING - 1 K blocks ahead of the decode
       constexpr int RING = PF_CODE_RING_BYTES / (M * 256 * 16);
       const uint32_t ring = smem_base + A_BYTES + B_BYTES + PF_TABLE_BYTES + tid * 16;
@@ -324,11 +328,11 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_projection_kernel(FastP
         const int next = item + gridDim.x;
         if (next < items) {
           const int ngi = next / row_tiles, ntile = next - ngi * row_tiles;
-          const int64_t nrow = min(static_cast<int64_t>(ntile) * PF_ROWS + quarter * 32 + lane, N_out - 1);
+          const int64_t nrow = static_cast<int64_t>(ntile) * ITEM_ROWS + quarter * 32 + lane;
           const int64_t nslot = p.groups_of_routes.slot[ngi];
 #pragma unroll
           for (int m = 0; m < M; ++m)
-            asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(mats[m].codes + (nslot * N_out + nrow) * cw), "r"(static_cast<uint32_t>(cw * 2)) : "memory");
+            asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(mats[m].codes + (nslot * N_out + min(nrow + m * TILE_STEP, N_out - 1)) * cw), "r"(static_cast<uint32_t>(cw * 2)) : "memory");
         }
       }
       int4* per_route = epi_all[quarter];
@@ -336,14 +340,14 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_projection_kernel(FastP
       for (int n = half * 16 + (lane & 15) + (lane >> 4) * 32; n < n_pad; n += 64) {  // the columns of this warp's chunks
         const int route = n < gsize ? p.groups_of_routes.routes[gstart + n] : -1;
         const int64_t xrow = route < 0 ? p.x_zero_row : static_cast<int64_t>(route / p.x_div);
-        const float weight = (M == 2 && route >= 0) ? p.route_weight[route] : 1.0f;
+        const float weight = (GLU && route >= 0) ? p.route_weight[route] : 1.0f;
         per_route[n] = make_int4(route, __float_as_int(p.x.scale[xrow]), __float_as_int(0.25f * static_cast<float>(p.x.sums[xrow])), __float_as_int(weight));
       }
       __syncwarp();
       const int64_t erow = row0 + quarter * 32 + lane;
       float scale[M];
 #pragma unroll
-      for (int m = 0; m < M; ++m) scale[m] = load_as_float(mats[m].scales, p.scales_dtype, slot * N_out + min(erow, N_out - 1));
+      for (int m = 0; m < M; ++m) scale[m] = load_as_float(mats[m].scales, p.scales_dtype, slot * N_out + min(erow + m * TILE_STEP, N_out - 1));
       if (mbar_wait(bar(ACC_FULL, acc_buf), acc_phase, aborted)) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t acc_base = tmem + acc_buf * ACC_COLS + (static_cast<uint32_t>(quarter * 32) << 16);
@@ -370,13 +374,16 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_projection_kernel(FastP
                 const float dot = 256.0f * static_cast<float>(static_cast<int>(acc[m][0][j])) + static_cast<float>(static_cast<int>(acc[m][1][j]));
                 y[m] = scale[m] * x_scale * (0.5f * dot + x_sum4);
               }
-              float result = y[0];
-              if (M == 2) {  // round G and U to the activation dtype first, as the separate kernels of the reference do
+              if (GLU) {  // round G and U to the activation dtype first, as the separate kernels of the reference do
                 const float gt = fminf(round_out(y[0]), limit);
                 const float up = fminf(fmaxf(round_out(y[M - 1]), -limit), limit);
-                result = gt / (1.0f + expf(-gt)) * up * __int_as_float(pr.w);
+                const float result = gt / (1.0f + expf(-gt)) * up * __int_as_float(pr.w);
+                if (pr.x >= 0 && row_ok) store_out(static_cast<int64_t>(pr.x) * N_out + erow, result);
+              } else {
+#pragma unroll
+                for (int m = 0; m < M; ++m)
+                  if (pr.x >= 0 && erow + m * TILE_STEP < N_out) store_out(static_cast<int64_t>(pr.x) * N_out + erow + m * TILE_STEP, y[m]);
               }
-              if (pr.x >= 0 && row_ok) store_out(static_cast<int64_t>(pr.x) * N_out + erow, result);
             }
           }
         };
@@ -406,12 +413,12 @@ bool prefill_supported(int64_t out_dim, int64_t in_dim, int64_t groups) {
   return groups == 1 && in_dim % (8 * PF_KBLOCK_CODES) == 0 && out_dim > 0;
 }
 
-template <int M>
+template <int M, bool GLU>
 static int launch_prefill(const FastProjectionArgs& p, int32_t* status, cudaStream_t s) {
   constexpr size_t smem = PF_A_STAGES * M * PF_TILE_BYTES + PF_B_STAGES * PF_B_STAGE_BYTES + PF_TABLE_BYTES + PF_CODE_RING_BYTES + 1024;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(prefill_projection_kernel<M>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    cudaError_t e = cudaFuncSetAttribute(prefill_projection_kernel<M, GLU>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     if (e != cudaSuccess) return note_cuda_error(e);
     configured = true;
   }
@@ -420,13 +427,16 @@ static int launch_prefill(const FastProjectionArgs& p, int32_t* status, cudaStre
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   static int diag = -1;  // measurement aid: KEEPVQ_PREFILL_DIAG = 1 no epilogue, 2 no decode, 3 no activation copies, 4 no MMAs (outputs meaningless)
   if (diag < 0) { const char* v = getenv("KEEPVQ_PREFILL_DIAG"); diag = v ? atoi(v) : 0; }
-  prefill_projection_kernel<M><<<sms, PF_THREADS, smem, s>>>(p, status, diag);
+  prefill_projection_kernel<M, GLU><<<sms, PF_THREADS, smem, s>>>(p, status, diag);
   KEEPVQ_CHECK_LAUNCH();
   return KEEPVQ_OK;
 }
 
-int prefill_gate_up(const FastProjectionArgs& p, int32_t* status, cudaStream_t s) { return launch_prefill<2>(p, status, s); }
-int prefill_down(const FastProjectionArgs& p, int32_t* status, cudaStream_t s) { return launch_prefill<1>(p, status, s); }
+int prefill_gate_up(const FastProjectionArgs& p, int32_t* status, cudaStream_t s) { return launch_prefill<2, true>(p, status, s); }
+// a single projection takes two row tiles per item when it has them (the activation copies serve both)
+int prefill_down(const FastProjectionArgs& p, int32_t* status, cudaStream_t s) {
+  return p.out_dim > PF_ROWS ? launch_prefill<2, false>(p, status, s) : launch_prefill<1, false>(p, status, s);
+}
 
 }  // namespace fast
 }  // namespace keepvq
