@@ -50,15 +50,40 @@ def measured_peaks() -> tuple[float, str]:
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples SM clocks and throttle reasons while the timed region runs: NVML every 5 ms (read
+    only), or nvidia-smi every 200 ms when the NVML binding is missing."""
 
     FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    REASON_BITS = (("hw_slowdown", 0x8), ("hw_thermal_slowdown", 0x40), ("sw_thermal_slowdown", 0x20), ("sw_power_cap", 0x4))
 
     def __init__(self, index: int):
         self.index, self.rows, self.stop_flag, self.thread = index, [], threading.Event(), None
 
+    def _nvml_handle(self):
+        import pynvml
+
+        pynvml.nvmlInit()
+        try:
+            bus = torch.cuda.get_device_properties(self.index).pci_bus_id
+            domain = getattr(torch.cuda.get_device_properties(self.index), "pci_domain_id", 0)
+            device = getattr(torch.cuda.get_device_properties(self.index), "pci_device_id", 0)
+            return pynvml, pynvml.nvmlDeviceGetHandleByPciBusId(f"{domain:08x}:{bus:02x}:{device:02x}.0".encode())
+        except Exception:
+            return pynvml, pynvml.nvmlDeviceGetHandleByIndex(self.index)
+
     def _run(self):
+        try:
+            nvml, handle = self._nvml_handle()
+            top = nvml.nvmlDeviceGetMaxClockInfo(handle, nvml.NVML_CLOCK_SM)
+            while not self.stop_flag.is_set():
+                mask = nvml.nvmlDeviceGetCurrentClocksThrottleReasons(handle)
+                self.rows.append([str(nvml.nvmlDeviceGetClockInfo(handle, nvml.NVML_CLOCK_SM)), str(top)] +
+                                 ["Active" if mask & bit else "Not Active" for _, bit in self.REASON_BITS])
+                self.stop_flag.wait(0.005)
+            return
+        except Exception:
+            pass
         while not self.stop_flag.is_set():
             try:
                 out = subprocess.run(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits"],
