@@ -44,6 +44,31 @@ __device__ __forceinline__ void store_from_float(void* base, int dtype, int64_t 
   else reinterpret_cast<float*>(base)[idx] = v;
 }
 
+// ---- programmatic dependent launch ------------------------------------------------------------
+// The kernels of a layer call run back to back on one stream.  Launched with launch_after(), a
+// kernel may start while its predecessor is still running: it announces itself at once
+// (grid_launch_dependents), does whatever needs none of the predecessor's results (building its
+// shared-memory tables), then waits for the predecessor to finish and flush (grid_wait) before it
+// reads or writes any global memory.  Both instructions are no-ops in a kernel launched the usual
+// way, and a successor launched the usual way still waits for full completion.
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void grid_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+template <typename... Params, typename... Args>
+inline cudaError_t launch_after(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t config = {};
+  config.gridDim = grid;
+  config.blockDim = block;
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  cudaLaunchAttribute attribute = {};
+  attribute.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute.val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = &attribute;
+  config.numAttrs = 1;
+  return cudaLaunchKernelEx(&config, kernel, static_cast<Params>(args)...);
+}
+
 // Streaming 128/64/32-bit loads that bypass L1 allocation: code bytes are read once.
 __device__ __forceinline__ uint4 ld_stream_u4(const void* p) {
   uint4 v;

@@ -28,6 +28,8 @@ namespace fast {
 // ------------------------------------------------------------------------------------------
 template <typename XT>
 __global__ void __launch_bounds__(256) quantize_rows_kernel(const XT* __restrict__ x, int64_t rows, int64_t in_dim, int64_t groups, QuantRows out, int planes) {
+  grid_launch_dependents();
+  grid_wait();
   __shared__ float warp_max[8];
   __shared__ float row_scale;
   extern __shared__ int32_t group_sum[];
@@ -113,10 +115,11 @@ int quantize_rows(const void* x, int32_t x_dtype, int64_t rows, int64_t in_dim, 
   const size_t smem = static_cast<size_t>(groups) * sizeof(int32_t);
   if (smem > 40 * 1024) return KEEPVQ_ERR_CAPACITY;
   const unsigned grid = static_cast<unsigned>(rows + 1);  // + the zero row
-  if (x_dtype == KEEPVQ_F32) quantize_rows_kernel<float><<<grid, 256, smem, s>>>(reinterpret_cast<const float*>(x), rows, in_dim, groups, out, planes ? 1 : 0);
-  else if (x_dtype == KEEPVQ_F16) quantize_rows_kernel<__half><<<grid, 256, smem, s>>>(reinterpret_cast<const __half*>(x), rows, in_dim, groups, out, planes ? 1 : 0);
-  else quantize_rows_kernel<__nv_bfloat16><<<grid, 256, smem, s>>>(reinterpret_cast<const __nv_bfloat16*>(x), rows, in_dim, groups, out, planes ? 1 : 0);
-  KEEPVQ_CHECK_LAUNCH();
+  cudaError_t err;
+  if (x_dtype == KEEPVQ_F32) err = launch_after(quantize_rows_kernel<float>, grid, 256, smem, s, reinterpret_cast<const float*>(x), rows, in_dim, groups, out, planes ? 1 : 0);
+  else if (x_dtype == KEEPVQ_F16) err = launch_after(quantize_rows_kernel<__half>, grid, 256, smem, s, reinterpret_cast<const __half*>(x), rows, in_dim, groups, out, planes ? 1 : 0);
+  else err = launch_after(quantize_rows_kernel<__nv_bfloat16>, grid, 256, smem, s, reinterpret_cast<const __nv_bfloat16*>(x), rows, in_dim, groups, out, planes ? 1 : 0);
+  if (err != cudaSuccess) return note_cuda_error(err);
   return KEEPVQ_OK;
 }
 
@@ -127,6 +130,8 @@ int quantize_rows(const void* x, int32_t x_dtype, int64_t rows, int64_t in_dim, 
 constexpr int GR_THREADS = 1024;
 
 __global__ void __launch_bounds__(GR_THREADS) group_routes_kernel(const uint32_t* __restrict__ served_slot, int routes, int slots, int max_group, RouteGroups out) {
+  grid_launch_dependents();
+  grid_wait();
   extern __shared__ int32_t sm[];
   int32_t* count = sm;               // [slots] routes per slot, then running cursor
   int32_t* first = sm + slots;       // [slots] first position of the slot in `routes`
@@ -191,8 +196,8 @@ int group_routes(const uint32_t* served_slot, int64_t routes, int64_t slots, int
     cudaError_t e = cudaFuncSetAttribute(group_routes_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     if (e != cudaSuccess) return note_cuda_error(e);
   }
-  group_routes_kernel<<<1, GR_THREADS, smem, s>>>(served_slot, static_cast<int>(routes), static_cast<int>(slots), max_group, out);
-  KEEPVQ_CHECK_LAUNCH();
+  cudaError_t err = launch_after(group_routes_kernel, 1, GR_THREADS, smem, s, served_slot, static_cast<int>(routes), static_cast<int>(slots), max_group, out);
+  if (err != cudaSuccess) return note_cuda_error(err);
   return KEEPVQ_OK;
 }
 
@@ -240,6 +245,7 @@ __device__ __forceinline__ void team_barrier(int team) {
 template <int M, int TILES>
 __global__ void __launch_bounds__(CTA_THREADS, 1) projection_kernel(FastProjectionArgs p) {
   extern __shared__ __align__(16) uint8_t smem[];
+  grid_launch_dependents();
   uint8_t* lut = smem;
   constexpr int ACCS = M * TILES * 4;  // fp32 partials per lane
   float* red = reinterpret_cast<float*>(smem + LUT_BYTES);  // [team][warp][ACCS][32]
@@ -260,6 +266,7 @@ __global__ void __launch_bounds__(CTA_THREADS, 1) projection_kernel(FastProjecti
 #pragma unroll
     for (int r = 0; r < LUT_REPLICAS; ++r) dst[r] = make_uint2(lo, hi);
   }
+  grid_wait();  // the tables came from constants; everything below reads what earlier kernels of the stream wrote
   __syncthreads();
 
   const int lane = threadIdx.x & 31, warp = (threadIdx.x >> 5) % TEAM_WARPS, team = threadIdx.x / (TEAM_WARPS * 32);
@@ -491,6 +498,7 @@ __device__ __forceinline__ void decode_chunk(uint32_t abs_lane, uint32_t sign_la
 template <int M, int TILES, int MODE, bool NESTED>
 __global__ void __launch_bounds__(CK_THREADS, 1) projection_cta_kernel(FastProjectionArgs p) {
   extern __shared__ __align__(16) uint8_t smem[];
+  grid_launch_dependents();
   // ---- tables -----------------------------------------------------------------------------
   for (int e = threadIdx.x; e < 768; e += CK_THREADS) {
     uint32_t lo = 0, hi = 0;
@@ -528,6 +536,7 @@ __global__ void __launch_bounds__(CK_THREADS, 1) projection_cta_kernel(FastProje
     for (int r = 0; r < LUT_REPLICAS; ++r) dst[r] = make_uint2(lo, hi);
   }
 
+  grid_wait();  // the tables came from constants; everything below reads what earlier kernels of the stream wrote
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int g = lane >> 2, t = lane & 3;
   const uint32_t smem_base = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
@@ -812,8 +821,8 @@ static int launch_projection(const FastProjectionArgs& p, cudaStream_t s) {
     if (e != cudaSuccess) return note_cuda_error(e);
     configured = true;
   }
-  projection_kernel<M, TILES><<<sm_count(), CTA_THREADS, smem, s>>>(p);
-  KEEPVQ_CHECK_LAUNCH();
+  cudaError_t err = launch_after(projection_kernel<M, TILES>, sm_count(), CTA_THREADS, smem, s, p);
+  if (err != cudaSuccess) return note_cuda_error(err);
   return KEEPVQ_OK;
 }
 
@@ -826,8 +835,8 @@ static int launch_projection_cta_mode(const FastProjectionArgs& p, cudaStream_t 
     if (e != cudaSuccess) return note_cuda_error(e);
     configured = true;
   }
-  projection_cta_kernel<M, TILES, MODE, NESTED><<<sm_count(), CK_THREADS, smem, s>>>(p);
-  KEEPVQ_CHECK_LAUNCH();
+  cudaError_t err = launch_after(projection_cta_kernel<M, TILES, MODE, NESTED>, sm_count(), CK_THREADS, smem, s, p);
+  if (err != cudaSuccess) return note_cuda_error(err);
   return KEEPVQ_OK;
 }
 

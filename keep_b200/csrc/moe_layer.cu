@@ -95,6 +95,8 @@ __global__ void __launch_bounds__(256) swiglu_weight_kernel(const T* __restrict_
 template <typename T>
 __global__ void __launch_bounds__(256) combine_kernel(const T* __restrict__ down, const uint32_t* __restrict__ served_slot, int64_t slots,
                                                       T* __restrict__ out, int64_t tokens, int64_t hidden, int top_k) {
+  grid_launch_dependents();
+  grid_wait();
   constexpr int tag = dtype_tag_of<T>::value;
   const int64_t total = tokens * hidden;
   for (int64_t i = blockIdx.x * 256ll + threadIdx.x; i < total; i += 256ll * gridDim.x) {
@@ -118,7 +120,8 @@ static void launch_elementwise(const keepvq_moe_layer_args& a, const LayerScratc
   } else {
     const int64_t total = a.tokens * a.hidden;
     const unsigned blocks = static_cast<unsigned>(std::min<int64_t>((total + 255) / 256, 148 * 16));
-    combine_kernel<T><<<blocks, 256, 0, s>>>(reinterpret_cast<const T*>(ws + sc.down), a.served_slot, a.slots, reinterpret_cast<T*>(a.out), a.tokens, a.hidden, a.top_k);
+    launch_after(combine_kernel<T>, blocks, 256, 0, s, reinterpret_cast<const T*>(ws + sc.down), static_cast<const uint32_t*>(a.served_slot), a.slots,
+                 reinterpret_cast<T*>(a.out), a.tokens, a.hidden, static_cast<int>(a.top_k));
   }
 }
 

@@ -33,6 +33,8 @@ constexpr float ABSENT_BIAS = -1e29f;  // served_bias at or below this marks an 
 // summed lane-sequentially, then by a butterfly over the lanes, then over the warps in order.
 template <typename XT, typename WT>
 __global__ void __launch_bounds__(RL_WARPS * 32) router_logits_kernel(keepvq_router_logits_args a) {
+  grid_launch_dependents();
+  grid_wait();
   __shared__ float part[RL_WARPS][RL_ROWS * RL_TOKENS];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int64_t e0 = static_cast<int64_t>(blockIdx.x) * RL_ROWS, t0 = static_cast<int64_t>(blockIdx.y) * RL_TOKENS;
@@ -88,6 +90,8 @@ constexpr int RT_MIN_TOKENS = 256;  // below this the tile grid is too small to 
 
 template <typename XT, typename WT>
 __global__ void __launch_bounds__(RT_THREADS) router_logits_tiled_kernel(keepvq_router_logits_args a) {
+  grid_launch_dependents();
+  grid_wait();
   __shared__ __align__(16) float xs[RT_K][RT_LD], ws[RT_K][RT_LD];
   const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
   const int64_t t0 = static_cast<int64_t>(blockIdx.y) * RT_TILE, e0 = static_cast<int64_t>(blockIdx.x) * RT_TILE;
@@ -157,6 +161,8 @@ __device__ __forceinline__ uint32_t ordered_key(float v) {
 // loads inside the selection loops.  Same arithmetic and the same results as routed_topk_kernel.
 template <int NPL>
 __global__ void __launch_bounds__(TK_WARPS * 32) routed_topk_reg_kernel(keepvq_routed_topk_args a) {
+  grid_launch_dependents();
+  grid_wait();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int64_t t = static_cast<int64_t>(blockIdx.x) * TK_WARPS + warp;
   if (t >= a.tokens) return;
@@ -254,6 +260,8 @@ __global__ void __launch_bounds__(TK_WARPS * 32) routed_topk_reg_kernel(keepvq_r
 }
 
 __global__ void __launch_bounds__(TK_WARPS * 32) routed_topk_kernel(keepvq_routed_topk_args a) {
+  grid_launch_dependents();
+  grid_wait();
   extern __shared__ float smem[];  // per warp: scores[pool]
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int64_t t = static_cast<int64_t>(blockIdx.x) * TK_WARPS + warp;
@@ -337,16 +345,16 @@ __global__ void __launch_bounds__(TK_WARPS * 32) routed_topk_kernel(keepvq_route
 
 template <typename XT>
 static void launch_logits_tiled(const keepvq_router_logits_args& a, dim3 grid, cudaStream_t s) {
-  if (a.router_dtype == KEEPVQ_F32) router_logits_tiled_kernel<XT, float><<<grid, RT_THREADS, 0, s>>>(a);
-  else if (a.router_dtype == KEEPVQ_F16) router_logits_tiled_kernel<XT, __half><<<grid, RT_THREADS, 0, s>>>(a);
-  else router_logits_tiled_kernel<XT, __nv_bfloat16><<<grid, RT_THREADS, 0, s>>>(a);
+  if (a.router_dtype == KEEPVQ_F32) launch_after(router_logits_tiled_kernel<XT, float>, grid, RT_THREADS, 0, s, a);
+  else if (a.router_dtype == KEEPVQ_F16) launch_after(router_logits_tiled_kernel<XT, __half>, grid, RT_THREADS, 0, s, a);
+  else launch_after(router_logits_tiled_kernel<XT, __nv_bfloat16>, grid, RT_THREADS, 0, s, a);
 }
 
 template <typename XT>
 static void launch_logits(const keepvq_router_logits_args& a, dim3 grid, cudaStream_t s) {
-  if (a.router_dtype == KEEPVQ_F32) router_logits_kernel<XT, float><<<grid, RL_WARPS * 32, 0, s>>>(a);
-  else if (a.router_dtype == KEEPVQ_F16) router_logits_kernel<XT, __half><<<grid, RL_WARPS * 32, 0, s>>>(a);
-  else router_logits_kernel<XT, __nv_bfloat16><<<grid, RL_WARPS * 32, 0, s>>>(a);
+  if (a.router_dtype == KEEPVQ_F32) launch_after(router_logits_kernel<XT, float>, grid, RL_WARPS * 32, 0, s, a);
+  else if (a.router_dtype == KEEPVQ_F16) launch_after(router_logits_kernel<XT, __half>, grid, RL_WARPS * 32, 0, s, a);
+  else launch_after(router_logits_kernel<XT, __nv_bfloat16>, grid, RL_WARPS * 32, 0, s, a);
 }
 
 }  // namespace keepvq
@@ -393,9 +401,9 @@ extern "C" int keepvq_routed_topk(const keepvq_routed_topk_args* args, void* str
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const unsigned blocks = static_cast<unsigned>((a.tokens + TK_WARPS - 1) / TK_WARPS);
   if (a.pool <= 1024) {  // the pool fits the registers of a warp
-    if (a.pool <= 128) routed_topk_reg_kernel<4><<<blocks, TK_WARPS * 32, 0, s>>>(a);
-    else if (a.pool <= 384) routed_topk_reg_kernel<12><<<blocks, TK_WARPS * 32, 0, s>>>(a);
-    else routed_topk_reg_kernel<32><<<blocks, TK_WARPS * 32, 0, s>>>(a);
+    if (a.pool <= 128) launch_after(routed_topk_reg_kernel<4>, blocks, TK_WARPS * 32, 0, s, a);
+    else if (a.pool <= 384) launch_after(routed_topk_reg_kernel<12>, blocks, TK_WARPS * 32, 0, s, a);
+    else launch_after(routed_topk_reg_kernel<32>, blocks, TK_WARPS * 32, 0, s, a);
     KEEPVQ_CHECK_LAUNCH();
     return KEEPVQ_OK;
   }
