@@ -495,7 +495,7 @@ def run_expert_parallel(ns, rank, world, local, device):
         "stack_tokens_per_s": round(EP_BATCH * ns.steps / (ms * 1e-3), 1), "cpu_baseline": None,
         "layer_us": round(ms / ns.steps / layers * 1e3, 1),
         "e2e": {"value": round(tokens / (e2e_ms * 1e-3), 1), "unit": UNIT, "h2d_bytes_per_step": EP_BATCH * HIDDEN * 2, "d2h_bytes_per_step": EP_BATCH * HIDDEN * 2},
-        "gpu_launches": 11 * layers * ns.steps * world, "kernel_path": stack[0].local.kernel_path, "clocks": clocks.summary(),
+        "gpu_launches": (14 if ns.exchange == "peer" else 11) * layers * ns.steps * world, "kernel_path": stack[0].local.kernel_path, "clocks": clocks.summary(),
     }
     print(json.dumps(line))
 
