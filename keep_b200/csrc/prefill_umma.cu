@@ -17,10 +17,10 @@
 // Pipeline per CTA (persistent, one per SM, 20 warps), item = (expert, 128 rows, <= 64 routes):
 //   warps 0-7    decode: a thread owns half a row of the K block (8 codewords per matrix); codes
 //                arrive through a private cp.async ring; two table reads and two XORs per
-//                codeword, 16-byte stores into a K-major SWIZZLE_128B tile (2 stages).
+//                codeword, 16-byte stores into a K-major SWIZZLE_128B tile (3 stages).
 //   warp  8      issues the MMAs (one thread) into one of two accumulator buffers in tensor
 //                memory, commits stages back to the producers.
-//   warps 9-11   cp.async the routes' quantised activations into the B tiles (4 stages).
+//   warps 9-11   cp.async the routes' quantised activations into the B tiles (3 stages).
 //   warps 12-19  epilogue, two warps per quarter of the rows taking alternate 16-column chunks:
 //                tcgen05.ld of the finished buffer while (down projection) the next item's MMAs
 //                fill the other one.
@@ -37,16 +37,17 @@ constexpr int PF_DECODE_WARPS = 8;
 constexpr int PF_B_WARPS = 3;
 constexpr int PF_EPI_WARPS = 8;                 // two per quarter of the rows, alternating 16-column chunks
 constexpr int PF_THREADS = (PF_DECODE_WARPS + 1 + PF_B_WARPS + PF_EPI_WARPS) * 32;  // 640
-constexpr int PF_A_STAGES = 2;
-constexpr int PF_B_STAGES = 4;
-constexpr int PF_B_LAG = 2;                     // K blocks of activation copies in flight behind the one being published
+constexpr int PF_A_STAGES = 3;
+constexpr int PF_B_STAGES = 3;
+constexpr int PF_B_LAG = 1;                     // K blocks of activation copies in flight behind the one being published
+static_assert(PF_B_LAG >= 1 && PF_B_LAG <= PF_B_STAGES - 2 && PF_B_LAG <= 2, "see the loader's publication rule");
 constexpr int PF_N_MAX = PREFILL_GROUP_ROUTES;  // routes per item
 constexpr int PF_ROWS = 128;                    // output rows per item
 constexpr int PF_KBLOCK_CODES = 16;             // codewords of a row per K block = 128 bytes of int8
 constexpr int PF_TILE_BYTES = PF_ROWS * 128;    // 16 KB: one A tile
 constexpr int PF_B_STAGE_BYTES = 2 * PF_N_MAX * 128;  // high-byte rows of the routes, then their low-byte rows
 constexpr int PF_TABLE_BYTES = 256 * 16 * 8;     // abs table, 16 replicas of 8 bytes
-constexpr int PF_CODE_RING_BYTES = 24 * 1024;    // per-thread code prefetch ring of the decode warps
+constexpr int PF_CODE_RING_BYTES = 16 * 1024;    // per-thread code prefetch ring of the decode warps
 constexpr uint32_t PF_SPIN_LIMIT = 1u << 24;
 
 __device__ __forceinline__ uint32_t smem_addr(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
@@ -272,7 +273,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_projection_kernel(FastP
     } else if (warp < PF_DECODE_WARPS + 1 + PF_B_WARPS) {
       // ================= activation (B operand) loaders =======================================
       // cp.async straight into the swizzled tiles (16 bytes = two codewords of one route); a K
-      // block is published when its copies have landed, two later ones already in flight.
+      // block is published when its copies have landed, PF_B_LAG later ones already in flight.
       // A thread keeps one (chunk, plane) and every sixth route: sources and destinations are
       // worked out once per item, a K block then costs an add and a copy per route.
       const int loader = tid - (PF_DECODE_WARPS + 1) * 32;  // 0..95
@@ -306,10 +307,10 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_projection_kernel(FastP
         for (int i = 0; i < SLOTS; ++i)
           if (n0 + i * (PF_B_WARPS * 2) < n_pad && diag != 3) cp_async16_pf(b_stage + dst[i], src[i] + kb * 128);
         asm volatile("cp.async.commit_group;" ::: "memory");
-        // Publish K block kb - 2 once its copies have landed.  Two blocks of lag, not three: the
-        // copies of kb reuse the stage of kb - 4, so publishing kb - 2 waits on nothing newer than
-        // the MMAs of kb - 4; with three blocks of lag every publication would wait for the MMAs
-        // just before it and the pipeline would run in lock step.
+        // Publish K block kb - LAG once its copies have landed, with LAG <= stages - 2: the copies
+        // of kb reuse the stage of kb - stages, so publishing kb - LAG then waits on nothing newer
+        // than MMAs two blocks before it.  With LAG = stages - 1 every publication waited for the
+        // MMAs just before it and the whole pipeline ran in lock step.
         if (kb >= PF_B_LAG) {
           asm volatile("cp.async.wait_group %0;" ::"n"(PF_B_LAG) : "memory");
           publish(it - PF_B_LAG);
