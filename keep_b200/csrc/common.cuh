@@ -54,8 +54,11 @@ __device__ __forceinline__ void store_from_float(void* base, int dtype, int64_t 
 __device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void grid_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
+// Early start pays at decode sizes, where launch latency is a visible share of a call; grids of
+// thousands of blocks gain nothing from it and measured slower (their early blocks crowd the SMs
+// while they wait), so the callers pass `early = false` there and get an ordinary launch.
 template <typename... Params, typename... Args>
-inline cudaError_t launch_after(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+inline cudaError_t launch_after(bool early, void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
   cudaLaunchConfig_t config = {};
   config.gridDim = grid;
   config.blockDim = block;
@@ -65,9 +68,10 @@ inline cudaError_t launch_after(void (*kernel)(Params...), dim3 grid, dim3 block
   attribute.id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attribute.val.programmaticStreamSerializationAllowed = 1;
   config.attrs = &attribute;
-  config.numAttrs = 1;
+  config.numAttrs = early ? 1 : 0;
   return cudaLaunchKernelEx(&config, kernel, static_cast<Params>(args)...);
 }
+constexpr int64_t EARLY_LAUNCH_MAX_BLOCKS = 1024;
 
 // Streaming 128/64/32-bit loads that bypass L1 allocation: code bytes are read once.
 __device__ __forceinline__ uint4 ld_stream_u4(const void* p) {

@@ -115,10 +115,11 @@ int quantize_rows(const void* x, int32_t x_dtype, int64_t rows, int64_t in_dim, 
   const size_t smem = static_cast<size_t>(groups) * sizeof(int32_t);
   if (smem > 40 * 1024) return KEEPVQ_ERR_CAPACITY;
   const unsigned grid = static_cast<unsigned>(rows + 1);  // + the zero row
+  const bool early = rows < EARLY_LAUNCH_MAX_BLOCKS;
   cudaError_t err;
-  if (x_dtype == KEEPVQ_F32) err = launch_after(quantize_rows_kernel<float>, grid, 256, smem, s, reinterpret_cast<const float*>(x), rows, in_dim, groups, out, planes ? 1 : 0);
-  else if (x_dtype == KEEPVQ_F16) err = launch_after(quantize_rows_kernel<__half>, grid, 256, smem, s, reinterpret_cast<const __half*>(x), rows, in_dim, groups, out, planes ? 1 : 0);
-  else err = launch_after(quantize_rows_kernel<__nv_bfloat16>, grid, 256, smem, s, reinterpret_cast<const __nv_bfloat16*>(x), rows, in_dim, groups, out, planes ? 1 : 0);
+  if (x_dtype == KEEPVQ_F32) err = launch_after(early, quantize_rows_kernel<float>, grid, 256, smem, s, reinterpret_cast<const float*>(x), rows, in_dim, groups, out, planes ? 1 : 0);
+  else if (x_dtype == KEEPVQ_F16) err = launch_after(early, quantize_rows_kernel<__half>, grid, 256, smem, s, reinterpret_cast<const __half*>(x), rows, in_dim, groups, out, planes ? 1 : 0);
+  else err = launch_after(early, quantize_rows_kernel<__nv_bfloat16>, grid, 256, smem, s, reinterpret_cast<const __nv_bfloat16*>(x), rows, in_dim, groups, out, planes ? 1 : 0);
   if (err != cudaSuccess) return note_cuda_error(err);
   return KEEPVQ_OK;
 }
@@ -196,7 +197,7 @@ int group_routes(const uint32_t* served_slot, int64_t routes, int64_t slots, int
     cudaError_t e = cudaFuncSetAttribute(group_routes_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     if (e != cudaSuccess) return note_cuda_error(e);
   }
-  cudaError_t err = launch_after(group_routes_kernel, 1, GR_THREADS, smem, s, served_slot, static_cast<int>(routes), static_cast<int>(slots), max_group, out);
+  cudaError_t err = launch_after(routes <= 4 * EARLY_LAUNCH_MAX_BLOCKS, group_routes_kernel, 1, GR_THREADS, smem, s, served_slot, static_cast<int>(routes), static_cast<int>(slots), max_group, out);
   if (err != cudaSuccess) return note_cuda_error(err);
   return KEEPVQ_OK;
 }
@@ -821,7 +822,7 @@ static int launch_projection(const FastProjectionArgs& p, cudaStream_t s) {
     if (e != cudaSuccess) return note_cuda_error(e);
     configured = true;
   }
-  cudaError_t err = launch_after(projection_kernel<M, TILES>, sm_count(), CTA_THREADS, smem, s, p);
+  cudaError_t err = launch_after(true, projection_kernel<M, TILES>, sm_count(), CTA_THREADS, smem, s, p);
   if (err != cudaSuccess) return note_cuda_error(err);
   return KEEPVQ_OK;
 }
@@ -835,7 +836,7 @@ static int launch_projection_cta_mode(const FastProjectionArgs& p, cudaStream_t 
     if (e != cudaSuccess) return note_cuda_error(e);
     configured = true;
   }
-  cudaError_t err = launch_after(projection_cta_kernel<M, TILES, MODE, NESTED>, sm_count(), CK_THREADS, smem, s, p);
+  cudaError_t err = launch_after(true, projection_cta_kernel<M, TILES, MODE, NESTED>, sm_count(), CK_THREADS, smem, s, p);
   if (err != cudaSuccess) return note_cuda_error(err);
   return KEEPVQ_OK;
 }

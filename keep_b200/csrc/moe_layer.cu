@@ -120,7 +120,7 @@ static void launch_elementwise(const keepvq_moe_layer_args& a, const LayerScratc
   } else {
     const int64_t total = a.tokens * a.hidden;
     const unsigned blocks = static_cast<unsigned>(std::min<int64_t>((total + 255) / 256, 148 * 16));
-    launch_after(combine_kernel<T>, blocks, 256, 0, s, reinterpret_cast<const T*>(ws + sc.down), static_cast<const uint32_t*>(a.served_slot), a.slots,
+    launch_after(a.tokens <= 256, combine_kernel<T>, blocks, 256, 0, s, reinterpret_cast<const T*>(ws + sc.down), static_cast<const uint32_t*>(a.served_slot), a.slots,
                  reinterpret_cast<T*>(a.out), a.tokens, a.hidden, static_cast<int>(a.top_k));
   }
 }

@@ -345,16 +345,16 @@ __global__ void __launch_bounds__(TK_WARPS * 32) routed_topk_kernel(keepvq_route
 
 template <typename XT>
 static void launch_logits_tiled(const keepvq_router_logits_args& a, dim3 grid, cudaStream_t s) {
-  if (a.router_dtype == KEEPVQ_F32) launch_after(router_logits_tiled_kernel<XT, float>, grid, RT_THREADS, 0, s, a);
-  else if (a.router_dtype == KEEPVQ_F16) launch_after(router_logits_tiled_kernel<XT, __half>, grid, RT_THREADS, 0, s, a);
-  else launch_after(router_logits_tiled_kernel<XT, __nv_bfloat16>, grid, RT_THREADS, 0, s, a);
+  if (a.router_dtype == KEEPVQ_F32) launch_after(false, router_logits_tiled_kernel<XT, float>, grid, RT_THREADS, 0, s, a);
+  else if (a.router_dtype == KEEPVQ_F16) launch_after(false, router_logits_tiled_kernel<XT, __half>, grid, RT_THREADS, 0, s, a);
+  else launch_after(false, router_logits_tiled_kernel<XT, __nv_bfloat16>, grid, RT_THREADS, 0, s, a);
 }
 
 template <typename XT>
 static void launch_logits(const keepvq_router_logits_args& a, dim3 grid, cudaStream_t s) {
-  if (a.router_dtype == KEEPVQ_F32) launch_after(router_logits_kernel<XT, float>, grid, RL_WARPS * 32, 0, s, a);
-  else if (a.router_dtype == KEEPVQ_F16) launch_after(router_logits_kernel<XT, __half>, grid, RL_WARPS * 32, 0, s, a);
-  else launch_after(router_logits_kernel<XT, __nv_bfloat16>, grid, RL_WARPS * 32, 0, s, a);
+  if (a.router_dtype == KEEPVQ_F32) launch_after(true, router_logits_kernel<XT, float>, grid, RL_WARPS * 32, 0, s, a);
+  else if (a.router_dtype == KEEPVQ_F16) launch_after(true, router_logits_kernel<XT, __half>, grid, RL_WARPS * 32, 0, s, a);
+  else launch_after(true, router_logits_kernel<XT, __nv_bfloat16>, grid, RL_WARPS * 32, 0, s, a);
 }
 
 }  // namespace keepvq
@@ -401,9 +401,9 @@ extern "C" int keepvq_routed_topk(const keepvq_routed_topk_args* args, void* str
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const unsigned blocks = static_cast<unsigned>((a.tokens + TK_WARPS - 1) / TK_WARPS);
   if (a.pool <= 1024) {  // the pool fits the registers of a warp
-    if (a.pool <= 128) launch_after(routed_topk_reg_kernel<4>, blocks, TK_WARPS * 32, 0, s, a);
-    else if (a.pool <= 384) launch_after(routed_topk_reg_kernel<12>, blocks, TK_WARPS * 32, 0, s, a);
-    else launch_after(routed_topk_reg_kernel<32>, blocks, TK_WARPS * 32, 0, s, a);
+    if (a.pool <= 128) launch_after(blocks <= EARLY_LAUNCH_MAX_BLOCKS / 4, routed_topk_reg_kernel<4>, blocks, TK_WARPS * 32, 0, s, a);
+    else if (a.pool <= 384) launch_after(blocks <= EARLY_LAUNCH_MAX_BLOCKS / 4, routed_topk_reg_kernel<12>, blocks, TK_WARPS * 32, 0, s, a);
+    else launch_after(blocks <= EARLY_LAUNCH_MAX_BLOCKS / 4, routed_topk_reg_kernel<32>, blocks, TK_WARPS * 32, 0, s, a);
     KEEPVQ_CHECK_LAUNCH();
     return KEEPVQ_OK;
   }
