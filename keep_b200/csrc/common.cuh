@@ -118,6 +118,32 @@ __device__ __forceinline__ void load8_as_float<__nv_bfloat16>(const __nv_bfloat1
   }
 }
 
+// Eight consecutive values rounded to T and stored at once.  `p` is aligned to 8 * sizeof(T).
+template <typename T>
+__device__ __forceinline__ void store8_from_float(T* p, const float (&v)[8]);
+
+template <>
+__device__ __forceinline__ void store8_from_float<float>(float* p, const float (&v)[8]) {
+  reinterpret_cast<float4*>(p)[0] = make_float4(v[0], v[1], v[2], v[3]);
+  reinterpret_cast<float4*>(p)[1] = make_float4(v[4], v[5], v[6], v[7]);
+}
+template <>
+__device__ __forceinline__ void store8_from_float<__half>(__half* p, const float (&v)[8]) {
+  uint4 raw;
+  __half2* h = reinterpret_cast<__half2*>(&raw);
+#pragma unroll
+  for (int k = 0; k < 4; ++k) h[k] = __floats2half2_rn(v[2 * k], v[2 * k + 1]);
+  *reinterpret_cast<uint4*>(p) = raw;
+}
+template <>
+__device__ __forceinline__ void store8_from_float<__nv_bfloat16>(__nv_bfloat16* p, const float (&v)[8]) {
+  uint4 raw;
+  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+  for (int k = 0; k < 4; ++k) h[k] = __floats2bfloat162_rn(v[2 * k], v[2 * k + 1]);
+  *reinterpret_cast<uint4*>(p) = raw;
+}
+
 // ---- table expansion ----------------------------------------------------------------------
 
 // Nibbles k and k+4 of `word` as an fp16 pair of (nibble - 8) / 2.

@@ -97,14 +97,18 @@ __global__ void __launch_bounds__(256) combine_kernel(const T* __restrict__ down
                                                       T* __restrict__ out, int64_t tokens, int64_t hidden, int top_k) {
   grid_launch_dependents();
   grid_wait();
-  constexpr int tag = dtype_tag_of<T>::value;
-  const int64_t total = tokens * hidden;
+  const int64_t vectors = hidden / 8, total = tokens * vectors;  // eight values (16 or 32 bytes) per thread and step
   for (int64_t i = blockIdx.x * 256ll + threadIdx.x; i < total; i += 256ll * gridDim.x) {
-    const int64_t t = i / hidden, d = i - t * hidden;
-    float y = 0.0f;
-    for (int j = 0; j < top_k; ++j)
-      if (served_slot[t * top_k + j] < static_cast<uint64_t>(slots)) y += load_as_float(down, tag, (t * top_k + j) * hidden + d);
-    store_from_float(out, tag, i, y);
+    const int64_t t = i / vectors, d = (i - t * vectors) * 8;
+    float y[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int j = 0; j < top_k; ++j) {
+      if (served_slot[t * top_k + j] >= static_cast<uint64_t>(slots)) continue;
+      float v[8];
+      load8_as_float<T>(down + (t * top_k + j) * hidden + d, v);
+#pragma unroll
+      for (int q = 0; q < 8; ++q) y[q] += v[q];
+    }
+    store8_from_float<T>(out + t * hidden + d, y);
   }
 }
 
@@ -118,7 +122,7 @@ static void launch_elementwise(const keepvq_moe_layer_args& a, const LayerScratc
     swiglu_weight_kernel<T><<<blocks, 256, 0, s>>>(reinterpret_cast<const T*>(ws + sc.gate), reinterpret_cast<const T*>(ws + sc.up),
                                                    a.served_weight, reinterpret_cast<T*>(ws + sc.h), routes, a.inter, a.swiglu_limit);
   } else {
-    const int64_t total = a.tokens * a.hidden;
+    const int64_t total = a.tokens * (a.hidden / 8);
     const unsigned blocks = static_cast<unsigned>(std::min<int64_t>((total + 255) / 256, 148 * 16));
     launch_after(a.tokens <= 256, combine_kernel<T>, blocks, 256, 0, s, reinterpret_cast<const T*>(ws + sc.down), static_cast<const uint32_t*>(a.served_slot), a.slots,
                  reinterpret_cast<T*>(a.out), a.tokens, a.hidden, static_cast<int>(a.top_k));
