@@ -17,16 +17,23 @@ from . import _lib
 from .kernels import qmv_output_dtype, routed_matvec
 
 _UNSUPPORTED = -5  # KEEPVQ_ERR_UNSUPPORTED
-_all_odd: dict = {}     # table data_ptr -> every nibble odd (read back once per table, never per call)
-_workspaces: dict = {}  # (device, routes, in_dim) -> scratch tensor
+_all_odd: dict = {}     # table data_ptr -> (the tensor, its version, every nibble odd): read back once per table, never per call
+_workspaces: dict = {}  # (device, routes, in_dim) -> scratch tensor; the most recent shapes only
+_MAX_CACHED = 8
 
 
 def _table_all_odd(table: torch.Tensor) -> bool:
+    """Whether every nibble of the table is odd (what the int8 kernels need).  The cache holds the
+    tensor itself, so its address cannot be handed to another table while the entry lives, and an
+    in-place change of the table (a new version) is looked at again."""
     key = (table.data_ptr(), str(table.device))
-    if key not in _all_odd:
+    hit = _all_odd.get(key)
+    if hit is None or hit[0] is not table or hit[1] != table._version:
         nibbles = (table.cpu().to(torch.int64) & 0xFFFFFFFF)[:, None] >> (4 * torch.arange(8))[None] & 1
-        _all_odd[key] = bool(nibbles.all())
-    return _all_odd[key]
+        if len(_all_odd) >= _MAX_CACHED:
+            _all_odd.pop(next(iter(_all_odd)))
+        _all_odd[key] = (table, table._version, bool(nibbles.all()))
+    return _all_odd[key][2]
 
 
 def tensor_core_projection(rows, codes, scales, table, rhs):
@@ -43,6 +50,8 @@ def tensor_core_projection(rows, codes, scales, table, rhs):
         nbytes = int(lib.keepvq_grouped_projection_workspace_bytes(routes, in_dim))
         if nbytes < 0:
             _lib.check(nbytes, "keepvq_grouped_projection_workspace_bytes")
+        if len(_workspaces) >= _MAX_CACHED:  # varying route counts must not pile up scratch
+            _workspaces.pop(next(iter(_workspaces)))
         _workspaces[key] = torch.empty(nbytes, dtype=torch.uint8, device=device)
     ws = _workspaces[key]
     out_dtype = qmv_output_dtype(rows.dtype)
