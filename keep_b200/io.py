@@ -101,3 +101,64 @@ def projection(layer: LayerFile, which: str, experts, device):
     codes = torch.from_numpy(layer.read(f"{which}_codes", experts)).to(device)
     scales = torch.from_numpy(layer.read(f"{which}_scales", experts)).to(device)
     return Projection(codes, scales)
+
+
+# ---- safetensors checkpoints ---------------------------------------------------------------
+# KEEP's converted checkpoints store a switch projection as ``<prefix>.codes`` (uint8 / uint16
+# [experts, out, in/8]) and ``<prefix>.scales`` ([experts, out, in/group]), optionally ``.bias``,
+# an optional shared ``model.vq_codebook.e8`` table, and a ``quantization_config`` JSON in the
+# file metadata that names the codebook by its SHA-256 (src/keep/io/schema.py:64-106,
+# src/keep/io/load.py:109-122,154-181,236-262).
+
+
+def switch_linear_dims(shapes: dict, dtypes: dict, prefix: str) -> tuple[int, int, int, int, int]:
+    """(in_dim, out_dim, experts, group_size, code_bits) from the tensors' shapes and dtypes, with
+    the reference's checks (``infer_vq_switch_linear_dims``, load.py:154-181)."""
+    codes_name, scales_name = f"{prefix}.codes", f"{prefix}.scales"
+    for name in (codes_name, scales_name):
+        if name not in shapes:
+            raise KeyError(f"missing tensor {name!r}")
+    codes, scales = tuple(shapes[codes_name]), tuple(shapes[scales_name])
+    if len(codes) != 3:
+        raise ValueError(f"{codes_name} must be 3D [experts, out, in/8], found {codes}")
+    if len(scales) != 3:
+        raise ValueError(f"{scales_name} must be 3D [experts, out, in/group], found {scales}")
+    if codes[:2] != scales[:2]:
+        raise ValueError("switch codes and scales must have the same expert and out dimensions")
+    code_bits = {"U8": 8, "UINT8": 8, "U16": 16, "UINT16": 16}.get(str(dtypes[codes_name]).upper())
+    if code_bits is None:
+        raise ValueError(f"{codes_name} must be uint8 or uint16, found {dtypes[codes_name]}")
+    experts, out_dim, codewords = codes
+    in_dim = codewords * 8
+    if scales[2] <= 0 or in_dim % scales[2] != 0:
+        raise ValueError("switch scale count must divide inferred in_dim")
+    return in_dim, out_dim, experts, in_dim // scales[2], code_bits
+
+
+def load_quantized_vq_switch_linear(path, prefix: str, device):
+    """``<prefix>.codes`` / ``.scales`` (/ ``.bias``) of a KEEP safetensors file as a
+    ``switch.QuantizedVQSwitchLinear`` on ``device``.  A codebook hash in the file's metadata must
+    be one of the two tables this library carries, as in the reference."""
+    import json
+
+    from safetensors import safe_open
+
+    from .switch import QuantizedVQSwitchLinear
+    from .vq import E8_1BIT_PACKED_SHA256, E8P_PACKED_ABS_SHA256
+
+    with safe_open(str(path), framework="pt", device="cpu") as f:
+        meta = f.metadata() or {}
+        config = json.loads(meta["quantization_config"]) if "quantization_config" in meta else {}
+        expected = (config.get("codebook") or {}).get("sha256") if isinstance(config, dict) else None
+        if expected is not None and expected not in (E8_1BIT_PACKED_SHA256, E8P_PACKED_ABS_SHA256):
+            raise ValueError(f"checkpoint E8 codebook hash {expected!r} is not supported by this runtime")
+        names = set(f.keys())
+        wanted = [n for n in (f"{prefix}.codes", f"{prefix}.scales") if n in names]
+        shapes = {n: tuple(f.get_slice(n).get_shape()) for n in wanted}
+        dtypes = {n: f.get_slice(n).get_dtype() for n in wanted}
+        in_dim, out_dim, experts, group_size, code_bits = switch_linear_dims(shapes, dtypes, prefix)
+        get = lambda n: f.get_tensor(n).to(device) if n in names else None  # noqa: E731
+        codes, scales, bias = get(f"{prefix}.codes"), get(f"{prefix}.scales"), get(f"{prefix}.bias")
+        codebook = get("model.vq_codebook.e8")
+    return QuantizedVQSwitchLinear(input_dims=in_dim, output_dims=out_dim, num_experts=experts, codes=codes, scales=scales,
+                                   codebook=codebook, bias=bias, group_size=group_size, code_bits=code_bits)

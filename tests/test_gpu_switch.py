@@ -119,3 +119,32 @@ def test_glu_fused_and_composed_match_the_dense_oracle(cuda, tokens, limit):
     got2 = composed(x.to(cuda), torch.from_numpy(idx).to(cuda))
     assert composed._fused_layer() is None
     assert e8.relative_gap(got2.float().cpu().numpy(), want) <= 1e-2
+
+
+def test_switch_linear_from_a_safetensors_checkpoint(cuda, tmp_path):
+    """<prefix>.codes / .scales with the codebook named by hash in the metadata -> a working holder."""
+    import json
+
+    from safetensors.torch import save_file
+
+    from keep_b200 import io as layer_io, vq
+
+    rng = np.random.default_rng(80)
+    codes, scales = synthetic.projection(rng, 5, 40, 256, group=64)
+    prefix = "model.layers.3.mlp.switch_mlp.gate_proj"
+    config = {"quant_method": "mlx_vq_e8", "version": 1, "default_code_bits": 16, "default_group_size": 64,
+              "codebook": {"name": "quip_e8p", "dtype": "uint32", "entries": 256, "sha256": vq.E8P_PACKED_ABS_SHA256}}
+    tensors = {f"{prefix}.codes": torch.from_numpy(codes), f"{prefix}.scales": torch.from_numpy(scales)}
+    save_file(tensors, str(tmp_path / "model.safetensors"), metadata={"quantization_config": json.dumps(config)})
+    layer = layer_io.load_quantized_vq_switch_linear(tmp_path / "model.safetensors", prefix, cuda)
+    assert (layer.input_dims, layer.output_dims, layer.num_experts, layer.group_size, layer.code_bits) == (256, 40, 5, 64, 16)
+    x = rng.normal(size=(3, 256)).astype(np.float32)
+    idx = rng.integers(0, 5, (3, 2))
+    got = layer(torch.from_numpy(x).to(cuda), torch.from_numpy(idx).to(cuda))
+    np.testing.assert_allclose(got.cpu().numpy(), ops.gather_vqmm(x, codes, scales, None, idx, code_bits=16), rtol=1e-4, atol=1e-3)
+    config["codebook"]["sha256"] = "0" * 64
+    save_file(tensors, str(tmp_path / "other.safetensors"), metadata={"quantization_config": json.dumps(config)})
+    with pytest.raises(ValueError, match="not supported by this runtime"):
+        layer_io.load_quantized_vq_switch_linear(tmp_path / "other.safetensors", prefix, cuda)
+    with pytest.raises(KeyError, match="missing tensor"):
+        layer_io.load_quantized_vq_switch_linear(tmp_path / "model.safetensors", "model.layers.4.x", cuda)

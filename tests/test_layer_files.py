@@ -50,3 +50,17 @@ def test_compressed_and_incomplete_files_are_refused(tmp_path):
     np.savez(tmp_path / "m.npz", w1_codes=np.zeros((2, 2, 2), np.uint16))
     with pytest.raises(ValueError, match="missing arrays"):
         layer_io.LayerFile(tmp_path / "m.npz")
+
+
+def test_safetensors_switch_dims_and_checks():
+    shapes = {"m.w.codes": (4, 6, 8), "m.w.scales": (4, 6, 2)}
+    assert layer_io.switch_linear_dims(shapes, {"m.w.codes": "U16", "m.w.scales": "F16"}, "m.w") == (64, 6, 4, 32, 16)
+    assert layer_io.switch_linear_dims(shapes, {"m.w.codes": "U8", "m.w.scales": "F16"}, "m.w")[4] == 8
+    with pytest.raises(KeyError, match="missing tensor"):
+        layer_io.switch_linear_dims(shapes, {}, "m.v")
+    with pytest.raises(ValueError, match="uint8 or uint16"):
+        layer_io.switch_linear_dims(shapes, {"m.w.codes": "I32", "m.w.scales": "F16"}, "m.w")
+    with pytest.raises(ValueError, match="same expert and out"):
+        layer_io.switch_linear_dims({"m.w.codes": (4, 6, 8), "m.w.scales": (4, 5, 2)}, {"m.w.codes": "U16"}, "m.w")
+    with pytest.raises(ValueError, match="must divide"):
+        layer_io.switch_linear_dims({"m.w.codes": (4, 6, 8), "m.w.scales": (4, 6, 3)}, {"m.w.codes": "U16"}, "m.w")
