@@ -199,6 +199,20 @@ def test_many_routes_spread_over_many_experts_stay_on_the_decode_kernels(cuda):
     check_layer(cfg, x, out, routing, top_k=3)
 
 
+@pytest.mark.parametrize("tokens", [2, 10])
+def test_shipped_artifact_shape_with_grouped_scales(cuda, tokens):
+    """The shape and scale groups of the reference's shipped artifacts: hidden 5120 in groups of
+    512, inter 2304 in groups of 256 (keep_quant.py:13-15).  Ten tokens x top-6 puts the down
+    projection on the CTA kernel while gate/up (5120 inputs, more than its activation stage
+    holds) stays on the small-batch kernel."""
+    cfg = synthetic.layer(seed=31, experts=10, hidden=5120, inter=2304, group_hidden=512, group_inter=256)
+    x = synthetic.tokens(32 + tokens, tokens, 5120)
+    layer = build_layer(cuda, cfg, top_k=6)
+    assert layer.kernel_path == "tensor"
+    out, routing = layer.decode(x.to(cuda))
+    check_layer(cfg, x, out, routing, top_k=6)
+
+
 @pytest.mark.parametrize("batch", [1, 16])
 def test_config2_shape_decode_layer(cuda, batch):
     """The benchmark layer shape (hidden 4096, inter 2048, top-6, softmax) on a 48-expert slice of
