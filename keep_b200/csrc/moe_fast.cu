@@ -418,6 +418,7 @@ constexpr int CK_WARPS = 16;
 constexpr int CK_THREADS = CK_WARPS * 32;
 constexpr int CK_MAX_CHUNKS = 16;                                   // in_dim <= 4096
 constexpr int CK_B_BYTES = CK_MAX_CHUNKS * 8 * 32 * 16;             // 64 KB
+constexpr int CK_MAX_CHUNKS_WIDE = 24;                              // in_dim <= 6144: the activations take the sign table's room too
 constexpr int CK_ABS_BYTES = LUT_BYTES;                             // 64 KB: [abs row][parity][replica]
 constexpr int CK_SIGN_BYTES = 256 * LUT_REPLICAS * 8;               // 32 KB: [sign byte][replica]
 constexpr int CK_STAGES = 2;
@@ -496,12 +497,15 @@ __device__ __forceinline__ void decode_chunk(uint32_t abs_lane, uint32_t sign_la
 // instead of the sign masks (the base decode does its signs on the integer pipe in every step),
 // and an item whose slot is hot runs a second pass over the residual's 8-bit codes: one table
 // read per codeword gives the int8 operand 2v directly (no signs, no parity, no offset term).
-template <int M, int TILES, int MODE, bool NESTED>
+// WIDE: input dimensions of 4097..6144 (the shipped artifacts' 5120).  Their staged activations
+// need 96 KB, so the sign table goes and every step decodes its signs on the integer pipe.
+template <int M, int TILES, int MODE, bool NESTED, bool WIDE = false>
 __global__ void __launch_bounds__(CK_THREADS, 1) projection_cta_kernel(FastProjectionArgs p) {
+  static_assert(!(NESTED && WIDE), "the residual table and the wide activation stage want the same shared memory");
   extern __shared__ __align__(16) uint8_t smem[];
   grid_launch_dependents();
   // ---- tables -----------------------------------------------------------------------------
-  for (int e = threadIdx.x; e < 768; e += CK_THREADS) {
+  for (int e = threadIdx.x; e < (WIDE ? 512 : 768); e += CK_THREADS) {
     uint32_t lo = 0, hi = 0;
     if (e >= 512 && NESTED) {  // residual entry: byte j of the low word is 2 * v[6 - 2j], of the high word 2 * v[7 - 2j]
       const uint32_t* row = p.res_table + (e - 512) * 4;
@@ -543,10 +547,11 @@ __global__ void __launch_bounds__(CK_THREADS, 1) projection_cta_kernel(FastProje
   const uint32_t smem_base = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
   const uint32_t abs_lane = smem_base + (lane & (LUT_REPLICAS - 1)) * 8;
   const uint32_t sign_lane = abs_lane + CK_ABS_BYTES;
-  const uint32_t b_base = smem_base + CK_ABS_BYTES + CK_SIGN_BYTES;
+  const uint32_t b_base = smem_base + CK_ABS_BYTES + (WIDE ? 0 : CK_SIGN_BYTES);
+  constexpr int B_BYTES = CK_B_BYTES + (WIDE ? CK_SIGN_BYTES : 0);
   constexpr int STREAMS = M * 2 * TILES;                 // 16-byte pieces a lane owns per chunk
   constexpr int STAGE_BYTES = STREAMS * 512;             // per warp
-  const uint32_t ring = b_base + CK_B_BYTES + warp * (CK_STAGES * STAGE_BYTES) + lane * 16;
+  const uint32_t ring = b_base + B_BYTES + warp * (CK_STAGES * STAGE_BYTES) + lane * 16;
   const int64_t N = p.out_dim, cw = p.in_dim / 8;
   const int n_chunks = static_cast<int>(cw / CHUNK_CODES);
   const int chunks_per_group = n_chunks / static_cast<int>(p.groups);
@@ -648,7 +653,7 @@ __global__ void __launch_bounds__(CK_THREADS, 1) projection_cta_kernel(FastProje
 #pragma unroll
           for (int j = 0; j < 2 * TILES; ++j) acc_h[0][m][j / 2][j & 1] += cur[m][j].x ^ cur[m][j].y ^ cur[m][j].z ^ cur[m][j].w;
       } else {
-        decode_chunk<M, TILES, MODE, !NESTED>(abs_lane, sign_lane, cur, b_base + lane * 16 + c * 8 * 512, acc_h, acc_l);
+        decode_chunk<M, TILES, MODE, !NESTED && !WIDE>(abs_lane, sign_lane, cur, b_base + lane * 16 + c * 8 * 512, acc_h, acc_l);
       }
       const int group = c / chunks_per_group;
       if (c + 1 == n_chunks || (c + 1) / chunks_per_group != group) {
@@ -827,16 +832,16 @@ static int launch_projection(const FastProjectionArgs& p, cudaStream_t s) {
   return KEEPVQ_OK;
 }
 
-template <int M, int TILES, int MODE, bool NESTED = false>
+template <int M, int TILES, int MODE, bool NESTED = false, bool WIDE = false>
 static int launch_projection_cta_mode(const FastProjectionArgs& p, cudaStream_t s) {
   constexpr size_t smem = CK_ABS_BYTES + CK_SIGN_BYTES + CK_B_BYTES + CK_WARPS * CK_STAGES * (M * 2 * TILES * 512);
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(projection_cta_kernel<M, TILES, MODE, NESTED>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    cudaError_t e = cudaFuncSetAttribute(projection_cta_kernel<M, TILES, MODE, NESTED, WIDE>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     if (e != cudaSuccess) return note_cuda_error(e);
     configured = true;
   }
-  cudaError_t err = launch_after(true, projection_cta_kernel<M, TILES, MODE, NESTED>, sm_count(), CK_THREADS, smem, s, p);
+  cudaError_t err = launch_after(true, projection_cta_kernel<M, TILES, MODE, NESTED, WIDE>, sm_count(), CK_THREADS, smem, s, p);
   if (err != cudaSuccess) return note_cuda_error(err);
   return KEEPVQ_OK;
 }
@@ -854,6 +859,7 @@ static int diagnostic_mode() {
 template <int M, int TILES>
 static int launch_projection_cta(const FastProjectionArgs& p, cudaStream_t s) {
   if (p.res_table) return launch_projection_cta_mode<M, TILES, 0, true>(p, s);
+  if (p.in_dim > 8 * CHUNK_CODES * CK_MAX_CHUNKS) return launch_projection_cta_mode<M, TILES, 0, false, true>(p, s);
   switch (diagnostic_mode()) {
     case 1: return launch_projection_cta_mode<M, TILES, 1>(p, s);
     case 3: return launch_projection_cta_mode<M, TILES, 3>(p, s);
@@ -864,7 +870,10 @@ static int launch_projection_cta(const FastProjectionArgs& p, cudaStream_t s) {
 
 // Enough routes to give every CTA of the machine its own (group, slab) items, and activations
 // that fit the shared-memory stage?
-static bool many_items(const FastProjectionArgs& p) { return p.max_routes >= 48 && p.in_dim <= 8 * CHUNK_CODES * CK_MAX_CHUNKS; }
+static bool many_items(const FastProjectionArgs& p) {
+  const int64_t widest = 8 * CHUNK_CODES * (p.res_table ? CK_MAX_CHUNKS : CK_MAX_CHUNKS_WIDE);
+  return p.max_routes >= 48 && p.in_dim <= widest;
+}
 
 // The residual pass lives in the CTA kernel only: a layer with a residual tier needs enough routes
 // for that kernel and residual scale groups that close on chunk boundaries.

@@ -202,9 +202,9 @@ def test_many_routes_spread_over_many_experts_stay_on_the_decode_kernels(cuda):
 @pytest.mark.parametrize("tokens", [2, 10])
 def test_shipped_artifact_shape_with_grouped_scales(cuda, tokens):
     """The shape and scale groups of the reference's shipped artifacts: hidden 5120 in groups of
-    512, inter 2304 in groups of 256 (keep_quant.py:13-15).  Ten tokens x top-6 puts the down
-    projection on the CTA kernel while gate/up (5120 inputs, more than its activation stage
-    holds) stays on the small-batch kernel."""
+    512, inter 2304 in groups of 256 (keep_quant.py:13-15).  Two tokens run the small-batch kernel;
+    ten tokens x top-6 run the CTA kernel, gate/up in its wide form (5120 inputs: the staged
+    activations take the sign table's shared memory)."""
     cfg = synthetic.layer(seed=31, experts=10, hidden=5120, inter=2304, group_hidden=512, group_inter=256)
     x = synthetic.tokens(32 + tokens, tokens, 5120)
     layer = build_layer(cuda, cfg, top_k=6)
