@@ -421,6 +421,8 @@ def run_expert_parallel(ns, rank, world, local, device):
             out = layer.forward(x)
         outs[0] = out
 
+    torch.cuda.synchronize()
+    dist.barrier()  # the ranks finish generating their layers at different times; the first exchange meets on the device
     for _ in range(max(ns.warmup, 3)):
         step()
     torch.cuda.synchronize()
