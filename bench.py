@@ -358,7 +358,8 @@ def run_reference(ns):
     line = {"metric": METRIC, "value": round(value, 4), "unit": UNIT, "n_gpus": ns.gpus, "steps": ns.steps, "warmup": ns.warmup,
             "ms_per_step": round(total / ns.steps * 1e3, 2), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic", "impl": "reference",
-            "config": {"workload": "decode layer (config 2): 384 experts, hidden 4096, inter 2048, top-6 softmax router; CPU path, one token per step (bounded sample)"},
+            "config": {"workload": ("decode layer (config 2)" if ns.gpus == 1 else "one layer of the expert-parallel stack (config 5; the unit is a token through one routed layer)")
+                                   + ": 384 experts, hidden 4096, inter 2048, top-6 softmax router; CPU path, one token per step (bounded sample)"},
             "cpu_baseline": {"value": round(value, 4), "unit": UNIT, "cores": threads, "kind": "port",
                              "sample": f"per step: router + {per_token} of a token's 6 served experts (decode of 3 projections each + SwiGLU path); value scaled to whole tokens"},
             "e2e": {"value": round(value, 4), "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
