@@ -64,6 +64,8 @@ __global__ void __launch_bounds__(EP_PLAN_THREADS) ep_plan_kernel(keepvq_ep_pack
 // ---- the exchange over peer-mapped memory --------------------------------------------------
 // The same plan, with each destination's slots and weights stored in that rank's recv_meta.
 __global__ void __launch_bounds__(EP_PLAN_THREADS) ep_plan_peer_kernel(keepvq_ep_pack_args a, keepvq_ep_peer_args peer) {
+  grid_launch_dependents();
+  grid_wait();
   __shared__ int warp_count[32][EP_MAX_WORLD];
   __shared__ int base[EP_MAX_WORLD];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -113,6 +115,8 @@ __global__ void __launch_bounds__(EP_PLAN_THREADS) ep_plan_peer_kernel(keepvq_ep
 }
 
 __global__ void __launch_bounds__(256) ep_copy_peer_kernel(keepvq_ep_pack_args a, keepvq_ep_peer_args peer) {
+  grid_launch_dependents();
+  grid_wait();
   const int64_t r = blockIdx.x, rows = static_cast<int64_t>(a.world) * a.capacity;
   const int64_t pos = a.position[r];
   if (pos >= rows) return;
@@ -124,6 +128,8 @@ __global__ void __launch_bounds__(256) ep_copy_peer_kernel(keepvq_ep_pack_args a
 
 // Row r of y, if it is a live route, back to the rank it came from.
 __global__ void __launch_bounds__(256) ep_return_peer_kernel(const uint8_t* __restrict__ y, keepvq_ep_peer_args peer) {
+  grid_launch_dependents();
+  grid_wait();
   const int64_t r = blockIdx.x;
   if (peer.recv_meta[peer.rank][r] < 0) return;
   const int64_t src_rank = r / peer.capacity, slot = r % peer.capacity;
@@ -139,6 +145,8 @@ __global__ void __launch_bounds__(256) ep_return_peer_kernel(const uint8_t* __re
 constexpr uint32_t EP_WAIT_LIMIT = 1u << 23;
 
 __global__ void __launch_bounds__(EP_MAX_WORLD) ep_barrier_kernel(keepvq_ep_peer_args peer) {
+  grid_launch_dependents();
+  grid_wait();
   const int w = threadIdx.x;
   const int32_t e = *peer.epoch + 1;
   __threadfence_system();
@@ -169,6 +177,8 @@ __global__ void __launch_bounds__(256) ep_copy_kernel(keepvq_ep_pack_args a) {
 
 template <typename T>
 __global__ void __launch_bounds__(256) ep_combine_kernel(keepvq_ep_combine_args a) {
+  grid_launch_dependents();
+  grid_wait();
   const int64_t t = blockIdx.x;
   const T* back = static_cast<const T*>(a.back);
   for (int64_t c = threadIdx.x * 8; c < a.hidden; c += blockDim.x * 8) {
@@ -223,9 +233,10 @@ extern "C" int keepvq_ep_combine(const keepvq_ep_combine_args* args, void* strea
   if (a.tokens >= (1ll << 31)) return KEEPVQ_ERR_CAPACITY;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const unsigned grid = static_cast<unsigned>(a.tokens);
-  if (a.dtype == KEEPVQ_F32) ep_combine_kernel<float><<<grid, 256, 0, s>>>(a);
-  else if (a.dtype == KEEPVQ_F16) ep_combine_kernel<__half><<<grid, 256, 0, s>>>(a);
-  else ep_combine_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(a);
+  const bool early = a.tokens <= EARLY_LAUNCH_MAX_BLOCKS;
+  if (a.dtype == KEEPVQ_F32) launch_after(early, ep_combine_kernel<float>, grid, 256, 0, s, a);
+  else if (a.dtype == KEEPVQ_F16) launch_after(early, ep_combine_kernel<__half>, grid, 256, 0, s, a);
+  else launch_after(early, ep_combine_kernel<__nv_bfloat16>, grid, 256, 0, s, a);
   KEEPVQ_CHECK_LAUNCH();
   return KEEPVQ_OK;
 }
@@ -251,13 +262,13 @@ extern "C" int keepvq_ep_dispatch_peer(const keepvq_ep_pack_args* pack, const ke
   if (routes > 0 && (!a.x || !a.served_expert || !a.served_weight || !a.position)) return KEEPVQ_ERR_NULL;
   if (!aligned_to(a.x, 16)) return KEEPVQ_ERR_ALIGN;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  ep_plan_peer_kernel<<<1, EP_PLAN_THREADS, 0, s>>>(a, p);
+  launch_after(true, ep_plan_peer_kernel, 1, EP_PLAN_THREADS, 0, s, a, p);
   KEEPVQ_CHECK_LAUNCH();
   if (routes > 0) {
-    ep_copy_peer_kernel<<<static_cast<unsigned>(routes), 256, 0, s>>>(a, p);
+    launch_after(routes <= EARLY_LAUNCH_MAX_BLOCKS, ep_copy_peer_kernel, static_cast<unsigned>(routes), 256, 0, s, a, p);
     KEEPVQ_CHECK_LAUNCH();
   }
-  ep_barrier_kernel<<<1, EP_MAX_WORLD, 0, s>>>(p);
+  launch_after(true, ep_barrier_kernel, 1, EP_MAX_WORLD, 0, s, p);
   KEEPVQ_CHECK_LAUNCH();
   return KEEPVQ_OK;
 }
@@ -269,9 +280,9 @@ extern "C" int keepvq_ep_return_peer(const void* y, const keepvq_ep_peer_args* p
   if (int rc = check_peer(p)) return rc;
   if (!aligned_to(y, 16)) return KEEPVQ_ERR_ALIGN;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  ep_return_peer_kernel<<<static_cast<unsigned>(p.world * p.capacity), 256, 0, s>>>(static_cast<const uint8_t*>(y), p);
+  launch_after(static_cast<int64_t>(p.world) * p.capacity <= EARLY_LAUNCH_MAX_BLOCKS, ep_return_peer_kernel, static_cast<unsigned>(p.world * p.capacity), 256, 0, s, static_cast<const uint8_t*>(y), p);
   KEEPVQ_CHECK_LAUNCH();
-  ep_barrier_kernel<<<1, EP_MAX_WORLD, 0, s>>>(p);
+  launch_after(true, ep_barrier_kernel, 1, EP_MAX_WORLD, 0, s, p);
   KEEPVQ_CHECK_LAUNCH();
   return KEEPVQ_OK;
 }
