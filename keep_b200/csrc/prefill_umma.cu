@@ -8,22 +8,24 @@
 //
 // Arithmetic: the same exact-integer form as the decode kernels (moe_fast.cuh).  A codeword
 // becomes eight int8 values q with 4w = 2q + 1; activations are 16-bit fixed point split in a
-// signed high and a signed low byte.  Per (expert, 128 output rows, up to 64 routes):
-//   D_hi[128 x N] += Q[128 x K] * Xhi[N x K]^T,   D_lo likewise   (int32, exact, in TMEM)
+// signed high and an unsigned low byte.  Per (expert, 128 output rows, up to 96 routes):
+//   [D_hi | D_lo][128 x 2N] += Q[128 x K] * [Xhi ; Xlo][2N x K]^T   (int32, exact, in TMEM)
 //   y = scale_row * scale_x * (0.5 * (256 D_hi + D_lo) + 0.25 * sum(x'))
-// The weights are the M operand (128 rows per tile) and the routes the N operand, so a ragged
-// expert group costs at most 15 padded columns, and a code is decoded once per 64 routes.
+// The weights are the M operand (128 rows per tile) and the routes the N operand (their high-byte
+// rows stacked on their low-byte rows, so one MMA reads the decoded tile once for both), so a
+// ragged expert group costs at most 15 padded columns, and a code is decoded once per 96 routes.
 //
-// Pipeline per CTA (persistent, one per SM, 20 warps), item = (expert, 128 rows, <= 64 routes):
-//   warps 0-7    decode: a thread owns half a row of the K block (8 codewords per matrix); codes
-//                arrive through a private cp.async ring; two table reads and two XORs per
-//                codeword, 16-byte stores into a K-major SWIZZLE_128B tile (3 stages).
-//   warp  8      issues the MMAs (one thread) into one of two accumulator buffers in tensor
-//                memory, commits stages back to the producers.
+// Pipeline per CTA (persistent, one per SM, 20 warps).  An item is (expert, two A tiles, <= 96
+// routes): the gate and the up matrix over the same 128 rows, or two consecutive 128-row tiles of
+// a single matrix; either way one set of activation tiles serves both.
+//   warps 0-7    decode: a thread owns half a row of the K block (8 codewords per tile); codes
+//                arrive through a private cp.async ring; one abs-table read plus sign arithmetic
+//                per codeword, 16-byte stores into a K-major SWIZZLE_128B tile (3 stages).
+//   warp  8      issues the MMAs (one thread) into the accumulators in tensor memory (a second
+//                buffer when the item's columns leave room for one), commits stages back.
 //   warps 9-11   cp.async the routes' quantised activations into the B tiles (3 stages).
 //   warps 12-19  epilogue, two warps per quarter of the rows taking alternate 16-column chunks:
-//                tcgen05.ld of the finished buffer while (down projection) the next item's MMAs
-//                fill the other one.
+//                tcgen05.ld of the finished buffer, dequantisation, SwiGLU, stores.
 // mbarrier full/empty pairs carry every dependency.  Every wait is bounded: on expiry the CTA
 // raises a flag in `status`, stops issuing work, frees its tensor memory and returns.
 #include <stdlib.h>
