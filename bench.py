@@ -191,7 +191,7 @@ def projection_roofline(layer, xs, steps, hbm_gbs, peak_kind):
     return {"bound": "hbm", "achieved": round(achieved, 1), "peak": hbm_gbs, "unit": "GB/s", "frac": round(achieved / hbm_gbs, 4),
             "traffic": traffic, "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch, scaled by code bytes" if tensor else None,
             "peak_kind": peak_kind,
-            "kernel": "projection_cta_kernel<2,1> (gate+up+SwiGLU, int8 tensor cores)" if tensor else "routed_matvec_kernel x2 + swiglu",
+            "kernel": "projection_slab_kernel<2,1> (gate+up+SwiGLU, int8 tensor cores)" if tensor else "routed_rowdot_kernel x2 + swiglu",
             "launches_per_stage": launches, "algorithmic_bytes_per_launch": int(bytes_per_stage),
             "us_per_launch": round(ms / steps * 1e3, 2)}
 

@@ -27,7 +27,7 @@
 extern "C" {
 #endif
 
-#define KEEPVQ_ABI_VERSION 1
+#define KEEPVQ_ABI_VERSION 2
 
 typedef enum keepvq_status {
   KEEPVQ_OK = 0,
@@ -90,13 +90,19 @@ int keepvq_decode_weights(const keepvq_decode_args* args, void* stream);
  *   e8_1bit_m1_token_layout / _per_route            src/ramp/kernels/e8_1bit_m1.py:76-97
  *   e8p_nested_m1_token_layout / _per_route         src/ramp/kernels/e8p_nested_m1.py:90-112
  *
- * out[r, n] = sum_k W[rhs[r]][n, k] * x[row(r), k], fp32 accumulation, one rounding to
- * out_dtype.  row(r) = lhs[r] if lhs != NULL else r / x_div.  With a residual,
+ * out[r, n] = sum_k W[rhs[r]][n, k] * x[row(r), k], one rounding to out_dtype.
+ * row(r) = lhs[r] if lhs != NULL else r / x_div.  With a residual,
  * W = base + residual[hot_of_slot[rhs[r]]] for slots whose entry is not KEEPVQ_NO_RESIDUAL;
  * base and residual are accumulated apart and added once in fp32.  A route whose rhs is
- * KEEPVQ_NO_RESIDUAL writes zeros (the 8-bit kernels of the reference do the same,
- * e8_1bit_m1.metal:25-32; here it holds for every code width, so a masked router pick is safe).
- * Indices are not range-checked (vq_switch.py:637,646-648).
+ * KEEPVQ_NO_RESIDUAL, or any other value >= experts, writes zeros (the 8-bit kernels of the
+ * reference do the same for NO_RESIDUAL, e8_1bit_m1.metal:25-32; here it holds for every code
+ * width, so a masked router pick is safe).  Activation row indices are not range-checked
+ * (vq_switch.py:637,646-648).
+ * Arithmetic: every weight is a multiple of 1/4, so the kernel works on the integers 4w and on
+ * activations quantised per row to fixed point with a power-of-two step: 16 bits for fp16 / bf16
+ * rows (error at most 2^-16 of the row's largest magnitude per element), 24 bits for fp32 rows
+ * (2^-24).  The integer sums are exact; scales are applied in fp32 per scale group.  Any table is
+ * accepted: one whose nibbles are all odd (the E8P table) takes a faster decode.
  * ------------------------------------------------------------------------------------------ */
 typedef struct keepvq_matvec_args {
   const void* x;            /* [x_rows, in_dim] */
@@ -274,6 +280,13 @@ int keepvq_moe_decode_layer(const keepvq_moe_layer_args* args, void* stream);
  * the reference. */
 int64_t keepvq_moe_layer_status_offset(int64_t tokens, int64_t hidden, int64_t inter, int64_t pool, int32_t top_k);
 
+/* Byte offset, inside the scratch, of the per-route outputs [tokens * top_k, hidden] (activation
+ * dtype) that the pick sum adds up: after the DOWN stage, row t * top_k + j holds round(W2 h) of
+ * token t's pick j (rows of picks without a slot are not written).  A caller that wants the
+ * routes' outputs unsummed, as QuantizedVQSwitchGLU returns them
+ * (src/ramp/models/glm4_moe_adapter.py:367-372), runs the stages up to DOWN and reads them here. */
+int64_t keepvq_moe_layer_route_output_offset(int64_t tokens, int64_t hidden, int64_t inter, int64_t pool, int32_t top_k);
+
 /* The same sequence, cut into stages: run the stages named in `stages` (a mask) on the same
  * arguments and scratch.  A later stage reads what earlier ones left in the outputs and the
  * scratch, so a profiler or benchmark can replay one stage after a full run.  No counterpart in
@@ -366,13 +379,19 @@ int keepvq_residency_tick(const keepvq_residency_args* args, void* stream);
  * expert on the device, so they need not arrive sorted; rhs 0xFFFFFFFF gives a zero row.
  * Returns KEEPVQ_ERR_UNSUPPORTED when the shapes or the table do not fit these kernels (16-bit
  * codes, in_dim % 256 == 0, whole scale groups per 256 inputs, every table nibble odd): the
- * caller then uses keepvq_routed_matvec.  Activations are rounded to 16-bit fixed point per row
- * (relative 2^-15 of the row maximum); everything else is exact integer arithmetic.
+ * caller then uses keepvq_routed_matvec.  Activations are rounded to 16-bit fixed point per row:
+ * an element's error is at most 2^-16 of the row's largest magnitude, whatever the input dtype
+ * (fp32 rows are narrowed too; keepvq_routed_matvec keeps 24 bits of them).  On a row with one
+ * channel far above the rest the small channels therefore lose relative precision: with an
+ * outlier of 300 (3000) times the row's RMS the output error stays near 1e-3 of the output's
+ * largest magnitude, while against the output the row would give WITHOUT the outlier channel it
+ * is about 0.5 % (3 %).  Everything else is exact integer arithmetic.  Rows of routes without an
+ * expert are written as zeros.
  * The scratch also holds, at keepvq_grouped_projection_status_offset, the int32 the tcgen05
  * kernel sets when a bounded wait expires (see keepvq_moe_layer_status_offset).
  * ------------------------------------------------------------------------------------------ */
 typedef struct keepvq_grouped_projection_args {
-  const void* x;             /* [routes, in_dim] */
+  const void* x;             /* [x_rows, in_dim]; fp16 or bf16 (fp32 rows belong to keepvq_routed_matvec, which keeps 24 bits of them) */
   int32_t x_dtype;
   int64_t routes;
   const uint32_t* rhs;       /* [routes] expert (slot) of each route */
@@ -386,6 +405,18 @@ typedef struct keepvq_grouped_projection_args {
   int32_t out_dtype;
   void* workspace;           /* keepvq_grouped_projection_workspace_bytes(), 256-byte aligned */
   int64_t workspace_bytes;
+  /* Route r reads activation row r / x_div: 1 (or 0) = a row per route, top_k = the token layout
+     of e8p_m1_token_layout (src/ramp/kernels/e8p_m1.py:134-157).  x_rows = routes / x_div. */
+  int32_t x_div;
+  /* Optional nested residual, as in keepvq_matvec_args (e8p_nested_m1.py:90-112); res_codes == NULL
+     turns it off.  Needs at least 48 routes and whole residual scale groups per 256 inputs,
+     otherwise KEEPVQ_ERR_UNSUPPORTED. */
+  const uint8_t* res_codes;    /* [res_rows, out_dim, in_dim/8] */
+  const void* res_scales;      /* [res_rows, out_dim, res_groups], dtype scales_dtype */
+  int64_t res_rows;
+  int64_t res_groups;
+  const uint32_t* res_table;   /* KEEPVQ_TABLE_HALF2_PAIRS */
+  const uint32_t* hot_of_slot; /* [slots] */
 } keepvq_grouped_projection_args;
 
 int64_t keepvq_grouped_projection_workspace_bytes(int64_t routes, int64_t in_dim);

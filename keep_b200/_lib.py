@@ -107,7 +107,9 @@ class GroupedProjectionArgs(Structure):
         ("x", c_void_p), ("x_dtype", c_int32), ("routes", c_int64), ("rhs", c_void_p), ("codes", c_void_p), ("scales", c_void_p),
         ("scales_dtype", c_int32), ("slots", c_int64), ("out_dim", c_int64), ("in_dim", c_int64), ("groups", c_int64),
         ("codebook", c_void_p), ("codebook_all_odd", c_int32), ("out", c_void_p), ("out_dtype", c_int32),
-        ("workspace", c_void_p), ("workspace_bytes", c_int64),
+        ("workspace", c_void_p), ("workspace_bytes", c_int64), ("x_div", c_int32),
+        ("res_codes", c_void_p), ("res_scales", c_void_p), ("res_rows", c_int64), ("res_groups", c_int64),
+        ("res_table", c_void_p), ("hot_of_slot", c_void_p),
     ]
 
 
@@ -155,6 +157,7 @@ _SIGNATURES = {
     "keepvq_routed_topk": (c_int, [POINTER(RoutedTopkArgs), c_void_p]),
     "keepvq_moe_layer_workspace_bytes": (c_int64, [c_int64, c_int64, c_int64, c_int64, c_int32]),
     "keepvq_moe_layer_status_offset": (c_int64, [c_int64, c_int64, c_int64, c_int64, c_int32]),
+    "keepvq_moe_layer_route_output_offset": (c_int64, [c_int64, c_int64, c_int64, c_int64, c_int32]),
     "keepvq_moe_decode_layer": (c_int, [POINTER(MoELayerArgs), c_void_p]),
     "keepvq_moe_decode_stages": (c_int, [POINTER(MoELayerArgs), c_int32, c_void_p]),
     "keepvq_moe_decode_layer_static": (c_int, [POINTER(MoELayerArgs), c_void_p]),

@@ -17,6 +17,13 @@ struct GroupedScratch {
 
 static inline int64_t up256(int64_t v) { return (v + 255) / 256 * 256; }
 
+// The grouped kernels never touch the output row of a route that names no expert: this does.
+__global__ void __launch_bounds__(128) zero_dead_rows_kernel(const uint32_t* __restrict__ rhs, int64_t slots, void* out, int64_t row_bytes) {
+  if (rhs[blockIdx.x] < static_cast<uint64_t>(slots)) return;
+  uint8_t* row = reinterpret_cast<uint8_t*>(out) + static_cast<int64_t>(blockIdx.x) * row_bytes;
+  for (int64_t i = threadIdx.x * 2; i < row_bytes; i += 256) *reinterpret_cast<uint16_t*>(row + i) = 0;
+}
+
 static GroupedScratch plan_grouped(int64_t routes, int64_t in_dim) {
   GroupedScratch s;
   int64_t at = 0;
@@ -53,7 +60,18 @@ extern "C" int keepvq_grouped_projection(const keepvq_grouped_projection_args* a
   if (a.routes < 0 || a.slots <= 0 || a.out_dim <= 0 || a.in_dim <= 0 || a.in_dim % 8 || a.groups <= 0) return KEEPVQ_ERR_SHAPE;
   if (a.routes == 0) return KEEPVQ_OK;
   if (!a.x || !a.rhs || !a.codes || !a.scales || !a.codebook || !a.out || !a.workspace) return KEEPVQ_ERR_NULL;
+  if (a.x_dtype == KEEPVQ_F32) return KEEPVQ_ERR_UNSUPPORTED;  // these kernels keep 16 bits of a row: not what an fp32 caller asked for
   if (!a.codebook_all_odd || !fast::shapes_supported(a.out_dim, a.in_dim, a.groups)) return KEEPVQ_ERR_UNSUPPORTED;
+  const int32_t x_div = a.x_div > 0 ? a.x_div : 1;
+  if (a.routes % x_div) return KEEPVQ_ERR_SHAPE;
+  const int64_t x_rows = a.routes / x_div;
+  const bool residual = a.res_codes != nullptr;
+  if (residual) {
+    if (!a.res_scales || !a.res_table || !a.hot_of_slot) return KEEPVQ_ERR_NULL;
+    if (a.res_rows <= 0 || a.res_groups <= 0) return KEEPVQ_ERR_SHAPE;
+    if (!fast::residual_supported(a.routes, a.in_dim, a.res_groups)) return KEEPVQ_ERR_UNSUPPORTED;
+    if (!aligned_to(a.res_codes, 8)) return KEEPVQ_ERR_ALIGN;
+  }
   if (!aligned_to(a.x, 16) || !aligned_to(a.codes, 16) || !aligned_to(a.workspace, 256)) return KEEPVQ_ERR_ALIGN;
   const GroupedScratch sc = plan_grouped(a.routes, a.in_dim);
   if (a.workspace_bytes < sc.total) return KEEPVQ_ERR_CAPACITY;
@@ -63,19 +81,24 @@ extern "C" int keepvq_grouped_projection(const keepvq_grouped_projection_args* a
                               reinterpret_cast<int32_t*>(ws + sc.gstart), reinterpret_cast<int32_t*>(ws + sc.gsize),
                               reinterpret_cast<int32_t*>(ws + sc.groutes)};
   fast::QuantRows xq = {reinterpret_cast<uint8_t*>(ws + sc.xq), reinterpret_cast<float*>(ws + sc.xscale), reinterpret_cast<int32_t*>(ws + sc.xsums)};
-  const bool many = a.routes >= 1024 && a.routes >= 24 * a.slots && fast::prefill_supported(a.out_dim, a.in_dim, a.groups);
+  const bool many = !residual && a.routes >= 1024 && a.routes >= 24 * a.slots && fast::prefill_supported(a.out_dim, a.in_dim, a.groups);
   int32_t* wait_status = reinterpret_cast<int32_t*>(ws + sc.status);
   int rc;
-  if (many) {
+  {
     cudaError_t e = cudaMemsetAsync(wait_status, 0, sizeof(int32_t), s);
     if (e != cudaSuccess) return note_cuda_error(e);
   }
-  if ((rc = fast::group_routes(a.rhs, a.routes, a.slots, many ? fast::PREFILL_GROUP_ROUTES : fast::MAX_GROUP_ROUTES, groups, s))) return rc;
-  if ((rc = fast::quantize_rows(a.x, a.x_dtype, a.routes, a.in_dim, a.groups, xq, many, s))) return rc;
+  const int group_cols = many ? fast::PREFILL_GROUP_ROUTES : fast::decode_group_routes(a.routes, a.slots, a.in_dim);
+  if ((rc = fast::group_routes(a.rhs, a.routes, a.slots, group_cols, groups, s))) return rc;
+  if ((rc = fast::quantize_rows(a.x, a.x_dtype, x_rows, a.in_dim, a.groups, xq, many, s))) return rc;
   fast::FastProjectionArgs p = {};
-  p.a = {a.codes, a.scales, nullptr, nullptr}; p.b = {nullptr, nullptr, nullptr, nullptr};
-  p.scales_dtype = a.scales_dtype; p.codebook = a.codebook; p.groups_of_routes = groups; p.max_routes = a.routes;
-  p.out_dim = a.out_dim; p.in_dim = a.in_dim; p.groups = a.groups; p.x = xq; p.x_zero_row = a.routes; p.x_div = 1;
+  p.a = {a.codes, a.scales, a.res_codes, a.res_scales}; p.b = {nullptr, nullptr, nullptr, nullptr};
+  if (residual) { p.res_groups = a.res_groups; p.hot_of_slot = a.hot_of_slot; p.res_table = a.res_table; }
+  p.scales_dtype = a.scales_dtype; p.codebook = a.codebook; p.groups_of_routes = groups; p.max_routes = a.routes; p.group_cols = group_cols; p.status = wait_status;
+  p.out_dim = a.out_dim; p.in_dim = a.in_dim; p.groups = a.groups; p.x = xq; p.x_zero_row = x_rows; p.x_div = x_div;
   p.out = a.out; p.out_dtype = a.out_dtype; p.swiglu_limit = 0.0f; p.route_weight = nullptr;
+  if (a.routes > 0x7FFFFFFFll) return KEEPVQ_ERR_CAPACITY;
+  zero_dead_rows_kernel<<<static_cast<unsigned>(a.routes), 128, 0, s>>>(a.rhs, a.slots, a.out, a.out_dim * dtype_size(a.out_dtype));
+  KEEPVQ_CHECK_LAUNCH();
   return many ? fast::prefill_down(p, wait_status, s) : fast::down(p, s);
 }

@@ -399,496 +399,78 @@ __global__ void __launch_bounds__(CTA_THREADS, 1) projection_kernel(FastProjecti
   }
 }
 
-// ------------------------------------------------------------------------------------------
-// The same projection for batches with many route groups.  A CTA takes (route group, slab of
-// output rows); its 16 warps each own 16*TILES rows of the slab over the whole input dimension,
-// so there is no split-K reduction.
-//   - Codes stream through a private two-stage cp.async ring per warp (a lane copies and later
-//     reads back its own 16-byte pieces), so the next chunk is always in flight behind the one
-//     being decoded, whatever order the compiler gives the instructions.
-//   - The group's quantised activations (the B operand, up to 64 KB) are staged once per item
-//     into shared memory in MMA-fragment order.
-//   - Two decoders share the work so that neither the integer pipe nor shared-memory bandwidth
-//     is the only limit: the arithmetic one of the team kernel (one table read), and one that
-//     reads a second table indexed by the sign byte, whose entry is the XOR mask the arithmetic
-//     computes (sign flips, the parity bit of every byte, the extra flip of table nibble 0 on
-//     odd parity).  TABLE_STEPS says which steps of a chunk use the second.
-// ------------------------------------------------------------------------------------------
-constexpr int CK_WARPS = 16;
-constexpr int CK_THREADS = CK_WARPS * 32;
-constexpr int CK_MAX_CHUNKS = 16;                                   // in_dim <= 4096
-constexpr int CK_B_BYTES = CK_MAX_CHUNKS * 8 * 32 * 16;             // 64 KB
-constexpr int CK_MAX_CHUNKS_WIDE = 24;                              // in_dim <= 6144: the activations take the sign table's room too
-constexpr int CK_ABS_BYTES = LUT_BYTES;                             // 64 KB: [abs row][parity][replica]
-constexpr int CK_SIGN_BYTES = 256 * LUT_REPLICAS * 8;               // 32 KB: [sign byte][replica]
-constexpr int CK_STAGES = 2;
-constexpr unsigned TABLE_STEPS = 0xEEu;  // bit i set: step i of a chunk decodes through the sign table
-
-__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
-
-__device__ __forceinline__ uint4 lds128(uint32_t addr) {
-  uint4 v;
-  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
-  return v;
-}
-__device__ __forceinline__ uint2 lds64(uint32_t addr) {
-  uint2 v;
-  asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
-  return v;
-}
-
-// The int8 MMA has a long dependent-accumulate latency (about 290 cycles measured), so each
-// (matrix, tile, byte) keeps two accumulators, used by alternate steps, to double the number of
-// independent MMA chains in flight.
-// MODE 0 is the product.  The others are measurement aids selected by KEEPVQ_PROJECTION_MODE and
-// their outputs are meaningless: 1 = loads only, 3 = no decode (raw words into the MMA),
-// 4 = no MMA.
-template <int M, int TILES, int MODE, bool USE_SIGN_TABLE>
-__device__ __forceinline__ void decode_chunk(uint32_t abs_lane, uint32_t sign_lane, const uint4 (&codes)[M][2 * TILES], uint32_t b_addr,
-                                             int (&acc_h)[2][M][TILES][4], int (&acc_l)[2][M][TILES][4]) {
-#pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    const uint4 b = lds128(b_addr + i * 512);  // (hi k0-3, hi k16-19, lo k0-3, lo k16-19) of step i
-#pragma unroll
-    for (int m = 0; m < M; ++m)
-#pragma unroll
-      for (int tl = 0; tl < TILES; ++tl) {
-        uint32_t a[4];
-#pragma unroll
-        for (int half = 0; half < 2; ++half) {  // rows g and g + 8 of the tile
-          const uint4 v = codes[m][2 * tl + half];
-          const uint32_t word = (i >> 1) == 0 ? v.x : (i >> 1) == 1 ? v.y : (i >> 1) == 2 ? v.z : v.w;
-          uint32_t sign, abs_off;  // sign byte; abs row * 256 (its even-parity entry, 16 replicas of 8 bytes)
-          if (i & 1) {
-            asm("prmt.b32 %0, %1, %2, %3;" : "=r"(sign) : "r"(word), "r"(0u), "r"(0x4442u));
-            asm("prmt.b32 %0, %1, %2, %3;" : "=r"(abs_off) : "r"(word), "r"(0u), "r"(0x4434u));
-          } else {
-            sign = word & 0xFFu;
-            abs_off = word & 0xFF00u;
-          }
-          if (MODE == 3) {
-            a[half] = sign;
-            a[2 + half] = abs_off;
-          } else if (USE_SIGN_TABLE && ((TABLE_STEPS >> i) & 1u)) {
-            const uint2 e = lds64(abs_lane + abs_off), x = lds64(sign_lane + (sign << 7));
-            a[half] = e.x ^ x.x;
-            a[2 + half] = e.y ^ x.y;
-          } else {
-            decode_to_fragment(abs_lane, sign, abs_off, a[half], a[2 + half]);
-          }
-        }
-        if (MODE == 4) {
-#pragma unroll
-          for (int r = 0; r < 4; ++r) acc_h[i & 1][m][tl][r] += a[r] ^ b.x;
-        } else {
-          mma_s8s8(acc_h[i & 1][m][tl], a[0], a[1], a[2], a[3], b.x, b.y);
-          mma_s8s8(acc_l[i & 1][m][tl], a[0], a[1], a[2], a[3], b.z, b.w);
-        }
-      }
-  }
-}
-
-// NESTED: the layer has a residual tier.  The second table then holds the residual codebook
-// instead of the sign masks (the base decode does its signs on the integer pipe in every step),
-// and an item whose slot is hot runs a second pass over the residual's 8-bit codes: one table
-// read per codeword gives the int8 operand 2v directly (no signs, no parity, no offset term).
-// WIDE: input dimensions of 4097..6144 (the shipped artifacts' 5120).  Their staged activations
-// need 96 KB, so the sign table goes and every step decodes its signs on the integer pipe.
-template <int M, int TILES, int MODE, bool NESTED, bool WIDE = false>
-__global__ void __launch_bounds__(CK_THREADS, 1) projection_cta_kernel(FastProjectionArgs p) {
-  static_assert(!(NESTED && WIDE), "the residual table and the wide activation stage want the same shared memory");
-  extern __shared__ __align__(16) uint8_t smem[];
-  grid_launch_dependents();
-  // ---- tables -----------------------------------------------------------------------------
-  for (int e = threadIdx.x; e < (WIDE ? 512 : 768); e += CK_THREADS) {
-    uint32_t lo = 0, hi = 0;
-    if (e >= 512 && NESTED) {  // residual entry: byte j of the low word is 2 * v[6 - 2j], of the high word 2 * v[7 - 2j]
-      const uint32_t* row = p.res_table + (e - 512) * 4;
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const __half2 pair = *reinterpret_cast<const __half2*>(&row[3 - j]);  // dims 6 - 2j, 7 - 2j
-        lo |= (static_cast<uint32_t>(__float2int_rn(2.0f * __low2float(pair))) & 0xFFu) << (8 * j);
-        hi |= (static_cast<uint32_t>(__float2int_rn(2.0f * __high2float(pair))) & 0xFFu) << (8 * j);
-      }
-    } else if (e < 512) {  // abs entry (row e/2, parity e&1): byte j of the low word is table nibble 3-j, of the high word 7-j
-      const uint32_t word = p.codebook[e >> 1], par = e & 1;
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const int nl = 3 - j, nh = 7 - j;
-        uint32_t hl = ((word >> (4 * nl)) & 0xFu) - 8u, hh = ((word >> (4 * nh)) & 0xFu) - 8u;
-        if (par) { hl = nl == 0 ? ~hl : hl ^ 1u; hh ^= 1u; }
-        lo |= (hl & 0xFFu) << (8 * j);
-        hi |= (hh & 0xFFu) << (8 * j);
-      }
-    } else {        // sign entry: 0xFE where the sign bit is set, ^1 everywhere (^0xFF on nibble 0) on odd parity
-      const uint32_t sb = e - 512, par = __popc(sb) & 1u;
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const int nl = 3 - j, nh = 7 - j;
-        uint32_t ml = ((sb >> nl) & 1u) ? 0xFEu : 0u, mh = ((sb >> nh) & 1u) ? 0xFEu : 0u;
-        if (par) { ml ^= nl == 0 ? 0xFFu : 0x01u; mh ^= 0x01u; }
-        lo |= ml << (8 * j);
-        hi |= mh << (8 * j);
-      }
-    }
-    uint2* dst = reinterpret_cast<uint2*>(smem) + e * LUT_REPLICAS;  // abs table, then sign table
-#pragma unroll
-    for (int r = 0; r < LUT_REPLICAS; ++r) dst[r] = make_uint2(lo, hi);
-  }
-
-  grid_wait();  // the tables came from constants; everything below reads what earlier kernels of the stream wrote
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int g = lane >> 2, t = lane & 3;
-  const uint32_t smem_base = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
-  const uint32_t abs_lane = smem_base + (lane & (LUT_REPLICAS - 1)) * 8;
-  const uint32_t sign_lane = abs_lane + CK_ABS_BYTES;
-  const uint32_t b_base = smem_base + CK_ABS_BYTES + (WIDE ? 0 : CK_SIGN_BYTES);
-  constexpr int B_BYTES = CK_B_BYTES + (WIDE ? CK_SIGN_BYTES : 0);
-  constexpr int STREAMS = M * 2 * TILES;                 // 16-byte pieces a lane owns per chunk
-  constexpr int STAGE_BYTES = STREAMS * 512;             // per warp
-  const uint32_t ring = b_base + B_BYTES + warp * (CK_STAGES * STAGE_BYTES) + lane * 16;
-  const int64_t N = p.out_dim, cw = p.in_dim / 8;
-  const int n_chunks = static_cast<int>(cw / CHUNK_CODES);
-  const int chunks_per_group = n_chunks / static_cast<int>(p.groups);
-  constexpr int ROWS = 16 * TILES;              // per warp
-  constexpr int SLAB = ROWS * CK_WARPS;         // per CTA item
-  const int slabs = static_cast<int>((N + SLAB - 1) / SLAB);
-  const int items = p.groups_of_routes.count[0] * slabs;
-  const Projection mats[2] = {p.a, p.b};
-
-  // A CTA takes a contiguous run of items, so consecutive items mostly belong to one route group
-  // and its activations are staged once for all of them.
-  // (With a residual tier the items of a hot slot cost half as much again, and a run of them on
-  // one CTA would unbalance the grid: those layers deal the items out round-robin instead.)
-  const int per_cta = (items + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x);
-  const int first_item = NESTED ? static_cast<int>(blockIdx.x) : static_cast<int>(blockIdx.x) * per_cta;
-  const int last_item = NESTED ? items : min(items, first_item + per_cta);
-  const int item_step = NESTED ? static_cast<int>(gridDim.x) : 1;
-  int staged_group = -1;
-  for (int item = first_item; item < last_item; item += item_step) {
-    const int gi = item / slabs, slab = item - gi * slabs;
-    const int64_t slot = p.groups_of_routes.slot[gi];
-    const int gsize = p.groups_of_routes.size[gi], gstart = p.groups_of_routes.start[gi];
-    const int64_t row0 = static_cast<int64_t>(slab) * SLAB + warp * ROWS;
-    const bool active = row0 < N;
-    const uint16_t* row_ptr[M][2 * TILES];
-#pragma unroll
-    for (int m = 0; m < M; ++m)
-#pragma unroll
-      for (int j = 0; j < 2 * TILES; ++j)
-        row_ptr[m][j] = mats[m].codes + (slot * N + min(row0 + 8 * j + g, N - 1)) * cw + t * 8;
-    auto fetch = [&](int c) {  // chunk c of this lane's row streams -> ring stage c % CK_STAGES
-      if (active && c < n_chunks) {
-        const uint32_t dst = ring + (c % CK_STAGES) * STAGE_BYTES;
-#pragma unroll
-        for (int m = 0; m < M; ++m)
-#pragma unroll
-          for (int j = 0; j < 2 * TILES; ++j) cp_async16(dst + (m * 2 * TILES + j) * 512, row_ptr[m][j] + c * CHUNK_CODES);
-      }
-      cp_async_commit();
-    };
-
-    if (gi != staged_group) {
-      __syncthreads();  // every warp is done with the previous group's activations (and the tables are built)
-      {                 // stage this group's activations in fragment order: [chunk * 8 + step][lane]
-        const int route = g < gsize ? p.groups_of_routes.routes[gstart + g] : -1;
-        const uint4* src = reinterpret_cast<const uint4*>(p.x.q) + (route < 0 ? p.x_zero_row : static_cast<int64_t>(route / p.x_div)) * cw + t * 8;
-        for (int step = warp; step < n_chunks * 8; step += CK_WARPS)
-          cp_async16(b_base + lane * 16 + step * 512, src + (step >> 3) * CHUNK_CODES + (step & 7));
-        cp_async_commit();
-      }
-      fetch(0);
-      cp_async_wait<1>();  // the activations (the older group) have landed
-      __syncthreads();
-      staged_group = gi;
-    } else {
-      fetch(0);
-    }
-    if (!active) { cp_async_wait<0>(); continue; }
-
-    float part[M][TILES][4];
-    int acc_h[2][M][TILES][4], acc_l[2][M][TILES][4];
-#pragma unroll
-    for (int m = 0; m < M; ++m)
-#pragma unroll
-      for (int tl = 0; tl < TILES; ++tl)
-#pragma unroll
-        for (int r = 0; r < 4; ++r) {
-          part[m][tl][r] = 0.0f;
-          acc_h[0][m][tl][r] = acc_h[1][m][tl][r] = 0;
-          acc_l[0][m][tl][r] = acc_l[1][m][tl][r] = 0;
-        }
-    // what the epilogue needs of this lane's two routes (columns 2t, 2t + 1), asked for now so
-    // that the loads fly behind the main loop instead of in front of the stores
-    int ep_route[2];
-    float ep_xs[2], ep_weight[2], ep_sum[2];
-#pragma unroll
-    for (int cc = 0; cc < 2; ++cc) {
-      const int col = 2 * t + cc;
-      ep_route[cc] = col < gsize ? p.groups_of_routes.routes[gstart + col] : -1;
-      const int64_t xrow = ep_route[cc] < 0 ? p.x_zero_row : static_cast<int64_t>(ep_route[cc] / p.x_div);
-      ep_xs[cc] = p.x.scale[xrow];
-      ep_weight[cc] = (M == 2 && ep_route[cc] >= 0) ? p.route_weight[ep_route[cc]] : 1.0f;
-      ep_sum[cc] = static_cast<float>(p.x.sums[xrow * p.groups]);  // the only group when the rows have one scale
-    }
-    float row_scale[M][TILES][4];  // the last scale group's scale of each accumulator row
-
-    for (int c = 0; c < n_chunks; ++c) {
-      fetch(c + 1);
-      cp_async_wait<1>();  // chunk c has landed (the younger group may still fly)
-      uint4 cur[M][2 * TILES];
-      const uint32_t src = ring + (c % CK_STAGES) * STAGE_BYTES;
-#pragma unroll
-      for (int m = 0; m < M; ++m)
-#pragma unroll
-        for (int j = 0; j < 2 * TILES; ++j) cur[m][j] = lds128(src + (m * 2 * TILES + j) * 512);
-      if (MODE == 1) {
-#pragma unroll
-        for (int m = 0; m < M; ++m)
-#pragma unroll
-          for (int j = 0; j < 2 * TILES; ++j) acc_h[0][m][j / 2][j & 1] += cur[m][j].x ^ cur[m][j].y ^ cur[m][j].z ^ cur[m][j].w;
-      } else {
-        decode_chunk<M, TILES, MODE, !NESTED && !WIDE>(abs_lane, sign_lane, cur, b_base + lane * 16 + c * 8 * 512, acc_h, acc_l);
-      }
-      const int group = c / chunks_per_group;
-      if (c + 1 == n_chunks || (c + 1) / chunks_per_group != group) {
-#pragma unroll
-        for (int m = 0; m < M; ++m)
-#pragma unroll
-          for (int tl = 0; tl < TILES; ++tl)
-#pragma unroll
-            for (int r = 0; r < 4; ++r) {
-              const int64_t row = min(row0 + 16 * tl + g + (r >= 2 ? 8 : 0), N - 1);
-              const float sc = load_as_float(mats[m].scales, p.scales_dtype, (slot * N + row) * p.groups + group);
-              const int hi = acc_h[0][m][tl][r] + acc_h[1][m][tl][r], lo = acc_l[0][m][tl][r] + acc_l[1][m][tl][r];
-              part[m][tl][r] = fmaf(sc, 256.0f * static_cast<float>(hi) + static_cast<float>(lo), part[m][tl][r]);
-              row_scale[m][tl][r] = sc;
-              acc_h[0][m][tl][r] = acc_h[1][m][tl][r] = 0;
-              acc_l[0][m][tl][r] = acc_l[1][m][tl][r] = 0;
-            }
-      }
-    }
-    cp_async_wait<0>();
-
-    // ---- the residual of a hot slot: a second pass over its 8-bit codes ---------------------
-    float rpart[M][TILES][4];
-#pragma unroll
-    for (int m = 0; m < M; ++m)
-#pragma unroll
-      for (int tl = 0; tl < TILES; ++tl)
-#pragma unroll
-        for (int r = 0; r < 4; ++r) rpart[m][tl][r] = 0.0f;
-    if (NESTED) {
-      const uint32_t hot = p.hot_of_slot[slot];
-      if (hot != 0xFFFFFFFFu) {
-        const int chunks_per_res_group = n_chunks / static_cast<int>(p.res_groups);
-        const uint8_t* res_ptr[M][2 * TILES];
-#pragma unroll
-        for (int m = 0; m < M; ++m)
-#pragma unroll
-          for (int j = 0; j < 2 * TILES; ++j)
-            res_ptr[m][j] = mats[m].res_codes + (static_cast<int64_t>(hot) * N + min(row0 + 8 * j + g, N - 1)) * cw + t * 8;
-        auto fetch_res = [&](int c) {  // 8 codes of 8 bits per row stream
-          if (c < n_chunks) {
-            const uint32_t dst = ring + (c % CK_STAGES) * STAGE_BYTES;
-#pragma unroll
-            for (int m = 0; m < M; ++m)
-#pragma unroll
-              for (int j = 0; j < 2 * TILES; ++j)
-                asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(dst + (m * 2 * TILES + j) * 512), "l"(res_ptr[m][j] + c * CHUNK_CODES) : "memory");
-          }
-          cp_async_commit();
-        };
-        fetch_res(0);
-        for (int c = 0; c < n_chunks; ++c) {
-          fetch_res(c + 1);
-          cp_async_wait<1>();
-          uint2 cur[M][2 * TILES];
-          const uint32_t src = ring + (c % CK_STAGES) * STAGE_BYTES;
-#pragma unroll
-          for (int m = 0; m < M; ++m)
-#pragma unroll
-            for (int j = 0; j < 2 * TILES; ++j) cur[m][j] = lds64(src + (m * 2 * TILES + j) * 512);
-          const uint32_t b_addr = b_base + lane * 16 + c * 8 * 512;
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const uint4 b = lds128(b_addr + i * 512);
-#pragma unroll
-            for (int m = 0; m < M; ++m)
-#pragma unroll
-              for (int tl = 0; tl < TILES; ++tl) {
-                uint32_t a[4];
-#pragma unroll
-                for (int half = 0; half < 2; ++half) {
-                  const uint2 v = cur[m][2 * tl + half];
-                  const uint32_t code = ((i < 4 ? v.x : v.y) >> (8 * (i & 3))) & 0xFFu;
-                  const uint2 e = lds64(sign_lane + (code << 7));  // the second table is the residual codebook here
-                  a[half] = e.x;
-                  a[2 + half] = e.y;
-                }
-                mma_s8s8(acc_h[i & 1][m][tl], a[0], a[1], a[2], a[3], b.x, b.y);
-                mma_s8s8(acc_l[i & 1][m][tl], a[0], a[1], a[2], a[3], b.z, b.w);
-              }
-          }
-          const int group = c / chunks_per_res_group;
-          if (c + 1 == n_chunks || (c + 1) / chunks_per_res_group != group) {
-#pragma unroll
-            for (int m = 0; m < M; ++m)
-#pragma unroll
-              for (int tl = 0; tl < TILES; ++tl)
-#pragma unroll
-                for (int r = 0; r < 4; ++r) {
-                  const int64_t row = min(row0 + 16 * tl + g + (r >= 2 ? 8 : 0), N - 1);
-                  const float sc = load_as_float(mats[m].res_scales, p.scales_dtype, (static_cast<int64_t>(hot) * N + row) * p.res_groups + group);
-                  const int hi = acc_h[0][m][tl][r] + acc_h[1][m][tl][r], lo = acc_l[0][m][tl][r] + acc_l[1][m][tl][r];
-                  rpart[m][tl][r] = fmaf(sc, 256.0f * static_cast<float>(hi) + static_cast<float>(lo), rpart[m][tl][r]);
-                  acc_h[0][m][tl][r] = acc_h[1][m][tl][r] = 0;
-                  acc_l[0][m][tl][r] = acc_l[1][m][tl][r] = 0;
-                }
-          }
-        }
-        cp_async_wait<0>();
-      }
-    }
-
-    // ---- epilogue in registers: lane (g, t) holds rows {g, g+8} of each tile, columns {2t, 2t+1}
-#pragma unroll
-    for (int cc = 0; cc < 2; ++cc) {
-      const int route = ep_route[cc];
-      if (route < 0) continue;
-      const int64_t xrow = route / p.x_div;
-      const float xs = ep_xs[cc];
-      const float weight = ep_weight[cc];
-#pragma unroll
-      for (int tl = 0; tl < TILES; ++tl)
-#pragma unroll
-        for (int rr = 0; rr < 2; ++rr) {
-          const int r = 2 * rr + cc;
-          const int64_t row = row0 + 16 * tl + g + 8 * rr;
-          if (row >= N) continue;
-          float y[M];
-#pragma unroll
-          for (int m = 0; m < M; ++m) {
-            float shift = 0.0f;  // the +-1/4 of every weight, folded into sum(x') per scale group
-            if (p.groups == 1) {
-              shift = row_scale[m][tl][r] * ep_sum[cc];
-            } else {
-              for (int64_t q = 0; q < p.groups; ++q)
-                shift = fmaf(load_as_float(mats[m].scales, p.scales_dtype, (slot * N + row) * p.groups + q),
-                             static_cast<float>(p.x.sums[xrow * p.groups + q]), shift);
-            }
-            y[m] = xs * (0.5f * (part[m][tl][r] + rpart[m][tl][r]) + 0.25f * shift);  // a residual weight is q / 2 with no offset
-          }
-          float result;
-          if (M == 2) {
-            float gt = y[0], up = y[M - 1];
-            if (p.out_dtype == KEEPVQ_BF16) { gt = __bfloat162float(__float2bfloat16_rn(gt)); up = __bfloat162float(__float2bfloat16_rn(up)); }
-            else if (p.out_dtype == KEEPVQ_F16) { gt = __half2float(__float2half_rn(gt)); up = __half2float(__float2half_rn(up)); }
-            if (p.swiglu_limit > 0.0f) { gt = fminf(gt, p.swiglu_limit); up = fminf(fmaxf(up, -p.swiglu_limit), p.swiglu_limit); }
-            result = gt / (1.0f + expf(-gt)) * up * weight;
-          } else {
-            result = y[0];
-          }
-          store_from_float(p.out, p.out_dtype, static_cast<int64_t>(route) * N + row, result);
-        }
-    }
-  }
-  cp_async_wait<0>();
-}
-
 bool shapes_supported(int64_t out_dim, int64_t in_dim, int64_t groups) {
   if (in_dim % (8 * CHUNK_CODES) != 0 || groups <= 0) return false;
   const int64_t chunks = in_dim / (8 * CHUNK_CODES);
   return chunks % groups == 0 && out_dim > 0;
 }
 
-static int sm_count() {
-  static int cached = 0;
-  if (!cached) {
-    int dev = 0, n = 0;
-    cudaGetDevice(&dev);
+// SM count of the current device (cached per device ordinal).
+static int sm_count(int* device_out) {
+  constexpr int MAX_DEVICES = 64;
+  static int cached[MAX_DEVICES] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (device_out) *device_out = dev;
+  if (dev < 0 || dev >= MAX_DEVICES) return 148;
+  if (!cached[dev]) {
+    int n = 0;
     cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
-    cached = n > 0 ? n : 148;
+    cached[dev] = n > 0 ? n : 148;
   }
-  return cached;
+  return cached[dev];
 }
 
 template <int M, int TILES>
 static int launch_projection(const FastProjectionArgs& p, cudaStream_t s) {
   constexpr size_t smem = LUT_BYTES + static_cast<size_t>(TEAMS) * TEAM_WARPS * (M * TILES * 4) * 32 * sizeof(float);
-  static bool configured = false;
-  if (!configured) {
+  static uint64_t configured = 0;  // one bit per device: the shared-memory opt-in is a per-device attribute of the function
+  int dev = 0;
+  const int sms = sm_count(&dev);
+  if (dev < 0 || dev >= 64 || !((configured >> dev) & 1ull)) {
     cudaError_t e = cudaFuncSetAttribute(projection_kernel<M, TILES>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     if (e != cudaSuccess) return note_cuda_error(e);
-    configured = true;
+    if (dev >= 0 && dev < 64) configured |= 1ull << dev;
   }
-  cudaError_t err = launch_after(true, projection_kernel<M, TILES>, sm_count(), CTA_THREADS, smem, s, p);
+  cudaError_t err = launch_after(true, projection_kernel<M, TILES>, sms, CTA_THREADS, smem, s, p);
   if (err != cudaSuccess) return note_cuda_error(err);
   return KEEPVQ_OK;
-}
-
-template <int M, int TILES, int MODE, bool NESTED = false, bool WIDE = false>
-static int launch_projection_cta_mode(const FastProjectionArgs& p, cudaStream_t s) {
-  constexpr size_t smem = CK_ABS_BYTES + CK_SIGN_BYTES + CK_B_BYTES + CK_WARPS * CK_STAGES * (M * 2 * TILES * 512);
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(projection_cta_kernel<M, TILES, MODE, NESTED, WIDE>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-    if (e != cudaSuccess) return note_cuda_error(e);
-    configured = true;
-  }
-  cudaError_t err = launch_after(true, projection_cta_kernel<M, TILES, MODE, NESTED, WIDE>, sm_count(), CK_THREADS, smem, s, p);
-  if (err != cudaSuccess) return note_cuda_error(err);
-  return KEEPVQ_OK;
-}
-
-static int diagnostic_mode() {
-  static int mode = -1;
-  if (mode < 0) {
-    const char* v = getenv("KEEPVQ_PROJECTION_MODE");
-    mode = v ? atoi(v) : 0;
-    if (mode < 0 || mode > 4) mode = 0;
-  }
-  return mode;
-}
-
-template <int M, int TILES>
-static int launch_projection_cta(const FastProjectionArgs& p, cudaStream_t s) {
-  if (p.res_table) return launch_projection_cta_mode<M, TILES, 0, true>(p, s);
-  if (p.in_dim > 8 * CHUNK_CODES * CK_MAX_CHUNKS) return launch_projection_cta_mode<M, TILES, 0, false, true>(p, s);
-  switch (diagnostic_mode()) {
-    case 1: return launch_projection_cta_mode<M, TILES, 1>(p, s);
-    case 3: return launch_projection_cta_mode<M, TILES, 3>(p, s);
-    case 4: return launch_projection_cta_mode<M, TILES, 4>(p, s);
-    default: return launch_projection_cta_mode<M, TILES, 0>(p, s);
-  }
 }
 
 // Enough routes to give every CTA of the machine its own (group, slab) items, and activations
 // that fit the shared-memory stage?
 static bool many_items(const FastProjectionArgs& p) {
-  const int64_t widest = 8 * CHUNK_CODES * (p.res_table ? CK_MAX_CHUNKS : CK_MAX_CHUNKS_WIDE);
-  return p.max_routes >= 48 && p.in_dim <= widest;
+  return p.max_routes >= 48 && p.in_dim <= slab_max_in_dim(p.group_cols > PAIRED_GROUP_ROUTES ? MAX_GROUP_ROUTES : PAIRED_GROUP_ROUTES);
 }
 
-// The residual pass lives in the CTA kernel only: a layer with a residual tier needs enough routes
+#ifdef KEEPVQ_DIAG
+static int g_force_cols = 0;
+extern "C" void keepvq_diag_set_group_cols(int cols) { g_force_cols = cols; }
+#endif
+
+int decode_group_routes(int64_t live, int64_t slots, int64_t widest_in_dim) {
+#ifdef KEEPVQ_DIAG
+  if (g_force_cols) return g_force_cols;
+#endif
+  if (live < 48) return MAX_GROUP_ROUTES;  // the team kernel: its tile has eight columns either way
+  if (widest_in_dim > slab_max_in_dim(MAX_GROUP_ROUTES)) return PAIRED_GROUP_ROUTES;
+  return live <= 2 * slots ? PAIRED_GROUP_ROUTES : MAX_GROUP_ROUTES;
+}
+
+// The residual pass lives in the slab kernel only: a layer with a residual tier needs enough routes
 // for that kernel and residual scale groups that close on chunk boundaries.
 bool residual_supported(int64_t routes, int64_t in_dim, int64_t res_groups) {
-  if (routes < 48 || in_dim > 8 * CHUNK_CODES * CK_MAX_CHUNKS || in_dim % (8 * CHUNK_CODES) != 0 || res_groups <= 0) return false;
+  if (routes < 48 || in_dim > slab_max_in_dim(PAIRED_GROUP_ROUTES) || in_dim % (8 * CHUNK_CODES) != 0 || res_groups <= 0) return false;
   return (in_dim / (8 * CHUNK_CODES)) % res_groups == 0;
 }
 
 int gate_up(const FastProjectionArgs& p, cudaStream_t s) {
   if (p.res_table && !many_items(p)) return KEEPVQ_ERR_UNSUPPORTED;
-  return many_items(p) ? launch_projection_cta<2, 1>(p, s) : launch_projection<2, 2>(p, s);
+  return many_items(p) ? slab_gate_up(p, p.group_cols > PAIRED_GROUP_ROUTES ? MAX_GROUP_ROUTES : PAIRED_GROUP_ROUTES, s) : launch_projection<2, 2>(p, s);
 }
 int down(const FastProjectionArgs& p, cudaStream_t s) {
   if (p.res_table && !many_items(p)) return KEEPVQ_ERR_UNSUPPORTED;
-  return many_items(p) ? launch_projection_cta<1, 2>(p, s) : launch_projection<1, 4>(p, s);
+  return many_items(p) ? slab_down(p, p.group_cols > PAIRED_GROUP_ROUTES ? MAX_GROUP_ROUTES : PAIRED_GROUP_ROUTES, s) : launch_projection<1, 4>(p, s);
 }
 
 }  // namespace fast

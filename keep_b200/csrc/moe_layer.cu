@@ -9,11 +9,12 @@
 //   6 fp32 sum over the k picks, one rounding       this file
 // The rounding points are the served path's (scripts/v41_build/omlx_lattice.py:356-371,583-589).
 //
-// Two sets of kernels serve steps 3-5.  The tensor-core set (moe_fast.cu) groups routes by slot,
-// quantises activations to 16-bit fixed point and runs the projections on the int8 tensor cores,
-// SwiGLU fused into the gate/up epilogue; it needs a table whose entries are all odd half-units
-// (true of the E8P table; the caller vouches with `codebook_all_odd`), input dims and scale groups
-// that are multiples of 256, and no residual tier.  Everything else takes the general kernels.
+// Two sets of kernels serve steps 3-5.  The tensor-core set (moe_fast.cu, projection_slab.cu,
+// prefill_umma.cu) groups routes by slot, quantises activations to 16-bit fixed point and runs the
+// projections on the int8 tensor cores, SwiGLU fused into the gate/up epilogue; it needs a table
+// whose entries are all odd half-units (true of the E8P table; the caller vouches with
+// `codebook_all_odd`) and input dims and scale groups that are multiples of 256.  Everything else
+// takes the general kernel (rowdot.cu).
 //
 // Scratch layout (all regions 256-byte aligned):
 //   logits [tokens, pool] f32 | gate [routes, inter] | up [routes, inter] | h [routes, inter]
@@ -157,6 +158,11 @@ extern "C" int64_t keepvq_moe_layer_status_offset(int64_t tokens, int64_t hidden
   return keepvq::plan_scratch(tokens, hidden, inter, pool, top_k).status;
 }
 
+extern "C" int64_t keepvq_moe_layer_route_output_offset(int64_t tokens, int64_t hidden, int64_t inter, int64_t pool, int32_t top_k) {
+  if (tokens < 0 || hidden <= 0 || inter <= 0 || pool <= 0 || top_k <= 0) return KEEPVQ_ERR_SHAPE;
+  return keepvq::plan_scratch(tokens, hidden, inter, pool, top_k).down;
+}
+
 extern "C" int keepvq_moe_decode_stages(const keepvq_moe_layer_args* args, int32_t stages, void* stream) {
   using namespace keepvq;
   if (!args) return KEEPVQ_ERR_NULL;
@@ -181,7 +187,8 @@ extern "C" int keepvq_moe_decode_stages(const keepvq_moe_layer_args* args, int32
   const bool residual_fits = !residual || (a.w1.res_codes && a.w3.res_codes && a.w2.res_codes && a.res_table && a.hot_of_slot &&
                                            a.w3.res_groups == a.w1.res_groups && fast::residual_supported(routes, a.hidden, a.w1.res_groups) &&
                                            fast::residual_supported(routes, a.inter, a.w2.res_groups));
-  const bool tensor_path = a.codebook_all_odd && residual_fits && fast::shapes_supported(a.inter, a.hidden, a.w1.groups) &&
+  // (fp32 activations take the general kernel, which keeps 24 bits of a row instead of 16)
+  const bool tensor_path = a.x_dtype != KEEPVQ_F32 && a.codebook_all_odd && residual_fits && fast::shapes_supported(a.inter, a.hidden, a.w1.groups) &&
                            fast::shapes_supported(a.hidden, a.inter, a.w2.groups);
   int rc = KEEPVQ_OK;
 
@@ -211,16 +218,17 @@ extern "C" int keepvq_moe_decode_stages(const keepvq_moe_layer_args* args, int32
     const bool prefill = !residual && live >= PREFILL_MIN_ROUTES && live >= PREFILL_MIN_ROUTES_PER_SLOT * a.slots && fast::prefill_supported(a.inter, a.hidden, a.w1.groups) &&
                          fast::prefill_supported(a.hidden, a.inter, a.w2.groups);
     int32_t* wait_status = reinterpret_cast<int32_t*>(ws + sc.status);
+    const int group_cols = prefill ? fast::PREFILL_GROUP_ROUTES : fast::decode_group_routes(live, a.slots, std::max(a.hidden, a.inter));
     if (stages & KEEPVQ_STAGE_PREPARE) {
-      if (prefill) {
+      if (prefill || routes >= 48) {  // the kernels that can set the word
         cudaError_t e = cudaMemsetAsync(wait_status, 0, sizeof(int32_t), s);
         if (e != cudaSuccess) return note_cuda_error(e);
       }
-      if ((rc = fast::group_routes(a.served_slot, routes, a.slots, prefill ? fast::PREFILL_GROUP_ROUTES : fast::MAX_GROUP_ROUTES, groups, s))) return rc;
+      if ((rc = fast::group_routes(a.served_slot, routes, a.slots, group_cols, groups, s))) return rc;
       if ((rc = fast::quantize_rows(a.x, a.x_dtype, a.tokens, a.hidden, a.w1.groups, xq, prefill, s))) return rc;
     }
     fast::FastProjectionArgs p = {};
-    p.scales_dtype = a.scales_dtype; p.codebook = a.codebook; p.groups_of_routes = groups; p.max_routes = routes;
+    p.scales_dtype = a.scales_dtype; p.codebook = a.codebook; p.groups_of_routes = groups; p.max_routes = routes; p.group_cols = group_cols; p.status = wait_status;
     p.out_dtype = a.x_dtype; p.swiglu_limit = a.swiglu_limit; p.route_weight = a.served_weight;
     if (stages & KEEPVQ_STAGE_GATE_UP) {
       p.a = {a.w1.codes, a.w1.scales, a.w1.res_codes, a.w1.res_scales}; p.b = {a.w3.codes, a.w3.scales, a.w3.res_codes, a.w3.res_scales};

@@ -416,20 +416,28 @@ bool prefill_supported(int64_t out_dim, int64_t in_dim, int64_t groups) {
   return groups == 1 && in_dim % (8 * PF_KBLOCK_CODES) == 0 && out_dim > 0;
 }
 
+#ifdef KEEPVQ_DIAG
+static int g_prefill_diag = 0;
+extern "C" void keepvq_diag_set_prefill(int mode) { g_prefill_diag = mode; }
+#endif
+
 template <int M, bool GLU>
 static int launch_prefill(const FastProjectionArgs& p, int32_t* status, cudaStream_t s) {
   constexpr size_t smem = PF_A_STAGES * M * PF_TILE_BYTES + PF_B_STAGES * PF_B_STAGE_BYTES + PF_TABLE_BYTES + PF_CODE_RING_BYTES + 1024;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(prefill_projection_kernel<M, GLU>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-    if (e != cudaSuccess) return note_cuda_error(e);
-    configured = true;
-  }
+  static uint64_t configured = 0;  // one bit per device: the shared-memory opt-in is a per-device attribute of the function
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64 || !((configured >> dev) & 1ull)) {
+    cudaError_t e = cudaFuncSetAttribute(prefill_projection_kernel<M, GLU>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (e != cudaSuccess) return note_cuda_error(e);
+    if (dev >= 0 && dev < 64) configured |= 1ull << dev;
+  }
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  static int diag = -1;  // measurement aid: KEEPVQ_PREFILL_DIAG = 1 no epilogue, 2 no decode, 3 no activation copies, 4 no MMAs (outputs meaningless)
-  if (diag < 0) { const char* v = getenv("KEEPVQ_PREFILL_DIAG"); diag = v ? atoi(v) : 0; }
+  int diag = 0;
+#ifdef KEEPVQ_DIAG
+  // measurement build only (outputs meaningless): 1 no epilogue, 2 no decode, 3 no activation copies, 4 no MMAs, 5 no code fetches
+  diag = g_prefill_diag;
+#endif
   prefill_projection_kernel<M, GLU><<<sms, PF_THREADS, smem, s>>>(p, status, diag);
   KEEPVQ_CHECK_LAUNCH();
   return KEEPVQ_OK;

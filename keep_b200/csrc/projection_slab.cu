@@ -1,0 +1,588 @@
+// Decode projections for batches with many route groups: the kernel the HBM roofline of a decode
+// layer is measured on.
+//
+// A persistent CTA per SM takes (route group, slab of output rows) items; each of its 16 warps owns
+// 16 * TILES rows of the slab over the whole input dimension, so there is no split-K reduction.
+// The kernel is bound by turning codes into int8 operands, not by memory, so every instruction a
+// codeword costs was counted (ncu's executed-instruction counters per opcode):
+//   - a group holds at most four routes, and their high-byte and low-byte planes sit side by side
+//     as the eight columns of ONE m16n8k32 MMA (a lane ends up with both planes of its route);
+//     groups of up to eight routes (two MMAs per tile and step) serve calls with more routes per
+//     expert;
+//   - a table address is one byte permute: the abs table sits on a 64 KB boundary of the shared
+//     window and an entry is 256 bytes wide (two parities x sixteen replicas x 8 bytes), so the
+//     abs byte of the code word dropped into byte 1 of (table base + lane offset) IS the address;
+//     the sign table gets the same treatment when there is room for 32 replicas of it;
+//   - two decoders share the work so that neither the integer pipe nor shared-memory bandwidth is
+//     the only limit: steps named in TABLE_STEPS read the sign masks (parity folded in) from the
+//     second table, the others spread the sign byte with two multiplies and byte permutes;
+//   - codes stream through a private cp.async ring per warp; a group's quantised activations are
+//     staged once per run of items in MMA-fragment order, and a lane whose column carries no
+//     route re-reads a live column's bytes (its own MMA column is never looked at), so the
+//     activation reads cost one wavefront for the typical one-route group.
+#include <type_traits>
+#include <utility>
+
+#include "moe_fast.cuh"
+
+namespace keepvq {
+namespace fast {
+
+constexpr int SK_WARPS = 16;
+constexpr int SK_THREADS = SK_WARPS * 32;
+constexpr int SK_CHUNK = 32;                              // codewords of a row per ring stage and lane quartet
+constexpr int SK_REPLICAS = 16;
+constexpr int SK_STAGES = 2;
+constexpr int SK_SMEM_BYTES = 227 * 1024;                 // the whole opt-in window: the tables want fixed 64 KB boundaries inside it
+constexpr int SK_WARP_RING = SK_STAGES * 4 * 512;         // four 16-byte streams per lane and stage
+constexpr uint32_t SK_ABS_BYTES = 256 * 2 * SK_REPLICAS * 8;   // 64 KB  [abs row][parity][replica]
+constexpr uint32_t SK_SPREAD_LO = (1u << 4) | (1u << 13) | (1u << 22) | (1u << 31);  // sign bits 3,2,1,0 -> bits 7,15,23,31
+constexpr uint32_t SK_SPREAD_HI = 1u | (1u << 9) | (1u << 18) | (1u << 27);          // sign bits 7,6,5,4 -> the same places
+
+// Shared window, in absolute shared addresses.  A0 = the first 64 KB boundary at or above the
+// dynamic base (the runtime keeps 1 KB below it, so A0 = 64 KB):
+//   [base, A0)            cp.async rings of as many warps as fit (15)
+//   [A0, +64 KB)          abs table
+//   WIDE_SIGN             [+64 KB, +128 KB) sign table, 32 replicas | [+128 KB, +160 KB) activations: 8 columns x 4096 inputs
+//   otherwise             [+64 KB, +96 KB) second table, 16 replicas | [+96 KB, +160 KB) activations: 8 x 8192 or 16 x 4096
+//   [+160 KB, ...)        the remaining rings
+constexpr uint32_t SK_SECOND_OFF = SK_ABS_BYTES;
+constexpr uint32_t SK_RING_HIGH_OFF = 160 * 1024;
+template <bool WIDE_SIGN> struct SlabLayout {
+  static constexpr uint32_t SECOND_REPLICAS = WIDE_SIGN ? 32 : 16;
+  static constexpr uint32_t B_OFF = SK_SECOND_OFF + 256 * SECOND_REPLICAS * 8;
+};
+
+template <int N, typename F, int... I>
+__device__ __forceinline__ void sk_static_for_impl(F&& f, std::integer_sequence<int, I...>) { (f(std::integral_constant<int, I>{}), ...); }
+template <int N, typename F>
+__device__ __forceinline__ void sk_static_for(F&& f) { sk_static_for_impl<N>(static_cast<F&&>(f), std::make_integer_sequence<int, N>{}); }
+
+template <int OFF>
+__device__ __forceinline__ void sk_cp_async16(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0+%2], [%1], 16;" ::"r"(dst), "l"(src), "n"(OFF) : "memory");
+}
+template <int OFF>
+__device__ __forceinline__ void sk_cp_async8(uint32_t dst, const void* src) {
+  asm volatile("cp.async.ca.shared.global [%0+%2], [%1], 8;" ::"r"(dst), "l"(src), "n"(OFF) : "memory");
+}
+__device__ __forceinline__ void sk_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void sk_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+template <int OFF>
+__device__ __forceinline__ uint4 sk_lds128(uint32_t addr) {  // data a cp.async wrote: ordered by the volatile wait before it
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4+%5];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr), "n"(OFF));
+  return v;
+}
+template <int OFF>
+__device__ __forceinline__ uint2 sk_lds64(uint32_t addr) {
+  uint2 v;
+  asm volatile("ld.shared.v2.u32 {%0,%1}, [%2+%3];" : "=r"(v.x), "=r"(v.y) : "r"(addr), "n"(OFF));
+  return v;
+}
+__device__ __forceinline__ uint2 sk_table(uint32_t addr) {  // tables never change after the set-up barrier: free to schedule
+  uint2 v;
+  asm("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ void sk_sts64(uint32_t addr, uint32_t lo, uint32_t hi) {
+  asm volatile("st.shared.v2.u32 [%0], {%1,%2};" ::"r"(addr), "r"(lo), "r"(hi) : "memory");
+}
+
+__device__ __forceinline__ uint32_t sk_byte_masks(uint32_t v) {  // the top bit of every byte, spread over the byte
+  uint32_t m;
+  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(m) : "r"(v), "r"(0u), "r"(0xBA98u));
+  return m;
+}
+__device__ __forceinline__ void sk_mma(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// One codeword -> the two A-fragment words q (4w = 2q + 1).  The codeword is the low (ODD = false)
+// or the high half of `word`.  abs_lane = address of the abs table + this lane's replica offset
+// (byte 1 of it is zero: the table sits on a 64 KB boundary); second_lane likewise for the
+// second table (WIDE_SIGN), or that table's address + replica offset as a plain addend.
+template <bool TABLE, bool ODD, bool WIDE_SIGN>
+__device__ __forceinline__ void sk_decode(uint32_t word, uint32_t abs_lane, uint32_t second_lane, uint32_t& lo, uint32_t& hi) {
+  const uint32_t entry = __byte_perm(word, abs_lane, ODD ? 0x7634 : 0x7614);  // the abs byte into byte 1 of the address
+  if (TABLE) {
+    uint32_t at;  // sign flips and parity
+    if (WIDE_SIGN) at = __byte_perm(word, second_lane, ODD ? 0x7624 : 0x7604);
+    else at = (ODD ? __byte_perm(word, 0u, 0x4442) : (word & 0xFFu)) * 128u + second_lane;
+    const uint2 e = sk_table(entry), m = sk_table(at);  // even-parity entry
+    lo = e.x ^ m.x;
+    hi = e.y ^ m.y;
+  } else {
+    const uint32_t sign = ODD ? __byte_perm(word, 0u, 0x4442) : (word & 0xFFu);
+    const uint2 e = sk_table(entry | ((static_cast<uint32_t>(__popc(sign)) << 7) & 0x80u));
+    lo = e.x ^ (sk_byte_masks(sign * SK_SPREAD_LO) & 0xFEFEFEFEu);
+    hi = e.y ^ (sk_byte_masks(sign * SK_SPREAD_HI) & 0xFEFEFEFEu);
+  }
+}
+
+template <int I>
+__device__ __forceinline__ uint32_t sk_word(const uint4& v) {
+  return (I >> 1) == 0 ? v.x : (I >> 1) == 1 ? v.y : (I >> 1) == 2 ? v.z : v.w;
+}
+
+// COLS = routes per group: 4 (both byte planes of a route in one MMA) or 8 (one MMA per plane).
+// NESTED: the layer has a residual tier; the second table then holds the residual codebook (the
+// base decode does every step's signs on the integer pipe) and an item whose slot is hot runs a
+// second pass over the residual's 8-bit codes.
+// `status` (may be null) is set to 2 if the shared window does not have the expected shape.
+template <int M, int TILES, int COLS, unsigned TABLE_STEPS, bool NESTED, bool WIDE_SIGN>
+__global__ void __launch_bounds__(SK_THREADS, 1) projection_slab_kernel(FastProjectionArgs p, int32_t* status) {
+  static_assert(COLS == 4 || COLS == 8, "a group is four or eight routes");
+  static_assert(!WIDE_SIGN || (COLS == 4 && !NESTED), "the wide sign table leaves room for eight activation columns of 4096 inputs");
+  static_assert(M * 2 * TILES == 4, "four code streams per lane");
+  using L = SlabLayout<WIDE_SIGN>;
+  extern __shared__ __align__(16) uint8_t smem[];
+  grid_launch_dependents();
+  constexpr int PLANES = COLS == 4 ? 1 : 2;     // MMAs per tile and step
+  constexpr int RPL = COLS == 4 ? 1 : 2;        // routes a lane holds in the epilogue
+  constexpr int PARTS = 2 * RPL;                // (row g | g + 8) x routes of the lane
+  constexpr int B_LANE = COLS == 4 ? 8 : 16;    // bytes of the B operand a lane reads per step
+  constexpr int B_STEP = 32 * B_LANE;
+  constexpr unsigned STEPS = NESTED ? 0u : TABLE_STEPS;
+
+  const uint32_t smem_base = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
+  const uint32_t a0 = (smem_base + 0xFFFFu) & ~0xFFFFu;
+  const int low_warps = min(SK_WARPS, static_cast<int>((a0 - smem_base) / SK_WARP_RING));
+  if (a0 + SK_RING_HIGH_OFF + (SK_WARPS - low_warps) * SK_WARP_RING > smem_base + SK_SMEM_BYTES) {  // uniform over the grid
+    if (status && threadIdx.x == 0) atomicExch(status, 2);
+    return;
+  }
+
+  // ---- tables -----------------------------------------------------------------------------
+  for (int e = threadIdx.x; e < 768; e += SK_THREADS) {
+    uint32_t lo = 0, hi = 0;
+    if (e >= 512 && NESTED) {  // residual entry: byte j of the low word is 2 * v[6 - 2j], of the high word 2 * v[7 - 2j]
+      const uint32_t* row = p.res_table + (e - 512) * 4;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const __half2 pair = *reinterpret_cast<const __half2*>(&row[3 - j]);  // dims 6 - 2j, 7 - 2j
+        lo |= (static_cast<uint32_t>(__float2int_rn(2.0f * __low2float(pair))) & 0xFFu) << (8 * j);
+        hi |= (static_cast<uint32_t>(__float2int_rn(2.0f * __high2float(pair))) & 0xFFu) << (8 * j);
+      }
+    } else if (e < 512) {  // abs entry (row e/2, parity e&1): byte j of the low word is table nibble 3-j, of the high word 7-j
+      const uint32_t word = p.codebook[e >> 1], par = e & 1;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int nl = 3 - j, nh = 7 - j;
+        uint32_t hl = ((word >> (4 * nl)) & 0xFu) - 8u, hh = ((word >> (4 * nh)) & 0xFu) - 8u;
+        if (par) { hl = nl == 0 ? ~hl : hl ^ 1u; hh ^= 1u; }
+        lo |= (hl & 0xFFu) << (8 * j);
+        hi |= (hh & 0xFFu) << (8 * j);
+      }
+    } else {  // sign entry: 0xFE where the sign bit is set; ^1 everywhere (^0xFF on nibble 0) on odd parity
+      const uint32_t sb = e - 512, par = __popc(sb) & 1u;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int nl = 3 - j, nh = 7 - j;
+        uint32_t ml = ((sb >> nl) & 1u) ? 0xFEu : 0u, mh = ((sb >> nh) & 1u) ? 0xFEu : 0u;
+        if (par) { ml ^= nl == 0 ? 0xFFu : 0x01u; mh ^= 0x01u; }
+        lo |= ml << (8 * j);
+        hi |= mh << (8 * j);
+      }
+    }
+    const uint32_t replicas = e < 512 ? SK_REPLICAS : L::SECOND_REPLICAS;
+    const uint32_t dst = e < 512 ? a0 + e * (SK_REPLICAS * 8) : a0 + SK_SECOND_OFF + (e - 512) * (L::SECOND_REPLICAS * 8);
+    for (uint32_t r = 0; r < replicas; ++r) sk_sts64(dst + r * 8, lo, hi);
+  }
+
+  grid_wait();  // the tables came from constants; everything below reads what earlier kernels of the stream wrote
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int g = lane >> 2, t = lane & 3;
+  const uint32_t abs_lane = a0 + static_cast<uint32_t>(lane & (SK_REPLICAS - 1)) * 8u;
+  const uint32_t second_lane = a0 + SK_SECOND_OFF + static_cast<uint32_t>(lane & (L::SECOND_REPLICAS - 1)) * 8u;
+  const uint32_t b_base = a0 + L::B_OFF;
+  constexpr int STAGE_BYTES = 4 * 512;                   // per warp
+  const uint32_t ring = (warp < low_warps ? smem_base + warp * SK_WARP_RING : a0 + SK_RING_HIGH_OFF + (warp - low_warps) * SK_WARP_RING) + lane * 16;
+  const int64_t N = p.out_dim, cw = p.in_dim / 8;
+  const int n_chunks = static_cast<int>(cw / SK_CHUNK);
+  const int chunks_per_group = n_chunks / static_cast<int>(p.groups);
+  const int chunks_per_res_group = NESTED ? n_chunks / static_cast<int>(p.res_groups) : n_chunks;
+  constexpr int ROWS = 16 * TILES;              // per warp
+  constexpr int SLAB = ROWS * SK_WARPS;         // per CTA item
+  const int slabs = static_cast<int>((N + SLAB - 1) / SLAB);
+  const int items = p.groups_of_routes.count[0] * slabs;
+  const Projection mats[2] = {p.a, p.b};
+
+  // A CTA takes a contiguous run of items, so consecutive items mostly belong to one route group
+  // and its activations are staged once for all of them.  (With a residual tier the items of a
+  // hot slot cost half as much again, and a run of them on one CTA would unbalance the grid:
+  // those layers deal the items out round-robin instead.)
+  const int grid = static_cast<int>(gridDim.x), cta = static_cast<int>(blockIdx.x);
+  const int first_item = NESTED ? cta : static_cast<int>(static_cast<int64_t>(items) * cta / grid);
+  const int last_item = NESTED ? items : static_cast<int>(static_cast<int64_t>(items) * (cta + 1) / grid);
+  const int item_step = NESTED ? grid : 1;
+  // What a lane needs to know of an item.  The next item's first chunk is requested while the
+  // current item's last chunk is being decoded, so an item does not start with an exposed wait.
+  struct Item {
+    int gi, gsize, gstart;
+    int64_t slot, row0;
+    bool active;
+    const uint16_t* row_ptr[4];  // stream s = matrix s / (2 * TILES), rows g + 8 * (s % (2 * TILES))
+  };
+  auto describe = [&](int item) {
+    Item it;
+    it.gi = item / slabs;
+    const int slab = item - it.gi * slabs;
+    it.slot = p.groups_of_routes.slot[it.gi];
+    it.gsize = p.groups_of_routes.size[it.gi];
+    it.gstart = p.groups_of_routes.start[it.gi];
+    it.row0 = static_cast<int64_t>(slab) * SLAB + warp * ROWS;
+    it.active = it.row0 < N;
+#pragma unroll
+    for (int s = 0; s < 4; ++s)
+      it.row_ptr[s] = mats[s / (2 * TILES)].codes + (it.slot * N + min(it.row0 + 8 * (s % (2 * TILES)) + g, N - 1)) * cw + t * 8;
+    return it;
+  };
+  uint32_t ring_turn = 0;  // chunks this warp has consumed: picks the ring stage
+  auto fetch = [&](const Item& it, int c, uint32_t turn) {  // chunk c of the lane's row streams -> ring stage turn % SK_STAGES
+    if (it.active && c < n_chunks) {
+      const uint32_t dst = ring + (turn % SK_STAGES) * STAGE_BYTES;
+      sk_static_for<4>([&](auto s) { sk_cp_async16<decltype(s)::value * 512>(dst, it.row_ptr[decltype(s)::value] + c * SK_CHUNK); });
+    }
+    sk_commit();
+  };
+  constexpr bool CARRY = !NESTED;  // the residual pass borrows the ring, so those layers start every item cold
+  Item next_item = {};
+  if (first_item < last_item) {
+    next_item = describe(first_item);
+    if (CARRY) fetch(next_item, 0, ring_turn);
+  }
+  int staged_group = -1;
+  for (int item = first_item; item < last_item; item += item_step) {
+    const Item it = next_item;
+    const bool has_next = item + item_step < last_item;
+    if (has_next) next_item = describe(item + item_step);
+    const int gi = it.gi, gsize = it.gsize, gstart = it.gstart;
+    const int64_t slot = it.slot, row0 = it.row0;
+    const bool active = it.active;
+
+    // column g of the MMA is (route g / 2, byte plane g % 2) with four routes, route g (both planes) with eight
+    const int col_route = COLS == 4 ? (g >> 1) : g;
+    const bool column_live = col_route < gsize;
+    if (gi != staged_group) {
+      __syncthreads();  // every warp is done with the previous group's activations (and the tables are built)
+      if (column_live) {  // stage this group's activations in fragment order: [chunk * 8 + step][lane]
+        const int route = p.groups_of_routes.routes[gstart + col_route];
+        const uint8_t* src = p.x.q + (static_cast<int64_t>(route / p.x_div) * cw + t * 8) * 16 + (COLS == 4 ? (g & 1) * 8 : 0);
+        const uint32_t dst = b_base + lane * B_LANE;
+        for (int step = warp; step < n_chunks * 8; step += SK_WARPS) {
+          const uint8_t* from = src + ((step >> 3) * SK_CHUNK + (step & 7)) * 16;
+          if (COLS == 4) sk_cp_async8<0>(dst + step * B_STEP, from);
+          else sk_cp_async16<0>(dst + step * B_STEP, from);
+        }
+      }
+      sk_commit();
+      if (CARRY) {
+        sk_wait<0>();  // the activations, and the first chunk asked for earlier
+      } else {
+        fetch(it, 0, ring_turn);
+        sk_wait<1>();  // the activations (the older group) have landed
+      }
+      __syncthreads();
+      staged_group = gi;
+    } else if (!CARRY) {
+      fetch(it, 0, ring_turn);
+    }
+    if (!active) {
+      if (CARRY && has_next) fetch(next_item, 0, ring_turn);
+      else sk_wait<0>();
+      continue;
+    }
+    // a lane whose column carries no route reads the bytes of route 0's column instead (always
+    // live): same addresses as live lanes, so no extra shared-memory traffic, and nothing ever
+    // looks at its column of the accumulators
+    const uint32_t b_lane = b_base + (column_live ? lane : (COLS == 4 ? (g & 1) * 4 + t : t)) * B_LANE;
+
+    float part[M][TILES][PARTS];
+    int acc[PLANES][2][M][TILES][4];  // two chains per (plane, matrix, tile), used by alternate steps: the MMA's dependent latency is long
+#pragma unroll
+    for (int m = 0; m < M; ++m)
+#pragma unroll
+      for (int tl = 0; tl < TILES; ++tl) {
+#pragma unroll
+        for (int r = 0; r < PARTS; ++r) part[m][tl][r] = 0.0f;
+#pragma unroll
+        for (int r = 0; r < 4; ++r)
+#pragma unroll
+          for (int pl = 0; pl < PLANES; ++pl) acc[pl][0][m][tl][r] = acc[pl][1][m][tl][r] = 0;
+      }
+    // what the epilogue needs of this lane's routes, asked for now so that the loads fly behind
+    // the main loop instead of in front of the stores
+    int ep_route[RPL];
+    float ep_xs[RPL], ep_weight[RPL], ep_sum[RPL];
+#pragma unroll
+    for (int cc = 0; cc < RPL; ++cc) {
+      const int col = RPL * t + cc;
+      ep_route[cc] = col < gsize ? p.groups_of_routes.routes[gstart + col] : -1;
+      const int64_t xrow = ep_route[cc] < 0 ? p.x_zero_row : static_cast<int64_t>(ep_route[cc] / p.x_div);
+      ep_xs[cc] = p.x.scale[xrow];
+      ep_weight[cc] = (M == 2 && ep_route[cc] >= 0) ? p.route_weight[ep_route[cc]] : 1.0f;
+      ep_sum[cc] = static_cast<float>(p.x.sums[xrow * p.groups]);  // the only group when the rows have one scale
+    }
+    float row_scale[M][TILES][2];  // the last scale group's scale of rows g and g + 8
+
+    // accumulators -> fp32 partials at the end of a scale group
+    auto close_group = [&](const void* const (&scales)[2], int64_t row_base, int64_t groups, int group, float (&into)[M][TILES][PARTS], bool keep_scale) {
+#pragma unroll
+      for (int m = 0; m < M; ++m)
+#pragma unroll
+        for (int tl = 0; tl < TILES; ++tl)
+#pragma unroll
+          for (int rr = 0; rr < 2; ++rr) {
+            const int64_t row = min(row0 + 16 * tl + g + 8 * rr, N - 1);
+            const float sc = load_as_float(scales[m], p.scales_dtype, (row_base + row) * groups + group);
+            if (keep_scale) row_scale[m][tl][rr] = sc;
+#pragma unroll
+            for (int cc = 0; cc < RPL; ++cc) {
+              int hi, lo;
+              if (COLS == 4) {  // columns 2t, 2t+1 of the one MMA are this lane's route: high plane, low plane
+                hi = acc[0][0][m][tl][2 * rr] + acc[0][1][m][tl][2 * rr];
+                lo = acc[0][0][m][tl][2 * rr + 1] + acc[0][1][m][tl][2 * rr + 1];
+              } else {
+                hi = acc[0][0][m][tl][2 * rr + cc] + acc[0][1][m][tl][2 * rr + cc];
+                lo = acc[PLANES - 1][0][m][tl][2 * rr + cc] + acc[PLANES - 1][1][m][tl][2 * rr + cc];
+              }
+              into[m][tl][rr * RPL + cc] = fmaf(sc, 256.0f * static_cast<float>(hi) + static_cast<float>(lo), into[m][tl][rr * RPL + cc]);
+            }
+#pragma unroll
+            for (int pl = 0; pl < PLANES; ++pl)
+#pragma unroll
+              for (int r = 2 * rr; r < 2 * rr + 2; ++r) acc[pl][0][m][tl][r] = acc[pl][1][m][tl][r] = 0;
+          }
+    };
+
+    int group = 0, left_in_group = chunks_per_group;
+    for (int c = 0; c < n_chunks; ++c, ++ring_turn) {
+      if (CARRY && c + 1 == n_chunks && has_next) fetch(next_item, 0, ring_turn + 1);
+      else fetch(it, c + 1, ring_turn + 1);
+      sk_wait<1>();  // chunk c has landed (the younger group may still fly)
+      uint4 cur[4];
+      const uint32_t src = ring + (ring_turn % SK_STAGES) * STAGE_BYTES;
+      sk_static_for<4>([&](auto s) { cur[decltype(s)::value] = sk_lds128<decltype(s)::value * 512>(src); });
+      const uint32_t b_addr = b_lane + c * 8 * B_STEP;
+      sk_static_for<8>([&](auto index) {
+        constexpr int I = decltype(index)::value;
+        constexpr bool TABLE = ((STEPS >> I) & 1u) != 0;
+        uint32_t b[4];
+        if (COLS == 4) { const uint2 v = sk_lds64<I * B_STEP>(b_addr); b[0] = v.x; b[1] = v.y; }
+        else { const uint4 v = sk_lds128<I * B_STEP>(b_addr); b[0] = v.x; b[1] = v.y; b[2] = v.z; b[3] = v.w; }
+#pragma unroll
+        for (int m = 0; m < M; ++m)
+#pragma unroll
+          for (int tl = 0; tl < TILES; ++tl) {
+            uint32_t a[4];
+            sk_decode<TABLE, (I & 1) != 0, WIDE_SIGN>(sk_word<I>(cur[(m * TILES + tl) * 2]), abs_lane, second_lane, a[0], a[2]);      // row g
+            sk_decode<TABLE, (I & 1) != 0, WIDE_SIGN>(sk_word<I>(cur[(m * TILES + tl) * 2 + 1]), abs_lane, second_lane, a[1], a[3]);  // row g + 8
+            sk_mma(acc[0][I & 1][m][tl], a[0], a[1], a[2], a[3], b[0], b[1]);
+            if (PLANES == 2) sk_mma(acc[PLANES - 1][I & 1][m][tl], a[0], a[1], a[2], a[3], b[2], b[3]);
+          }
+      });
+      if (--left_in_group == 0) {
+        const void* const scales[2] = {mats[0].scales, mats[1].scales};
+        close_group(scales, slot * N, p.groups, group, part, true);
+        ++group;
+        left_in_group = chunks_per_group;
+      }
+    }
+    if (!CARRY) sk_wait<0>();
+
+    // ---- the residual of a hot slot: a second pass over its 8-bit codes ---------------------
+    float rpart[M][TILES][PARTS];
+#pragma unroll
+    for (int m = 0; m < M; ++m)
+#pragma unroll
+      for (int tl = 0; tl < TILES; ++tl)
+#pragma unroll
+        for (int r = 0; r < PARTS; ++r) rpart[m][tl][r] = 0.0f;
+    if (NESTED) {
+      const uint32_t hot = p.hot_of_slot[slot];
+      if (hot != 0xFFFFFFFFu) {
+        const uint8_t* res_ptr[4];
+#pragma unroll
+        for (int s = 0; s < 4; ++s)
+          res_ptr[s] = mats[s / (2 * TILES)].res_codes + (static_cast<int64_t>(hot) * N + min(row0 + 8 * (s % (2 * TILES)) + g, N - 1)) * cw + t * 8;
+        auto fetch_res = [&](int c) {  // 8 codes of 8 bits per row stream
+          if (c < n_chunks) {
+            const uint32_t dst = ring + (c % SK_STAGES) * STAGE_BYTES;  // the ring is idle here: the base pass has drained it
+            sk_static_for<4>([&](auto s) { sk_cp_async8<decltype(s)::value * 512>(dst, res_ptr[decltype(s)::value] + c * SK_CHUNK); });
+          }
+          sk_commit();
+        };
+        fetch_res(0);
+        int res_group = 0, left_in_res_group = chunks_per_res_group;
+        for (int c = 0; c < n_chunks; ++c) {
+          fetch_res(c + 1);
+          sk_wait<1>();
+          uint2 cur[4];
+          const uint32_t src = ring + (c % SK_STAGES) * STAGE_BYTES;
+          sk_static_for<4>([&](auto s) { cur[decltype(s)::value] = sk_lds64<decltype(s)::value * 512>(src); });
+          const uint32_t b_addr = b_lane + c * 8 * B_STEP;
+          sk_static_for<8>([&](auto index) {
+            constexpr int I = decltype(index)::value;
+            uint32_t b[4];
+            if (COLS == 4) { const uint2 v = sk_lds64<I * B_STEP>(b_addr); b[0] = v.x; b[1] = v.y; }
+            else { const uint4 v = sk_lds128<I * B_STEP>(b_addr); b[0] = v.x; b[1] = v.y; b[2] = v.z; b[3] = v.w; }
+#pragma unroll
+            for (int m = 0; m < M; ++m)
+#pragma unroll
+              for (int tl = 0; tl < TILES; ++tl) {
+                uint32_t a[4];
+#pragma unroll
+                for (int half = 0; half < 2; ++half) {
+                  const uint2 v = cur[(m * TILES + tl) * 2 + half];
+                  const uint32_t code = ((I < 4 ? v.x : v.y) >> (8 * (I & 3))) & 0xFFu;
+                  const uint2 e = sk_table(code * 128u + second_lane);  // the second table is the residual codebook here
+                  a[half] = e.x;
+                  a[2 + half] = e.y;
+                }
+                sk_mma(acc[0][I & 1][m][tl], a[0], a[1], a[2], a[3], b[0], b[1]);
+                if (PLANES == 2) sk_mma(acc[PLANES - 1][I & 1][m][tl], a[0], a[1], a[2], a[3], b[2], b[3]);
+              }
+          });
+          if (--left_in_res_group == 0) {
+            const void* const scales[2] = {mats[0].res_scales, mats[1].res_scales};
+            close_group(scales, static_cast<int64_t>(hot) * N, p.res_groups, res_group, rpart, false);
+            ++res_group;
+            left_in_res_group = chunks_per_res_group;
+          }
+        }
+        sk_wait<0>();
+      }
+    }
+
+    // ---- epilogue in registers: lane (g, t) holds rows {g, g+8} of each tile for its route(s)
+#pragma unroll
+    for (int cc = 0; cc < RPL; ++cc) {
+      const int route = ep_route[cc];
+      if (route < 0) continue;
+      const int64_t xrow = route / p.x_div;
+      const float xs = ep_xs[cc];
+      const float weight = ep_weight[cc];
+#pragma unroll
+      for (int tl = 0; tl < TILES; ++tl)
+#pragma unroll
+        for (int rr = 0; rr < 2; ++rr) {
+          const int r = rr * RPL + cc;
+          const int64_t row = row0 + 16 * tl + g + 8 * rr;
+          if (row >= N) continue;
+          float y[M];
+#pragma unroll
+          for (int m = 0; m < M; ++m) {
+            float shift = 0.0f;  // the +-1/4 of every weight, folded into sum(x') per scale group
+            if (p.groups == 1) {
+              shift = row_scale[m][tl][rr] * ep_sum[cc];
+            } else {
+              for (int64_t q = 0; q < p.groups; ++q)
+                shift = fmaf(load_as_float(mats[m].scales, p.scales_dtype, (slot * N + row) * p.groups + q),
+                             static_cast<float>(p.x.sums[xrow * p.groups + q]), shift);
+            }
+            y[m] = xs * (0.5f * (part[m][tl][r] + rpart[m][tl][r]) + 0.25f * shift);  // a residual weight is q / 2 with no offset
+          }
+          float result;
+          if (M == 2) {
+            float gt = y[0], up = y[M - 1];
+            if (p.out_dtype == KEEPVQ_BF16) { gt = __bfloat162float(__float2bfloat16_rn(gt)); up = __bfloat162float(__float2bfloat16_rn(up)); }
+            else if (p.out_dtype == KEEPVQ_F16) { gt = __half2float(__float2half_rn(gt)); up = __half2float(__float2half_rn(up)); }
+            if (p.swiglu_limit > 0.0f) { gt = fminf(gt, p.swiglu_limit); up = fminf(fmaxf(up, -p.swiglu_limit), p.swiglu_limit); }
+            result = gt / (1.0f + expf(-gt)) * up * weight;
+          } else {
+            result = y[0];
+          }
+          store_from_float(p.out, p.out_dtype, static_cast<int64_t>(route) * N + row, result);
+        }
+    }
+  }
+  sk_wait<0>();
+}
+
+// ---- launch -----------------------------------------------------------------------------------
+
+int slab_max_in_dim(int cols) { return cols == 4 ? 8192 : 4096; }  // what the 64 KB activation stage holds
+
+static int device_sm_count(int* device_out) {
+  constexpr int MAX_DEVICES = 64;
+  static int cached[MAX_DEVICES] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (device_out) *device_out = dev;
+  if (dev < 0 || dev >= MAX_DEVICES) return 148;
+  if (!cached[dev]) {
+    int n = 0;
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    cached[dev] = n > 0 ? n : 148;
+  }
+  return cached[dev];
+}
+
+template <int M, int TILES, int COLS, unsigned TABLE_STEPS, bool NESTED, bool WIDE_SIGN>
+static int launch_slab(const FastProjectionArgs& p, cudaStream_t s) {
+  auto kernel = projection_slab_kernel<M, TILES, COLS, TABLE_STEPS, NESTED, WIDE_SIGN>;
+  static uint64_t configured = 0;  // one bit per device: the shared-memory opt-in is a per-device attribute of the function
+  int dev = 0;
+  const int sms = device_sm_count(&dev);
+  if (dev < 0 || dev >= 64 || !((configured >> dev) & 1ull)) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SK_SMEM_BYTES);
+    if (e != cudaSuccess) return note_cuda_error(e);
+    if (dev >= 0 && dev < 64) configured |= 1ull << dev;
+  }
+  cudaError_t err = launch_after(true, kernel, sms, SK_THREADS, SK_SMEM_BYTES, s, p, p.status);
+  if (err != cudaSuccess) return note_cuda_error(err);
+  return KEEPVQ_OK;
+}
+
+#ifdef KEEPVQ_DIAG
+// Measurement build only: which steps of a chunk decode through the sign table, and the table width.
+static unsigned g_table_steps = 0xEAu;
+static int g_wide_sign = 1;
+extern "C" void keepvq_diag_set_table_steps(unsigned mask) { g_table_steps = mask; }
+extern "C" void keepvq_diag_set_variant(int wide_sign, int) { g_wide_sign = wide_sign; }
+template <int M, int TILES, unsigned STEPS>
+static int diag_cols4(const FastProjectionArgs& p, cudaStream_t s) {
+  if (g_wide_sign && p.in_dim <= 4096) return launch_slab<M, TILES, 4, STEPS, false, true>(p, s);
+  return launch_slab<M, TILES, 4, STEPS, false, false>(p, s);
+}
+template <int M, int TILES>
+static int launch_plain(const FastProjectionArgs& p, int cols, cudaStream_t s) {
+  if (cols == 8) {
+    if (g_table_steps == 0xAAu) return launch_slab<M, TILES, 8, 0xAAu, false, false>(p, s);
+    return launch_slab<M, TILES, 8, 0xEEu, false, false>(p, s);
+  }
+  switch (g_table_steps) {
+    case 0x88u: return diag_cols4<M, TILES, 0x88u>(p, s);
+    case 0xAAu: return diag_cols4<M, TILES, 0xAAu>(p, s);
+    case 0xEAu: return diag_cols4<M, TILES, 0xEAu>(p, s);
+    case 0xEEu: return diag_cols4<M, TILES, 0xEEu>(p, s);
+    case 0xFEu: return diag_cols4<M, TILES, 0xFEu>(p, s);
+    default: return KEEPVQ_ERR_UNSUPPORTED;
+  }
+}
+#else
+constexpr unsigned SK_TABLE_STEPS_4 = 0xEAu, SK_TABLE_STEPS_8 = 0xEEu;
+template <int M, int TILES>
+static int launch_plain(const FastProjectionArgs& p, int cols, cudaStream_t s) {
+  if (cols == 8) return launch_slab<M, TILES, 8, SK_TABLE_STEPS_8, false, false>(p, s);
+  if (p.in_dim <= 4096) return launch_slab<M, TILES, 4, SK_TABLE_STEPS_4, false, true>(p, s);
+  return launch_slab<M, TILES, 4, SK_TABLE_STEPS_4, false, false>(p, s);
+}
+#endif
+
+template <int M, int TILES>
+static int launch_slab_projection(const FastProjectionArgs& p, int cols, cudaStream_t s) {
+  if (p.in_dim > slab_max_in_dim(cols)) return KEEPVQ_ERR_UNSUPPORTED;
+  if (p.res_table) return cols == 4 ? launch_slab<M, TILES, 4, 0u, true, false>(p, s) : launch_slab<M, TILES, 8, 0u, true, false>(p, s);
+  return launch_plain<M, TILES>(p, cols, s);
+}
+
+int slab_gate_up(const FastProjectionArgs& p, int cols, cudaStream_t s) { return launch_slab_projection<2, 1>(p, cols, s); }
+int slab_down(const FastProjectionArgs& p, int cols, cudaStream_t s) { return launch_slab_projection<1, 2>(p, cols, s); }
+
+}  // namespace fast
+}  // namespace keepvq

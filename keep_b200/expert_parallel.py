@@ -14,11 +14,10 @@ carry slot id ``NO_SLOT`` and the expert kernels skip them.  At decode sizes the
 few MB per layer on NVLink and the whole step stays capturable in a CUDA graph.
 
 ``PeerExchange`` is the NVLink form: rows go straight into the peers' buffers, no collective in the
-data path.  ``RouteExchange`` is the NCCL form.  On CUDA tensors its packing and pick summation are the library's own kernels
-(``keepvq_ep_pack``, ``keepvq_ep_combine``: a memset and three launches per layer besides the
-all-to-alls).  On CPU tensors ``RouteExchange`` is plain ``torch`` + ``torch.distributed`` with
-the same positions, which is how the index arithmetic is tested on gloo ranks without GPUs; it
-is the checker of the CUDA kernels, not a serving path.
+data path.  ``RouteExchange`` is the NCCL form: its packing and pick summation are the library's own
+kernels (``keepvq_ep_pack``, ``keepvq_ep_combine``: a memset and three launches per layer besides
+the all-to-alls).  Both take CUDA tensors only; there is no CPU path.  (The index arithmetic is
+checked against a plain ``torch`` restatement that lives with the tests.)
 """
 
 from __future__ import annotations
@@ -41,55 +40,15 @@ class RouteExchange:
         self.capacity = capacity
         self._cuda_buffers: dict = {}
 
-    def plan(self, served_expert: torch.Tensor):
-        """served_expert [tokens, k] (global ids, negative = dead pick) -> (position [tokens, k] of
-        each route in the send buffer, with ``world * capacity`` for a dead or overflowing route;
-        capacity).  Fixed-shape device arithmetic only: nothing is read back, so the exchange can
-        sit inside a CUDA graph."""
-        tokens, k = served_expert.shape
-        routes = tokens * k
-        capacity = self.capacity or routes
-        rows = self.world * capacity
-        flat = served_expert.reshape(-1).long()
-        dest = torch.where(flat >= 0, flat // self.experts_per_rank, torch.full_like(flat, self.world))  # dead routes sort last
-        order = torch.argsort(dest, stable=True)
-        counts = torch.zeros(self.world + 1, dtype=torch.long, device=flat.device).scatter_add_(0, dest, torch.ones_like(dest))
-        starts = torch.cumsum(counts, 0) - counts
-        sorted_dest = dest[order]
-        rank_in_bucket = torch.arange(routes, device=flat.device) - starts[sorted_dest]
-        ok = (sorted_dest < self.world) & (rank_in_bucket < capacity)
-        sorted_pos = torch.where(ok, sorted_dest * capacity + rank_in_bucket, torch.full_like(rank_in_bucket, rows))
-        position = torch.empty_like(sorted_pos).scatter_(0, order, sorted_pos)
-        return position.reshape(tokens, k), capacity
-
     def dispatch(self, x: torch.Tensor, served_expert: torch.Tensor, served_weight: torch.Tensor):
         """-> (recv_x [world * capacity, hidden], recv_slot [..] local expert or NO_SLOT,
-        recv_weight [..], position [tokens, k])."""
-        if x.is_cuda:
-            return self._dispatch_cuda(x, served_expert, served_weight)
-        send_x, send_slot, send_weight, position = self.pack_torch(x, served_expert, served_weight)
-        return self._all_to_all(send_x), self._all_to_all(send_slot), self._all_to_all(send_weight), position
-
-    def pack_torch(self, x: torch.Tensor, served_expert: torch.Tensor, served_weight: torch.Tensor):
-        """The send buffers in plain torch: (send_x [rows, hidden], send_slot [rows], send_weight
-        [rows], position [tokens, k])."""
-        tokens, k = served_expert.shape
-        position, capacity = self.plan(served_expert)
-        rows = self.world * capacity
-        flat_pos = position.reshape(-1)  # dead routes point at the spare row `rows`, cut off below
-        token_of_route = torch.arange(tokens * k, device=x.device) // k
-        send_x = torch.zeros((rows + 1, x.shape[1]), dtype=x.dtype, device=x.device)
-        send_x.index_copy_(0, flat_pos, x[token_of_route])
-        local_slot = (served_expert.reshape(-1).long().clamp(min=0) % self.experts_per_rank).to(torch.int32)
-        send_slot = torch.full((rows + 1,), NO_SLOT, dtype=torch.int32, device=x.device)
-        send_slot.index_copy_(0, flat_pos, local_slot)
-        send_weight = torch.zeros((rows + 1,), dtype=torch.float32, device=x.device)
-        send_weight.index_copy_(0, flat_pos, served_weight.reshape(-1).float())
-        return send_x[:rows], send_slot[:rows], send_weight[:rows], position
+        recv_weight [..], position [tokens, k]).  One library call packs rows, slots and weights;
+        two all-to-alls carry them.  Buffers are cached per shape so the step can be graph-captured."""
+        if not x.is_cuda:
+            raise ValueError("RouteExchange works on CUDA tensors only")
+        return self._dispatch_cuda(x, served_expert, served_weight)
 
     def _dispatch_cuda(self, x: torch.Tensor, served_expert: torch.Tensor, served_weight: torch.Tensor):
-        """The CUDA form of ``dispatch``: one library call packs rows, slots and weights; two
-        all-to-alls carry them.  Buffers are cached per shape so the step can be graph-captured."""
         send_x, send_meta, position = self.pack_cuda(x, served_expert, served_weight)
         if self.world == 1:
             recv_x, recv_meta = send_x, send_meta
@@ -143,15 +102,12 @@ class RouteExchange:
     def combine(self, y_routes: torch.Tensor, position: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
         """y_routes [world * capacity, hidden] (per received route) -> [tokens, hidden]: each token's
         picks summed in fp32 in pick order, one rounding."""
+        if not y_routes.is_cuda:
+            raise ValueError("RouteExchange works on CUDA tensors only")
         back = self._all_to_all(y_routes)
-        if back.is_cuda and back.dtype == out_dtype:
-            return self._combine_cuda(back, position)
-        back = torch.cat([back, torch.zeros((1, back.shape[1]), dtype=back.dtype, device=back.device)])  # row of a dead route
-        tokens, k = position.shape
-        acc = torch.zeros((tokens, back.shape[1]), dtype=torch.float32, device=back.device)
-        for j in range(k):  # pick order, as the single-GPU combine
-            acc += back[position[:, j]].float()
-        return acc.to(out_dtype)
+        if back.dtype != out_dtype:
+            raise ValueError(f"the routes arrive as {back.dtype}; the sum over the picks is rounded to that dtype, not {out_dtype}")
+        return self._combine_cuda(back, position)
 
     def _all_to_all(self, send: torch.Tensor) -> torch.Tensor:
         if self.world == 1:

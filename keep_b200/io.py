@@ -153,6 +153,14 @@ def load_quantized_vq_switch_linear(path, prefix: str, device):
         if expected is not None and expected not in (E8_1BIT_PACKED_SHA256, E8P_PACKED_ABS_SHA256):
             raise ValueError(f"checkpoint E8 codebook hash {expected!r} is not supported by this runtime")
         names = set(f.keys())
+        # tensors the reference's loader would hand to the layer and its forward would apply
+        # (src/keep/io/load.py:245-257, src/ramp/nn/linear.py:77-82): loading without them would
+        # give wrong outputs silently, so a checkpoint that carries one is refused by name
+        from .switch import _OUTSIDE
+
+        for sidecar in _OUTSIDE:
+            if f"{prefix}.{sidecar}" in names:
+                raise NotImplementedError(f"{prefix}.{sidecar} is present: {sidecar} belongs to the conversion tooling and is not applied by the routed hot path")
         wanted = [n for n in (f"{prefix}.codes", f"{prefix}.scales") if n in names]
         shapes = {n: tuple(f.get_slice(n).get_shape()) for n in wanted}
         dtypes = {n: f.get_slice(n).get_dtype() for n in wanted}

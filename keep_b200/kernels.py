@@ -7,8 +7,11 @@
 * ``e8p_nested_m1_token_layout/per_route``  ``src/ramp/kernels/e8p_nested_m1.py:90-112``
 
 Tensors are torch CUDA tensors (numpy inputs are uploaded).  Output dtype follows the activations:
-fp16 -> fp16, bf16 -> bf16, anything else -> fp32 (``vq_qmv.py:40-46``).  Every call enqueues one
-launch of ``keepvq_routed_matvec`` on the current stream and does not synchronise.
+fp16 -> fp16, bf16 -> bf16, anything else -> fp32 (``vq_qmv.py:40-46``).  Calls enqueue on the
+current stream and do not synchronise.  16-bit E8P codes with fp16 / bf16 activations and shapes
+that fit (inputs and scale groups in multiples of 256) run on the layer's int8 tensor-core kernels
+(``keepvq_grouped_projection``); everything else is one launch of the general kernel
+(``keepvq_routed_matvec``), which keeps fp32 rows at 24 bits.
 """
 
 from __future__ import annotations
@@ -209,8 +212,15 @@ def _few_token(x, codes, scales, codebook, rhs_indices, *, output_dims, code_bit
     chunk_for(int(codes_t.shape[2]), int(scales_t.shape[2]))
     table = as_device(codebook, device).contiguous()
     flat = _index_tensor(rhs_t.reshape(-1), device)
-    out = routed_matvec(x_t, codes_t.contiguous(), scales_t, table, flat, x_div=x_div, code_bits=code_bits,
-                        layout=layout, residual=residual, hot_of_slot=hot_of_slot)
+    out = None
+    if code_bits == 16 and x_t.dtype in (torch.float16, torch.bfloat16):
+        # 16-bit activations: the layer's own tensor-core kernels when the shapes fit them
+        from .prefill import tensor_core_projection
+
+        out = tensor_core_projection(x_t, codes_t.contiguous(), scales_t, table, flat, x_div=x_div, residual=residual, hot_of_slot=hot_of_slot)
+    if out is None:
+        out = routed_matvec(x_t, codes_t.contiguous(), scales_t, table, flat, x_div=x_div, code_bits=code_bits,
+                            layout=layout, residual=residual, hot_of_slot=hot_of_slot)
     if token_layout:
         return out.reshape(int(rhs_t.shape[0]), int(rhs_t.shape[1]), output_dims)
     return out.reshape(int(rhs_t.numel()), output_dims)

@@ -104,8 +104,8 @@ class RoutedMoELayer:
                 routing=Routing(served_expert=i32(), served_slot=i32(), served_weight=f32(), want=i32(), want_score=f32(), admit=i32()))
         return self._buffers[key]
 
-    def _layer_args(self, x, out, r: Routing, *, workspace, nbytes) -> _lib.MoELayerArgs:
-        """Argument struct for ``decode_without_scratch`` (the caller's tensors, no scratch)."""
+    def _layer_args(self, x, out, r: Routing, *, workspace, nbytes, expected_routes: int = 0) -> _lib.MoELayerArgs:
+        """The argument struct of a layer call over the caller's tensors."""
         return _lib.MoELayerArgs(
             x=_lib.ptr(x), x_dtype=_lib.dtype_tag(x.dtype), tokens=int(x.shape[0]), hidden=self.hidden, inter=self.inter,
             router_w=_lib.ptr(self.router_w), router_dtype=_lib.dtype_tag(self.router_w.dtype), pool=self.pool,
@@ -118,7 +118,18 @@ class RoutedMoELayer:
             codebook_all_odd=int(self.codebook_all_odd),
             out=_lib.ptr(out), served_expert=_lib.ptr(r.served_expert), served_slot=_lib.ptr(r.served_slot),
             served_weight=_lib.ptr(r.served_weight), want=_lib.ptr(r.want), want_score=_lib.ptr(r.want_score),
-            admit=_lib.ptr(r.admit), workspace=_lib.ptr(workspace), workspace_bytes=nbytes, expected_routes=0)
+            admit=_lib.ptr(r.admit), workspace=_lib.ptr(workspace), workspace_bytes=nbytes, expected_routes=int(expected_routes))
+
+    def route_outputs(self, tokens: int, dtype: torch.dtype, state: int = 0) -> torch.Tensor:
+        """The per-route outputs ``[tokens * top_k, hidden]`` the last call of this shape left in its
+        scratch (the rows the pick sum adds up): a view, overwritten by the next call."""
+        buf = self._buffers_for(tokens, dtype, state)
+        offset = int(_lib.load().keepvq_moe_layer_route_output_offset(tokens, self.hidden, self.inter, self.pool, self.top_k))
+        if offset < 0:
+            _lib.check(offset, "keepvq_moe_layer_route_output_offset")
+        base = (-buf["workspace"].data_ptr()) % 256
+        nbytes = tokens * self.top_k * self.hidden * dtype.itemsize
+        return buf["workspace"][base + offset: base + offset + nbytes].view(dtype).view(tokens * self.top_k, self.hidden)
 
     def wait_expired(self, tokens: int, dtype: torch.dtype, state: int = 0) -> bool:
         """True when a bounded wait of the tcgen05 kernels expired during the last call of this
@@ -192,19 +203,7 @@ class RoutedMoELayer:
         buf = self._buffers_for(tokens, x.dtype, state)
         r: Routing = buf["routing"]
         target = buf["out"] if out is None else out
-        args = _lib.MoELayerArgs(
-            x=_lib.ptr(x), x_dtype=_lib.dtype_tag(x.dtype), tokens=tokens, hidden=self.hidden, inter=self.inter,
-            router_w=_lib.ptr(self.router_w), router_dtype=_lib.dtype_tag(self.router_w.dtype), pool=self.pool,
-            top_k=self.top_k, score_func=_lib.SCORE_FUNCS[self.score_func], norm_topk_prob=int(self.norm_topk_prob),
-            gate_temp=self.gate_temp, route_scale=self.route_scale, tau=self.tau,
-            served_bias=_lib.ptr(self.served_bias), pool_bias=_lib.ptr(self.pool_bias), slot_of=_lib.ptr(self.slot_of),
-            slots=self.slots, w1=self.w1.struct(), w3=self.w3.struct(), w2=self.w2.struct(),
-            scales_dtype=_lib.dtype_tag(self.w1.scales.dtype), codebook=_lib.ptr(self.codebook), res_rows=self.res_rows,
-            res_table=_lib.ptr(self.res_table), hot_of_slot=_lib.ptr(self.hot_of_slot), swiglu_limit=self.swiglu_limit,
-            codebook_all_odd=int(self.codebook_all_odd),
-            out=_lib.ptr(target), served_expert=_lib.ptr(r.served_expert), served_slot=_lib.ptr(r.served_slot),
-            served_weight=_lib.ptr(r.served_weight), want=_lib.ptr(r.want), want_score=_lib.ptr(r.want_score),
-            admit=_lib.ptr(r.admit), workspace=_lib.ptr(buf["workspace"]), workspace_bytes=buf["nbytes"], expected_routes=int(expected_routes))
+        args = self._layer_args(x, target, r, workspace=buf["workspace"], nbytes=buf["nbytes"], expected_routes=expected_routes)
         with torch.cuda.device(self.device):
             _lib.check(_lib.load().keepvq_moe_decode_stages(args, int(stages), _lib.stream_handle(self.device)), "keepvq_moe_decode_stages")
         return target, r

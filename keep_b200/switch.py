@@ -167,16 +167,17 @@ class QuantizedVQSwitchGLU:
             raise ValueError("prefill_engine must be 'auto', 'vq_metal', 'nax_e8', or 'nax_e8p'")
         self.gate_proj, self.up_proj, self.down_proj = gate_proj, up_proj, down_proj
         self.prefill_engine, self.activation = prefill_engine, activation
-        self._fused = None
+        self._fused: dict = {}
 
     def _apply_activation(self, up: torch.Tensor, gate: torch.Tensor) -> torch.Tensor:
         if self.activation is None:
             return torch.nn.functional.silu(gate) * up
         return self.activation(up, gate)
 
-    def _fused_layer(self):
-        """The three projections as one ``RoutedMoELayer`` (its router unused), or None."""
-        if self._fused is None:
+    def _fused_layer(self, top_k: int):
+        """The three projections as one ``RoutedMoELayer`` with ``top_k`` picks per token (its
+        router unused), or None when the configuration does not fit the layer kernels."""
+        if top_k not in self._fused:
             from .moe import Projection, RoutedMoELayer
 
             projs = (self.gate_proj, self.up_proj, self.down_proj)
@@ -184,28 +185,33 @@ class QuantizedVQSwitchGLU:
             act_ok = self.activation is None or hasattr(self.activation, "limit")
             same_book = all(p.codebook is self.gate_proj.codebook or (p.codebook is not None and self.gate_proj.codebook is not None
                                                                      and torch.equal(p.codebook, self.gate_proj.codebook)) for p in projs)
-            self._fused = False
+            self._fused[top_k] = None
             if plain and act_ok and same_book:
                 g = self.gate_proj
                 layer = RoutedMoELayer(torch.zeros((g.num_experts, g.input_dims), dtype=torch.bfloat16, device=g.codes.device),
                                        Projection(g.codes, g.scales), Projection(self.up_proj.codes, self.up_proj.scales),
-                                       Projection(self.down_proj.codes, self.down_proj.scales), top_k=1, codebook=g.codebook,
+                                       Projection(self.down_proj.codes, self.down_proj.scales), top_k=top_k, codebook=g.codebook,
                                        swiglu_limit=float(getattr(self.activation, "limit", 0.0)))
                 if layer.kernel_path == "tensor":
-                    self._fused = layer
-        return self._fused or None
+                    self._fused[top_k] = layer
+        return self._fused[top_k]
 
     def __call__(self, x: torch.Tensor, indices: torch.Tensor) -> torch.Tensor:
-        layer = self._fused_layer()
-        if layer is not None and x.ndim == 2 and indices.ndim == 2 and x.shape[0] == indices.shape[0] and x.dtype in (torch.bfloat16, torch.float16):
+        fits = x.ndim == 2 and indices.ndim == 2 and x.shape[0] == indices.shape[0] and x.dtype in (torch.bfloat16, torch.float16)
+        layer = self._fused_layer(int(indices.shape[1])) if fits else None
+        if layer is not None:
+            # token layout straight through the layer kernels: route t * k + j reads activation row t
+            # (no copy of x per pick); the stages stop before the pick sum and the per-route rows
+            # are what this operator returns
             tokens, k = indices.shape
-            rows = x.repeat_interleave(k, dim=0)  # one activation row per route
-            buf = layer._buffers_for(int(rows.shape[0]), rows.dtype)
-            r = buf["routing"]
-            r.served_slot.copy_(indices.reshape(-1, 1))
+            r = layer._buffers_for(tokens, x.dtype)["routing"]
+            r.served_slot.copy_(indices)
             r.served_weight.fill_(1.0)
-            y, _ = layer.decode(rows, stages=_lib.STAGE_ALL & ~_lib.STAGE_ROUTER, expected_routes=int(rows.shape[0]))
-            return y.reshape(tokens, k, -1).clone()
+            layer.decode(x, stages=_lib.STAGE_PREPARE | _lib.STAGE_GATE_UP | _lib.STAGE_DOWN)
+            out = layer.route_outputs(tokens, x.dtype).reshape(tokens, k, -1).clone()
+            picks = indices.to(torch.int64)
+            dead = (picks < 0) | (picks >= self.gate_proj.num_experts)  # rows the kernels never write
+            return out.masked_fill_(dead[..., None], 0)
         gate = self.gate_proj(x, indices)
         up = self.up_proj(x, indices)
         return self.down_proj(self._apply_activation(up, gate), indices)

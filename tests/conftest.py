@@ -7,8 +7,9 @@ import numpy as np
 import pytest
 
 ROOT = Path(__file__).resolve().parent.parent
-if str(ROOT) not in sys.path:
-    sys.path.insert(0, str(ROOT))
+for entry in (ROOT, ROOT / "tests"):
+    if str(entry) not in sys.path:
+        sys.path.insert(0, str(entry))
 GOLDEN = ROOT / "tests" / "golden"
 
 

@@ -1,4 +1,5 @@
-"""Dispatch / combine index arithmetic of expert parallelism on two CPU ranks (gloo).
+"""Dispatch / combine index arithmetic of expert parallelism on two CPU ranks (gloo), on the torch
+restatement of the exchange (``ep_reference.py``) that the GPU tests check the kernels against.
 
 The experts themselves are a stand-in (a seeded linear map per expert), so what is checked is the
 exchange: every route reaches the rank that owns its expert, carries the right hidden state and
@@ -33,7 +34,11 @@ def worker(rank, port, results):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=WORLD)
     try:
-        from keep_b200.expert_parallel import NO_SLOT, RouteExchange
+        import sys
+        from pathlib import Path
+
+        sys.path.insert(0, str(Path(__file__).resolve().parent))
+        from ep_reference import NO_SLOT, TorchRouteExchange as RouteExchange
 
         rng = np.random.default_rng(10 + rank)
         x = torch.from_numpy(rng.normal(size=(TOKENS, HIDDEN)).astype(np.float32))
@@ -80,9 +85,9 @@ def test_two_rank_dispatch_and_combine_match_the_single_process_sum():
 
 
 def test_single_rank_plan_is_dense_and_ordered():
-    from keep_b200.expert_parallel import RouteExchange
+    from ep_reference import TorchRouteExchange
 
-    exchange = RouteExchange(4)
+    exchange = TorchRouteExchange(4)
     served = torch.tensor([[3, 0], [1, -1], [2, 2]])
     position, capacity = exchange.plan(served)
     assert capacity == 6

@@ -90,9 +90,12 @@ def test_pack_and_combine_kernels_match_the_torch_exchange(cuda, tokens, k, worl
     experts[torch.rand((tokens, k), generator=gen) < 0.15] = -1                       # dead picks
     weights = torch.rand((tokens, k), generator=gen)
     x = torch.randn((tokens, 512), generator=gen).to(torch.bfloat16)
+    from ep_reference import TorchRouteExchange
+
     ex = expert_parallel.RouteExchange(per_rank, capacity=capacity)
-    ex.world = world                                                                   # no process group: pack only
-    want_x, want_slot, want_weight, want_pos = ex.pack_torch(x, experts, weights)
+    ref = TorchRouteExchange(per_rank, capacity=capacity)
+    ex.world = ref.world = world                                                       # no process group: pack only
+    want_x, want_slot, want_weight, want_pos = ref.pack(x, experts, weights)
     got_x, got_meta, got_pos = ex.pack_cuda(x.to(cuda), experts.to(cuda), weights.to(cuda))
     np.testing.assert_array_equal(got_pos.cpu().numpy(), want_pos.numpy())
     np.testing.assert_array_equal(got_meta[:, 0].cpu().numpy(), want_slot.numpy())
@@ -102,8 +105,8 @@ def test_pack_and_combine_kernels_match_the_torch_exchange(cuda, tokens, k, worl
         assert int((want_pos == world * capacity).sum()) > int((experts < 0).sum())     # the small capacity did overflow
 
     back = torch.randn((int(want_x.shape[0]), 512), generator=gen).to(torch.bfloat16)   # stands for the returned expert outputs
-    ex.world = 1                                                                       # combine without an all-to-all
-    want = ex.combine(back, want_pos, torch.bfloat16)
+    ex.world = ref.world = 1                                                           # combine without an all-to-all
+    want = ref.combine(back, want_pos, torch.bfloat16)
     got = ex.combine(back.to(cuda), got_pos, torch.bfloat16)
     assert torch.equal(got.cpu(), want)
 
