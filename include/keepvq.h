@@ -286,6 +286,10 @@ int64_t keepvq_moe_layer_status_offset(int64_t tokens, int64_t hidden, int64_t i
  * routes' outputs unsummed, as QuantizedVQSwitchGLU returns them
  * (src/ramp/models/glm4_moe_adapter.py:367-372), runs the stages up to DOWN and reads them here. */
 int64_t keepvq_moe_layer_route_output_offset(int64_t tokens, int64_t hidden, int64_t inter, int64_t pool, int32_t top_k);
+/* Likewise the routes' hidden rows h = round(silu(G) * U * g), [tokens * top_k, inter], that the
+ * GATE_UP stage leaves for the DOWN stage (the activation step of the reference's switch MLP,
+ * glm4_moe_adapter.py:363-364, with the gate weight applied as omlx_lattice.py:368 does). */
+int64_t keepvq_moe_layer_route_hidden_offset(int64_t tokens, int64_t hidden, int64_t inter, int64_t pool, int32_t top_k);
 
 /* The same sequence, cut into stages: run the stages named in `stages` (a mask) on the same
  * arguments and scratch.  A later stage reads what earlier ones left in the outputs and the

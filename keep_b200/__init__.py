@@ -12,6 +12,7 @@ Modules, by the reference interface they stand in for:
 ``residency``        admission / eviction policy on the device and the slot installer
 ``expert_parallel``  experts sharded over the GPUs of a node (peer-memory or NCCL exchange)
 ``io``               ``layer-NN.npz`` files and safetensors switch projections
+``torch_ops``        the same operators registered as PyTorch custom ops (``torch.ops.keepvq.*``); importing it registers them
 
 Everything computes on the GPU through ``libkeepvq.so`` (``include/keepvq.h``); build it with
 ``python -m keep_b200.build``.  There is no CPU path.

@@ -158,6 +158,7 @@ _SIGNATURES = {
     "keepvq_moe_layer_workspace_bytes": (c_int64, [c_int64, c_int64, c_int64, c_int64, c_int32]),
     "keepvq_moe_layer_status_offset": (c_int64, [c_int64, c_int64, c_int64, c_int64, c_int32]),
     "keepvq_moe_layer_route_output_offset": (c_int64, [c_int64, c_int64, c_int64, c_int64, c_int32]),
+    "keepvq_moe_layer_route_hidden_offset": (c_int64, [c_int64, c_int64, c_int64, c_int64, c_int32]),
     "keepvq_moe_decode_layer": (c_int, [POINTER(MoELayerArgs), c_void_p]),
     "keepvq_moe_decode_stages": (c_int, [POINTER(MoELayerArgs), c_int32, c_void_p]),
     "keepvq_moe_decode_layer_static": (c_int, [POINTER(MoELayerArgs), c_void_p]),

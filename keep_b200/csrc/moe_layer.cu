@@ -163,6 +163,11 @@ extern "C" int64_t keepvq_moe_layer_route_output_offset(int64_t tokens, int64_t 
   return keepvq::plan_scratch(tokens, hidden, inter, pool, top_k).down;
 }
 
+extern "C" int64_t keepvq_moe_layer_route_hidden_offset(int64_t tokens, int64_t hidden, int64_t inter, int64_t pool, int32_t top_k) {
+  if (tokens < 0 || hidden <= 0 || inter <= 0 || pool <= 0 || top_k <= 0) return KEEPVQ_ERR_SHAPE;
+  return keepvq::plan_scratch(tokens, hidden, inter, pool, top_k).h;
+}
+
 extern "C" int keepvq_moe_decode_stages(const keepvq_moe_layer_args* args, int32_t stages, void* stream) {
   using namespace keepvq;
   if (!args) return KEEPVQ_ERR_NULL;

@@ -120,16 +120,24 @@ class RoutedMoELayer:
             served_weight=_lib.ptr(r.served_weight), want=_lib.ptr(r.want), want_score=_lib.ptr(r.want_score),
             admit=_lib.ptr(r.admit), workspace=_lib.ptr(workspace), workspace_bytes=nbytes, expected_routes=int(expected_routes))
 
+    def _scratch_rows(self, which: str, width: int, tokens: int, dtype: torch.dtype, state: int) -> torch.Tensor:
+        buf = self._buffers_for(tokens, dtype, state)
+        offset = int(getattr(_lib.load(), which)(tokens, self.hidden, self.inter, self.pool, self.top_k))
+        if offset < 0:
+            _lib.check(offset, which)
+        base = (-buf["workspace"].data_ptr()) % 256  # the library aligns the scratch to 256 bytes
+        nbytes = tokens * self.top_k * width * dtype.itemsize
+        return buf["workspace"][base + offset: base + offset + nbytes].view(dtype).view(tokens * self.top_k, width)
+
     def route_outputs(self, tokens: int, dtype: torch.dtype, state: int = 0) -> torch.Tensor:
         """The per-route outputs ``[tokens * top_k, hidden]`` the last call of this shape left in its
         scratch (the rows the pick sum adds up): a view, overwritten by the next call."""
-        buf = self._buffers_for(tokens, dtype, state)
-        offset = int(_lib.load().keepvq_moe_layer_route_output_offset(tokens, self.hidden, self.inter, self.pool, self.top_k))
-        if offset < 0:
-            _lib.check(offset, "keepvq_moe_layer_route_output_offset")
-        base = (-buf["workspace"].data_ptr()) % 256
-        nbytes = tokens * self.top_k * self.hidden * dtype.itemsize
-        return buf["workspace"][base + offset: base + offset + nbytes].view(dtype).view(tokens * self.top_k, self.hidden)
+        return self._scratch_rows("keepvq_moe_layer_route_output_offset", self.hidden, tokens, dtype, state)
+
+    def route_hidden(self, tokens: int, dtype: torch.dtype, state: int = 0) -> torch.Tensor:
+        """The routes' hidden rows ``h = silu(G) * U * weight``, ``[tokens * top_k, inter]``, that
+        the gate/up stage of the last call of this shape left for the down stage: a view."""
+        return self._scratch_rows("keepvq_moe_layer_route_hidden_offset", self.inter, tokens, dtype, state)
 
     def wait_expired(self, tokens: int, dtype: torch.dtype, state: int = 0) -> bool:
         """True when a bounded wait of the tcgen05 kernels expired during the last call of this

@@ -61,3 +61,15 @@ def test_operators_refuse_cpu_tensors():
     with pytest.raises(_lib.KeepVQError):
         kernels.vq_qmv(x, torch.zeros(8, 8, dtype=torch.uint16), torch.ones(8, 1), None, in_dim=64, out_dim=8,
                        group_size=64, code_bits=16)
+
+
+def test_custom_ops_register_without_a_gpu():
+    """Importing ``keep_b200.torch_ops`` defines every operator under ``torch.ops.keepvq`` with a
+    schema (no compute happens without a device)."""
+    import torch
+
+    from keep_b200 import torch_ops
+
+    for name in torch_ops.OPS:
+        schema = getattr(torch.ops.keepvq, name).default._schema
+        assert schema.name == f"keepvq::{name}" and len(schema.returns) >= 1

@@ -110,14 +110,14 @@ def test_glu_fused_and_composed_match_the_dense_oracle(cuda, tokens, limit):
     act = limited_swiglu(limit) if limit else None
     fused = QuantizedVQSwitchGLU(gate_proj=linear(cuda, *cfg["w1"]), up_proj=linear(cuda, *cfg["w3"]), down_proj=linear(cuda, *cfg["w2"]), activation=act)
     got = fused(x.to(cuda), torch.from_numpy(idx).to(cuda))
-    assert fused._fused_layer() is not None and tuple(got.shape) == (tokens, 3, 512) and got.dtype == torch.bfloat16
+    assert fused._fused_layer(3) is not None and tuple(got.shape) == (tokens, 3, 512) and got.dtype == torch.bfloat16
     assert e8.relative_gap(got.float().cpu().numpy(), want) <= 1e-2
     # a bias on one projection takes the composed path (three operator calls, activation in torch)
     zero = torch.zeros((6, 512), device=cuda)
     composed = QuantizedVQSwitchGLU(gate_proj=linear(cuda, *cfg["w1"]), up_proj=linear(cuda, *cfg["w3"]),
                                     down_proj=linear(cuda, *cfg["w2"], bias=zero), activation=act)
     got2 = composed(x.to(cuda), torch.from_numpy(idx).to(cuda))
-    assert composed._fused_layer() is None
+    assert composed._fused_layer(3) is None
     assert e8.relative_gap(got2.float().cpu().numpy(), want) <= 1e-2
 
 

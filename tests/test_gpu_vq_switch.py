@@ -106,10 +106,11 @@ def test_metadata_errors_match_the_reference_messages(cuda):
 @pytest.mark.parametrize("routes,experts", [(300, 6), (1500, 6), (1200, 40)])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_sorted_routes_on_the_tensor_core_kernels(cuda, routes, experts, dtype):
-    """Prefill-shaped sorted calls (16-bit codes, in_dim % 256 == 0, one scale group per row) run
-    keepvq_grouped_projection: the mma.sync kernel for 300 routes, the tcgen05 kernel for 1500
-    routes over 6 experts, the mma.sync one again for 1200 routes spread over 40 experts.  The
-    only rounding is the 16-bit fixed-point step on the activations."""
+    """Prefill-shaped sorted calls (16-bit codes, in_dim % 256 == 0, one scale group per row) with
+    bf16 activations run keepvq_grouped_projection: the mma.sync kernel for 300 routes, the tcgen05
+    kernel for 1500 routes over 6 experts, the mma.sync one again for 1200 routes spread over 40
+    experts; the only rounding there is the 16-bit fixed-point step on the activations.  fp32
+    activations are not narrowed: they take the general kernel (24-bit fixed point)."""
     from keep_b200 import prefill, vq, vq_switch
 
     rng = np.random.default_rng(90 + routes)
@@ -128,4 +129,65 @@ def test_sorted_routes_on_the_tensor_core_kernels(cuda, routes, experts, dtype):
     rows = x.to(cuda)[torch.from_numpy(lhs).to(cuda)]
     direct = prefill.tensor_core_projection(rows, torch.from_numpy(codes).to(cuda), torch.from_numpy(scales).to(cuda),
                                             vq.table_on(cuda, "e8p"), torch.from_numpy(rhs).to(cuda))
-    assert direct is not None and torch.equal(direct, got)  # the operator did take this entry point
+    if dtype == torch.float32:
+        assert direct is None
+    else:
+        assert direct is not None and torch.equal(direct, got)  # the operator did take this entry point
+
+
+def test_routes_without_an_expert_give_zero_rows_on_every_path(cuda):
+    """A route whose index names no expert (0xFFFFFFFF, or any value past the last expert) returns
+    a row of zeros from the tensor-core kernels and from the general kernel alike."""
+    from keep_b200 import kernels, prefill, vq
+
+    rng = np.random.default_rng(21)
+    experts, out, inp = 4, 64, 256
+    codes = rng.integers(0, 1 << 16, (experts, out, inp // 8), dtype=np.uint16)
+    scales = (0.02 * rng.uniform(0.5, 1.5, (experts, out, 1))).astype(np.float16)
+    table = vq.table_on(cuda, "e8p")
+    for routes in (6, 64):  # the team kernel and the slab kernel
+        rhs = rng.integers(0, experts, routes).astype(np.int64)
+        rhs[1], rhs[routes - 2] = 0xFFFFFFFF, experts + 3
+        x = torch.from_numpy(rng.normal(size=(routes, inp)).astype(np.float32)).to(cuda)
+        dead = torch.tensor([1, routes - 2])
+        rhs_t = torch.from_numpy(rhs.astype(np.uint32).view(np.int32)).to(cuda)
+        fast = prefill.tensor_core_projection(x.to(torch.bfloat16), torch.from_numpy(codes).to(cuda), torch.from_numpy(scales).to(cuda), table, rhs_t)
+        assert fast is not None and bool((fast[dead] == 0).all()) and bool((fast[0] != 0).any())
+        general = kernels.e8p_m1_per_route(x, codes, scales, table, rhs.astype(np.uint32), output_dims=out)
+        assert bool((general[dead] == 0).all()) and bool((general[0] != 0).any())
+
+
+@pytest.mark.parametrize("factor", [300.0, 3000.0])
+def test_one_outlier_channel_costs_what_the_header_says(cuda, factor):
+    """fp16 / bf16 rows are held as 16-bit fixed point with one power-of-two step per row, so a
+    channel far above the rest takes precision from the small channels.  Bounds stated beside
+    ``keepvq_grouped_projection``: against the true output the gap stays near 1e-3 of its largest
+    magnitude; against the output the row would give without the outlier channel it is below 1 %
+    at 300 times the row's RMS and below 5 % at 3000 times.  fp32 rows go to the general kernel,
+    which keeps 24 bits of a row: 256 times tighter."""
+    from keep_b200 import kernels, prefill, vq
+
+    rng = np.random.default_rng(22)
+    experts, out, inp, routes = 2, 256, 4096, 64
+    codes = rng.integers(0, 1 << 16, (experts, out, inp // 8), dtype=np.uint16)
+    scales = (0.02 * rng.uniform(0.5, 1.5, (experts, out, 1))).astype(np.float16)
+    dense = ops.dense_experts(codes, scales, dtype=np.float64)
+    rhs = rng.integers(0, experts, routes).astype(np.uint32)
+    x = rng.normal(size=(routes, inp)).astype(np.float32)
+    x[:, 7] = factor
+    xb = torch.from_numpy(x).to(cuda).to(torch.bfloat16)
+    xn = xb.float().cpu().numpy().astype(np.float64)
+    want = np.stack([xn[r] @ dense[e].T for r, e in enumerate(rhs)])
+    quiet = xn.copy()
+    quiet[:, 7] = 0.0
+    want_quiet = np.stack([quiet[r] @ dense[e].T for r, e in enumerate(rhs)])
+    table = vq.table_on(cuda, "e8p")
+    got = prefill.tensor_core_projection(xb, torch.from_numpy(codes).to(cuda), torch.from_numpy(scales).to(cuda), table,
+                                         torch.from_numpy(rhs.view(np.int32)).to(cuda)).float().cpu().numpy()
+    # bf16 output rounding alone is 2^-9 relative; the activation step adds the rest
+    assert np.abs(got - want).max() <= 6e-3 * np.abs(want).max()
+    noise = np.abs((got - want)).max() / np.abs(want_quiet).max()
+    assert noise <= (0.01 if factor == 300.0 else 0.05) + 2 ** -8 * np.abs(want).max() / np.abs(want_quiet).max(), noise
+    # fp32 rows: 24-bit fixed point in the general kernel
+    got32 = kernels.e8p_m1_per_route(torch.from_numpy(xn.astype(np.float32)).to(cuda), codes, scales, table, rhs, output_dims=out).cpu().numpy()
+    assert np.abs(got32 - want).max() <= (5e-5 if factor == 300.0 else 4e-4) * np.abs(want_quiet).max()

@@ -64,3 +64,20 @@ def test_safetensors_switch_dims_and_checks():
         layer_io.switch_linear_dims({"m.w.codes": (4, 6, 8), "m.w.scales": (4, 5, 2)}, {"m.w.codes": "U16"}, "m.w")
     with pytest.raises(ValueError, match="must divide"):
         layer_io.switch_linear_dims({"m.w.codes": (4, 6, 8), "m.w.scales": (4, 6, 3)}, {"m.w.codes": "U16"}, "m.w")
+
+
+@pytest.mark.parametrize("sidecar", ["rht_signs", "rotation_matrix", "continuous_low_rank_left"])
+def test_a_checkpoint_with_a_rotation_or_residual_sidecar_is_refused(tmp_path, sidecar):
+    """The reference's loader hands ``<prefix>.rht_signs`` / ``.rotation_matrix`` (and the other
+    conversion-side tensors) to the layer, whose forward applies them (src/keep/io/load.py:245-257,
+    src/ramp/nn/linear.py:77-82).  This runtime does not apply them, so it must not load such a
+    file as if they were absent: the refusal comes before any tensor reaches a device."""
+    import torch
+    from safetensors.torch import save_file
+
+    tensors = {"m.w.codes": torch.zeros((2, 8, 4), dtype=torch.uint8), "m.w.scales": torch.ones((2, 8, 1), dtype=torch.float16),
+               f"m.w.{sidecar}": torch.ones(32, dtype=torch.float16)}
+    path = tmp_path / "layer.safetensors"
+    save_file(tensors, str(path))
+    with pytest.raises(NotImplementedError, match=sidecar):
+        layer_io.load_quantized_vq_switch_linear(path, "m.w", "cpu")
