@@ -134,8 +134,13 @@ def token_batches(device, batch, count=ROTATION):
     return [torch.randn((batch, HIDDEN), generator=gen).to(torch.bfloat16).to(device) for _ in range(count)]
 
 
-def time_graph(fn, steps, warmup):
-    """CUDA-event time of `steps` calls of fn(i) replayed from one CUDA graph, in ms."""
+REPLAYS = 7
+
+
+def time_graph(fn, steps, warmup, replays=REPLAYS, every=False):
+    """CUDA-event time of `steps` calls of fn(i) replayed from one CUDA graph, in ms: the median of
+    `replays` timed replays (after one untimed replay).  With ``every`` the list of all replay
+    times is returned as well."""
     stream = torch.cuda.Stream()
     stream.wait_stream(torch.cuda.current_stream())
     with torch.cuda.stream(stream):
@@ -148,12 +153,15 @@ def time_graph(fn, steps, warmup):
                 fn(i)
         graph.replay()  # one untimed replay
         torch.cuda.synchronize()
-        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        begin.record(stream)
-        graph.replay()
-        end.record(stream)
-        torch.cuda.synchronize()
-    return begin.elapsed_time(end)
+        times = []
+        for _ in range(max(replays, 1)):
+            begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            begin.record(stream)
+            graph.replay()
+            end.record(stream)
+            torch.cuda.synchronize()
+            times.append(begin.elapsed_time(end))
+    return (statistics.median(times), times) if every else statistics.median(times)
 
 
 def distinct_experts(layer, xs):
@@ -184,19 +192,19 @@ def projection_roofline(layer, xs, steps, hbm_gbs, peak_kind):
     launches = 1 if tensor else 3  # general kernels: gate, up and the SwiGLU pass
     bytes_per_stage = statistics.fmean(uniq[i % len(xs)] for i in range(steps)) * 2 * CODE_BYTES_PER_PROJECTION
     achieved = bytes_per_stage / (ms / steps * 1e-3) / 1e9
-    # DRAM bytes per launch from the ncu capture summarised in profiles/projection_cta_kernel_decode_b64_ncu.md:
-    # 995.4 MB read + written for 1025.4 MB of distinct code bytes at batch 64; traffic grows with the
-    # number of distinct experts a launch touches, so other batches scale it by their code bytes.
+    # DRAM bytes per launch are not measured in this run: they come from one ncu capture of this kernel
+    # at batch 64 (dram__bytes_read.sum + dram__bytes_write.sum = 999.4 MB for 1025.4 MB of distinct code
+    # bytes) and are scaled by the code bytes of the launch timed here.
     traffic = int(NCU_TRAFFIC_PER_CODE_BYTE * bytes_per_stage) if tensor else None
     return {"bound": "hbm", "achieved": round(achieved, 1), "peak": hbm_gbs, "unit": "GB/s", "frac": round(achieved / hbm_gbs, 4),
-            "traffic": traffic, "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch, scaled by code bytes" if tensor else None,
+            "traffic": traffic, "traffic_source": "one ncu capture of this kernel at batch 64 (dram__bytes_read.sum + dram__bytes_write.sum), scaled by this launch's code bytes; not measured in this run" if tensor else None,
             "peak_kind": peak_kind,
             "kernel": "projection_slab_kernel<2,1> (gate+up+SwiGLU, int8 tensor cores)" if tensor else "routed_rowdot_kernel x2 + swiglu",
             "launches_per_stage": launches, "algorithmic_bytes_per_launch": int(bytes_per_stage),
             "us_per_launch": round(ms / steps * 1e3, 2)}
 
 
-NCU_TRAFFIC_PER_CODE_BYTE = 995.4 / 1025.4
+NCU_TRAFFIC_PER_CODE_BYTE = 999.4 / 1025.4
 
 
 def batch_sweep(layer, device, rotation, steps, hbm_gbs, batches=(1, 4, 16)):
@@ -311,8 +319,72 @@ def prefill_leg(layer, device, steps=6):
                                      for k, m in names.items()}
         layer.pool_bias, layer.served_bias = saved
     out["peak_tflops"], out["useful_flops"] = peak, PREFILL_FLOPS
-    out["kernel"] = "prefill_projection_kernel (tcgen05.mma kind::i8, two int8 MMAs per bf16-equivalent product)"
+    out["kernel"] = "prefill_projection_kernel (tcgen05.mma kind::i8, A from tensor memory, two int8 MMAs per bf16-equivalent product)"
+    threads = os.cpu_count() or 1
+    cpu_s = cpu_expert_sample(layer, threads)
+    out["cpu_baseline"] = {"seconds_per_expert": round(cpu_s, 3), "routes": 64, "cores": threads, "kind": "port",
+                           "sample": "one of the 384 experts: decode of its three matrices + SwiGLU path for 64 token rows; the 4096-token call has 384 such experts",
+                           "extrapolated_layer_tokens_per_s": round(PREFILL_TOKENS / (cpu_s * EXPERTS), 2)}
     return out
+
+
+def operator_legs(layer, device, hbm_gbs, steps=32):
+    """Config 1 (`vq_qmv`, one expert's gate matrix [2048 x 4096], one bf16 vector) and `gather_vqmm`
+    with the direct strategy at 1, 4 and 16 tokens (top-6 routes over the layer's gate matrices),
+    each replayed from a CUDA graph: microseconds per call and GB/s on the distinct code bytes the
+    call touches, beside the CPU path of the same operator (decode + fp32 product, warmed once)."""
+    from keep_b200 import kernels, vq, vq_switch
+    from oracle import ops as oracle_ops
+
+    table = vq.table_on(device, "e8p")
+    gen = torch.Generator(device="cpu").manual_seed(0)
+    x1 = torch.randn((HIDDEN,), generator=gen).to(torch.bfloat16).to(device)
+    codes, scales = layer.w1.codes, layer.w1.scales
+    out = {}
+    # rotate over experts so that successive calls do not find their codes in L2
+    ms = time_graph(lambda i: kernels.vq_qmv(x1, codes[i % EXPERTS], scales[i % EXPERTS], table, in_dim=HIDDEN, out_dim=INTER,
+                                             group_size=HIDDEN, code_bits=16), steps, 3)
+    us = ms / steps * 1e3
+    c0, s0 = codes[0].cpu().numpy(), scales[0].cpu().numpy()
+    xr = x1.float().cpu().numpy()
+    oracle_ops.vq_qmv_reference(xr, c0, s0, None, code_bits=16)  # warm: builds the tables once
+    begin = time.perf_counter()
+    oracle_ops.vq_qmv_reference(xr, c0, s0, None, code_bits=16)
+    cpu_s = time.perf_counter() - begin
+    out["vq_qmv_2048x4096"] = {"us_per_call": round(us, 2), "code_gbs": round(CODE_BYTES_PER_PROJECTION / (us * 1e-6) / 1e9, 1),
+                               "code_frac_of_hbm": round(CODE_BYTES_PER_PROJECTION / (us * 1e-6) / 1e9 / hbm_gbs, 4),
+                               "cpu_us_per_call": round(cpu_s * 1e6, 1), "kernel": "routed_rowdot_kernel (general kernel: one route, 24/16-bit fixed point, dp4a)"}
+    for tokens in (1, 4, 16):
+        xs, picks, uniq = [], [], []
+        for j in range(8):
+            g = torch.Generator(device="cpu").manual_seed(100 + 8 * tokens + j)
+            xs.append(torch.randn((tokens, HIDDEN), generator=g).to(torch.bfloat16).to(device))
+            rhs = torch.stack([torch.randperm(EXPERTS, generator=g)[:TOP_K] for _ in range(tokens)]).to(torch.int32)
+            uniq.append(len(set(rhs.reshape(-1).tolist())))
+            picks.append(rhs.to(device))
+        ms = time_graph(lambda i: vq_switch.gather_vqmm(xs[i % 8], codes, scales, table, picks[i % 8], input_dims=HIDDEN, output_dims=INTER,
+                                                        group_size=HIDDEN, code_bits=16, route_strategy="direct"), steps, 3)
+        us = ms / steps * 1e3
+        touched = statistics.fmean(uniq) * CODE_BYTES_PER_PROJECTION
+        out[f"gather_vqmm_direct_b{tokens}"] = {"us_per_call": round(us, 2), "routes": tokens * TOP_K, "code_gbs": round(touched / (us * 1e-6) / 1e9, 1),
+                                                  "code_frac_of_hbm": round(touched / (us * 1e-6) / 1e9 / hbm_gbs, 4)}
+    return out
+
+
+def cpu_expert_sample(layer, threads, routes=64):
+    """One expert of the prefill leg on the CPU path: decode of its three matrices and the SwiGLU
+    path for `routes` token rows (what the reference's CPU code does per expert).  Seconds."""
+    from oracle import router as oracle_router
+
+    torch.set_num_threads(threads)
+    gen = torch.Generator(device="cpu").manual_seed(9)
+    rows = torch.randn((routes, HIDDEN), generator=gen).to(torch.bfloat16)
+    oracle_router.decode_torch(layer.w1.codes[1].cpu().numpy(), layer.w1.scales[1].cpu().numpy())  # warm the decode grid
+    begin = time.perf_counter()
+    w = {n: oracle_router.decode_torch(getattr(layer, n).codes[0].cpu().numpy(), getattr(layer, n).scales[0].cpu().numpy()) for n in ("w1", "w3", "w2")}
+    slots = np.zeros((routes, 1), dtype=np.int64)
+    oracle_router.moe_layer(rows, slots, np.ones((routes, 1), dtype=np.float32), {0: w["w1"]}, {0: w["w3"]}, {0: w["w2"]})
+    return time.perf_counter() - begin
 
 
 def cpu_layer_sample(layer, x_row, threads, experts_per_token=TOP_K):
@@ -369,6 +441,27 @@ def run_reference(ns):
 EP_LAYERS, EP_BATCH = 40, 256
 
 
+def ep_shard(device, index, rank, per_rank):
+    """The three projections of layer `index` for the experts rank `rank` owns (seeded per layer and rank)."""
+    from keep_b200 import moe
+
+    shard = torch.Generator(device=device)
+    shard.manual_seed(100_000 + 1000 * index + rank)
+
+    def proj(out, inp):
+        codes = torch.randint(0, 1 << 16, (per_rank, out, inp // 8), generator=shard, device=device, dtype=torch.int32).to(torch.uint16)
+        scales = (0.02 * (0.5 + torch.rand((per_rank, out, 1), generator=shard, device=device))).to(torch.float16)
+        return moe.Projection(codes, scales)
+
+    return proj(INTER, HIDDEN), proj(INTER, HIDDEN), proj(HIDDEN, INTER)
+
+
+def ep_router(device, index):
+    shared = torch.Generator(device=device)
+    shared.manual_seed(100 + index)
+    return (0.02 * torch.randn((EXPERTS, HIDDEN), generator=shared, device=device)).to(torch.bfloat16)
+
+
 def build_ep_stack(device, rank, world, layers, exchange_kind="peer"):
     """Config 5: `layers` MoE layers, each with its 384 experts sharded contiguously over the ranks
     and a replicated router (same seed on every rank)."""
@@ -380,28 +473,81 @@ def build_ep_stack(device, rank, world, layers, exchange_kind="peer"):
     if exchange_kind == "peer":  # one set of peer-mapped buffers serves every layer of the stack
         exchange = expert_parallel.PeerExchange(per_rank, tokens=EP_BATCH // world, top_k=TOP_K, hidden=HIDDEN, dtype=torch.bfloat16, device=device)
     for index in range(layers):
-        shard = torch.Generator(device=device)
-        shard.manual_seed(100_000 + 1000 * index + rank)
-
-        def proj(out, inp):
-            codes = torch.randint(0, 1 << 16, (per_rank, out, inp // 8), generator=shard, device=device, dtype=torch.int32).to(torch.uint16)
-            scales = (0.02 * (0.5 + torch.rand((per_rank, out, 1), generator=shard, device=device))).to(torch.float16)
-            return moe.Projection(codes, scales)
-
-        shared = torch.Generator(device=device)
-        shared.manual_seed(100 + index)
-        router = (0.02 * torch.randn((EXPERTS, HIDDEN), generator=shared, device=device)).to(torch.bfloat16)
-        local = moe.RoutedMoELayer(torch.zeros((per_rank, HIDDEN), dtype=torch.bfloat16, device=device),
-                                   proj(INTER, HIDDEN), proj(INTER, HIDDEN), proj(HIDDEN, INTER), top_k=1)
-        stack.append(expert_parallel.ExpertParallelLayer(router, local, experts_per_rank=per_rank, top_k=TOP_K, exchange=exchange))
+        w1, w3, w2 = ep_shard(device, index, rank, per_rank)
+        local = moe.RoutedMoELayer(torch.zeros((per_rank, HIDDEN), dtype=torch.bfloat16, device=device), w1, w3, w2, top_k=1)
+        stack.append(expert_parallel.ExpertParallelLayer(ep_router(device, index), local, experts_per_rank=per_rank, top_k=TOP_K, exchange=exchange))
     return stack
+
+
+def ep_parity_gap(stack, x, rank, world, device):
+    """Layer 0 through the exchange against the same layer with every expert on one GPU: each rank
+    regenerates the other ranks' shards of layer 0 from their seeds, runs the whole layer on the
+    tokens of all ranks and compares its own rows.  Returns max|a - b| / max|b| over all ranks."""
+    import torch.distributed as dist
+    from keep_b200 import moe
+
+    per_rank = EXPERTS // world
+    shards = [ep_shard(device, 0, r, per_rank) for r in range(world)]
+    cat = lambda k: moe.Projection(torch.cat([s[k].codes.view(torch.int16) for s in shards]).view(torch.uint16), torch.cat([s[k].scales for s in shards]))  # noqa: E731
+    whole = moe.RoutedMoELayer(stack[0].router_w, cat(0), cat(1), cat(2), top_k=TOP_K)
+    every = [torch.empty_like(x) for _ in range(world)]
+    dist.all_gather(every, x)
+    want = whole.decode(torch.cat(every))[0][rank * x.shape[0]:(rank + 1) * x.shape[0]].float()
+    got = stack[0].forward(x).float()
+    gap = ((got - want).abs().max() / want.abs().max()).reshape(1)
+    dist.all_reduce(gap, op=dist.ReduceOp.MAX)
+    del whole, shards
+    torch.cuda.empty_cache()
+    return float(gap.item())
+
+
+def between_layers(y):
+    """What the model does between two routed layers, reduced to its effect on scale: an RMS norm
+    (torch).  Without it the tokens of a random-weight stack shrink layer by layer until every
+    router sees zeros and all tokens pick the same six experts."""
+    return torch.nn.functional.rms_norm(y, (y.shape[-1],))
+
+
+def ep_single_gpu_record(device, layers, steps, hbm_gbs):
+    """Config 5 on ONE GPU (all 384 experts of every layer local, no exchange): the base of the
+    strong-scaling curve.  40 layers x 2.4 GB of codes = 96.6 GB; 256 tokens run through the
+    layers one after the other (each layer's output is the next layer's input)."""
+    from keep_b200 import moe
+
+    stack = []
+    for index in range(layers):
+        w1, w3, w2 = ep_shard(device, index, 0, EXPERTS)
+        stack.append(moe.RoutedMoELayer(ep_router(device, index), w1, w3, w2, top_k=TOP_K))
+    gen = torch.Generator(device="cpu").manual_seed(5)
+    x = torch.randn((EP_BATCH, HIDDEN), generator=gen).to(torch.bfloat16).to(device)
+
+    def step(_):
+        h = x
+        for layer in stack:
+            h = between_layers(layer.decode(h)[0])
+
+    ms = time_graph(step, steps, 3, replays=5)
+    layer_us = ms / steps / layers * 1e3
+    touched = statistics.fmean(int(torch.unique(layer._buffers_for(EP_BATCH, torch.bfloat16, 0)["routing"].served_expert).numel()) for layer in stack)
+    record = {"layers": layers, "batch": EP_BATCH, "layer_us": round(layer_us, 1), "tokens_x_layers_per_s": round(EP_BATCH * layers * steps / (ms * 1e-3), 1),
+              "distinct_experts_per_layer": round(touched, 1),
+              "code_frac_of_hbm": round(touched * CODE_BYTES_PER_EXPERT / (layer_us * 1e-6) / 1e9 / hbm_gbs, 4)}
+    del stack
+    torch.cuda.empty_cache()
+    return record
+
+
+def ep_n1_path():
+    import tempfile
+
+    return Path(tempfile.gettempdir()) / "keep_b200_ep_n1.json"
 
 
 def run_expert_parallel(ns, rank, world, local, device):
     """N > 1: the 40-layer expert-parallel stack (config 5).  256 decode tokens in total, split
     evenly over the ranks; per layer: router, dispatch all-to-all, local experts, combine
-    all-to-all.  The same tokens enter every layer (the layers differ in weights), so the stack
-    is 40 dependent-in-stream layer passes per step."""
+    all-to-all.  Each layer's output (RMS-normalised) is the next layer's input, so the stack
+    is 40 dependent layer passes per step."""
     import torch.distributed as dist
     from keep_b200 import _lib
 
@@ -417,13 +563,16 @@ def run_expert_parallel(ns, rank, world, local, device):
     outs = [None]
 
     def step():
-        out = None
-        for layer in stack:
-            out = layer.forward(x)
-        outs[0] = out
+        h = x
+        for layer in stack:  # each layer's output, RMS-normalised, is the next layer's input
+            h = between_layers(layer.forward(h))
+        outs[0] = h
 
     torch.cuda.synchronize()
     dist.barrier()  # the ranks finish generating their layers at different times; the first exchange meets on the device
+    parity_gap = ep_parity_gap(stack, x, rank, world, device)
+    if parity_gap > 1e-2:
+        raise RuntimeError(f"the expert-parallel layer differs from the single-GPU layer by {parity_gap}: the timing is invalid")
     for _ in range(max(ns.warmup, 3)):
         step()
     torch.cuda.synchronize()
@@ -468,9 +617,31 @@ def run_expert_parallel(ns, rank, world, local, device):
         torch.cuda.synchronize()
         e2e_ms = begin.elapsed_time(end)
     expired = float(stack[0].exchange.wait_expired()) if ns.exchange == "peer" else 0.0
-    t = torch.tensor([ms, e2e_ms, expired], device=device)
+    # BASELINE words config 5 with NCCL all-to-alls: the same local layers behind the NCCL exchange, a few eager steps
+    nccl_ms = 0.0
+    if ns.exchange == "peer":
+        from keep_b200 import expert_parallel
+
+        nccl_stack = [expert_parallel.ExpertParallelLayer(l.router_w, l.local, experts_per_rank=EXPERTS // world, top_k=TOP_K) for l in stack]
+
+        def nccl_step():
+            h = x
+            for layer in nccl_stack:
+                h = between_layers(layer.forward(h))
+
+        for _ in range(2):
+            nccl_step()
+        torch.cuda.synchronize()
+        dist.barrier()
+        begin.record()
+        for _ in range(3):
+            nccl_step()
+        end.record()
+        torch.cuda.synchronize()
+        nccl_ms = begin.elapsed_time(end) / 3
+    t = torch.tensor([ms, e2e_ms, expired, nccl_ms], device=device)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms, e2e_ms, expired = (float(v) for v in t.cpu())
+    ms, e2e_ms, expired, nccl_ms = (float(v) for v in t.cpu())
     if expired:
         raise RuntimeError("a barrier of the peer exchange gave up waiting for a rank: the timing is invalid")
     if rank != 0:
@@ -482,6 +653,15 @@ def run_expert_parallel(ns, rank, world, local, device):
     hbm_gbs = float(peaks.get("hbm_gbs", 6650.0))
     local_experts = EXPERTS // world
     touched = local_experts * (1.0 - (1.0 - 1.0 / EXPERTS) ** (EP_BATCH * TOP_K))  # expected distinct local experts per layer
+    # the one-GPU run of this same stack, if an N = 1 run of this benchmark left its record on this machine
+    strong = None
+    try:
+        base = json.loads(ep_n1_path().read_text())
+        if base.get("layers") == layers:
+            strong = {"n1_layer_us": base["layer_us"], "speedup": round(base["layer_us"] / (ms / ns.steps / layers * 1e3), 3),
+                      "efficiency": round(base["layer_us"] / (ms / ns.steps / layers * 1e3) / world, 3)}
+    except (OSError, ValueError, KeyError):
+        pass
     achieved = touched * CODE_BYTES_PER_EXPERT / layer_s / 1e9
     line = {
         "metric": METRIC, "value": round(tokens / (ms * 1e-3), 1), "unit": UNIT, "n_gpus": world, "steps": ns.steps, "warmup": ns.warmup,
@@ -497,6 +677,9 @@ def run_expert_parallel(ns, rank, world, local, device):
                      "algorithmic_bytes_per_layer": int(touched * CODE_BYTES_PER_EXPERT)},
         "stack_tokens_per_s": round(EP_BATCH * ns.steps / (ms * 1e-3), 1), "cpu_baseline": None,
         "layer_us": round(ms / ns.steps / layers * 1e3, 1),
+        "ep_parity_gap": parity_gap, "ep_parity": "layer 0 through the exchange vs the same layer with all 384 experts on one GPU, max|a-b|/max|b| over all ranks",
+        "nccl_layer_us": round(nccl_ms / layers * 1e3, 1) if nccl_ms else None,
+        "strong_scaling_vs_n1": strong,
         "e2e": {"value": round(tokens / (e2e_ms * 1e-3), 1), "unit": UNIT, "h2d_bytes_per_step": EP_BATCH * HIDDEN * 2, "d2h_bytes_per_step": EP_BATCH * HIDDEN * 2},
         "gpu_launches": (14 if ns.exchange == "peer" else 11) * layers * ns.steps * world, "kernel_path": stack[0].local.kernel_path, "clocks": clocks.summary(),
     }
@@ -536,7 +719,7 @@ def run_ours(ns):
 
     barrier()
     with ClockSampler(local) as clocks:
-        ms = time_graph(step, ns.steps, ns.warmup)
+        ms, replay_ms = time_graph(step, ns.steps, ns.warmup, every=True)
         barrier()
         # end to end: pinned host tokens in, layer output back to the host, every step
         host_in = [x.cpu().pin_memory() for x in xs]
@@ -565,6 +748,7 @@ def run_ours(ns):
     code_gbs = mean_u * CODE_BYTES_PER_EXPERT / (ms / ns.steps * 1e-3) / 1e9
     roofline = projection_roofline(layer, xs, ns.steps, hbm_gbs, peak_kind)
     threads = os.cpu_count() or 1
+    cpu_layer_sample(layer, xs[1 % len(xs)][:1].cpu(), threads, 1)  # warm: the first call builds the 65,536-entry decode grid
     cpu_s, cpu_out = cpu_layer_sample(layer, xs[0][:1].cpu(), threads)
     gpu_out, _ = layer.decode(xs[0])
     ref = cpu_out.numpy()
@@ -575,18 +759,29 @@ def run_ours(ns):
         "dtype": "bf16", "data": "synthetic",
         "config": {"workload": f"decode layer (config 2): 384 experts, hidden 4096, inter 2048, top-6 softmax router, batch {batch}",
                    "batch": batch, "l2": "inputs larger than L2: 64 rotating token batches over a 2.4 GB expert pool",
-                   "distinct_experts_per_step": round(mean_u, 2)},
+                   "distinct_experts_per_step": round(mean_u, 2),
+                   "timing": f"one CUDA graph of {ns.steps} steps, replayed {REPLAYS} times after an untimed replay; ms_per_step and value are the median replay"},
+        "replays": REPLAYS, "replay_ms": [round(v, 4) for v in replay_ms], "timed_region_s": round(sum(replay_ms) * 1e-3, 4),
         "layer_code_gbs": round(code_gbs, 1), "layer_code_frac_of_hbm": round(code_gbs / hbm_gbs, 4),
         "roofline": roofline, "stage_us": stage_times(layer, xs, ns.steps),
         "cpu_baseline": {"value": round(1.0 / cpu_s, 4), "unit": UNIT, "cores": threads, "kind": "port",
-                         "sample": "one token: router + decode of 6 experts x 3 projections + SwiGLU path", "parity_gap_vs_gpu": parity_gap},
+                         "sample": "one token (after one warm-up token): router + decode of 6 experts x 3 projections + SwiGLU path", "parity_gap_vs_gpu": parity_gap},
         "e2e": {"value": round(e2e_value, 1), "unit": UNIT, "h2d_bytes_per_step": batch * HIDDEN * 2, "d2h_bytes_per_step": batch * HIDDEN * 2},
         "batch_sweep": batch_sweep(layer, device, ns.rotation, ns.steps, hbm_gbs) if not ns.no_prefill else None,
         "residency": residency_leg(layer, device, ns.rotation, ns.steps, hbm_gbs) if not ns.no_prefill else None,
         "prefill": prefill_leg(layer, device) if not ns.no_prefill else None,
+        "operators": operator_legs(layer, device, hbm_gbs) if not ns.no_prefill else None,
+        "ep_n1": None,
         "gpu_launches": layer.launches_per_call * ns.steps, "kernel_path": layer.kernel_path,
         "clocks": clocks.summary(),
     }
+    if not ns.no_prefill:  # config 5 on this one GPU: the base the N > 1 lines compare their layer time with
+        torch.cuda.empty_cache()
+        line["ep_n1"] = ep_single_gpu_record(device, ns.layers, 4, hbm_gbs)
+        try:
+            ep_n1_path().write_text(json.dumps(line["ep_n1"]))
+        except OSError:
+            pass
     print(json.dumps(line))
 
 

@@ -538,6 +538,18 @@ int keepvq_ep_return_peer(const void* y, const keepvq_ep_peer_args* peer, void* 
 #define KEEPVQ_STATIC_SCRATCH_BYTES (8u << 20)
 int keepvq_moe_decode_layer_static(const keepvq_moe_layer_args* args, void* stream);
 
+/* ------------------------------------------------------------------------------------------
+ * Self-test of the bounded waits of the tcgen05 kernels.  Runs one thread block of the prefill
+ * projection kernel on a tiny problem laid out inside `workspace`, with the producers of its
+ * activation tiles told never to publish.  The consumer's wait must run into its deadline
+ * (`wait_ns` nanoseconds on the GPU's global timer, at most one second), after which the block
+ * writes 1 into the first int32 of `workspace`, releases its tensor memory and returns; the
+ * device stays usable.  A host checks that word after synchronising.  No counterpart in the
+ * reference.
+ * ------------------------------------------------------------------------------------------ */
+int64_t keepvq_wait_selftest_workspace_bytes(void);
+int keepvq_wait_selftest(void* workspace, int64_t workspace_bytes, int64_t wait_ns, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

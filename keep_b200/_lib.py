@@ -166,6 +166,8 @@ _SIGNATURES = {
     "keepvq_grouped_projection_workspace_bytes": (c_int64, [c_int64, c_int64]),
     "keepvq_grouped_projection_status_offset": (c_int64, [c_int64, c_int64]),
     "keepvq_grouped_projection": (c_int, [POINTER(GroupedProjectionArgs), c_void_p]),
+    "keepvq_wait_selftest_workspace_bytes": (c_int64, []),
+    "keepvq_wait_selftest": (c_int, [c_void_p, c_int64, c_int64, c_void_p]),
     "keepvq_ep_pack": (c_int, [POINTER(EpPackArgs), c_void_p]),
     "keepvq_ep_combine": (c_int, [POINTER(EpCombineArgs), c_void_p]),
     "keepvq_ep_dispatch_peer": (c_int, [POINTER(EpPackArgs), POINTER(EpPeerArgs), c_void_p]),

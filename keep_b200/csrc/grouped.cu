@@ -102,3 +102,46 @@ extern "C" int keepvq_grouped_projection(const keepvq_grouped_projection_args* a
   KEEPVQ_CHECK_LAUNCH();
   return many ? fast::prefill_down(p, wait_status, s) : fast::down(p, s);
 }
+
+// ------------------------------------------------------------------------------------------
+// Self-test of the bounded waits of the tcgen05 kernel: one CTA on a tiny problem laid out in the
+// caller's scratch, whose activation loaders never publish their tiles.  The MMA issuer's first
+// wait then runs into its deadline (wait_ns on the global timer); the CTA must set the status
+// word to 1, free its tensor memory and return, and the context must stay usable.  Nothing
+// faults and nothing spins without a limit.  No counterpart in the reference.
+// ------------------------------------------------------------------------------------------
+namespace keepvq {
+constexpr int64_t SELFTEST_BYTES = 32 * 1024;
+__global__ void selftest_init_kernel(int32_t* count, int32_t* size, int32_t* routes, float* x_scale) {
+  if (threadIdx.x == 0) { count[0] = 1; size[0] = 16; }
+  if (threadIdx.x < 16) routes[threadIdx.x] = threadIdx.x;
+  if (threadIdx.x < 17) x_scale[threadIdx.x] = 1.0f;
+}
+}  // namespace keepvq
+
+extern "C" int64_t keepvq_wait_selftest_workspace_bytes(void) { return keepvq::SELFTEST_BYTES; }
+
+extern "C" int keepvq_wait_selftest(void* workspace, int64_t workspace_bytes, int64_t wait_ns, void* stream) {
+  using namespace keepvq;
+  if (!workspace) return KEEPVQ_ERR_NULL;
+  if (workspace_bytes < SELFTEST_BYTES) return KEEPVQ_ERR_CAPACITY;
+  if (!aligned_to(workspace, 256)) return KEEPVQ_ERR_ALIGN;
+  if (wait_ns <= 0 || wait_ns > 1000000000ll) return KEEPVQ_ERR_SHAPE;  // a self-test may hold the GPU for a second at most
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  char* ws = reinterpret_cast<char*>(workspace);
+  cudaError_t e = cudaMemsetAsync(ws, 0, SELFTEST_BYTES, s);
+  if (e != cudaSuccess) return note_cuda_error(e);
+  // status 0 | groups 256.. | routes 1280 | table 2048 | scales 3072 | codes 4096 | planes 8192 | x scale 16384 | x sums 16640 | out 20480
+  fast::RouteGroups groups = {reinterpret_cast<int32_t*>(ws + 256), reinterpret_cast<int32_t*>(ws + 512), reinterpret_cast<int32_t*>(ws + 768),
+                              reinterpret_cast<int32_t*>(ws + 1024), reinterpret_cast<int32_t*>(ws + 1280)};
+  fast::QuantRows xq = {reinterpret_cast<uint8_t*>(ws + 8192), reinterpret_cast<float*>(ws + 16384), reinterpret_cast<int32_t*>(ws + 16640)};
+  selftest_init_kernel<<<1, 32, 0, s>>>(groups.count, groups.size, groups.routes, xq.scale);
+  KEEPVQ_CHECK_LAUNCH();
+  fast::FastProjectionArgs p = {};
+  p.a = {reinterpret_cast<const uint16_t*>(ws + 4096), ws + 3072, nullptr, nullptr};
+  p.scales_dtype = KEEPVQ_F16; p.out_dim = 128; p.in_dim = 128; p.groups = 1;
+  p.codebook = reinterpret_cast<const uint32_t*>(ws + 2048);
+  p.x = xq; p.x_zero_row = 16; p.x_div = 1; p.groups_of_routes = groups; p.max_routes = 16; p.group_cols = fast::PREFILL_GROUP_ROUTES;
+  p.out = ws + 20480; p.out_dtype = KEEPVQ_BF16;
+  return fast::prefill_wait_selftest(p, reinterpret_cast<int32_t*>(ws), static_cast<uint64_t>(wait_ns), s);
+}

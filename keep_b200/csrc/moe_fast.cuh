@@ -17,7 +17,82 @@ namespace fast {
 
 constexpr int MAX_GROUP_ROUTES = 8;     // routes of one expert that share an mma.sync tile (its 8 columns)
 constexpr int PAIRED_GROUP_ROUTES = 4;  // ... when a route's two byte planes take a column each (one MMA per step)
-constexpr int PREFILL_GROUP_ROUTES = 96;   // routes of one expert per tcgen05 item
+constexpr int PREFILL_GROUP_ROUTES = 96;   // routes of one expert per tcgen05 item (its accumulators and two operand stages fill tensor memory)
+
+
+// ------------------------------------------------------------------------------------------
+// Codeword decoders shared by the slab kernel (projection_slab.cu) and the tcgen05 kernel
+// (prefill_umma.cu).  Tables live in shared memory at addresses the kernels choose:
+//   abs table     [abs row][parity][16 replicas] x 8 bytes, ON A 64 KB BOUNDARY of the shared
+//                 window, so that the abs byte of a code word dropped into byte 1 of
+//                 (table address + lane offset) is the entry's address: one byte permute;
+//   second table  [sign byte][replicas] x 8 bytes: the XOR masks of the sign byte (sign flips,
+//                 the parity bit of every byte, the extra flip of table nibble 0 on odd parity);
+//                 with 32 replicas and a 64 KB boundary of its own it is addressed the same way.
+// Entry bytes: byte j of the low word is table nibble 3 - j, of the high word nibble 7 - j.
+// ------------------------------------------------------------------------------------------
+constexpr uint32_t SK_SPREAD_LO = (1u << 4) | (1u << 13) | (1u << 22) | (1u << 31);  // sign bits 3,2,1,0 -> bits 7,15,23,31
+constexpr uint32_t SK_SPREAD_HI = 1u | (1u << 9) | (1u << 18) | (1u << 27);          // sign bits 7,6,5,4 -> the same places
+
+// The eight bytes q (4w = 2q + 1 for positive signs) of abs row `word` under one parity.
+__device__ __forceinline__ uint2 abs_table_entry(uint32_t word, uint32_t par) {
+  uint32_t lo = 0, hi = 0;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int nl = 3 - j, nh = 7 - j;
+    uint32_t hl = ((word >> (4 * nl)) & 0xFu) - 8u, hh = ((word >> (4 * nh)) & 0xFu) - 8u;
+    if (par) { hl = nl == 0 ? ~hl : hl ^ 1u; hh ^= 1u; }
+    lo |= (hl & 0xFFu) << (8 * j);
+    hi |= (hh & 0xFFu) << (8 * j);
+  }
+  return make_uint2(lo, hi);
+}
+// The XOR masks of sign byte `sb`: 0xFE where the sign bit is set; ^1 everywhere (^0xFF on nibble 0) on odd parity.
+__device__ __forceinline__ uint2 sign_table_entry(uint32_t sb) {
+  const uint32_t par = __popc(sb) & 1u;
+  uint32_t lo = 0, hi = 0;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int nl = 3 - j, nh = 7 - j;
+    uint32_t ml = ((sb >> nl) & 1u) ? 0xFEu : 0u, mh = ((sb >> nh) & 1u) ? 0xFEu : 0u;
+    if (par) { ml ^= nl == 0 ? 0xFFu : 0x01u; mh ^= 0x01u; }
+    lo |= ml << (8 * j);
+    hi |= mh << (8 * j);
+  }
+  return make_uint2(lo, hi);
+}
+
+__device__ __forceinline__ uint2 table_entry(uint32_t addr) {  // tables never change after the set-up barrier: free to schedule
+  uint2 v;
+  asm("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ uint32_t byte_masks(uint32_t v) {  // the top bit of every byte, spread over the byte
+  uint32_t m;
+  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(m) : "r"(v), "r"(0u), "r"(0xBA98u));
+  return m;
+}
+// One codeword -> the two A-fragment words q (4w = 2q + 1).  The codeword is the low (ODD = false)
+// or the high half of `word`.  abs_lane = address of the abs table + this lane's replica offset
+// (byte 1 of it is zero: the table sits on a 64 KB boundary); second_lane likewise for the
+// second table (WIDE_SIGN), or that table's address + replica offset as a plain addend.
+template <bool TABLE, bool ODD, bool WIDE_SIGN>
+__device__ __forceinline__ void decode_codeword(uint32_t word, uint32_t abs_lane, uint32_t second_lane, uint32_t& lo, uint32_t& hi) {
+  const uint32_t entry = __byte_perm(word, abs_lane, ODD ? 0x7634 : 0x7614);  // the abs byte into byte 1 of the address
+  if (TABLE) {
+    uint32_t at;  // sign flips and parity
+    if (WIDE_SIGN) at = __byte_perm(word, second_lane, ODD ? 0x7624 : 0x7604);
+    else at = (ODD ? __byte_perm(word, 0u, 0x4442) : (word & 0xFFu)) * 128u + second_lane;
+    const uint2 e = table_entry(entry), m = table_entry(at);  // even-parity entry
+    lo = e.x ^ m.x;
+    hi = e.y ^ m.y;
+  } else {
+    const uint32_t sign = ODD ? __byte_perm(word, 0u, 0x4442) : (word & 0xFFu);
+    const uint2 e = table_entry(entry | ((static_cast<uint32_t>(__popc(sign)) << 7) & 0x80u));
+    lo = e.x ^ (byte_masks(sign * SK_SPREAD_LO) & 0xFEFEFEFEu);
+    hi = e.y ^ (byte_masks(sign * SK_SPREAD_HI) & 0xFEFEFEFEu);
+  }
+}
 
 // Quantised activation rows: the B operand of the projections.
 struct QuantRows {
@@ -91,6 +166,8 @@ int slab_down(const FastProjectionArgs& args, int cols, cudaStream_t s);
 bool prefill_supported(int64_t out_dim, int64_t in_dim, int64_t groups);
 int prefill_gate_up(const FastProjectionArgs& args, int32_t* status, cudaStream_t s);
 int prefill_down(const FastProjectionArgs& args, int32_t* status, cudaStream_t s);
+// One CTA whose activation loaders never publish, with a deadline of wait_ns: the wait runs out, the CTA sets *status = 1 and returns.
+int prefill_wait_selftest(const FastProjectionArgs& args, int32_t* status, uint64_t wait_ns, cudaStream_t s);
 
 }  // namespace fast
 }  // namespace keepvq

@@ -36,8 +36,6 @@ constexpr int SK_STAGES = 2;
 constexpr int SK_SMEM_BYTES = 227 * 1024;                 // the whole opt-in window: the tables want fixed 64 KB boundaries inside it
 constexpr int SK_WARP_RING = SK_STAGES * 4 * 512;         // four 16-byte streams per lane and stage
 constexpr uint32_t SK_ABS_BYTES = 256 * 2 * SK_REPLICAS * 8;   // 64 KB  [abs row][parity][replica]
-constexpr uint32_t SK_SPREAD_LO = (1u << 4) | (1u << 13) | (1u << 22) | (1u << 31);  // sign bits 3,2,1,0 -> bits 7,15,23,31
-constexpr uint32_t SK_SPREAD_HI = 1u | (1u << 9) | (1u << 18) | (1u << 27);          // sign bits 7,6,5,4 -> the same places
 
 // Shared window, in absolute shared addresses.  A0 = the first 64 KB boundary at or above the
 // dynamic base (the runtime keeps 1 KB below it, so A0 = 64 KB):
@@ -82,45 +80,13 @@ __device__ __forceinline__ uint2 sk_lds64(uint32_t addr) {
   asm volatile("ld.shared.v2.u32 {%0,%1}, [%2+%3];" : "=r"(v.x), "=r"(v.y) : "r"(addr), "n"(OFF));
   return v;
 }
-__device__ __forceinline__ uint2 sk_table(uint32_t addr) {  // tables never change after the set-up barrier: free to schedule
-  uint2 v;
-  asm("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
-  return v;
-}
 __device__ __forceinline__ void sk_sts64(uint32_t addr, uint32_t lo, uint32_t hi) {
   asm volatile("st.shared.v2.u32 [%0], {%1,%2};" ::"r"(addr), "r"(lo), "r"(hi) : "memory");
 }
 
-__device__ __forceinline__ uint32_t sk_byte_masks(uint32_t v) {  // the top bit of every byte, spread over the byte
-  uint32_t m;
-  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(m) : "r"(v), "r"(0u), "r"(0xBA98u));
-  return m;
-}
 __device__ __forceinline__ void sk_mma(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
   asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
       : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-
-// One codeword -> the two A-fragment words q (4w = 2q + 1).  The codeword is the low (ODD = false)
-// or the high half of `word`.  abs_lane = address of the abs table + this lane's replica offset
-// (byte 1 of it is zero: the table sits on a 64 KB boundary); second_lane likewise for the
-// second table (WIDE_SIGN), or that table's address + replica offset as a plain addend.
-template <bool TABLE, bool ODD, bool WIDE_SIGN>
-__device__ __forceinline__ void sk_decode(uint32_t word, uint32_t abs_lane, uint32_t second_lane, uint32_t& lo, uint32_t& hi) {
-  const uint32_t entry = __byte_perm(word, abs_lane, ODD ? 0x7634 : 0x7614);  // the abs byte into byte 1 of the address
-  if (TABLE) {
-    uint32_t at;  // sign flips and parity
-    if (WIDE_SIGN) at = __byte_perm(word, second_lane, ODD ? 0x7624 : 0x7604);
-    else at = (ODD ? __byte_perm(word, 0u, 0x4442) : (word & 0xFFu)) * 128u + second_lane;
-    const uint2 e = sk_table(entry), m = sk_table(at);  // even-parity entry
-    lo = e.x ^ m.x;
-    hi = e.y ^ m.y;
-  } else {
-    const uint32_t sign = ODD ? __byte_perm(word, 0u, 0x4442) : (word & 0xFFu);
-    const uint2 e = sk_table(entry | ((static_cast<uint32_t>(__popc(sign)) << 7) & 0x80u));
-    lo = e.x ^ (sk_byte_masks(sign * SK_SPREAD_LO) & 0xFEFEFEFEu);
-    hi = e.y ^ (sk_byte_masks(sign * SK_SPREAD_HI) & 0xFEFEFEFEu);
-  }
 }
 
 template <int I>
@@ -167,26 +133,12 @@ __global__ void __launch_bounds__(SK_THREADS, 1) projection_slab_kernel(FastProj
         lo |= (static_cast<uint32_t>(__float2int_rn(2.0f * __low2float(pair))) & 0xFFu) << (8 * j);
         hi |= (static_cast<uint32_t>(__float2int_rn(2.0f * __high2float(pair))) & 0xFFu) << (8 * j);
       }
-    } else if (e < 512) {  // abs entry (row e/2, parity e&1): byte j of the low word is table nibble 3-j, of the high word 7-j
-      const uint32_t word = p.codebook[e >> 1], par = e & 1;
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const int nl = 3 - j, nh = 7 - j;
-        uint32_t hl = ((word >> (4 * nl)) & 0xFu) - 8u, hh = ((word >> (4 * nh)) & 0xFu) - 8u;
-        if (par) { hl = nl == 0 ? ~hl : hl ^ 1u; hh ^= 1u; }
-        lo |= (hl & 0xFFu) << (8 * j);
-        hi |= (hh & 0xFFu) << (8 * j);
-      }
-    } else {  // sign entry: 0xFE where the sign bit is set; ^1 everywhere (^0xFF on nibble 0) on odd parity
-      const uint32_t sb = e - 512, par = __popc(sb) & 1u;
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const int nl = 3 - j, nh = 7 - j;
-        uint32_t ml = ((sb >> nl) & 1u) ? 0xFEu : 0u, mh = ((sb >> nh) & 1u) ? 0xFEu : 0u;
-        if (par) { ml ^= nl == 0 ? 0xFFu : 0x01u; mh ^= 0x01u; }
-        lo |= ml << (8 * j);
-        hi |= mh << (8 * j);
-      }
+    } else if (e < 512) {  // abs entry (row e / 2, parity e & 1)
+      const uint2 v = abs_table_entry(p.codebook[e >> 1], e & 1);
+      lo = v.x; hi = v.y;
+    } else {
+      const uint2 v = sign_table_entry(e - 512);
+      lo = v.x; hi = v.y;
     }
     const uint32_t replicas = e < 512 ? SK_REPLICAS : L::SECOND_REPLICAS;
     const uint32_t dst = e < 512 ? a0 + e * (SK_REPLICAS * 8) : a0 + SK_SECOND_OFF + (e - 512) * (L::SECOND_REPLICAS * 8);
@@ -379,8 +331,8 @@ __global__ void __launch_bounds__(SK_THREADS, 1) projection_slab_kernel(FastProj
 #pragma unroll
           for (int tl = 0; tl < TILES; ++tl) {
             uint32_t a[4];
-            sk_decode<TABLE, (I & 1) != 0, WIDE_SIGN>(sk_word<I>(cur[(m * TILES + tl) * 2]), abs_lane, second_lane, a[0], a[2]);      // row g
-            sk_decode<TABLE, (I & 1) != 0, WIDE_SIGN>(sk_word<I>(cur[(m * TILES + tl) * 2 + 1]), abs_lane, second_lane, a[1], a[3]);  // row g + 8
+            decode_codeword<TABLE, (I & 1) != 0, WIDE_SIGN>(sk_word<I>(cur[(m * TILES + tl) * 2]), abs_lane, second_lane, a[0], a[2]);      // row g
+            decode_codeword<TABLE, (I & 1) != 0, WIDE_SIGN>(sk_word<I>(cur[(m * TILES + tl) * 2 + 1]), abs_lane, second_lane, a[1], a[3]);  // row g + 8
             sk_mma(acc[0][I & 1][m][tl], a[0], a[1], a[2], a[3], b[0], b[1]);
             if (PLANES == 2) sk_mma(acc[PLANES - 1][I & 1][m][tl], a[0], a[1], a[2], a[3], b[2], b[3]);
           }
@@ -439,7 +391,7 @@ __global__ void __launch_bounds__(SK_THREADS, 1) projection_slab_kernel(FastProj
                 for (int half = 0; half < 2; ++half) {
                   const uint2 v = cur[(m * TILES + tl) * 2 + half];
                   const uint32_t code = ((I < 4 ? v.x : v.y) >> (8 * (I & 3))) & 0xFFu;
-                  const uint2 e = sk_table(code * 128u + second_lane);  // the second table is the residual codebook here
+                  const uint2 e = table_entry(code * 128u + second_lane);  // the second table is the residual codebook here
                   a[half] = e.x;
                   a[2 + half] = e.y;
                 }

@@ -222,3 +222,25 @@ def test_config2_shape_decode_layer(cuda, batch):
     layer = build_layer(cuda, cfg, top_k=6)
     out, routing = layer.decode(x.to(cuda))
     check_layer(cfg, x, out, routing, top_k=6)
+
+
+def test_a_wait_that_nothing_satisfies_runs_out_and_the_kernel_returns(cuda):
+    """The tcgen05 kernel's waits are bounded by a deadline on the GPU's timer.  The library's
+    self-test launches one block whose activation producers never publish their tiles: the MMA
+    issuer's wait must expire after the 2 ms it is given, the block must report (status word 1),
+    free its tensor memory and return, and the device must answer afterwards.  No fault, no
+    endless loop: the failure is a flag that nothing sets."""
+    from keep_b200 import _lib, vq
+
+    lib = _lib.load()
+    nbytes = int(lib.keepvq_wait_selftest_workspace_bytes())
+    ws = torch.full((nbytes,), 0x5A, dtype=torch.uint8, device=cuda)
+    with torch.cuda.device(cuda):
+        _lib.check(lib.keepvq_wait_selftest(_lib.ptr(ws), nbytes, 2_000_000, _lib.stream_handle(cuda)), "keepvq_wait_selftest")
+    torch.cuda.synchronize()
+    assert int(ws[:4].view(torch.int32).item()) == 1
+    # the context still answers, and tensor memory was handed back: a real tcgen05 call runs right after
+    codes = torch.zeros((1, 128, 16), dtype=torch.uint16, device=cuda)
+    grid = vq.decode_weight_matrix(codes[0], torch.ones((128, 1), dtype=torch.float16, device=cuda), code_bits=16)
+    assert torch.isfinite(grid).all()
+    assert lib.keepvq_wait_selftest(_lib.ptr(ws), nbytes, 0, _lib.stream_handle(cuda)) == -2  # a deadline is mandatory (and at most a second)
