@@ -84,17 +84,14 @@ extern "C" int keepvq_grouped_projection(const keepvq_grouped_projection_args* a
   const bool many = !residual && a.routes >= 1024 && a.routes >= 24 * a.slots && fast::prefill_supported(a.out_dim, a.in_dim, a.groups);
   int32_t* wait_status = reinterpret_cast<int32_t*>(ws + sc.status);
   int rc;
-  {
-    cudaError_t e = cudaMemsetAsync(wait_status, 0, sizeof(int32_t), s);
-    if (e != cudaSuccess) return note_cuda_error(e);
-  }
   const int group_cols = many ? fast::PREFILL_GROUP_ROUTES : fast::decode_group_routes(a.routes, a.slots, a.in_dim);
-  if ((rc = fast::group_routes(a.rhs, a.routes, a.slots, group_cols, groups, s))) return rc;
+  if ((rc = fast::group_routes(a.rhs, a.routes, a.slots, group_cols, groups, wait_status, s))) return rc;
   if ((rc = fast::quantize_rows(a.x, a.x_dtype, x_rows, a.in_dim, a.groups, xq, many, s))) return rc;
   fast::FastProjectionArgs p = {};
   p.a = {a.codes, a.scales, a.res_codes, a.res_scales}; p.b = {nullptr, nullptr, nullptr, nullptr};
   if (residual) { p.res_groups = a.res_groups; p.hot_of_slot = a.hot_of_slot; p.res_table = a.res_table; }
   p.scales_dtype = a.scales_dtype; p.codebook = a.codebook; p.groups_of_routes = groups; p.max_routes = a.routes; p.group_cols = group_cols; p.status = wait_status;
+  p.few_groups = !many && fast::few_route_groups(a.routes, a.slots);
   p.out_dim = a.out_dim; p.in_dim = a.in_dim; p.groups = a.groups; p.x = xq; p.x_zero_row = x_rows; p.x_div = x_div;
   p.out = a.out; p.out_dtype = a.out_dtype; p.swiglu_limit = 0.0f; p.route_weight = nullptr;
   if (a.routes > 0x7FFFFFFFll) return KEEPVQ_ERR_CAPACITY;

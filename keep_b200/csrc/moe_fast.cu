@@ -130,9 +130,10 @@ int quantize_rows(const void* x, int32_t x_dtype, int64_t rows, int64_t in_dim, 
 // ------------------------------------------------------------------------------------------
 constexpr int GR_THREADS = 1024;
 
-__global__ void __launch_bounds__(GR_THREADS) group_routes_kernel(const uint32_t* __restrict__ served_slot, int routes, int slots, int max_group, RouteGroups out) {
+__global__ void __launch_bounds__(GR_THREADS) group_routes_kernel(const uint32_t* __restrict__ served_slot, int routes, int slots, int max_group, RouteGroups out, int32_t* clear) {
   grid_launch_dependents();
   grid_wait();
+  if (clear && threadIdx.x == 0) *clear = 0;
   extern __shared__ int32_t sm[];
   int32_t* count = sm;               // [slots] routes per slot, then running cursor
   int32_t* first = sm + slots;       // [slots] first position of the slot in `routes`
@@ -190,14 +191,14 @@ __global__ void __launch_bounds__(GR_THREADS) group_routes_kernel(const uint32_t
   }
 }
 
-int group_routes(const uint32_t* served_slot, int64_t routes, int64_t slots, int max_group, const RouteGroups& out, cudaStream_t s) {
+int group_routes(const uint32_t* served_slot, int64_t routes, int64_t slots, int max_group, const RouteGroups& out, int32_t* clear, cudaStream_t s) {
   if (routes > (1 << 20) || slots > 16384) return KEEPVQ_ERR_CAPACITY;
   const size_t smem = static_cast<size_t>(slots) * 3 * sizeof(int32_t);
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(group_routes_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     if (e != cudaSuccess) return note_cuda_error(e);
   }
-  cudaError_t err = launch_after(routes <= 4 * EARLY_LAUNCH_MAX_BLOCKS, group_routes_kernel, 1, GR_THREADS, smem, s, served_slot, static_cast<int>(routes), static_cast<int>(slots), max_group, out);
+  cudaError_t err = launch_after(routes <= 4 * EARLY_LAUNCH_MAX_BLOCKS, group_routes_kernel, 1, GR_THREADS, smem, s, served_slot, static_cast<int>(routes), static_cast<int>(slots), max_group, out, clear);
   if (err != cudaSuccess) return note_cuda_error(err);
   return KEEPVQ_OK;
 }
@@ -440,7 +441,11 @@ static int launch_projection(const FastProjectionArgs& p, cudaStream_t s) {
 // Enough routes to give every CTA of the machine its own (group, slab) items, and activations
 // that fit the shared-memory stage?
 static bool many_items(const FastProjectionArgs& p) {
-  return p.max_routes >= 48 && p.in_dim <= slab_max_in_dim(p.group_cols > PAIRED_GROUP_ROUTES ? MAX_GROUP_ROUTES : PAIRED_GROUP_ROUTES);
+  return p.max_routes >= SMALL_CALL_ROUTES && p.in_dim <= slab_max_in_dim(p.group_cols > PAIRED_GROUP_ROUTES ? MAX_GROUP_ROUTES : PAIRED_GROUP_ROUTES);
+}
+// Few route groups of at most four routes, activations that leave room in the stage: the split slab kernel.
+static bool few_items(const FastProjectionArgs& p) {
+  return p.few_groups && p.group_cols <= PAIRED_GROUP_ROUTES && p.in_dim <= slab_split_max_in_dim();
 }
 
 #ifdef KEEPVQ_DIAG
@@ -452,23 +457,27 @@ int decode_group_routes(int64_t live, int64_t slots, int64_t widest_in_dim) {
 #ifdef KEEPVQ_DIAG
   if (g_force_cols) return g_force_cols;
 #endif
-  if (live < 48) return MAX_GROUP_ROUTES;  // the team kernel: its tile has eight columns either way
+  if (live < SMALL_CALL_ROUTES) return widest_in_dim <= slab_split_max_in_dim() ? PAIRED_GROUP_ROUTES : MAX_GROUP_ROUTES;  // split slab kernel | team kernel
   if (widest_in_dim > slab_max_in_dim(MAX_GROUP_ROUTES)) return PAIRED_GROUP_ROUTES;
   return live <= 2 * slots ? PAIRED_GROUP_ROUTES : MAX_GROUP_ROUTES;
 }
 
-// The residual pass lives in the slab kernel only: a layer with a residual tier needs enough routes
-// for that kernel and residual scale groups that close on chunk boundaries.
+// The residual pass lives in the slab kernels only: a layer with a residual tier needs activations
+// that fit their stage (half of it for calls with few routes) and residual scale groups that close
+// on chunk boundaries.
 bool residual_supported(int64_t routes, int64_t in_dim, int64_t res_groups) {
-  if (routes < 48 || in_dim > slab_max_in_dim(PAIRED_GROUP_ROUTES) || in_dim % (8 * CHUNK_CODES) != 0 || res_groups <= 0) return false;
+  const int64_t widest = routes < SMALL_CALL_ROUTES ? slab_split_max_in_dim() : slab_max_in_dim(PAIRED_GROUP_ROUTES);
+  if (in_dim > widest || in_dim % (8 * CHUNK_CODES) != 0 || res_groups <= 0) return false;
   return (in_dim / (8 * CHUNK_CODES)) % res_groups == 0;
 }
 
 int gate_up(const FastProjectionArgs& p, cudaStream_t s) {
+  if (few_items(p)) return slab_split_gate_up(p, s);
   if (p.res_table && !many_items(p)) return KEEPVQ_ERR_UNSUPPORTED;
   return many_items(p) ? slab_gate_up(p, p.group_cols > PAIRED_GROUP_ROUTES ? MAX_GROUP_ROUTES : PAIRED_GROUP_ROUTES, s) : launch_projection<2, 2>(p, s);
 }
 int down(const FastProjectionArgs& p, cudaStream_t s) {
+  if (few_items(p)) return slab_split_down(p, s);
   if (p.res_table && !many_items(p)) return KEEPVQ_ERR_UNSUPPORTED;
   return many_items(p) ? slab_down(p, p.group_cols > PAIRED_GROUP_ROUTES ? MAX_GROUP_ROUTES : PAIRED_GROUP_ROUTES, s) : launch_projection<1, 4>(p, s);
 }

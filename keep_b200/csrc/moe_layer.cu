@@ -225,15 +225,12 @@ extern "C" int keepvq_moe_decode_stages(const keepvq_moe_layer_args* args, int32
     int32_t* wait_status = reinterpret_cast<int32_t*>(ws + sc.status);
     const int group_cols = prefill ? fast::PREFILL_GROUP_ROUTES : fast::decode_group_routes(live, a.slots, std::max(a.hidden, a.inter));
     if (stages & KEEPVQ_STAGE_PREPARE) {
-      if (prefill || routes >= 48) {  // the kernels that can set the word
-        cudaError_t e = cudaMemsetAsync(wait_status, 0, sizeof(int32_t), s);
-        if (e != cudaSuccess) return note_cuda_error(e);
-      }
-      if ((rc = fast::group_routes(a.served_slot, routes, a.slots, group_cols, groups, s))) return rc;
+      if ((rc = fast::group_routes(a.served_slot, routes, a.slots, group_cols, groups, wait_status, s))) return rc;
       if ((rc = fast::quantize_rows(a.x, a.x_dtype, a.tokens, a.hidden, a.w1.groups, xq, prefill, s))) return rc;
     }
     fast::FastProjectionArgs p = {};
     p.scales_dtype = a.scales_dtype; p.codebook = a.codebook; p.groups_of_routes = groups; p.max_routes = routes; p.group_cols = group_cols; p.status = wait_status;
+    p.few_groups = !prefill && fast::few_route_groups(live, a.slots);
     p.out_dtype = a.x_dtype; p.swiglu_limit = a.swiglu_limit; p.route_weight = a.served_weight;
     if (stages & KEEPVQ_STAGE_GATE_UP) {
       p.a = {a.w1.codes, a.w1.scales, a.w1.res_codes, a.w1.res_scales}; p.b = {a.w3.codes, a.w3.scales, a.w3.res_codes, a.w3.res_scales};

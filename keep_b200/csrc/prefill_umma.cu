@@ -372,8 +372,10 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_projection_kernel(FastP
       }
     } else if (warp == PF_MMA_WARP) {
       // ================= per-route facts for the drain, then the MMAs ============================
-      // The facts go into the buffer item n - 2 used; that item was drained before item n - 1's
-      // MMAs began, so the buffer is free and the gathering hides behind the previous item's drain.
+      // The facts go into the buffer item n - 2 used; every warp finished that item's drain before
+      // it produced the stages of item n - 1, all of which have been consumed by now (see the
+      // __syncwarp at the end of this branch), so the buffer is free; the gathering hides behind
+      // the drain of item n - 1.
       bool ok = true;
       {
         for (int n = lane; n < n_pad; n += 32) {
@@ -421,6 +423,12 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_projection_kernel(FastP
         }
         if (ok) umma_commit(bar(ACC_FULL, 0));
       }
+      // The other lanes wait here for the issuing lane.  Without this they would run one item ahead
+      // and refill the per-route buffer of item n - 1 while that item's drain is still doing the
+      // arithmetic of its last chunks (the drain gives the accumulators back BEFORE that arithmetic).
+      // Behind this point every K block of item n has been issued, which took the decode warps'
+      // stages of item n, and they produce those only after they are done with item n - 1.
+      __syncwarp();
     } else {
       // ================= activation (B operand) loaders =======================================
       // cp.async straight into the swizzled tiles (16 bytes = two codewords of one route); a K

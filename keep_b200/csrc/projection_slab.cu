@@ -20,6 +20,10 @@
 //     staged once per run of items in MMA-fragment order, and a lane whose column carries no
 //     route re-reads a live column's bytes (its own MMA column is never looked at), so the
 //     activation reads cost one wavefront for the typical one-route group.
+// Calls with few route groups (a handful of tokens) run the SPLIT form: the warps of a CTA share a
+// slab's rows AND the input dimension (`ks` warps per row set, each over 1/ks of the codewords),
+// their partial sums meet in shared memory, and `ks` is picked on the device from the number of
+// groups so that every SM gets several items however few experts the call touches.
 #include <type_traits>
 #include <utility>
 
@@ -99,10 +103,16 @@ __device__ __forceinline__ uint32_t sk_word(const uint4& v) {
 // base decode does every step's signs on the integer pipe) and an item whose slot is hot runs a
 // second pass over the residual's 8-bit codes.
 // `status` (may be null) is set to 2 if the shared window does not have the expected shape.
-template <int M, int TILES, int COLS, unsigned TABLE_STEPS, bool NESTED, bool WIDE_SIGN>
+// SPLIT: see the head of the file; the partial sums (16 KB) live at the end of the 64 KB activation
+// stage, which leaves 48 KB for the activations (eight columns of 6144 inputs).
+constexpr uint32_t SK_SPLIT_RED_OFF = 48 * 1024;          // from the start of the activation stage
+constexpr int SK_SPLIT_ITEMS_PER_CTA = 4;                 // items per CTA the split factor aims for
+
+template <int M, int TILES, int COLS, unsigned TABLE_STEPS, bool NESTED, bool WIDE_SIGN, bool SPLIT>
 __global__ void __launch_bounds__(SK_THREADS, 1) projection_slab_kernel(FastProjectionArgs p, int32_t* status) {
   static_assert(COLS == 4 || COLS == 8, "a group is four or eight routes");
   static_assert(!WIDE_SIGN || (COLS == 4 && !NESTED), "the wide sign table leaves room for eight activation columns of 4096 inputs");
+  static_assert(!SPLIT || (COLS == 4 && !WIDE_SIGN), "the split form keeps its partial sums at the end of the 64 KB activation stage");
   static_assert(M * 2 * TILES == 4, "four code streams per lane");
   using L = SlabLayout<WIDE_SIGN>;
   extern __shared__ __align__(16) uint8_t smem[];
@@ -123,6 +133,8 @@ __global__ void __launch_bounds__(SK_THREADS, 1) projection_slab_kernel(FastProj
   }
 
   // ---- tables -----------------------------------------------------------------------------
+  // every thread computes one entry per pass; the warp then writes its 32 entries two at a time,
+  // sixteen lanes storing the sixteen replicas of one entry side by side (no bank conflicts)
   for (int e = threadIdx.x; e < 768; e += SK_THREADS) {
     uint32_t lo = 0, hi = 0;
     if (e >= 512 && NESTED) {  // residual entry: byte j of the low word is 2 * v[6 - 2j], of the high word 2 * v[7 - 2j]
@@ -140,9 +152,16 @@ __global__ void __launch_bounds__(SK_THREADS, 1) projection_slab_kernel(FastProj
       const uint2 v = sign_table_entry(e - 512);
       lo = v.x; hi = v.y;
     }
-    const uint32_t replicas = e < 512 ? SK_REPLICAS : L::SECOND_REPLICAS;
-    const uint32_t dst = e < 512 ? a0 + e * (SK_REPLICAS * 8) : a0 + SK_SECOND_OFF + (e - 512) * (L::SECOND_REPLICAS * 8);
-    for (uint32_t r = 0; r < replicas; ++r) sk_sts64(dst + r * 8, lo, hi);
+    const uint32_t replicas = e < 512 ? SK_REPLICAS : L::SECOND_REPLICAS;  // uniform over a warp: 512 is a multiple of 32
+    const int e_warp = e & ~31, ln = threadIdx.x & 31;
+    const uint32_t dst_warp = e < 512 ? a0 + e_warp * (SK_REPLICAS * 8) : a0 + SK_SECOND_OFF + (e_warp - 512) * (L::SECOND_REPLICAS * 8);
+    const uint32_t per_store = 32 / replicas;  // entries one warp-wide store covers: 2 or 1
+#pragma unroll 4
+    for (uint32_t i = 0; i < 32; i += per_store) {
+      const int from = static_cast<int>(i + (replicas == 16 ? (ln >> 4) : 0));
+      const uint32_t vlo = __shfl_sync(0xFFFFFFFFu, lo, from), vhi = __shfl_sync(0xFFFFFFFFu, hi, from);
+      sk_sts64(dst_warp + from * replicas * 8 + (ln & (replicas - 1)) * 8, vlo, vhi);
+    }
   }
 
   grid_wait();  // the tables came from constants; everything below reads what earlier kernels of the stream wrote
@@ -158,16 +177,28 @@ __global__ void __launch_bounds__(SK_THREADS, 1) projection_slab_kernel(FastProj
   const int chunks_per_group = n_chunks / static_cast<int>(p.groups);
   const int chunks_per_res_group = NESTED ? n_chunks / static_cast<int>(p.res_groups) : n_chunks;
   constexpr int ROWS = 16 * TILES;              // per warp
-  constexpr int SLAB = ROWS * SK_WARPS;         // per CTA item
-  const int slabs = static_cast<int>((N + SLAB - 1) / SLAB);
+  const int grid = static_cast<int>(gridDim.x), cta = static_cast<int>(blockIdx.x);
+  // `ks` warps share a row set, each over n_chunks / ks chunks of the input dimension.  It grows
+  // (in powers of two, as far as the chunks allow) until every CTA has several items.
+  int ks = 1;
+  if (SPLIT) {
+    const int64_t want = static_cast<int64_t>(SK_SPLIT_ITEMS_PER_CTA) * grid, found = p.groups_of_routes.count[0];
+    while (2 * ks <= SK_WARPS && n_chunks % (2 * ks) == 0 && found * ((N * ks + ROWS * SK_WARPS - 1) / (ROWS * SK_WARPS)) < want) ks *= 2;
+  }
+  const int row_sets = SK_WARPS / ks;           // row sets of a CTA item
+  const int row_set = SPLIT ? warp / ks : warp, k_part = SPLIT ? warp % ks : 0;
+  const int c_first = k_part * (n_chunks / ks), c_end = c_first + n_chunks / ks;  // this warp's chunks
+  const int slab_rows = ROWS * row_sets;        // per CTA item
+  const int slabs = static_cast<int>((N + slab_rows - 1) / slab_rows);
   const int items = p.groups_of_routes.count[0] * slabs;
   const Projection mats[2] = {p.a, p.b};
+  const uint32_t red_base = b_base + SK_SPLIT_RED_OFF;  // [turn & 1][warp][value][lane] fp32
+  uint32_t red_turn = 0;                                // items this row set has reduced
 
   // A CTA takes a contiguous run of items, so consecutive items mostly belong to one route group
   // and its activations are staged once for all of them.  (With a residual tier the items of a
   // hot slot cost half as much again, and a run of them on one CTA would unbalance the grid:
   // those layers deal the items out round-robin instead.)
-  const int grid = static_cast<int>(gridDim.x), cta = static_cast<int>(blockIdx.x);
   const int first_item = NESTED ? cta : static_cast<int>(static_cast<int64_t>(items) * cta / grid);
   const int last_item = NESTED ? items : static_cast<int>(static_cast<int64_t>(items) * (cta + 1) / grid);
   const int item_step = NESTED ? grid : 1;
@@ -186,7 +217,7 @@ __global__ void __launch_bounds__(SK_THREADS, 1) projection_slab_kernel(FastProj
     it.slot = p.groups_of_routes.slot[it.gi];
     it.gsize = p.groups_of_routes.size[it.gi];
     it.gstart = p.groups_of_routes.start[it.gi];
-    it.row0 = static_cast<int64_t>(slab) * SLAB + warp * ROWS;
+    it.row0 = static_cast<int64_t>(slab) * slab_rows + row_set * ROWS;
     it.active = it.row0 < N;
 #pragma unroll
     for (int s = 0; s < 4; ++s)
@@ -195,7 +226,7 @@ __global__ void __launch_bounds__(SK_THREADS, 1) projection_slab_kernel(FastProj
   };
   uint32_t ring_turn = 0;  // chunks this warp has consumed: picks the ring stage
   auto fetch = [&](const Item& it, int c, uint32_t turn) {  // chunk c of the lane's row streams -> ring stage turn % SK_STAGES
-    if (it.active && c < n_chunks) {
+    if (it.active && c < c_end) {
       const uint32_t dst = ring + (turn % SK_STAGES) * STAGE_BYTES;
       sk_static_for<4>([&](auto s) { sk_cp_async16<decltype(s)::value * 512>(dst, it.row_ptr[decltype(s)::value] + c * SK_CHUNK); });
     }
@@ -205,7 +236,7 @@ __global__ void __launch_bounds__(SK_THREADS, 1) projection_slab_kernel(FastProj
   Item next_item = {};
   if (first_item < last_item) {
     next_item = describe(first_item);
-    if (CARRY) fetch(next_item, 0, ring_turn);
+    if (CARRY) fetch(next_item, c_first, ring_turn);
   }
   int staged_group = -1;
   for (int item = first_item; item < last_item; item += item_step) {
@@ -235,16 +266,16 @@ __global__ void __launch_bounds__(SK_THREADS, 1) projection_slab_kernel(FastProj
       if (CARRY) {
         sk_wait<0>();  // the activations, and the first chunk asked for earlier
       } else {
-        fetch(it, 0, ring_turn);
+        fetch(it, c_first, ring_turn);
         sk_wait<1>();  // the activations (the older group) have landed
       }
       __syncthreads();
       staged_group = gi;
     } else if (!CARRY) {
-      fetch(it, 0, ring_turn);
+      fetch(it, c_first, ring_turn);
     }
     if (!active) {
-      if (CARRY && has_next) fetch(next_item, 0, ring_turn);
+      if (CARRY && has_next) fetch(next_item, c_first, ring_turn);
       else sk_wait<0>();
       continue;
     }
@@ -311,9 +342,9 @@ __global__ void __launch_bounds__(SK_THREADS, 1) projection_slab_kernel(FastProj
           }
     };
 
-    int group = 0, left_in_group = chunks_per_group;
-    for (int c = 0; c < n_chunks; ++c, ++ring_turn) {
-      if (CARRY && c + 1 == n_chunks && has_next) fetch(next_item, 0, ring_turn + 1);
+    int group = c_first / chunks_per_group, left_in_group = chunks_per_group - c_first % chunks_per_group;
+    for (int c = c_first; c < c_end; ++c, ++ring_turn) {
+      if (CARRY && c + 1 == c_end && has_next) fetch(next_item, c_first, ring_turn + 1);
       else fetch(it, c + 1, ring_turn + 1);
       sk_wait<1>();  // chunk c has landed (the younger group may still fly)
       uint4 cur[4];
@@ -344,6 +375,10 @@ __global__ void __launch_bounds__(SK_THREADS, 1) projection_slab_kernel(FastProj
         left_in_group = chunks_per_group;
       }
     }
+    if (SPLIT && left_in_group != chunks_per_group) {  // this warp's share ends inside a scale group
+      const void* const scales[2] = {mats[0].scales, mats[1].scales};
+      close_group(scales, slot * N, p.groups, group, part, true);
+    }
     if (!CARRY) sk_wait<0>();
 
     // ---- the residual of a hot slot: a second pass over its 8-bit codes ---------------------
@@ -362,15 +397,15 @@ __global__ void __launch_bounds__(SK_THREADS, 1) projection_slab_kernel(FastProj
         for (int s = 0; s < 4; ++s)
           res_ptr[s] = mats[s / (2 * TILES)].res_codes + (static_cast<int64_t>(hot) * N + min(row0 + 8 * (s % (2 * TILES)) + g, N - 1)) * cw + t * 8;
         auto fetch_res = [&](int c) {  // 8 codes of 8 bits per row stream
-          if (c < n_chunks) {
+          if (c < c_end) {
             const uint32_t dst = ring + (c % SK_STAGES) * STAGE_BYTES;  // the ring is idle here: the base pass has drained it
             sk_static_for<4>([&](auto s) { sk_cp_async8<decltype(s)::value * 512>(dst, res_ptr[decltype(s)::value] + c * SK_CHUNK); });
           }
           sk_commit();
         };
-        fetch_res(0);
-        int res_group = 0, left_in_res_group = chunks_per_res_group;
-        for (int c = 0; c < n_chunks; ++c) {
+        fetch_res(c_first);
+        int res_group = c_first / chunks_per_res_group, left_in_res_group = chunks_per_res_group - c_first % chunks_per_res_group;
+        for (int c = c_first; c < c_end; ++c) {
           fetch_res(c + 1);
           sk_wait<1>();
           uint2 cur[4];
@@ -406,7 +441,44 @@ __global__ void __launch_bounds__(SK_THREADS, 1) projection_slab_kernel(FastProj
             left_in_res_group = chunks_per_res_group;
           }
         }
+        if (SPLIT && left_in_res_group != chunks_per_res_group) {
+          const void* const scales[2] = {mats[0].res_scales, mats[1].res_scales};
+          close_group(scales, static_cast<int64_t>(hot) * N, p.res_groups, res_group, rpart, false);
+        }
         sk_wait<0>();
+      }
+    }
+
+    // ---- split form: the row set's warps add up their shares; its first warp carries on --------
+    if (SPLIT && ks > 1) {
+      constexpr int VALUES = M * TILES * PARTS;
+      const uint32_t mine = red_base + (((red_turn & 1u) * SK_WARPS + warp) * VALUES) * 128u + lane * 4u;
+      ++red_turn;
+      if (k_part != 0) {
+#pragma unroll
+        for (int m = 0; m < M; ++m)
+#pragma unroll
+          for (int tl = 0; tl < TILES; ++tl)
+#pragma unroll
+            for (int r = 0; r < PARTS; ++r)
+              asm volatile("st.shared.f32 [%0], %1;" ::"r"(mine + ((m * TILES + tl) * PARTS + r) * 128u), "f"(part[m][tl][r] + rpart[m][tl][r]) : "memory");
+      }
+      // a barrier of the row set's warps only (ids 1..8; id 0 is __syncthreads).  Two buffers by
+      // turn: a warp writes buffer (n & 1) again only after the barrier of turn n + 1, which the
+      // reading warp joins after it has finished with turn n.
+      asm volatile("bar.sync %0, %1;" ::"r"(row_set + 1), "r"(ks * 32) : "memory");
+      if (k_part != 0) continue;
+      for (int w = 1; w < ks; ++w) {
+#pragma unroll
+        for (int m = 0; m < M; ++m)
+#pragma unroll
+          for (int tl = 0; tl < TILES; ++tl)
+#pragma unroll
+            for (int r = 0; r < PARTS; ++r) {
+              float v;
+              asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(mine + (w * VALUES + (m * TILES + tl) * PARTS + r) * 128u));
+              part[m][tl][r] += v;
+            }
       }
     }
 
@@ -474,9 +546,9 @@ static int device_sm_count(int* device_out) {
   return cached[dev];
 }
 
-template <int M, int TILES, int COLS, unsigned TABLE_STEPS, bool NESTED, bool WIDE_SIGN>
+template <int M, int TILES, int COLS, unsigned TABLE_STEPS, bool NESTED, bool WIDE_SIGN, bool SPLIT = false>
 static int launch_slab(const FastProjectionArgs& p, cudaStream_t s) {
-  auto kernel = projection_slab_kernel<M, TILES, COLS, TABLE_STEPS, NESTED, WIDE_SIGN>;
+  auto kernel = projection_slab_kernel<M, TILES, COLS, TABLE_STEPS, NESTED, WIDE_SIGN, SPLIT>;
   static uint64_t configured = 0;  // one bit per device: the shared-memory opt-in is a per-device attribute of the function
   int dev = 0;
   const int sms = device_sm_count(&dev);
@@ -535,6 +607,17 @@ static int launch_slab_projection(const FastProjectionArgs& p, int cols, cudaStr
 
 int slab_gate_up(const FastProjectionArgs& p, int cols, cudaStream_t s) { return launch_slab_projection<2, 1>(p, cols, s); }
 int slab_down(const FastProjectionArgs& p, int cols, cudaStream_t s) { return launch_slab_projection<1, 2>(p, cols, s); }
+
+// The split form, for calls with few route groups (groups of at most four routes).
+int slab_split_max_in_dim() { return static_cast<int>(SK_SPLIT_RED_OFF / 8); }  // eight activation columns in front of the partial sums
+template <int M, int TILES>
+static int launch_split(const FastProjectionArgs& p, cudaStream_t s) {
+  if (p.in_dim > slab_split_max_in_dim()) return KEEPVQ_ERR_UNSUPPORTED;
+  if (p.res_table) return launch_slab<M, TILES, 4, 0u, true, false, true>(p, s);
+  return launch_slab<M, TILES, 4, 0xAAu, false, false, true>(p, s);
+}
+int slab_split_gate_up(const FastProjectionArgs& p, cudaStream_t s) { return launch_split<2, 1>(p, s); }
+int slab_split_down(const FastProjectionArgs& p, cudaStream_t s) { return launch_split<1, 2>(p, s); }
 
 }  // namespace fast
 }  // namespace keepvq

@@ -131,6 +131,19 @@ def _dense_reference(x2d, codes, scales, codebook, code_bits):
     return x2d.to(torch.float32) @ weights.T
 
 
+def _one_matrix(rows, codes, scales, table, rhs, code_bits):
+    """Every row of ``rows`` against the one matrix ``codes``: the int8 tensor-core kernels for
+    16-bit codes with fp16 / bf16 rows when the shapes fit them, else the general kernel."""
+    out = None
+    if code_bits == 16 and rows.dtype in (torch.float16, torch.bfloat16):
+        from .prefill import tensor_core_projection
+
+        out = tensor_core_projection(rows, codes[None], scales.contiguous()[None], table, rhs)
+    if out is None:
+        out = routed_matvec(rows, codes[None], scales.contiguous()[None], table, rhs, x_div=1, code_bits=code_bits)
+    return out
+
+
 def vq_qmv(x, codes, scales, codebook=None, *, in_dim: int, out_dim: int, group_size: int = 512, code_bits: int = 8,
            implementation: str = "cuda", codebook_duplication: int = 1) -> torch.Tensor:
     """``y[n] = sum_k W[n, k] x[k]`` with ``W`` decoded inside the kernel.  ``x`` [in] -> [out].
@@ -154,8 +167,7 @@ def vq_qmv(x, codes, scales, codebook=None, *, in_dim: int, out_dim: int, group_
     if implementation == "reference":
         return _dense_reference(x_t[None], codes_t, scales_t, table, code_bits)[0]
     rhs = torch.zeros(1, dtype=torch.int32, device=device)
-    out = routed_matvec(x_t[None], codes_t[None], scales_t.contiguous()[None], table, rhs, x_div=1, code_bits=code_bits)
-    return out[0]
+    return _one_matrix(x_t[None], codes_t, scales_t, table, rhs, code_bits)[0]
 
 
 def vq_qmm(x, codes, scales, codebook=None, *, in_dim: int, out_dim: int, group_size: int = 512, code_bits: int = 8,
@@ -178,7 +190,7 @@ def vq_qmm(x, codes, scales, codebook=None, *, in_dim: int, out_dim: int, group_
     if implementation == "reference":
         return _dense_reference(x_t, codes_t, scales_t, table, code_bits)
     rhs = torch.zeros(int(x_t.shape[0]), dtype=torch.int32, device=device)
-    return routed_matvec(x_t, codes_t[None], scales_t.contiguous()[None], table, rhs, x_div=1, code_bits=code_bits)
+    return _one_matrix(x_t, codes_t, scales_t, table, rhs, code_bits)
 
 
 # --- few-token kernels -------------------------------------------------------------------------

@@ -277,8 +277,16 @@ def gather_vqmm(x, codes, scales, codebook, rhs_indices, *, lhs_indices=None, in
         return _dense_routes(x_t[rows], codes_t, scales_t, table, flat_rhs, code_bits).reshape(output_shape)
 
     if strategy == "direct":
-        out = routed_matvec(x_t, codes_t.contiguous(), scales_t.contiguous(), table, flat_rhs, lhs=flat_lhs,
-                            x_div=x_div, code_bits=code_bits)
+        out = None
+        if code_bits == 16 and flat_lhs is None and x_t.dtype in (torch.float16, torch.bfloat16):
+            # token layout with 16-bit rows: the int8 tensor-core kernels, which group the routes by
+            # expert on the device and read each touched expert's codes once
+            from .prefill import tensor_core_projection
+
+            out = tensor_core_projection(x_t, codes_t.contiguous(), scales_t.contiguous(), table, flat_rhs, x_div=x_div)
+        if out is None:
+            out = routed_matvec(x_t, codes_t.contiguous(), scales_t.contiguous(), table, flat_rhs, lhs=flat_lhs,
+                                x_div=x_div, code_bits=code_bits)
         return out.reshape(output_shape)
 
     # sorted_tiled: sort routes by expert on the device, run the grouped kernel, undo the sort.

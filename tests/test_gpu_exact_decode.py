@@ -62,9 +62,10 @@ def check_rows(got, want_by_expert, rhs, which_input):
 @pytest.mark.parametrize("family", ["team", "slab8", "slab4", "tcgen05"])
 def test_single_projection_kernels_return_scale_times_weight_exactly(cuda, family):
     """The M = 1 (down-shaped) kernels through ``keepvq_grouped_projection``.  The route count and
-    the expert count pick the kernel: under 48 routes the team kernel, from there the slab kernel
-    with eight routes per group (many routes per expert) or four (few), and from 1024 routes with
-    24 per expert the tcgen05 kernel."""
+    the expert count pick the kernel: under 48 routes the split form of the slab kernel (called
+    "team" here after the kernel it shares its small calls with), from there the slab kernel with
+    eight routes per group (many routes per expert) or four (few), and from 1024 routes with 24
+    per expert the tcgen05 kernel."""
     copies = {"team": 1, "slab8": 1, "slab4": 32, "tcgen05": 1}[family]
     codes, scales = all_codes_experts(copies), None
     scales = scales_for(codes.shape[0], 1)
@@ -89,6 +90,41 @@ def test_single_projection_kernels_return_scale_times_weight_exactly(cuda, famil
         rhs = np.repeat(np.arange(4, dtype=np.int32), IN)   # 1024 routes, 256 per expert
         got = run_grouped(cuda, np.tile(x, (4, 1)), codes, scales, rhs)
         check_rows(got, want, rhs, np.tile(np.arange(IN), 4))
+
+
+@pytest.mark.parametrize("family,in_dim,routes", [("split", 2048, 6), ("split", 4096, 40), ("split-residual", 2048, 5), ("team", 8192, 6)])
+def test_few_route_kernels_over_wide_inputs_exactly(cuda, family, in_dim, routes):
+    """Calls with few routes.  Inputs up to 6144 wide run the split form of the slab kernel: several
+    warps share a row set, each over a part of the input dimension, and add their partial sums up in
+    shared memory (the 256-input cases above give every warp the whole row).  Wider inputs run the
+    team kernel.  A one-hot row at a random input picks one weight per output row, so whichever
+    warp owns that part of the row must deliver it, exactly."""
+    from keep_b200 import vq
+
+    experts, cw = 4, in_dim // 8
+    rng = np.random.default_rng(in_dim + routes)
+    codes = rng.integers(0, 1 << 16, (experts, ROWS, cw), dtype=np.uint16)
+    scales = scales_for(experts, 6)
+    dense = e8.decode_weight_matrix(codes.reshape(-1, cw), scales.reshape(-1, 1).astype(np.float32), code_bits=16).reshape(experts, ROWS, in_dim)
+    kw = {}
+    if family == "split-residual":
+        res_codes = rng.integers(0, 256, (2, ROWS, cw), dtype=np.uint8)
+        res_scales = np.full((2, ROWS, 1), 2.0 ** -8, dtype=np.float16)
+        hot = np.array([1, e8.NO_RESIDUAL, e8.NO_RESIDUAL, 0], dtype=np.uint32)
+        res = e8.decode_weight_matrix(res_codes.reshape(-1, cw), res_scales.reshape(-1, 1).astype(np.float32), code_bits=8).reshape(2, ROWS, in_dim)
+        dense[0] += res[1]
+        dense[3] += res[0]
+        kw = dict(residual=(torch.from_numpy(res_codes).to(cuda), torch.from_numpy(res_scales).to(cuda), vq.table_on(cuda, "e8_1bit_half2")),
+                  hot_of_slot=torch.from_numpy(hot.astype(np.int32)).to(cuda))
+    for call in range(4):
+        rhs = rng.integers(0, experts, routes).astype(np.int32)
+        which = rng.integers(0, in_dim, routes)
+        which[0], which[-1] = 0, in_dim - 1   # the first and the last warp's share
+        x = np.zeros((routes, in_dim), dtype=np.float32)
+        x[np.arange(routes), which] = VALUE
+        got = run_grouped(cuda, x, codes, scales, rhs, **kw)
+        want = dense[rhs, :, which] * np.float32(VALUE)           # [routes, ROWS]
+        np.testing.assert_array_equal(got, torch.from_numpy(want).to(torch.bfloat16).float().numpy())
 
 
 @pytest.mark.parametrize("cols", [8, 4])

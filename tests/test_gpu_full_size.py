@@ -61,6 +61,33 @@ def test_prefill_and_decode_kernels_agree_on_every_token(cuda, full_layer):
     assert (a - b).abs().max() <= 2 ** -7 * b.abs().max()
 
 
+@pytest.mark.parametrize("routing", ["uniform", "zipf"])
+def test_every_token_of_the_4096_token_call_is_repeatable_and_matches_the_slab_kernels(cuda, full_layer, routing):
+    """Every CTA of the tcgen05 kernels works through some forty items, and what one item leaves
+    behind (accumulators being drained, per-route facts, staged activations, the code ring) meets
+    the next.  All 4096 outputs are compared with the mma.sync slab kernels run on the same call
+    (``expected_routes`` below the tcgen05 threshold picks them), and the call is repeated: the
+    outputs may not change from run to run."""
+    x = tokens(cuda, 4096, 11)
+    saved = full_layer.pool_bias, full_layer.served_bias
+    if routing == "zipf":
+        rank = torch.randperm(EXPERTS, generator=torch.Generator().manual_seed(7)).float() + 1.0
+        full_layer.pool_bias = full_layer.served_bias = (-1.1 * torch.log(rank)).to(cuda)
+    try:
+        want = full_layer.decode(x, expected_routes=1000, state=1)[0].float().clone()
+        first = None
+        for _ in range(4):
+            got = full_layer.decode(x)[0].clone()
+            assert not full_layer.wait_expired(4096, x.dtype)
+            if first is None:
+                first = got
+            assert torch.equal(got, first)
+            per_token = (got.float() - want).abs().amax(dim=1) / want.abs().amax()
+            assert float(per_token.max()) <= 2 ** -7, int((per_token > 2 ** -7).sum())
+    finally:
+        full_layer.pool_bias, full_layer.served_bias = saved
+
+
 def test_sorted_route_operator_is_linear_in_the_activations(cuda, full_layer):
     """Doubling the activations doubles every output exactly (the activation step is a power of
     two, everything after it is integer arithmetic and one scaling), and the sum of two calls on
