@@ -91,7 +91,7 @@ extern "C" int keepvq_grouped_projection(const keepvq_grouped_projection_args* a
   p.a = {a.codes, a.scales, a.res_codes, a.res_scales}; p.b = {nullptr, nullptr, nullptr, nullptr};
   if (residual) { p.res_groups = a.res_groups; p.hot_of_slot = a.hot_of_slot; p.res_table = a.res_table; }
   p.scales_dtype = a.scales_dtype; p.codebook = a.codebook; p.groups_of_routes = groups; p.max_routes = a.routes; p.group_cols = group_cols; p.status = wait_status;
-  p.few_groups = !many && fast::few_route_groups(a.routes, a.slots);
+  p.few_groups = many ? 0 : fast::few_route_groups(a.routes, a.slots);
   p.out_dim = a.out_dim; p.in_dim = a.in_dim; p.groups = a.groups; p.x = xq; p.x_zero_row = x_rows; p.x_div = x_div;
   p.out = a.out; p.out_dtype = a.out_dtype; p.swiglu_limit = 0.0f; p.route_weight = nullptr;
   if (a.routes > 0x7FFFFFFFll) return KEEPVQ_ERR_CAPACITY;

@@ -1,18 +1,15 @@
 // Tensor-core decode path for the routed E8P experts: activation quantisation, route grouping
-// and the grouped projection kernels.  See moe_fast.cuh for the arithmetic identity it rests on.
+// and the choice of projection kernel.  See moe_fast.cuh for the arithmetic identity it rests on.
 //
-// Projection kernel layout (HBM-bound: every code byte is read once per group of routes):
-//   - persistent CTAs, one per SM, 16 warps = 2 teams of 8.  A team takes a work item = (route
-//     group, block of 32 or 64 output rows) and splits the input dimension across its 8 warps in
-//     chunks of 32 codewords; partial sums meet in shared memory in a fixed order.
-//   - a lane loads 16 bytes (8 codewords) per row per chunk, straight to registers
-//     (ld.global.nc, no L1 allocation): 4 lanes cover 64 contiguous bytes of a row.
-//   - a codeword becomes the A fragment of one m16n8k32 int8 MMA with: one popc, one 8-byte
-//     shared-memory read from a table indexed by (abs row, parity), two integer multiplies that
-//     spread the eight sign bits to byte tops, two byte-permutes that widen them to byte masks,
-//     two XORs.  The table is replicated 16x so lanes never share a bank.
+// The projection kernels themselves (HBM-bound by design: every code byte is read once per group
+// of routes) live in their own files: projection_slab.cu (calls with many route groups, and their
+// split form for a residual tier with few), projection_sweep.cu (few route groups) and
+// prefill_umma.cu (many routes per expert, tcgen05).  They share:
+//   - a codeword becomes the A fragment of an m16n8k32 int8 MMA through a table indexed by
+//     (abs row, parity), replicated 16x so lanes never share a bank, and sign masks from a second
+//     table or from two integer multiplies and byte permutes;
 //   - the K order inside an MMA is permuted (byte j of the low word is table nibble 3-j, of the
-//     high word nibble 7-j); the activations are stored in that same order by quantize_rows.
+//     high word nibble 7-j); the activations are stored in that same order by quantize_rows;
 //   - accumulation is exact in int32; one conversion to fp32 per scale group.
 #include <stdlib.h>
 
@@ -204,201 +201,9 @@ int group_routes(const uint32_t* served_slot, int64_t routes, int64_t slots, int
 }
 
 // ------------------------------------------------------------------------------------------
-// Grouped projections on the int8 tensor cores.
+// Which kernel runs a grouped projection.
 // ------------------------------------------------------------------------------------------
-constexpr int TEAM_WARPS = 8;
-constexpr int TEAMS = 2;
-constexpr int CTA_THREADS = TEAMS * TEAM_WARPS * 32;
-constexpr int CHUNK_CODES = 32;               // codewords of a row one warp consumes per step
-constexpr int LUT_REPLICAS = 16;
-constexpr int LUT_BYTES = 2 * 256 * LUT_REPLICAS * 8;  // [abs row][parity][replica] 8-byte entries
-// Spreads of the sign byte: S * SPREAD_LO puts sign bits 3,2,1,0 on bits 7,15,23,31 and
-// S * SPREAD_HI puts bits 7,6,5,4 there; the shifted copies of S never overlap, so no carries.
-constexpr uint32_t SPREAD_LO = (1u << 4) | (1u << 13) | (1u << 22) | (1u << 31);
-constexpr uint32_t SPREAD_HI = 1u | (1u << 9) | (1u << 18) | (1u << 27);
-
-__device__ __forceinline__ uint32_t top_bits_to_byte_masks(uint32_t v) {
-  uint32_t m;  // selector nibble 8+j: replicate the top bit of byte j over the output byte
-  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(m) : "r"(v), "r"(0u), "r"(0xBA98u));
-  return m;
-}
-
-__device__ __forceinline__ void mma_s8s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
-  asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-      : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-// One codeword -> two A-fragment words.  `sign` is its low byte, `abs_off` its high byte * 256,
-// `lut_lane` the 32-bit shared-memory address of this lane's replica.
-// q = table[abs][parity] ^ (neg ? 0xFE : 0).
-__device__ __forceinline__ void decode_to_fragment(uint32_t lut_lane, uint32_t sign, uint32_t abs_off, uint32_t& lo, uint32_t& hi) {
-  const uint32_t parity_off = (__popc(sign) & 1u) << 7;
-  uint32_t ex, ey;
-  // volatile: keeps the table reads after the code prefetch that precedes them in program order,
-  // so the compiler cannot sink that prefetch to the end of the step to save registers
-  asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(ex), "=r"(ey) : "r"(lut_lane + abs_off + parity_off));
-  lo = ex ^ (top_bits_to_byte_masks(sign * SPREAD_LO) & 0xFEFEFEFEu);
-  hi = ey ^ (top_bits_to_byte_masks(sign * SPREAD_HI) & 0xFEFEFEFEu);
-}
-
-__device__ __forceinline__ void team_barrier(int team) {
-  asm volatile("bar.sync %0, %1;" ::"r"(team + 1), "r"(TEAM_WARPS * 32) : "memory");
-}
-
-template <int M, int TILES>
-__global__ void __launch_bounds__(CTA_THREADS, 1) projection_kernel(FastProjectionArgs p) {
-  extern __shared__ __align__(16) uint8_t smem[];
-  grid_launch_dependents();
-  uint8_t* lut = smem;
-  constexpr int ACCS = M * TILES * 4;  // fp32 partials per lane
-  float* red = reinterpret_cast<float*>(smem + LUT_BYTES);  // [team][warp][ACCS][32]
-
-  // ---- table: entry (abs, parity) = eight bytes q for a positive sign pattern -----------------
-  for (int e = threadIdx.x; e < 512; e += CTA_THREADS) {
-    const uint32_t word = p.codebook[e >> 1], par = e & 1;
-    uint32_t lo = 0, hi = 0;
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const int nl = 3 - j, nh = 7 - j;
-      uint32_t hl = ((word >> (4 * nl)) & 0xFu) - 8u, hh = ((word >> (4 * nh)) & 0xFu) - 8u;
-      if (par) { hl = nl == 0 ? ~hl : hl ^ 1u; hh ^= 1u; }
-      lo |= (hl & 0xFFu) << (8 * j);
-      hi |= (hh & 0xFFu) << (8 * j);
-    }
-    uint2* dst = reinterpret_cast<uint2*>(lut) + e * LUT_REPLICAS;
-#pragma unroll
-    for (int r = 0; r < LUT_REPLICAS; ++r) dst[r] = make_uint2(lo, hi);
-  }
-  grid_wait();  // the tables came from constants; everything below reads what earlier kernels of the stream wrote
-  __syncthreads();
-
-  const int lane = threadIdx.x & 31, warp = (threadIdx.x >> 5) % TEAM_WARPS, team = threadIdx.x / (TEAM_WARPS * 32);
-  const int g = lane >> 2, t = lane & 3;
-  const uint32_t lut_lane = static_cast<uint32_t>(__cvta_generic_to_shared(lut)) + (lane & (LUT_REPLICAS - 1)) * 8;
-  float* team_red = red + static_cast<size_t>(team) * TEAM_WARPS * ACCS * 32;
-  const int64_t N = p.out_dim, cw = p.in_dim / 8;
-  const int n_chunks = static_cast<int>(cw / CHUNK_CODES);
-  const int chunks_per_group = n_chunks / static_cast<int>(p.groups);
-  const int rows_per_item = 16 * TILES;
-  const int row_blocks = static_cast<int>((N + rows_per_item - 1) / rows_per_item);
-  const int items = p.groups_of_routes.count[0] * row_blocks;
-  const Projection mats[2] = {p.a, p.b};
-
-  for (int item = blockIdx.x * TEAMS + team; item < items; item += gridDim.x * TEAMS) {
-    const int gi = item / row_blocks, rb = item - gi * row_blocks;
-    const int64_t slot = p.groups_of_routes.slot[gi];
-    const int gsize = p.groups_of_routes.size[gi], gstart = p.groups_of_routes.start[gi];
-    const int64_t row0 = static_cast<int64_t>(rb) * rows_per_item;
-    const int my_route = g < gsize ? p.groups_of_routes.routes[gstart + g] : -1;
-    const uint4* bsrc = reinterpret_cast<const uint4*>(p.x.q) + (my_route < 0 ? p.x_zero_row : static_cast<int64_t>(my_route / p.x_div)) * cw;
-
-    float part[M][TILES][4];
-    int acc_h[M][TILES][4], acc_l[M][TILES][4];
-#pragma unroll
-    for (int m = 0; m < M; ++m)
-#pragma unroll
-      for (int tl = 0; tl < TILES; ++tl)
-#pragma unroll
-        for (int r = 0; r < 4; ++r) { part[m][tl][r] = 0.0f; acc_h[m][tl][r] = 0; acc_l[m][tl][r] = 0; }
-
-    for (int c = warp; c < n_chunks; c += TEAM_WARPS) {
-      const int64_t cb = static_cast<int64_t>(c) * CHUNK_CODES + t * 8;
-      uint4 codes[M][2 * TILES];
-#pragma unroll
-      for (int m = 0; m < M; ++m)
-#pragma unroll
-        for (int j = 0; j < 2 * TILES; ++j) {
-          const int64_t row = min(row0 + 8 * j + g, N - 1);
-          codes[m][j] = ld_stream_u4(mats[m].codes + (slot * N + row) * cw + cb);
-        }
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const uint4 b = bsrc[cb + i];
-#pragma unroll
-        for (int m = 0; m < M; ++m)
-#pragma unroll
-          for (int tl = 0; tl < TILES; ++tl) {
-            uint32_t a[4];
-#pragma unroll
-            for (int half = 0; half < 2; ++half) {  // rows g and g + 8 of the tile
-              const uint4 v = codes[m][2 * tl + half];
-              const uint32_t word = (i >> 1) == 0 ? v.x : (i >> 1) == 1 ? v.y : (i >> 1) == 2 ? v.z : v.w;
-              uint32_t sign, abs_off;
-              if (i & 1) {
-                asm("prmt.b32 %0, %1, %2, %3;" : "=r"(sign) : "r"(word), "r"(0u), "r"(0x4442u));
-                asm("prmt.b32 %0, %1, %2, %3;" : "=r"(abs_off) : "r"(word), "r"(0u), "r"(0x4434u));
-              } else {
-                sign = word & 0xFFu;
-                abs_off = word & 0xFF00u;
-              }
-              decode_to_fragment(lut_lane, sign, abs_off, a[half], a[2 + half]);
-            }
-            mma_s8s8(acc_h[m][tl], a[0], a[1], a[2], a[3], b.x, b.y);
-            mma_s8s8(acc_l[m][tl], a[0], a[1], a[2], a[3], b.z, b.w);
-          }
-      }
-      // close the scale group when this warp's next chunk belongs to another one
-      const int group = c / chunks_per_group;
-      if (c + TEAM_WARPS >= n_chunks || (c + TEAM_WARPS) / chunks_per_group != group) {
-#pragma unroll
-        for (int m = 0; m < M; ++m)
-#pragma unroll
-          for (int tl = 0; tl < TILES; ++tl)
-#pragma unroll
-            for (int r = 0; r < 4; ++r) {
-              const int64_t row = min(row0 + 16 * tl + g + (r >= 2 ? 8 : 0), N - 1);
-              const float sc = load_as_float(mats[m].scales, p.scales_dtype, (slot * N + row) * p.groups + group);
-              part[m][tl][r] = fmaf(sc, 256.0f * static_cast<float>(acc_h[m][tl][r]) + static_cast<float>(acc_l[m][tl][r]), part[m][tl][r]);
-              acc_h[m][tl][r] = 0;
-              acc_l[m][tl][r] = 0;
-            }
-      }
-    }
-
-    // ---- meet the other warps of the team ---------------------------------------------------
-#pragma unroll
-    for (int m = 0; m < M; ++m)
-#pragma unroll
-      for (int tl = 0; tl < TILES; ++tl)
-#pragma unroll
-        for (int r = 0; r < 4; ++r) team_red[(warp * ACCS + (m * TILES + tl) * 4 + r) * 32 + lane] = part[m][tl][r];
-    team_barrier(team);
-
-    const int tid = threadIdx.x % (TEAM_WARPS * 32);
-    for (int o = tid; o < TILES * 4 * 32; o += TEAM_WARPS * 32) {
-      const int tl = o / 128, r = (o >> 5) & 3, ln = o & 31;
-      const int col = 2 * (ln & 3) + (r & 1);
-      const int64_t row = row0 + 16 * tl + (ln >> 2) + (r >= 2 ? 8 : 0);
-      if (col >= gsize || row >= N) continue;
-      const int route = p.groups_of_routes.routes[gstart + col];
-      const int64_t xrow = route / p.x_div;
-      float y[M];
-#pragma unroll
-      for (int m = 0; m < M; ++m) {
-        float dot = 0.0f;
-#pragma unroll
-        for (int w = 0; w < TEAM_WARPS; ++w) dot += team_red[(w * ACCS + (m * TILES + tl) * 4 + r) * 32 + ln];
-        float shift = 0.0f;  // the +-1/4 of every weight, folded into sum(x') per scale group
-        for (int64_t q = 0; q < p.groups; ++q)
-          shift = fmaf(load_as_float(mats[m].scales, p.scales_dtype, (slot * N + row) * p.groups + q),
-                       static_cast<float>(p.x.sums[xrow * p.groups + q]), shift);
-        y[m] = p.x.scale[xrow] * (0.5f * dot + 0.25f * shift);
-      }
-      float result;
-      if (M == 2) {
-        // round G and U to the activation dtype first, as the separate kernels of the reference do
-        float gt = y[0], up = y[1];
-        if (p.out_dtype == KEEPVQ_BF16) { gt = __bfloat162float(__float2bfloat16_rn(gt)); up = __bfloat162float(__float2bfloat16_rn(up)); }
-        else if (p.out_dtype == KEEPVQ_F16) { gt = __half2float(__float2half_rn(gt)); up = __half2float(__float2half_rn(up)); }
-        if (p.swiglu_limit > 0.0f) { gt = fminf(gt, p.swiglu_limit); up = fminf(fmaxf(up, -p.swiglu_limit), p.swiglu_limit); }
-        result = gt / (1.0f + expf(-gt)) * up * p.route_weight[route];
-      } else {
-        result = y[0];
-      }
-      store_from_float(p.out, p.out_dtype, static_cast<int64_t>(route) * N + row, result);
-    }
-    team_barrier(team);  // the reduction buffer is reused by the next item
-  }
-}
+constexpr int CHUNK_CODES = 32;               // codewords of a row a warp consumes per step: inputs come in multiples of 256
 
 bool shapes_supported(int64_t out_dim, int64_t in_dim, int64_t groups) {
   if (in_dim % (8 * CHUNK_CODES) != 0 || groups <= 0) return false;
@@ -406,46 +211,20 @@ bool shapes_supported(int64_t out_dim, int64_t in_dim, int64_t groups) {
   return chunks % groups == 0 && out_dim > 0;
 }
 
-// SM count of the current device (cached per device ordinal).
-static int sm_count(int* device_out) {
-  constexpr int MAX_DEVICES = 64;
-  static int cached[MAX_DEVICES] = {};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (device_out) *device_out = dev;
-  if (dev < 0 || dev >= MAX_DEVICES) return 148;
-  if (!cached[dev]) {
-    int n = 0;
-    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
-    cached[dev] = n > 0 ? n : 148;
-  }
-  return cached[dev];
-}
-
-template <int M, int TILES>
-static int launch_projection(const FastProjectionArgs& p, cudaStream_t s) {
-  constexpr size_t smem = LUT_BYTES + static_cast<size_t>(TEAMS) * TEAM_WARPS * (M * TILES * 4) * 32 * sizeof(float);
-  static uint64_t configured = 0;  // one bit per device: the shared-memory opt-in is a per-device attribute of the function
-  int dev = 0;
-  const int sms = sm_count(&dev);
-  if (dev < 0 || dev >= 64 || !((configured >> dev) & 1ull)) {
-    cudaError_t e = cudaFuncSetAttribute(projection_kernel<M, TILES>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-    if (e != cudaSuccess) return note_cuda_error(e);
-    if (dev >= 0 && dev < 64) configured |= 1ull << dev;
-  }
-  cudaError_t err = launch_after(true, projection_kernel<M, TILES>, sms, CTA_THREADS, smem, s, p);
-  if (err != cudaSuccess) return note_cuda_error(err);
-  return KEEPVQ_OK;
-}
-
 // Enough routes to give every CTA of the machine its own (group, slab) items, and activations
 // that fit the shared-memory stage?
 static bool many_items(const FastProjectionArgs& p) {
   return p.max_routes >= SMALL_CALL_ROUTES && p.in_dim <= slab_max_in_dim(p.group_cols > PAIRED_GROUP_ROUTES ? MAX_GROUP_ROUTES : PAIRED_GROUP_ROUTES);
 }
-// Few route groups of at most four routes, activations that leave room in the stage: the split slab kernel.
-static bool few_items(const FastProjectionArgs& p) {
-  return p.few_groups && p.group_cols <= PAIRED_GROUP_ROUTES && p.in_dim <= slab_split_max_in_dim();
+// Few route groups of at most four routes.  Small calls run the sweep kernel (measured on a B200 at
+// 4096 inputs: ahead of the split slab kernel up to four tokens of top-6, behind it at eight); the
+// rest, and every layer with a residual tier (the slab kernels hold the residual pass), the split
+// form of the slab kernel when the activations leave it room.  0 = neither, 1 = split slab, 2 = sweep.
+static int few_items(const FastProjectionArgs& p) {
+  if (!p.few_groups || p.group_cols > PAIRED_GROUP_ROUTES) return 0;
+  const bool split_fits = p.in_dim <= slab_split_max_in_dim(), sweep_fits = !p.res_table && sweep_supported(p.in_dim);
+  if (p.few_groups == 2 && sweep_fits) return 2;
+  return split_fits ? 1 : sweep_fits ? 2 : 0;
 }
 
 #ifdef KEEPVQ_DIAG
@@ -457,14 +236,14 @@ int decode_group_routes(int64_t live, int64_t slots, int64_t widest_in_dim) {
 #ifdef KEEPVQ_DIAG
   if (g_force_cols) return g_force_cols;
 #endif
-  if (live < SMALL_CALL_ROUTES) return widest_in_dim <= slab_split_max_in_dim() ? PAIRED_GROUP_ROUTES : MAX_GROUP_ROUTES;  // split slab kernel | team kernel
+  if (live < SMALL_CALL_ROUTES) return PAIRED_GROUP_ROUTES;  // the sweep kernel (the split slab kernel with a residual tier)
   if (widest_in_dim > slab_max_in_dim(MAX_GROUP_ROUTES)) return PAIRED_GROUP_ROUTES;
   return live <= 2 * slots ? PAIRED_GROUP_ROUTES : MAX_GROUP_ROUTES;
 }
 
 // The residual pass lives in the slab kernels only: a layer with a residual tier needs activations
-// that fit their stage (half of it for calls with few routes) and residual scale groups that close
-// on chunk boundaries.
+// that fit their stage (three quarters of it for calls with few routes) and residual scale groups
+// that close on chunk boundaries.
 bool residual_supported(int64_t routes, int64_t in_dim, int64_t res_groups) {
   const int64_t widest = routes < SMALL_CALL_ROUTES ? slab_split_max_in_dim() : slab_max_in_dim(PAIRED_GROUP_ROUTES);
   if (in_dim > widest || in_dim % (8 * CHUNK_CODES) != 0 || res_groups <= 0) return false;
@@ -472,14 +251,14 @@ bool residual_supported(int64_t routes, int64_t in_dim, int64_t res_groups) {
 }
 
 int gate_up(const FastProjectionArgs& p, cudaStream_t s) {
-  if (few_items(p)) return slab_split_gate_up(p, s);
-  if (p.res_table && !many_items(p)) return KEEPVQ_ERR_UNSUPPORTED;
-  return many_items(p) ? slab_gate_up(p, p.group_cols > PAIRED_GROUP_ROUTES ? MAX_GROUP_ROUTES : PAIRED_GROUP_ROUTES, s) : launch_projection<2, 2>(p, s);
+  if (const int few = few_items(p)) return few == 2 ? sweep_gate_up(p, s) : slab_split_gate_up(p, s);
+  if (!many_items(p)) return KEEPVQ_ERR_UNSUPPORTED;
+  return slab_gate_up(p, p.group_cols > PAIRED_GROUP_ROUTES ? MAX_GROUP_ROUTES : PAIRED_GROUP_ROUTES, s);
 }
 int down(const FastProjectionArgs& p, cudaStream_t s) {
-  if (few_items(p)) return slab_split_down(p, s);
-  if (p.res_table && !many_items(p)) return KEEPVQ_ERR_UNSUPPORTED;
-  return many_items(p) ? slab_down(p, p.group_cols > PAIRED_GROUP_ROUTES ? MAX_GROUP_ROUTES : PAIRED_GROUP_ROUTES, s) : launch_projection<1, 4>(p, s);
+  if (const int few = few_items(p)) return few == 2 ? sweep_down(p, s) : slab_split_down(p, s);
+  if (!many_items(p)) return KEEPVQ_ERR_UNSUPPORTED;
+  return slab_down(p, p.group_cols > PAIRED_GROUP_ROUTES ? MAX_GROUP_ROUTES : PAIRED_GROUP_ROUTES, s);
 }
 
 }  // namespace fast

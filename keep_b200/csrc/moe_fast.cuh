@@ -17,7 +17,7 @@ namespace fast {
 
 constexpr int MAX_GROUP_ROUTES = 8;     // routes of one expert that share an mma.sync tile (its 8 columns)
 constexpr int SMALL_CALL_ROUTES = 48;   // calls with fewer routes never run the plain slab kernel
-constexpr int FEW_ROUTE_GROUPS = 96;    // below this many route groups the split slab kernel shares rows AND inputs among a CTA's warps
+constexpr int FEW_ROUTE_GROUPS = 96;    // below this many route groups a CTA's warps share rows AND inputs (sweep kernel, split slab kernel)
 constexpr int PAIRED_GROUP_ROUTES = 4;  // ... when a route's two byte planes take a column each (one MMA per step)
 constexpr int PREFILL_GROUP_ROUTES = 96;   // routes of one expert per tcgen05 item (its accumulators and two operand stages fill tensor memory)
 
@@ -136,7 +136,7 @@ struct FastProjectionArgs {
   int64_t max_routes;
   int32_t* status;        // device word a kernel sets when it gives up (bounded wait expired: 1; unexpected shared window: 2), or null
   int32_t group_cols;     // most routes a group holds: PAIRED_GROUP_ROUTES or MAX_GROUP_ROUTES (what group_routes was given)
-  int32_t few_groups;     // the call is expected to form few route groups (few_route_groups said so)
+  int32_t few_groups;     // what few_route_groups said of the call: 0 many route groups, 1 few, 2 a small call
   // nested residual tier (all null / 0 when the layer has none): slot s adds the 8-bit residual of
   // row hot_of_slot[s] unless that is 0xFFFFFFFF.  res_table is [256][4] fp16 pairs (dims 2k, 2k+1).
   int64_t res_groups;
@@ -157,8 +157,8 @@ int group_routes(const uint32_t* served_slot, int64_t routes, int64_t slots, int
 // Routes per group for a decode call: four while experts rarely get more (the kernels then run one
 // MMA per step for both byte planes), eight beyond.  `live` = routes expected to carry a slot.
 int decode_group_routes(int64_t live, int64_t slots, int64_t widest_in_dim);
-// Whether a decode call with `live` routes over `slots` experts forms few route groups.
-inline bool few_route_groups(int64_t live, int64_t slots) { return live < SMALL_CALL_ROUTES || (live < slots ? live : slots) < FEW_ROUTE_GROUPS; }
+// Whether a decode call with `live` routes over `slots` experts forms few route groups: 0 no, 1 yes, 2 a small call.
+inline int few_route_groups(int64_t live, int64_t slots) { return live < SMALL_CALL_ROUTES ? 2 : (live < slots ? live : slots) < FEW_ROUTE_GROUPS ? 1 : 0; }
 int gate_up(const FastProjectionArgs& args, cudaStream_t s);   // h = round(silu(G) * U * weight)
 int down(const FastProjectionArgs& args, cudaStream_t s);      // out = round(W2 h)
 
@@ -170,6 +170,11 @@ int slab_down(const FastProjectionArgs& args, int cols, cudaStream_t s);
 int slab_split_max_in_dim();
 int slab_split_gate_up(const FastProjectionArgs& args, cudaStream_t s);
 int slab_split_down(const FastProjectionArgs& args, cudaStream_t s);
+// The sweep kernels for calls with few route groups and no residual tier (projection_sweep.cu):
+// inputs of any width in multiples of 256.
+bool sweep_supported(int64_t in_dim);
+int sweep_gate_up(const FastProjectionArgs& args, cudaStream_t s);
+int sweep_down(const FastProjectionArgs& args, cudaStream_t s);
 
 // tcgen05 kernels for many routes per expert (prefill_umma.cu).  `status` is a device word that
 // a CTA sets to 1 if one of its bounded waits expires.

@@ -1,0 +1,370 @@
+// Decode projections for calls with few route groups (a handful of tokens): the sweep kernel.
+//
+// With six experts touched, a call is twelve matrices of codes and nothing else; what decides its
+// time is that every SM gets an equal share, that every warp has loads in flight, and that no
+// instruction is spent on anything but codewords.  So the work is cut into units of 16 output rows
+// of one route group (both matrices of a gate/up pair), the units are dealt to the CTAs as
+// contiguous runs of equal length, and inside a CTA the 16 warps split the INPUT dimension: warp
+// (row set, k part) walks down its row set's units and takes only its own chunk(s) of 32 codewords
+// per row from each.  Its slice of the group's quantised activations is 16 registers, kept across
+// the units of a group; its codes arrive through a private cp.async ring that runs ahead across
+// units.  A warp leaves the partial sums of up to eight units in shared memory; then the CTA meets
+// once and the warps share the units' epilogues (sum over the k parts, scales, SwiGLU, store).
+// Units are walked by increments: no division, no per-unit barrier.
+//
+// Same arithmetic as the slab kernel (projection_slab.cu): int8 mma.sync m16n8k32 with a route's
+// two byte planes as neighbouring columns, codes decoded through the permute-addressed tables.
+#include <type_traits>
+#include <utility>
+
+#include "moe_fast.cuh"
+
+namespace keepvq {
+namespace fast {
+
+constexpr int SW_WARPS = 16;
+constexpr int SW_THREADS = SW_WARPS * 32;
+constexpr int SW_CHUNK = 32;                     // codewords of a row per step of a warp
+constexpr int SW_PASS_UNITS = 8;                 // units a warp carries in registers between two meetings of the CTA
+constexpr int SW_REPLICAS = 16;
+constexpr int SW_SMEM_BYTES = 227 * 1024;
+constexpr uint32_t SW_ABS_BYTES = 256 * 2 * SW_REPLICAS * 8;   // 64 KB, on a 64 KB boundary of the shared window
+constexpr uint32_t SW_SIGN_BYTES = 256 * SW_REPLICAS * 8;      // 32 KB
+constexpr uint32_t SW_RED_BYTES = SW_PASS_UNITS * SW_WARPS * 4 * 128;  // 64 KB: [unit of the pass][k part][value][lane] fp32
+
+template <int N, typename F, int... I>
+__device__ __forceinline__ void sw_static_for_impl(F&& f, std::integer_sequence<int, I...>) { (f(std::integral_constant<int, I>{}), ...); }
+template <int N, typename F>
+__device__ __forceinline__ void sw_static_for(F&& f) { sw_static_for_impl<N>(static_cast<F&&>(f), std::make_integer_sequence<int, N>{}); }
+
+template <int OFF>
+__device__ __forceinline__ void sw_cp_async16(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0+%2], [%1], 16;" ::"r"(dst), "l"(src), "n"(OFF) : "memory");
+}
+template <int OFF>
+__device__ __forceinline__ uint4 sw_lds128(uint32_t addr) {  // data a cp.async wrote: ordered by the volatile wait before it
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4+%5];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr), "n"(OFF));
+  return v;
+}
+__device__ __forceinline__ void sw_mma(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+// The first MMA of a chain: accumulates onto zero, so the accumulators need no clearing.
+__device__ __forceinline__ void sw_mma_first(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+      : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+}
+template <int I>
+__device__ __forceinline__ uint32_t sw_word(const uint4& v) {
+  return (I >> 1) == 0 ? v.x : (I >> 1) == 1 ? v.y : (I >> 1) == 2 ? v.z : v.w;
+}
+
+// M = 2: gate and up over the same rows, fused by SwiGLU; M = 1: one matrix.
+// TABLE_STEPS: which of a lane's eight codewords per chunk take their sign masks from the second
+// table (the others spread the sign byte on the integer pipe); 0 = no second table, and the room
+// it would take goes to a deeper code ring (DEPTH stages of one chunk per warp).
+// `status` (may be null) is set to 2 if the shared window does not have the expected shape.
+template <int M, unsigned TABLE_STEPS, int DEPTH>
+__global__ void __launch_bounds__(SW_THREADS, 1) projection_sweep_kernel(FastProjectionArgs p, int32_t* status) {
+  extern __shared__ __align__(16) uint8_t smem[];
+  grid_launch_dependents();
+  constexpr int STREAMS = 2 * M;                       // row g and row g + 8 of each matrix
+  constexpr int VALUES = 2 * M;                        // per lane and unit: (matrix, row g | g + 8) for the lane's route
+  constexpr uint32_t STAGE_BYTES = STREAMS * 512;      // per warp: 16 bytes per lane and stream
+  constexpr uint32_t RING_BYTES = DEPTH * STAGE_BYTES;
+  constexpr uint32_t SECOND_BYTES = TABLE_STEPS ? SW_SIGN_BYTES : 0u;
+
+  // ---- the shared window: rings below the first 64 KB boundary as far as they fit, then the abs
+  // table on the boundary, the second table, the partial sums, the remaining rings
+  const uint32_t base = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
+  const uint32_t a0 = (base + 0xFFFFu) & ~0xFFFFu;
+  const int low_warps = min(SW_WARPS, static_cast<int>((a0 - base) / RING_BYTES));
+  const uint32_t red_base = a0 + SW_ABS_BYTES + SECOND_BYTES;
+  const uint32_t high_rings = red_base + SW_RED_BYTES;
+  if (high_rings + (SW_WARPS - low_warps) * RING_BYTES > base + SW_SMEM_BYTES) {  // uniform over the grid
+    if (status && threadIdx.x == 0) atomicExch(status, 2);
+    return;
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int g = lane >> 2, t = lane & 3;
+
+  // ---- tables (from constants: before the wait on the previous kernel) -------------------------
+  for (int e = threadIdx.x; e < (TABLE_STEPS ? 768 : 512); e += SW_THREADS) {
+    const uint2 v = e < 512 ? abs_table_entry(p.codebook[e >> 1], e & 1) : sign_table_entry(e - 512);
+    const int e_warp = e & ~31;
+    const uint32_t dst_warp = e < 512 ? a0 + e_warp * (SW_REPLICAS * 8) : a0 + SW_ABS_BYTES + (e_warp - 512) * (SW_REPLICAS * 8);
+#pragma unroll 4
+    for (int i = 0; i < 32; i += 2) {  // sixteen lanes store the sixteen replicas of one entry side by side: no bank conflicts
+      const int from = i + (lane >> 4);
+      const uint32_t lo = __shfl_sync(0xFFFFFFFFu, v.x, from), hi = __shfl_sync(0xFFFFFFFFu, v.y, from);
+      asm volatile("st.shared.v2.u32 [%0], {%1,%2};" ::"r"(dst_warp + from * (SW_REPLICAS * 8) + (lane & 15) * 8), "r"(lo), "r"(hi) : "memory");
+    }
+  }
+  grid_wait();  // everything below reads what earlier kernels of the stream wrote
+  __syncthreads();
+
+  const uint32_t abs_lane = a0 + static_cast<uint32_t>(lane & (SW_REPLICAS - 1)) * 8u;
+  const uint32_t second_lane = a0 + SW_ABS_BYTES + static_cast<uint32_t>(lane & (SW_REPLICAS - 1)) * 8u;
+  const uint32_t ring = (warp < low_warps ? base + warp * RING_BYTES : high_rings + (warp - low_warps) * RING_BYTES) + lane * 16;
+  const int64_t N = p.out_dim, cw = p.in_dim / 8;
+  const int n_chunks = static_cast<int>(cw / SW_CHUNK);
+  const int chunks_per_group = n_chunks / static_cast<int>(p.groups);
+  // warps per row set: as many k parts as the chunks give, in powers of two
+  const int ks = n_chunks >= 12 ? 16 : n_chunks >= 6 ? 8 : n_chunks >= 3 ? 4 : n_chunks >= 2 ? 2 : 1;
+  const int row_sets = SW_WARPS / ks;
+  const int row_set = warp / ks, k_part = warp - row_set * ks;
+  const int c_first = k_part * n_chunks / ks, c_end = (k_part + 1) * n_chunks / ks;
+  const int my_chunks = c_end - c_first;
+  const int units_per_group = static_cast<int>((N + 15) / 16);
+  const int64_t units = static_cast<int64_t>(p.groups_of_routes.count[0]) * units_per_group;
+  const int grid = static_cast<int>(gridDim.x), cta = static_cast<int>(blockIdx.x);
+  const int u_begin = static_cast<int>(units * cta / grid), u_end = static_cast<int>(units * (cta + 1) / grid);
+  const Projection mats[2] = {p.a, M == 2 ? p.b : p.a};
+
+  // A warp's walk over its units (u_begin + row_set, + row_sets, ...), kept twice: once for the
+  // code fetches, which run ahead, once for the arithmetic.
+  const int last_row = static_cast<int>(N - 1);
+  const bool ragged = (N & 15) != 0;  // the last tile of a group has fewer than 16 rows: its row indices are clamped
+  const uint64_t codes0 = reinterpret_cast<uint64_t>(mats[0].codes), row_bytes = static_cast<uint64_t>(cw) * 2u;
+  const uint64_t matrix_delta = reinterpret_cast<uint64_t>(mats[1].codes) - codes0;  // wraps for a lower address: the sum is taken modulo 2^64 again
+  const uint64_t lane_offset = static_cast<uint64_t>(g) * row_bytes + static_cast<uint64_t>(c_first * SW_CHUNK + t * 8) * 2u;
+  const uint64_t unit_stride = static_cast<uint64_t>(row_sets) * 16u * row_bytes;
+  struct Walk {
+    int u, gi, tile;     // unit, its group and its 16-row tile
+    int c;               // next chunk of the unit
+    int64_t slot_rows;   // slot * N
+    uint64_t codes;      // address of this lane's first codes of the unit: matrix 0, row tile * 16 + g, chunk c_first
+  };
+  auto enter_group = [&](Walk& w) {
+    w.slot_rows = static_cast<int64_t>(p.groups_of_routes.slot[w.gi]) * N;
+    w.codes = codes0 + static_cast<uint64_t>(w.slot_rows + w.tile * 16) * row_bytes + lane_offset;
+  };
+  auto start_walk = [&](Walk& w) {
+    w.u = u_begin + row_set;
+    w.gi = w.u / units_per_group;
+    w.tile = w.u - w.gi * units_per_group;
+    w.c = c_first;
+    w.slot_rows = 0;
+    w.codes = 0;
+    if (w.u < u_end) enter_group(w);
+  };
+  auto next_unit = [&](Walk& w) {
+    w.u += row_sets;
+    w.tile += row_sets;
+    w.c = c_first;
+    w.codes += unit_stride;
+    if (w.tile >= units_per_group) {  // (a loop: tiny outputs have fewer units per group than a CTA has row sets)
+      while (w.tile >= units_per_group) { w.tile -= units_per_group; ++w.gi; }
+      if (w.u < u_end) enter_group(w);
+    }
+  };
+  uint32_t fetch_turn = 0, use_turn = 0;
+  Walk ahead;
+  start_walk(ahead);
+  auto fetch = [&]() {  // the next chunk of the walk `ahead` -> ring stage fetch_turn % DEPTH; always commits a group
+    if (ahead.u < u_end && my_chunks > 0) {
+      const uint32_t dst = ring + (fetch_turn % DEPTH) * STAGE_BYTES;
+      // stream 0 = row g of the first matrix; the others are fixed byte distances away
+      uint64_t first = ahead.codes + static_cast<uint32_t>(ahead.c - c_first) * (SW_CHUNK * 2u), hi_delta = 8u * row_bytes;
+      if (ragged) {
+        const int row_lo = min(ahead.tile * 16 + g, last_row), row_hi = min(ahead.tile * 16 + g + 8, last_row);
+        first = codes0 + static_cast<uint64_t>((ahead.slot_rows + row_lo) * cw + ahead.c * SW_CHUNK + t * 8) * 2u;
+        hi_delta = static_cast<uint64_t>(row_hi - row_lo) * row_bytes;
+      }
+      sw_static_for<STREAMS>([&](auto s) {
+        constexpr int S = decltype(s)::value;
+        sw_cp_async16<S * 512>(dst, reinterpret_cast<const void*>(first + ((S & 1) ? hi_delta : 0u) + ((S >> 1) ? matrix_delta : 0u)));
+      });
+      if (++ahead.c == c_end) next_unit(ahead);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    ++fetch_turn;
+  };
+#pragma unroll
+  for (int i = 0; i < DEPTH - 1; ++i) fetch();
+
+  Walk at;
+  start_walk(at);
+  const uint8_t* x_lane = nullptr;
+  int x_group = -1;  // whose activations x_lane points at
+  uint2 b[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) b[i] = make_uint2(0u, 0u);
+  auto load_slice = [&](int c) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i)  // (volatile: held in registers, not re-issued at every use)
+      asm volatile("ld.global.nc.v2.u32 {%0,%1}, [%2];" : "=r"(b[i].x), "=r"(b[i].y) : "l"(x_lane + (static_cast<int64_t>(c) * SW_CHUNK + i) * 16));
+  };
+  const int local_units = u_end - u_begin;
+  const int per_pass = SW_PASS_UNITS * row_sets;  // units of the CTA per pass
+  const uint32_t red_mine = red_base + ((row_set * ks + k_part) * 128u + lane) * 4u;  // + (j * 16 warps * 4 + v) * 128 bytes
+  for (int pass_first = 0; pass_first < local_units; pass_first += per_pass) {
+    // ---- this warp's units of the pass: the partial sums of unit j go straight to their place in
+    // shared memory, so the loop stays rolled (unrolled eight times it did not fit the instruction cache)
+    const int pass_end = u_begin + pass_first + per_pass;
+#pragma unroll 1
+    for (int j = 0; j < SW_PASS_UNITS && at.u < u_end && at.u < pass_end; ++j) {
+      float part[VALUES];
+#pragma unroll
+      for (int v = 0; v < VALUES; ++v) part[v] = 0.0f;
+      // The lane's slice of the group's activations: 8 bytes of one plane per step of a chunk.  The
+      // reads are scattered (sixteen cache lines per warp-wide load), so a warp with one chunk per
+      // unit keeps them across the units of a group.
+      if (at.gi != x_group) {
+        const int gsize = p.groups_of_routes.size[at.gi], gstart = p.groups_of_routes.start[at.gi];
+        // column g of the MMA is (route g / 2, byte plane g % 2); a lane whose column carries no route
+        // reads route 0's bytes (always there), and nothing ever looks at its column
+        const int col_route = (g >> 1) < gsize ? (g >> 1) : 0;
+        const int route = p.groups_of_routes.routes[gstart + col_route];
+        x_lane = p.x.q + (static_cast<int64_t>(route / p.x_div) * cw + t * 8) * 16 + (g & 1) * 8;
+        x_group = at.gi;
+        if (my_chunks == 1) load_slice(c_first);
+      }
+      for (int c = c_first; c < c_end; ++c) {
+        if (my_chunks != 1) load_slice(c);
+        fetch();
+        asm volatile("cp.async.wait_group %0;" ::"n"(DEPTH - 1) : "memory");  // this chunk has landed
+        const uint32_t src = ring + (use_turn % DEPTH) * STAGE_BYTES;
+        ++use_turn;
+        uint4 cur[STREAMS];
+        sw_static_for<STREAMS>([&](auto s) { cur[decltype(s)::value] = sw_lds128<decltype(s)::value * 512>(src); });
+        float sc[M][2];  // with one scale per row the epilogue applies it; otherwise asked for now, used behind the MMAs
+#pragma unroll
+        for (int m = 0; m < M; ++m)
+#pragma unroll
+          for (int rr = 0; rr < 2; ++rr) {
+            sc[m][rr] = 1.0f;
+            if (p.groups > 1) {
+              const int64_t row = min(static_cast<int64_t>(at.tile) * 16 + g + 8 * rr, N - 1);
+              sc[m][rr] = load_as_float(mats[m].scales, p.scales_dtype, (at.slot_rows + row) * p.groups + c / chunks_per_group);
+            }
+          }
+        int acc[2][M][4];  // two chains per matrix, used by alternate steps: the MMA's dependent latency is long
+        sw_static_for<8>([&](auto index) {
+          constexpr int I = decltype(index)::value;
+          constexpr bool TABLE = ((TABLE_STEPS >> I) & 1u) != 0;
+#pragma unroll
+          for (int m = 0; m < M; ++m) {
+            uint32_t a[4];
+            decode_codeword<TABLE, (I & 1) != 0, false>(sw_word<I>(cur[2 * m]), abs_lane, second_lane, a[0], a[2]);      // row g
+            decode_codeword<TABLE, (I & 1) != 0, false>(sw_word<I>(cur[2 * m + 1]), abs_lane, second_lane, a[1], a[3]);  // row g + 8
+            if (I < 2) sw_mma_first(acc[I][m], a[0], a[1], a[2], a[3], b[I].x, b[I].y);
+            else sw_mma(acc[I & 1][m], a[0], a[1], a[2], a[3], b[I].x, b[I].y);
+          }
+        });
+        // columns 2t, 2t + 1 of the MMA are this lane's route: high plane, low plane
+#pragma unroll
+        for (int m = 0; m < M; ++m)
+#pragma unroll
+          for (int rr = 0; rr < 2; ++rr) {
+            // 256 * high + low of one chunk fits 32 bits (256 products of at most 2^15 each, times 256)
+            const int dot = ((acc[0][m][2 * rr] + acc[1][m][2 * rr]) << 8) + acc[0][m][2 * rr + 1] + acc[1][m][2 * rr + 1];
+            part[2 * m + rr] = fmaf(sc[m][rr], static_cast<float>(dot), part[2 * m + rr]);
+          }
+      }
+#pragma unroll
+      for (int v = 0; v < VALUES; ++v)
+        asm volatile("st.shared.f32 [%0], %1;" ::"r"(red_mine + j * (SW_WARPS * 512u) + v * 128u), "f"(part[v]) : "memory");
+      next_unit(at);
+    }
+
+    // ---- the CTA meets: epilogues shared out -----------------------------------------------------
+    __syncthreads();
+    const int in_pass = min(per_pass, local_units - pass_first);
+    for (int e = warp; e < in_pass; e += SW_WARPS) {  // unit e of the pass: j = e / row_sets of row set e % row_sets
+      const int u = u_begin + pass_first + e;
+      const int gi = u / units_per_group, tile = u - gi * units_per_group;
+      const int gsize = p.groups_of_routes.size[gi], gstart = p.groups_of_routes.start[gi];
+      const int64_t slot_rows = static_cast<int64_t>(p.groups_of_routes.slot[gi]) * N;
+      if (t >= gsize) continue;  // lane (g, t) holds rows g and g + 8 of route t
+      const int route = p.groups_of_routes.routes[gstart + t];
+      const int64_t xrow = route / p.x_div;
+      const float xs = p.x.scale[xrow];
+      float sum[VALUES];
+#pragma unroll
+      for (int v = 0; v < VALUES; ++v) sum[v] = 0.0f;
+      for (int k = 0; k < ks; ++k)
+#pragma unroll
+        for (int v = 0; v < VALUES; ++v) {
+          float got;
+          asm volatile("ld.shared.f32 %0, [%1];" : "=f"(got) : "r"(red_base + (((e * ks + k) * 4 + v) * 32 + lane) * 4u));
+          sum[v] += got;
+        }
+#pragma unroll
+      for (int rr = 0; rr < 2; ++rr) {
+        const int64_t row = static_cast<int64_t>(tile) * 16 + g + 8 * rr;
+        if (row >= N) continue;
+        float y[M];
+#pragma unroll
+        for (int m = 0; m < M; ++m) {
+          float dot = sum[2 * m + rr], shift = 0.0f;  // shift: the +-1/4 of every weight, folded into sum(x') per scale group
+          if (p.groups == 1) {
+            const float sc = load_as_float(mats[m].scales, p.scales_dtype, slot_rows + row);
+            dot *= sc;
+            shift = sc * static_cast<float>(p.x.sums[xrow]);
+          } else {
+            for (int64_t q = 0; q < p.groups; ++q)
+              shift = fmaf(load_as_float(mats[m].scales, p.scales_dtype, (slot_rows + row) * p.groups + q), static_cast<float>(p.x.sums[xrow * p.groups + q]), shift);
+          }
+          y[m] = xs * (0.5f * dot + 0.25f * shift);
+        }
+        float result;
+        if (M == 2) {  // round G and U to the activation dtype first, as the separate kernels of the reference do
+          float gt = y[0], up = y[M - 1];
+          if (p.out_dtype == KEEPVQ_BF16) { gt = __bfloat162float(__float2bfloat16_rn(gt)); up = __bfloat162float(__float2bfloat16_rn(up)); }
+          else if (p.out_dtype == KEEPVQ_F16) { gt = __half2float(__float2half_rn(gt)); up = __half2float(__float2half_rn(up)); }
+          if (p.swiglu_limit > 0.0f) { gt = fminf(gt, p.swiglu_limit); up = fminf(fmaxf(up, -p.swiglu_limit), p.swiglu_limit); }
+          result = gt / (1.0f + expf(-gt)) * up * p.route_weight[route];
+        } else {
+          result = y[0];
+        }
+        store_from_float(p.out, p.out_dtype, static_cast<int64_t>(route) * N + row, result);
+      }
+    }
+    __syncthreads();  // the partial sums are read; the next pass may overwrite them
+  }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+}
+
+// ---- launch -----------------------------------------------------------------------------------
+
+bool sweep_supported(int64_t in_dim) { return in_dim % (8 * SW_CHUNK) == 0; }
+
+template <int M, unsigned TABLE_STEPS, int DEPTH>
+static int launch_sweep(const FastProjectionArgs& p, cudaStream_t s) {
+  auto kernel = projection_sweep_kernel<M, TABLE_STEPS, DEPTH>;
+  static uint64_t configured = 0;  // one bit per device: the shared-memory opt-in is a per-device attribute of the function
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64 || !((configured >> dev) & 1ull)) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SW_SMEM_BYTES);
+    if (e != cudaSuccess) return note_cuda_error(e);
+    if (dev >= 0 && dev < 64) configured |= 1ull << dev;
+  }
+  static int cached_sms[64] = {};
+  if (dev >= 0 && dev < 64) {
+    if (!cached_sms[dev]) {
+      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+      cached_sms[dev] = sms > 0 ? sms : 148;
+    }
+    sms = cached_sms[dev];
+  }
+  cudaError_t err = launch_after(true, kernel, sms, SW_THREADS, SW_SMEM_BYTES, s, p, p.status);
+  if (err != cudaSuccess) return note_cuda_error(err);
+  return KEEPVQ_OK;
+}
+
+#ifdef KEEPVQ_DIAG
+static int g_sweep_variant = 0;  // measurement build only: 0 = second table + ring of 2, 1 = no second table + ring of 3
+extern "C" void keepvq_diag_set_sweep(int variant) { g_sweep_variant = variant; }
+int sweep_gate_up(const FastProjectionArgs& p, cudaStream_t s) { return g_sweep_variant ? launch_sweep<2, 0u, 3>(p, s) : launch_sweep<2, 0xAAu, 2>(p, s); }
+int sweep_down(const FastProjectionArgs& p, cudaStream_t s) { return g_sweep_variant ? launch_sweep<1, 0u, 6>(p, s) : launch_sweep<1, 0xAAu, 4>(p, s); }
+#else
+int sweep_gate_up(const FastProjectionArgs& p, cudaStream_t s) { return launch_sweep<2, 0xAAu, 2>(p, s); }
+int sweep_down(const FastProjectionArgs& p, cudaStream_t s) { return launch_sweep<1, 0xAAu, 4>(p, s); }
+#endif
+
+}  // namespace fast
+}  // namespace keepvq

@@ -59,19 +59,18 @@ def check_rows(got, want_by_expert, rhs, which_input):
     np.testing.assert_array_equal(got, want)
 
 
-@pytest.mark.parametrize("family", ["team", "slab8", "slab4", "tcgen05"])
+@pytest.mark.parametrize("family", ["few", "slab8", "slab4", "tcgen05"])
 def test_single_projection_kernels_return_scale_times_weight_exactly(cuda, family):
     """The M = 1 (down-shaped) kernels through ``keepvq_grouped_projection``.  The route count and
-    the expert count pick the kernel: under 48 routes the split form of the slab kernel (called
-    "team" here after the kernel it shares its small calls with), from there the slab kernel with
-    eight routes per group (many routes per expert) or four (few), and from 1024 routes with 24
-    per expert the tcgen05 kernel."""
-    copies = {"team": 1, "slab8": 1, "slab4": 32, "tcgen05": 1}[family]
+    the expert count pick the kernel: under 48 routes the sweep kernel ("few" below), from there the
+    slab kernel with eight routes per group (many routes per expert) or four (few), and from 1024
+    routes with 24 per expert the tcgen05 kernel."""
+    copies = {"few": 1, "slab8": 1, "slab4": 32, "tcgen05": 1}[family]
     codes, scales = all_codes_experts(copies), None
     scales = scales_for(codes.shape[0], 1)
     want = expected(codes[:4], scales[:4], VALUE) if copies == 1 else None
     x = one_hot_rows()
-    if family == "team":
+    if family == "few":
         for e in range(4):
             for first in range(0, IN, 32):   # 32 routes per call
                 rhs = np.full(32, e, dtype=np.int32)
@@ -92,13 +91,14 @@ def test_single_projection_kernels_return_scale_times_weight_exactly(cuda, famil
         check_rows(got, want, rhs, np.tile(np.arange(IN), 4))
 
 
-@pytest.mark.parametrize("family,in_dim,routes", [("split", 2048, 6), ("split", 4096, 40), ("split-residual", 2048, 5), ("team", 8192, 6)])
+@pytest.mark.parametrize("family,in_dim,routes", [("sweep", 2048, 6), ("sweep", 4096, 40), ("sweep", 2304, 7), ("sweep", 8192, 6), ("split-residual", 2048, 5)])
 def test_few_route_kernels_over_wide_inputs_exactly(cuda, family, in_dim, routes):
-    """Calls with few routes.  Inputs up to 6144 wide run the split form of the slab kernel: several
-    warps share a row set, each over a part of the input dimension, and add their partial sums up in
-    shared memory (the 256-input cases above give every warp the whole row).  Wider inputs run the
-    team kernel.  A one-hot row at a random input picks one weight per output row, so whichever
-    warp owns that part of the row must deliver it, exactly."""
+    """Calls with few routes run the sweep kernel: the sixteen warps of a CTA split the input
+    dimension (evenly or not: 2304 inputs are nine chunks over eight warps), carry the partial sums
+    of several 16-row units and add them up in shared memory.  With a residual tier the split form
+    of the slab kernel does the same per item.  (The 256-input cases above give every warp the
+    whole row.)  A one-hot row at a random input picks one weight per output row, so whichever warp
+    owns that part of the row must deliver it, exactly."""
     from keep_b200 import vq
 
     experts, cw = 4, in_dim // 8
@@ -160,7 +160,7 @@ def test_residual_pass_returns_base_plus_residual_exactly(cuda, cols):
     check_rows(got, want, rhs, which)
 
 
-@pytest.mark.parametrize("family", ["team", "slab4", "slab8", "tcgen05"])
+@pytest.mark.parametrize("family", ["few", "slab4", "slab8", "tcgen05"])
 def test_gate_up_kernels_decode_both_matrices_exactly(cuda, family):
     """The M = 2 kernels fuse gate, up and SwiGLU, so G and U are not visible on their own.  With
     a one-hot activation of +-2^14 and a gate weight that is positive, G is at least 41 and
@@ -170,8 +170,8 @@ def test_gate_up_kernels_decode_both_matrices_exactly(cuda, family):
     the activation's sign chosen per output so that G stays positive."""
     from keep_b200 import _lib, moe, vq
 
-    tokens = {"team": 6, "slab4": 256, "slab8": 256, "tcgen05": 1024}[family]
-    experts = {"team": 4, "slab4": 128, "slab8": 4, "tcgen05": 4}[family]
+    tokens = {"few": 6, "slab4": 256, "slab8": 256, "tcgen05": 1024}[family]
+    experts = {"few": 4, "slab4": 128, "slab8": 4, "tcgen05": 4}[family]
     every = all_codes_experts(experts // 4)
     # a codeword whose eight weights are all positive (the first one there is)
     grid = e8.decode_e8p(np.arange(1 << 16, dtype=np.uint16))
@@ -201,8 +201,8 @@ def test_gate_up_kernels_decode_both_matrices_exactly(cuda, family):
         return (g16 * u16).to(torch.bfloat16).float().numpy()
 
     rng = np.random.default_rng(7)
-    for call in range(8 if family == "team" else 2):
-        which = rng.integers(0, IN, tokens) if family in ("team",) else np.arange(tokens) % IN
+    for call in range(8 if family == "few" else 2):
+        which = rng.integers(0, IN, tokens) if family in ("few",) else np.arange(tokens) % IN
         if family == "slab4":
             slots = (np.arange(tokens) % experts).astype(np.int32)
         elif family == "slab8" or family == "tcgen05":

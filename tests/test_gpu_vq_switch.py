@@ -145,7 +145,7 @@ def test_routes_without_an_expert_give_zero_rows_on_every_path(cuda):
     codes = rng.integers(0, 1 << 16, (experts, out, inp // 8), dtype=np.uint16)
     scales = (0.02 * rng.uniform(0.5, 1.5, (experts, out, 1))).astype(np.float16)
     table = vq.table_on(cuda, "e8p")
-    for routes in (6, 64):  # the team kernel and the slab kernel
+    for routes in (6, 64):  # the sweep kernel and the slab kernel
         rhs = rng.integers(0, experts, routes).astype(np.int64)
         rhs[1], rhs[routes - 2] = 0xFFFFFFFF, experts + 3
         x = torch.from_numpy(rng.normal(size=(routes, inp)).astype(np.float32)).to(cuda)
