@@ -2,8 +2,9 @@
 //
 // With six experts touched, a call is twelve matrices of codes and nothing else; what decides its
 // time is that every SM gets an equal share, that every warp has loads in flight, and that no
-// instruction is spent on anything but codewords.  So the work is cut into units of 16 output rows
-// of one route group (both matrices of a gate/up pair), the units are dealt to the CTAs as
+// instruction is spent on anything but codewords.  So the work is cut into units of two MMA row
+// tiles of one route group (16 rows of both matrices of a gate/up pair, or 32 rows of a single
+// matrix), the units are dealt to the CTAs as
 // contiguous runs of equal length, and inside a CTA the 16 warps split the INPUT dimension: warp
 // (row set, k part) walks down its row set's units and takes only its own chunk(s) of 32 codewords
 // per row from each.  Its slice of the group's quantised activations is 16 registers, kept across
@@ -66,12 +67,16 @@ __device__ __forceinline__ uint32_t sw_word(const uint4& v) {
 // table (the others spread the sign byte on the integer pipe); 0 = no second table, and the room
 // it would take goes to a deeper code ring (DEPTH stages of one chunk per warp).
 // `status` (may be null) is set to 2 if the shared window does not have the expected shape.
-template <int M, unsigned TABLE_STEPS, int DEPTH>
+// RAGGED: the output rows are not a multiple of a unit's rows, so the last unit of a group clamps its row indices.
+template <int M, unsigned TABLE_STEPS, int DEPTH, bool RAGGED>
 __global__ void __launch_bounds__(SW_THREADS, 1) projection_sweep_kernel(FastProjectionArgs p, int32_t* status) {
   extern __shared__ __align__(16) uint8_t smem[];
   grid_launch_dependents();
-  constexpr int STREAMS = 2 * M;                       // row g and row g + 8 of each matrix
-  constexpr int VALUES = 2 * M;                        // per lane and unit: (matrix, row g | g + 8) for the lane's route
+  // A unit is two MMA row tiles: the same 16 rows of the gate and of the up matrix (M = 2), or 32
+  // consecutive rows of the one matrix (M = 1).
+  constexpr int ROWS = M == 2 ? 16 : 32;               // output rows per unit
+  constexpr int STREAMS = 4;                           // row g and row g + 8 of each sub-tile
+  constexpr int VALUES = 4;                            // per lane and unit: (sub-tile, row g | g + 8) for the lane's route
   constexpr uint32_t STAGE_BYTES = STREAMS * 512;      // per warp: 16 bytes per lane and stream
   constexpr uint32_t RING_BYTES = DEPTH * STAGE_BYTES;
   constexpr uint32_t SECOND_BYTES = TABLE_STEPS ? SW_SIGN_BYTES : 0u;
@@ -117,7 +122,7 @@ __global__ void __launch_bounds__(SW_THREADS, 1) projection_sweep_kernel(FastPro
   const int row_set = warp / ks, k_part = warp - row_set * ks;
   const int c_first = k_part * n_chunks / ks, c_end = (k_part + 1) * n_chunks / ks;
   const int my_chunks = c_end - c_first;
-  const int units_per_group = static_cast<int>((N + 15) / 16);
+  const int units_per_group = static_cast<int>((N + ROWS - 1) / ROWS);
   const int64_t units = static_cast<int64_t>(p.groups_of_routes.count[0]) * units_per_group;
   const int grid = static_cast<int>(gridDim.x), cta = static_cast<int>(blockIdx.x);
   const int u_begin = static_cast<int>(units * cta / grid), u_end = static_cast<int>(units * (cta + 1) / grid);
@@ -126,20 +131,20 @@ __global__ void __launch_bounds__(SW_THREADS, 1) projection_sweep_kernel(FastPro
   // A warp's walk over its units (u_begin + row_set, + row_sets, ...), kept twice: once for the
   // code fetches, which run ahead, once for the arithmetic.
   const int last_row = static_cast<int>(N - 1);
-  const bool ragged = (N & 15) != 0;  // the last tile of a group has fewer than 16 rows: its row indices are clamped
   const uint64_t codes0 = reinterpret_cast<uint64_t>(mats[0].codes), row_bytes = static_cast<uint64_t>(cw) * 2u;
   const uint64_t matrix_delta = reinterpret_cast<uint64_t>(mats[1].codes) - codes0;  // wraps for a lower address: the sum is taken modulo 2^64 again
   const uint64_t lane_offset = static_cast<uint64_t>(g) * row_bytes + static_cast<uint64_t>(c_first * SW_CHUNK + t * 8) * 2u;
-  const uint64_t unit_stride = static_cast<uint64_t>(row_sets) * 16u * row_bytes;
+  const uint64_t unit_stride = static_cast<uint64_t>(row_sets) * ROWS * row_bytes;
+  const uint64_t sub_delta = M == 2 ? matrix_delta : 16u * row_bytes;  // from the first sub-tile's codes to the second's
   struct Walk {
-    int u, gi, tile;     // unit, its group and its 16-row tile
+    int u, gi, tile;     // unit, its group and its place among the group's units
     int c;               // next chunk of the unit
     int64_t slot_rows;   // slot * N
-    uint64_t codes;      // address of this lane's first codes of the unit: matrix 0, row tile * 16 + g, chunk c_first
+    uint64_t codes;      // address of this lane's first codes of the unit: matrix 0, row tile * ROWS + g, chunk c_first
   };
   auto enter_group = [&](Walk& w) {
     w.slot_rows = static_cast<int64_t>(p.groups_of_routes.slot[w.gi]) * N;
-    w.codes = codes0 + static_cast<uint64_t>(w.slot_rows + w.tile * 16) * row_bytes + lane_offset;
+    w.codes = codes0 + static_cast<uint64_t>(w.slot_rows + w.tile * ROWS) * row_bytes + lane_offset;
   };
   auto start_walk = [&](Walk& w) {
     w.u = u_begin + row_set;
@@ -166,16 +171,16 @@ __global__ void __launch_bounds__(SW_THREADS, 1) projection_sweep_kernel(FastPro
   auto fetch = [&]() {  // the next chunk of the walk `ahead` -> ring stage fetch_turn % DEPTH; always commits a group
     if (ahead.u < u_end && my_chunks > 0) {
       const uint32_t dst = ring + (fetch_turn % DEPTH) * STAGE_BYTES;
-      // stream 0 = row g of the first matrix; the others are fixed byte distances away
-      uint64_t first = ahead.codes + static_cast<uint32_t>(ahead.c - c_first) * (SW_CHUNK * 2u), hi_delta = 8u * row_bytes;
-      if (ragged) {
-        const int row_lo = min(ahead.tile * 16 + g, last_row), row_hi = min(ahead.tile * 16 + g + 8, last_row);
-        first = codes0 + static_cast<uint64_t>((ahead.slot_rows + row_lo) * cw + ahead.c * SW_CHUNK + t * 8) * 2u;
-        hi_delta = static_cast<uint64_t>(row_hi - row_lo) * row_bytes;
-      }
+      // stream 0 = row g of the first sub-tile; the others are fixed byte distances away
+      const uint64_t first = ahead.codes + static_cast<uint32_t>(ahead.c - c_first) * (SW_CHUNK * 2u);
       sw_static_for<STREAMS>([&](auto s) {
         constexpr int S = decltype(s)::value;
-        sw_cp_async16<S * 512>(dst, reinterpret_cast<const void*>(first + ((S & 1) ? hi_delta : 0u) + ((S >> 1) ? matrix_delta : 0u)));
+        uint64_t from = first + ((S & 1) ? 8u * row_bytes : 0u) + ((S >> 1) ? sub_delta : 0u);
+        if (RAGGED) {
+          const int row = min(ahead.tile * ROWS + (M == 1 ? 16 * (S >> 1) : 0) + g + 8 * (S & 1), last_row);
+          from = codes0 + ((M == 2 && (S >> 1)) ? matrix_delta : 0u) + static_cast<uint64_t>((ahead.slot_rows + row) * cw + ahead.c * SW_CHUNK + t * 8) * 2u;
+        }
+        sw_cp_async16<S * 512>(dst, reinterpret_cast<const void*>(from));
       });
       if (++ahead.c == c_end) next_unit(ahead);
     }
@@ -230,38 +235,38 @@ __global__ void __launch_bounds__(SW_THREADS, 1) projection_sweep_kernel(FastPro
         ++use_turn;
         uint4 cur[STREAMS];
         sw_static_for<STREAMS>([&](auto s) { cur[decltype(s)::value] = sw_lds128<decltype(s)::value * 512>(src); });
-        float sc[M][2];  // with one scale per row the epilogue applies it; otherwise asked for now, used behind the MMAs
+        float sc[2][2];  // with one scale per row the epilogue applies it; otherwise asked for now, used behind the MMAs
 #pragma unroll
-        for (int m = 0; m < M; ++m)
+        for (int sub = 0; sub < 2; ++sub)
 #pragma unroll
           for (int rr = 0; rr < 2; ++rr) {
-            sc[m][rr] = 1.0f;
+            sc[sub][rr] = 1.0f;
             if (p.groups > 1) {
-              const int64_t row = min(static_cast<int64_t>(at.tile) * 16 + g + 8 * rr, N - 1);
-              sc[m][rr] = load_as_float(mats[m].scales, p.scales_dtype, (at.slot_rows + row) * p.groups + c / chunks_per_group);
+              const int64_t row = min(static_cast<int64_t>(at.tile) * ROWS + (M == 1 ? 16 * sub : 0) + g + 8 * rr, N - 1);
+              sc[sub][rr] = load_as_float(mats[M == 2 ? sub : 0].scales, p.scales_dtype, (at.slot_rows + row) * p.groups + c / chunks_per_group);
             }
           }
-        int acc[2][M][4];  // two chains per matrix, used by alternate steps: the MMA's dependent latency is long
+        int acc[2][2][4];  // two chains per sub-tile, used by alternate steps: the MMA's dependent latency is long
         sw_static_for<8>([&](auto index) {
           constexpr int I = decltype(index)::value;
           constexpr bool TABLE = ((TABLE_STEPS >> I) & 1u) != 0;
 #pragma unroll
-          for (int m = 0; m < M; ++m) {
+          for (int sub = 0; sub < 2; ++sub) {
             uint32_t a[4];
-            decode_codeword<TABLE, (I & 1) != 0, false>(sw_word<I>(cur[2 * m]), abs_lane, second_lane, a[0], a[2]);      // row g
-            decode_codeword<TABLE, (I & 1) != 0, false>(sw_word<I>(cur[2 * m + 1]), abs_lane, second_lane, a[1], a[3]);  // row g + 8
-            if (I < 2) sw_mma_first(acc[I][m], a[0], a[1], a[2], a[3], b[I].x, b[I].y);
-            else sw_mma(acc[I & 1][m], a[0], a[1], a[2], a[3], b[I].x, b[I].y);
+            decode_codeword<TABLE, (I & 1) != 0, false>(sw_word<I>(cur[2 * sub]), abs_lane, second_lane, a[0], a[2]);      // row g
+            decode_codeword<TABLE, (I & 1) != 0, false>(sw_word<I>(cur[2 * sub + 1]), abs_lane, second_lane, a[1], a[3]);  // row g + 8
+            if (I < 2) sw_mma_first(acc[I][sub], a[0], a[1], a[2], a[3], b[I].x, b[I].y);
+            else sw_mma(acc[I & 1][sub], a[0], a[1], a[2], a[3], b[I].x, b[I].y);
           }
         });
         // columns 2t, 2t + 1 of the MMA are this lane's route: high plane, low plane
 #pragma unroll
-        for (int m = 0; m < M; ++m)
+        for (int sub = 0; sub < 2; ++sub)
 #pragma unroll
           for (int rr = 0; rr < 2; ++rr) {
             // 256 * high + low of one chunk fits 32 bits (256 products of at most 2^15 each, times 256)
-            const int dot = ((acc[0][m][2 * rr] + acc[1][m][2 * rr]) << 8) + acc[0][m][2 * rr + 1] + acc[1][m][2 * rr + 1];
-            part[2 * m + rr] = fmaf(sc[m][rr], static_cast<float>(dot), part[2 * m + rr]);
+            const int dot = ((acc[0][sub][2 * rr] + acc[1][sub][2 * rr]) << 8) + acc[0][sub][2 * rr + 1] + acc[1][sub][2 * rr + 1];
+            part[2 * sub + rr] = fmaf(sc[sub][rr], static_cast<float>(dot), part[2 * sub + rr]);
           }
       }
 #pragma unroll
@@ -278,7 +283,7 @@ __global__ void __launch_bounds__(SW_THREADS, 1) projection_sweep_kernel(FastPro
       const int gi = u / units_per_group, tile = u - gi * units_per_group;
       const int gsize = p.groups_of_routes.size[gi], gstart = p.groups_of_routes.start[gi];
       const int64_t slot_rows = static_cast<int64_t>(p.groups_of_routes.slot[gi]) * N;
-      if (t >= gsize) continue;  // lane (g, t) holds rows g and g + 8 of route t
+      if (t >= gsize) continue;  // lane (g, t) holds rows g and g + 8 of each sub-tile for route t
       const int route = p.groups_of_routes.routes[gstart + t];
       const int64_t xrow = route / p.x_div;
       const float xs = p.x.scale[xrow];
@@ -292,35 +297,37 @@ __global__ void __launch_bounds__(SW_THREADS, 1) projection_sweep_kernel(FastPro
           asm volatile("ld.shared.f32 %0, [%1];" : "=f"(got) : "r"(red_base + (((e * ks + k) * 4 + v) * 32 + lane) * 4u));
           sum[v] += got;
         }
+      // y of (sub-tile, row g | g + 8): scale and the +-1/4 of every weight, folded into sum(x') per scale group
+      auto finish = [&](int sub, float dot, int64_t row) {
+        const void* scales = mats[M == 2 ? sub : 0].scales;
+        float shift = 0.0f;
+        if (p.groups == 1) {
+          const float sc = load_as_float(scales, p.scales_dtype, slot_rows + row);
+          dot *= sc;
+          shift = sc * static_cast<float>(p.x.sums[xrow]);
+        } else {
+          for (int64_t q = 0; q < p.groups; ++q)
+            shift = fmaf(load_as_float(scales, p.scales_dtype, (slot_rows + row) * p.groups + q), static_cast<float>(p.x.sums[xrow * p.groups + q]), shift);
+        }
+        return xs * (0.5f * dot + 0.25f * shift);
+      };
 #pragma unroll
       for (int rr = 0; rr < 2; ++rr) {
-        const int64_t row = static_cast<int64_t>(tile) * 16 + g + 8 * rr;
-        if (row >= N) continue;
-        float y[M];
-#pragma unroll
-        for (int m = 0; m < M; ++m) {
-          float dot = sum[2 * m + rr], shift = 0.0f;  // shift: the +-1/4 of every weight, folded into sum(x') per scale group
-          if (p.groups == 1) {
-            const float sc = load_as_float(mats[m].scales, p.scales_dtype, slot_rows + row);
-            dot *= sc;
-            shift = sc * static_cast<float>(p.x.sums[xrow]);
-          } else {
-            for (int64_t q = 0; q < p.groups; ++q)
-              shift = fmaf(load_as_float(mats[m].scales, p.scales_dtype, (slot_rows + row) * p.groups + q), static_cast<float>(p.x.sums[xrow * p.groups + q]), shift);
-          }
-          y[m] = xs * (0.5f * dot + 0.25f * shift);
-        }
-        float result;
-        if (M == 2) {  // round G and U to the activation dtype first, as the separate kernels of the reference do
-          float gt = y[0], up = y[M - 1];
+        if (M == 2) {  // gate and up of one row: round G and U to the activation dtype first, as the separate kernels of the reference do
+          const int64_t row = static_cast<int64_t>(tile) * ROWS + g + 8 * rr;
+          if (row >= N) continue;
+          float gt = finish(0, sum[rr], row), up = finish(1, sum[2 + rr], row);
           if (p.out_dtype == KEEPVQ_BF16) { gt = __bfloat162float(__float2bfloat16_rn(gt)); up = __bfloat162float(__float2bfloat16_rn(up)); }
           else if (p.out_dtype == KEEPVQ_F16) { gt = __half2float(__float2half_rn(gt)); up = __half2float(__float2half_rn(up)); }
           if (p.swiglu_limit > 0.0f) { gt = fminf(gt, p.swiglu_limit); up = fminf(fmaxf(up, -p.swiglu_limit), p.swiglu_limit); }
-          result = gt / (1.0f + expf(-gt)) * up * p.route_weight[route];
+          store_from_float(p.out, p.out_dtype, static_cast<int64_t>(route) * N + row, gt / (1.0f + expf(-gt)) * up * p.route_weight[route]);
         } else {
-          result = y[0];
+#pragma unroll
+          for (int sub = 0; sub < 2; ++sub) {
+            const int64_t row = static_cast<int64_t>(tile) * ROWS + 16 * sub + g + 8 * rr;
+            if (row < N) store_from_float(p.out, p.out_dtype, static_cast<int64_t>(route) * N + row, finish(sub, sum[2 * sub + rr], row));
+          }
         }
-        store_from_float(p.out, p.out_dtype, static_cast<int64_t>(route) * N + row, result);
       }
     }
     __syncthreads();  // the partial sums are read; the next pass may overwrite them
@@ -332,9 +339,9 @@ __global__ void __launch_bounds__(SW_THREADS, 1) projection_sweep_kernel(FastPro
 
 bool sweep_supported(int64_t in_dim) { return in_dim % (8 * SW_CHUNK) == 0; }
 
-template <int M, unsigned TABLE_STEPS, int DEPTH>
-static int launch_sweep(const FastProjectionArgs& p, cudaStream_t s) {
-  auto kernel = projection_sweep_kernel<M, TABLE_STEPS, DEPTH>;
+template <int M, unsigned TABLE_STEPS, int DEPTH, bool RAGGED>
+static int launch_sweep_kernel(const FastProjectionArgs& p, cudaStream_t s) {
+  auto kernel = projection_sweep_kernel<M, TABLE_STEPS, DEPTH, RAGGED>;
   static uint64_t configured = 0;  // one bit per device: the shared-memory opt-in is a per-device attribute of the function
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
@@ -356,14 +363,22 @@ static int launch_sweep(const FastProjectionArgs& p, cudaStream_t s) {
   return KEEPVQ_OK;
 }
 
+template <int M, unsigned TABLE_STEPS, int DEPTH>
+static int launch_sweep(const FastProjectionArgs& p, cudaStream_t s) {
+  if (p.out_dim % (M == 2 ? 16 : 32) == 0) return launch_sweep_kernel<M, TABLE_STEPS, DEPTH, false>(p, s);
+  // a gate/up pair's outputs are the down projection's inputs, which come in multiples of 256
+  if (M == 2) return KEEPVQ_ERR_UNSUPPORTED;
+  return launch_sweep_kernel<1, TABLE_STEPS, DEPTH, true>(p, s);
+}
+
 #ifdef KEEPVQ_DIAG
 static int g_sweep_variant = 0;  // measurement build only: 0 = second table + ring of 2, 1 = no second table + ring of 3
 extern "C" void keepvq_diag_set_sweep(int variant) { g_sweep_variant = variant; }
 int sweep_gate_up(const FastProjectionArgs& p, cudaStream_t s) { return g_sweep_variant ? launch_sweep<2, 0u, 3>(p, s) : launch_sweep<2, 0xAAu, 2>(p, s); }
-int sweep_down(const FastProjectionArgs& p, cudaStream_t s) { return g_sweep_variant ? launch_sweep<1, 0u, 6>(p, s) : launch_sweep<1, 0xAAu, 4>(p, s); }
+int sweep_down(const FastProjectionArgs& p, cudaStream_t s) { return g_sweep_variant ? launch_sweep<1, 0u, 3>(p, s) : launch_sweep<1, 0xAAu, 2>(p, s); }
 #else
 int sweep_gate_up(const FastProjectionArgs& p, cudaStream_t s) { return launch_sweep<2, 0xAAu, 2>(p, s); }
-int sweep_down(const FastProjectionArgs& p, cudaStream_t s) { return launch_sweep<1, 0xAAu, 4>(p, s); }
+int sweep_down(const FastProjectionArgs& p, cudaStream_t s) { return launch_sweep<1, 0xAAu, 2>(p, s); }
 #endif
 
 }  // namespace fast

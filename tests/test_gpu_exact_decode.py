@@ -91,27 +91,30 @@ def test_single_projection_kernels_return_scale_times_weight_exactly(cuda, famil
         check_rows(got, want, rhs, np.tile(np.arange(IN), 4))
 
 
-@pytest.mark.parametrize("family,in_dim,routes", [("sweep", 2048, 6), ("sweep", 4096, 40), ("sweep", 2304, 7), ("sweep", 8192, 6), ("split-residual", 2048, 5)])
-def test_few_route_kernels_over_wide_inputs_exactly(cuda, family, in_dim, routes):
+@pytest.mark.parametrize("family,in_dim,routes,rows", [("sweep", 2048, 6, ROWS), ("sweep", 4096, 40, ROWS), ("sweep", 2304, 7, ROWS), ("sweep", 8192, 6, ROWS),
+                                                       ("sweep", 1024, 9, 200), ("split", 2048, 60, ROWS), ("split-residual", 2048, 5, ROWS)])
+def test_few_route_kernels_over_wide_inputs_exactly(cuda, family, in_dim, routes, rows):
     """Calls with few routes run the sweep kernel: the sixteen warps of a CTA split the input
     dimension (evenly or not: 2304 inputs are nine chunks over eight warps), carry the partial sums
     of several 16-row units and add them up in shared memory.  With a residual tier the split form
     of the slab kernel does the same per item.  (The 256-input cases above give every warp the
     whole row.)  A one-hot row at a random input picks one weight per output row, so whichever warp
-    owns that part of the row must deliver it, exactly."""
+    owns that part of the row must deliver it, exactly.  200 output rows leave the last unit of an
+    expert short (its row indices are clamped); 60 routes over 32 experts are few route groups of
+    a call too large for the sweep kernel: the split slab kernel without a residual."""
     from keep_b200 import vq
 
-    experts, cw = 4, in_dim // 8
+    experts, cw = (32 if family == "split" else 4), in_dim // 8  # 60 routes over 32 experts: groups of four, and few of them
     rng = np.random.default_rng(in_dim + routes)
-    codes = rng.integers(0, 1 << 16, (experts, ROWS, cw), dtype=np.uint16)
-    scales = scales_for(experts, 6)
-    dense = e8.decode_weight_matrix(codes.reshape(-1, cw), scales.reshape(-1, 1).astype(np.float32), code_bits=16).reshape(experts, ROWS, in_dim)
+    codes = rng.integers(0, 1 << 16, (experts, rows, cw), dtype=np.uint16)
+    scales = np.ascontiguousarray(scales_for(experts, 6)[:, :rows])
+    dense = e8.decode_weight_matrix(codes.reshape(-1, cw), scales.reshape(-1, 1).astype(np.float32), code_bits=16).reshape(experts, rows, in_dim)
     kw = {}
     if family == "split-residual":
-        res_codes = rng.integers(0, 256, (2, ROWS, cw), dtype=np.uint8)
-        res_scales = np.full((2, ROWS, 1), 2.0 ** -8, dtype=np.float16)
+        res_codes = rng.integers(0, 256, (2, rows, cw), dtype=np.uint8)
+        res_scales = np.full((2, rows, 1), 2.0 ** -8, dtype=np.float16)
         hot = np.array([1, e8.NO_RESIDUAL, e8.NO_RESIDUAL, 0], dtype=np.uint32)
-        res = e8.decode_weight_matrix(res_codes.reshape(-1, cw), res_scales.reshape(-1, 1).astype(np.float32), code_bits=8).reshape(2, ROWS, in_dim)
+        res = e8.decode_weight_matrix(res_codes.reshape(-1, cw), res_scales.reshape(-1, 1).astype(np.float32), code_bits=8).reshape(2, rows, in_dim)
         dense[0] += res[1]
         dense[3] += res[0]
         kw = dict(residual=(torch.from_numpy(res_codes).to(cuda), torch.from_numpy(res_scales).to(cuda), vq.table_on(cuda, "e8_1bit_half2")),
