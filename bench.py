@@ -137,15 +137,15 @@ def token_batches(device, batch, count=ROTATION):
 REPLAYS = 7
 
 
-def time_graph(fn, steps, warmup, replays=REPLAYS, every=False):
+def time_graph(fn, steps, warmup, replays=REPLAYS, every=False, warm_fn=None):
     """CUDA-event time of `steps` calls of fn(i) replayed from one CUDA graph, in ms: the median of
     `replays` timed replays (after one untimed replay).  With ``every`` the list of all replay
-    times is returned as well."""
+    times is returned as well.  ``warm_fn`` (default fn) runs the untimed eager warm-up calls."""
     stream = torch.cuda.Stream()
     stream.wait_stream(torch.cuda.current_stream())
     with torch.cuda.stream(stream):
         for i in range(max(warmup, 3)):
-            fn(i)
+            (warm_fn or fn)(i)
         torch.cuda.synchronize()
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph, stream=stream):
@@ -681,7 +681,7 @@ def run_expert_parallel(ns, rank, world, local, device):
         "nccl_layer_us": round(nccl_ms / layers * 1e3, 1) if nccl_ms else None,
         "strong_scaling_vs_n1": strong,
         "e2e": {"value": round(tokens / (e2e_ms * 1e-3), 1), "unit": UNIT, "h2d_bytes_per_step": EP_BATCH * HIDDEN * 2, "d2h_bytes_per_step": EP_BATCH * HIDDEN * 2},
-        "gpu_launches": (14 if ns.exchange == "peer" else 11) * layers * ns.steps * world, "kernel_path": stack[0].local.kernel_path, "clocks": clocks.summary(),
+        "gpu_launches": (10 if ns.exchange == "peer" else 11) * layers * ns.steps * world, "kernel_path": stack[0].local.kernel_path, "clocks": clocks.summary(),
     }
     print(json.dumps(line))
 
@@ -731,9 +731,46 @@ def run_ours(ns):
             out, _ = layer.decode(dev_in)
             host_out.copy_(out, non_blocking=True)
 
-        # the same capture-and-replay as the device-resident number: a serving loop replays one graph
-        # per step too, and the copies from and to pinned host memory are nodes of that graph
-        e2e_ms = time_graph(e2e_step, ns.steps, ns.warmup)
+        # The same capture-and-replay as the device-resident number: a serving loop replays one graph
+        # per step too, and the copies from and to pinned host memory are nodes of that graph.  The
+        # loop is double-buffered the way a server's is: while the layer works on step i, a copy
+        # stream brings in the tokens of step i + 1 and another takes the outputs of step i - 1 out.
+        # Every step's tokens still come from pinned host memory and every step's output still
+        # lands in host memory inside the timed region.
+        dev_ins = [torch.empty_like(dev_in) for _ in range(2)]
+        dev_outs = [torch.empty_like(dev_in) for _ in range(2)]
+        h2d, d2h = torch.cuda.Stream(), torch.cuda.Stream()
+        in_ready = [torch.cuda.Event() for _ in range(2)]
+        out_ready = [torch.cuda.Event() for _ in range(2)]
+        out_taken = [torch.cuda.Event() for _ in range(2)]
+
+        def e2e_pipelined(i):
+            main, k = torch.cuda.current_stream(), i % 2
+            if i == 0:  # the first step's tokens: nothing to hide them behind
+                h2d.wait_stream(main)
+                with torch.cuda.stream(h2d):
+                    dev_ins[0].copy_(host_in[0], non_blocking=True)
+                    in_ready[0].record(h2d)
+            main.wait_event(in_ready[k])
+            if i + 1 < ns.steps:  # next step's tokens, behind the previous layer call (the last reader of that buffer)
+                h2d.wait_stream(main)
+                with torch.cuda.stream(h2d):
+                    dev_ins[1 - k].copy_(host_in[(i + 1) % len(xs)], non_blocking=True)
+                    in_ready[1 - k].record(h2d)
+            if i >= 2:
+                main.wait_event(out_taken[k])  # the outputs of step i - 2 have left this buffer
+            layer.decode(dev_ins[k], out=dev_outs[k])
+            out_ready[k].record(main)
+            d2h.wait_event(out_ready[k])
+            with torch.cuda.stream(d2h):
+                host_out.copy_(dev_outs[k], non_blocking=True)
+                out_taken[k].record(d2h)
+            if i + 1 == ns.steps:  # join the copy streams
+                main.wait_stream(h2d)
+                main.wait_stream(d2h)
+
+        e2e_ms = time_graph(e2e_pipelined, ns.steps, ns.warmup, warm_fn=e2e_step)
+        e2e_serial_ms = time_graph(e2e_step, ns.steps, ns.warmup)
     if world > 1:
         import torch.distributed as dist
         t = torch.tensor([ms, e2e_ms], device=device)
@@ -766,7 +803,9 @@ def run_ours(ns):
         "roofline": roofline, "stage_us": stage_times(layer, xs, ns.steps),
         "cpu_baseline": {"value": round(1.0 / cpu_s, 4), "unit": UNIT, "cores": threads, "kind": "port",
                          "sample": "one token (after one warm-up token): router + decode of 6 experts x 3 projections + SwiGLU path", "parity_gap_vs_gpu": parity_gap},
-        "e2e": {"value": round(e2e_value, 1), "unit": UNIT, "h2d_bytes_per_step": batch * HIDDEN * 2, "d2h_bytes_per_step": batch * HIDDEN * 2},
+        "e2e": {"value": round(e2e_value, 1), "unit": UNIT, "h2d_bytes_per_step": batch * HIDDEN * 2, "d2h_bytes_per_step": batch * HIDDEN * 2,
+                "how": "double-buffered: the copies of steps i + 1 (in) and i - 1 (out) run on copy streams beside the layer call of step i",
+                "serial_value": round(tokens / (e2e_serial_ms * 1e-3), 1)},
         "batch_sweep": batch_sweep(layer, device, ns.rotation, ns.steps, hbm_gbs) if not ns.no_prefill else None,
         "residency": residency_leg(layer, device, ns.rotation, ns.steps, hbm_gbs) if not ns.no_prefill else None,
         "prefill": prefill_leg(layer, device) if not ns.no_prefill else None,
@@ -775,7 +814,7 @@ def run_ours(ns):
         "gpu_launches": layer.launches_per_call * ns.steps, "kernel_path": layer.kernel_path,
         "clocks": clocks.summary(),
     }
-    if not ns.no_prefill:  # config 5 on this one GPU: the base the N > 1 lines compare their layer time with
+    if not ns.no_prefill and not ns.no_ep_base:  # config 5 on this one GPU: the base the N > 1 lines compare their layer time with
         torch.cuda.empty_cache()
         line["ep_n1"] = ep_single_gpu_record(device, ns.layers, 4, hbm_gbs)
         try:
@@ -796,6 +835,7 @@ def main():
     ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"], help="expert-parallel run: how routes travel between the GPUs")
     ap.add_argument("--no-graph", action="store_true", help="expert-parallel run: time eager launches instead of a CUDA graph")
     ap.add_argument("--no-prefill", action="store_true", help="skip the 4096-token prefill leg (config 3) and the batch sweep")
+    ap.add_argument("--no-ep-base", action="store_true", help="skip the one-GPU run of the 40-layer expert-parallel stack (96.6 GB of codes; profiling runs skip it)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ns = ap.parse_args()
     if ns.impl == "reference":

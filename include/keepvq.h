@@ -510,6 +510,8 @@ typedef struct keepvq_ep_peer_args {
   int32_t* epoch;               /* [1] this rank's barrier count, zero at start */
   int32_t* status;              /* [1] */
   uint32_t wait_spins;          /* polls (about a microsecond each) before a barrier gives up; 0 = 8,388,608 */
+  int32_t* arrivals;            /* [1] this rank's count of finished blocks of the running exchange kernel, zero at start
+                                   (the last block to finish runs the barrier and clears it) */
 } keepvq_ep_peer_args;
 
 int keepvq_ep_dispatch_peer(const keepvq_ep_pack_args* pack, const keepvq_ep_peer_args* peer, void* stream);

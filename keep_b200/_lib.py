@@ -125,7 +125,7 @@ class EpPeerArgs(Structure):
     _fields_ = [
         ("world", c_int32), ("rank", c_int32), ("capacity", c_int64), ("row_bytes", c_int64),
         ("recv_x", c_void_p), ("recv_meta", c_void_p), ("back", c_void_p), ("flags", c_void_p), ("epoch", c_void_p), ("status", c_void_p),
-        ("wait_spins", ctypes.c_uint32),
+        ("wait_spins", ctypes.c_uint32), ("arrivals", c_void_p),
     ]
 
 

@@ -156,11 +156,12 @@ class PeerExchange:
         self._tables = tuple(table(h) for h in self._handles)
         self.epoch = torch.zeros(1, dtype=torch.int32, device=device)
         self.status = torch.zeros(1, dtype=torch.int32, device=device)
+        self._arrivals = torch.zeros(1, dtype=torch.int32, device=device)  # finished blocks of the running exchange kernel
         self.position = torch.empty((tokens, top_k), dtype=torch.int32, device=device)
         self._peer = _lib.EpPeerArgs(world=self.world, rank=self.rank, capacity=self.capacity, row_bytes=self.row_bytes,
                                      recv_x=_lib.ptr(self._tables[0]), recv_meta=_lib.ptr(self._tables[1]), back=_lib.ptr(self._tables[2]),
                                      flags=_lib.ptr(self._tables[3]), epoch=_lib.ptr(self.epoch), status=_lib.ptr(self.status),
-                                     wait_spins=int(wait_spins))
+                                     wait_spins=int(wait_spins), arrivals=_lib.ptr(self._arrivals))
         torch.cuda.synchronize(device)
         dist.barrier(self.group)  # every rank's buffers are zeroed and mapped before anyone writes
 

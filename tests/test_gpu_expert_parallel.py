@@ -129,8 +129,10 @@ def test_peer_barrier_gives_up_when_a_peer_never_arrives(cuda):
     tables = [table(ts) for ts in (recv_x, recv_meta, back, flags)]
     epoch, status = torch.zeros(1, dtype=torch.int32, device=cuda), torch.zeros(1, dtype=torch.int32, device=cuda)
     position = torch.empty((tokens, k), dtype=torch.int32, device=cuda)
+    arrivals = torch.zeros(1, dtype=torch.int32, device=cuda)
     peer = _lib.EpPeerArgs(world=world, rank=0, capacity=capacity, row_bytes=hidden * 2, recv_x=_lib.ptr(tables[0]), recv_meta=_lib.ptr(tables[1]),
-                           back=_lib.ptr(tables[2]), flags=_lib.ptr(tables[3]), epoch=_lib.ptr(epoch), status=_lib.ptr(status), wait_spins=2000)
+                           back=_lib.ptr(tables[2]), flags=_lib.ptr(tables[3]), epoch=_lib.ptr(epoch), status=_lib.ptr(status), wait_spins=2000,
+                           arrivals=_lib.ptr(arrivals))
     pack = _lib.EpPackArgs(x=_lib.ptr(x), row_bytes=hidden * 2, served_expert=_lib.ptr(experts), served_weight=_lib.ptr(weights), tokens=tokens,
                            top_k=k, world=world, experts_per_rank=per_rank, capacity=capacity, send_x=None, send_meta=None, position=_lib.ptr(position))
     _lib.check(_lib.load().keepvq_ep_dispatch_peer(pack, peer, _lib.stream_handle(cuda)), "keepvq_ep_dispatch_peer")
