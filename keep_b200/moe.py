@@ -152,14 +152,14 @@ class RoutedMoELayer:
     @property
     def kernel_path(self) -> str:
         """``"tensor"`` when calls run on the int8 tensor-core kernels, else ``"general"``.  With a
-        residual tier the tensor-core kernels need at least 48 routes in the call (the residual
-        pass lives in the kernel for larger batches); smaller calls of such a layer run the
-        general kernels."""
+        residual tier the inputs may be at most 6144 wide (the residual pass lives in the slab
+        kernels, whose split form for small calls keeps 48 KB of activations in shared memory);
+        wider layers with a residual tier run the general kernels."""
         ok = lambda inp, groups: inp % 256 == 0 and (inp // 256) % groups == 0  # noqa: E731
         fits = ok(self.hidden, int(self.w1.scales.shape[2])) and ok(self.inter, int(self.w2.scales.shape[2]))
         if self.res_rows:
             tiers = (self.w1, self.w3, self.w2)
-            fits = fits and all(p.res_codes is not None for p in tiers) and self.hidden <= 4096 and self.inter <= 4096 \
+            fits = fits and all(p.res_codes is not None for p in tiers) and self.hidden <= 6144 and self.inter <= 6144 \
                 and ok(self.hidden, int(self.w1.res_scales.shape[2])) and ok(self.inter, int(self.w2.res_scales.shape[2]))
         return "tensor" if self.codebook_all_odd and fits else "general"
 

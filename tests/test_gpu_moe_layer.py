@@ -88,7 +88,7 @@ def test_residency_mask_and_nested_residual(cuda):
     assert (routing.admit.cpu().numpy() >= 0).any(), "seed should produce at least one admission"
 
 
-@pytest.mark.parametrize("tokens", [20, 6])  # 60 routes: the tensor-core kernels with the residual pass; 18 routes: the general kernels
+@pytest.mark.parametrize("tokens", [20, 6])  # 60 routes and 18 routes: the slab kernel and its split form, both with the residual pass
 def test_nested_residual_at_tensor_core_shapes(cuda, tokens):
     """Half the pool resident, three hot slots with the 8-bit residual, shapes the int8 kernels take."""
     rng = np.random.default_rng(18)
@@ -128,7 +128,7 @@ def test_fewer_residents_than_top_k_leaves_dead_picks_at_zero(cuda):
     check_layer(cfg, x, out, routing, top_k=3, served_bias=served_bias, slot_of=np.arange(6))
 
 
-@pytest.mark.parametrize("tokens", [3, 30, 400])  # the small-batch kernel, the CTA kernel, the tcgen05 kernel
+@pytest.mark.parametrize("tokens", [3, 30, 400])  # the sweep kernel, the slab kernel, the tcgen05 kernel
 def test_dead_picks_at_tensor_core_shapes(cuda, tokens):
     """Two residents, top-3: every token has a pick without a slot, which must add nothing,
     whichever of the grouped kernels runs (they never touch the rows of such routes)."""
@@ -202,9 +202,9 @@ def test_many_routes_spread_over_many_experts_stay_on_the_decode_kernels(cuda):
 @pytest.mark.parametrize("tokens", [2, 10])
 def test_shipped_artifact_shape_with_grouped_scales(cuda, tokens):
     """The shape and scale groups of the reference's shipped artifacts: hidden 5120 in groups of
-    512, inter 2304 in groups of 256 (keep_quant.py:13-15).  Two tokens run the small-batch kernel;
-    ten tokens x top-6 run the CTA kernel, gate/up in its wide form (5120 inputs: the staged
-    activations take the sign table's shared memory)."""
+    512, inter 2304 in groups of 256 (keep_quant.py:13-15).  Two tokens run the sweep kernel (20
+    and 9 chunks of inputs over its 16 and 8 k parts, several scale groups per row); ten tokens x
+    top-6 run the split slab kernel with eight and two scale groups per row."""
     cfg = synthetic.layer(seed=31, experts=10, hidden=5120, inter=2304, group_hidden=512, group_inter=256)
     x = synthetic.tokens(32 + tokens, tokens, 5120)
     layer = build_layer(cuda, cfg, top_k=6)
