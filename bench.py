@@ -811,7 +811,7 @@ def run_ours(ns):
         "prefill": prefill_leg(layer, device) if not ns.no_prefill else None,
         "operators": operator_legs(layer, device, hbm_gbs) if not ns.no_prefill else None,
         "ep_n1": None,
-        "gpu_launches": layer.launches_per_call * ns.steps, "kernel_path": layer.kernel_path,
+        "gpu_launches": layer.launches_per_call(batch) * ns.steps, "kernel_path": layer.kernel_path,
         "clocks": clocks.summary(),
     }
     if not ns.no_prefill and not ns.no_ep_base:  # config 5 on this one GPU: the base the N > 1 lines compare their layer time with

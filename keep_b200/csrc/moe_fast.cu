@@ -16,6 +16,7 @@
 #include <algorithm>
 
 #include "moe_fast.cuh"
+#include "router_logits.cuh"
 
 namespace keepvq {
 namespace fast {
@@ -23,14 +24,13 @@ namespace fast {
 // ------------------------------------------------------------------------------------------
 // Activation quantisation: x -> 16-bit fixed point with a power-of-two scale per row.
 // ------------------------------------------------------------------------------------------
+// One row per block of 256 threads; row == rows is the extra all-zero row.
 template <typename XT>
-__global__ void __launch_bounds__(256) quantize_rows_kernel(const XT* __restrict__ x, int64_t rows, int64_t in_dim, int64_t groups, QuantRows out, int planes) {
-  grid_launch_dependents();
-  grid_wait();
+__device__ __forceinline__ void quantize_row(const XT* __restrict__ x, int64_t rows, int64_t in_dim, int64_t groups, const QuantRows& out, int planes, int64_t row) {
   __shared__ float warp_max[8];
   __shared__ float row_scale;
   extern __shared__ int32_t group_sum[];
-  const int64_t row = blockIdx.x, cw = in_dim / 8, per_group = cw / groups;
+  const int64_t cw = in_dim / 8, per_group = cw / groups;
   if (row == rows) {  // one extra all-zero row: the B operand of MMA columns that carry no route
     // (both layouts: the buffer is (rows + 1) * cw * 16 bytes either way)
     for (int64_t c = threadIdx.x; c < cw; c += 256) {
@@ -106,6 +106,48 @@ __global__ void __launch_bounds__(256) quantize_rows_kernel(const XT* __restrict
   }
   __syncthreads();
   for (int64_t g = threadIdx.x; g < groups; g += 256) out.sums[row * groups + g] = group_sum[g];
+}
+
+template <typename XT>
+__global__ void __launch_bounds__(256) quantize_rows_kernel(const XT* __restrict__ x, int64_t rows, int64_t in_dim, int64_t groups, QuantRows out, int planes) {
+  grid_launch_dependents();
+  grid_wait();
+  quantize_row<XT>(x, rows, in_dim, groups, out, planes, blockIdx.x);
+}
+
+// The front of a decode layer call in one launch: the router's logits (the few-token kernel's
+// blocks, router_logits.cuh) and the quantisation of the same token rows for the projections
+// (rows + 1 further blocks).  Neither needs the other's result, and at a handful of tokens a launch
+// costs more than either does.
+template <typename XT, typename WT>
+__global__ void __launch_bounds__(256) logits_and_quantize_kernel(keepvq_router_logits_args a, int logit_blocks_x, int logit_blocks, int64_t groups, QuantRows out) {
+  static_assert(RL_WARPS * 32 == 256, "both halves run on blocks of 256 threads");
+  grid_launch_dependents();
+  grid_wait();
+  const int b = static_cast<int>(blockIdx.x);
+  if (b < logit_blocks) router_logits_block<XT, WT>(a, b % logit_blocks_x, b / logit_blocks_x);
+  else quantize_row<XT>(reinterpret_cast<const XT*>(a.x), a.tokens, a.hidden, groups, out, 0, b - logit_blocks);
+}
+
+template <typename XT>
+static cudaError_t launch_front(const keepvq_router_logits_args& a, int bx, int blocks, int64_t groups, const QuantRows& out, size_t smem, cudaStream_t s) {
+  const unsigned grid = static_cast<unsigned>(blocks + a.tokens + 1);
+  if (a.router_dtype == KEEPVQ_F32) return launch_after(true, logits_and_quantize_kernel<XT, float>, grid, 256, smem, s, a, bx, blocks, groups, out);
+  if (a.router_dtype == KEEPVQ_F16) return launch_after(true, logits_and_quantize_kernel<XT, __half>, grid, 256, smem, s, a, bx, blocks, groups, out);
+  return launch_after(true, logits_and_quantize_kernel<XT, __nv_bfloat16>, grid, 256, smem, s, a, bx, blocks, groups, out);
+}
+
+bool logits_and_quantize_supported(const keepvq_router_logits_args& a, int64_t groups) {
+  return a.tokens > 0 && a.tokens <= FRONT_MAX_TOKENS && a.x_dtype != KEEPVQ_F32 && a.hidden % 8 == 0 && groups * sizeof(int32_t) <= 40 * 1024 &&
+         (a.pool + RL_ROWS - 1) / RL_ROWS * ((a.tokens + RL_TOKENS - 1) / RL_TOKENS) <= EARLY_LAUNCH_MAX_BLOCKS;
+}
+
+int logits_and_quantize(const keepvq_router_logits_args& a, int64_t groups, const QuantRows& out, cudaStream_t s) {
+  const int bx = static_cast<int>((a.pool + RL_ROWS - 1) / RL_ROWS), by = static_cast<int>((a.tokens + RL_TOKENS - 1) / RL_TOKENS);
+  const size_t smem = static_cast<size_t>(groups) * sizeof(int32_t);
+  const cudaError_t err = a.x_dtype == KEEPVQ_F16 ? launch_front<__half>(a, bx, bx * by, groups, out, smem, s) : launch_front<__nv_bfloat16>(a, bx, bx * by, groups, out, smem, s);
+  if (err != cudaSuccess) return note_cuda_error(err);
+  return KEEPVQ_OK;
 }
 
 int quantize_rows(const void* x, int32_t x_dtype, int64_t rows, int64_t in_dim, int64_t groups, const QuantRows& out, bool planes, cudaStream_t s) {

@@ -153,6 +153,11 @@ bool residual_supported(int64_t routes, int64_t in_dim, int64_t res_groups);
 // planes = true: all high bytes [rows + 1, in_dim] then all low bytes, what the tcgen05 kernels copy.
 int quantize_rows(const void* x, int32_t x_dtype, int64_t rows, int64_t in_dim, int64_t groups, const QuantRows& out, bool planes, cudaStream_t s);
 // `clear` (may be null): a status word the kernel zeroes for the projection kernels that follow it.
+// The router's logits and quantize_rows (planes = false) of the same token rows in one launch, for
+// calls of at most FRONT_MAX_TOKENS tokens with fp16 / bf16 activations.
+constexpr int64_t FRONT_MAX_TOKENS = 64;
+bool logits_and_quantize_supported(const keepvq_router_logits_args& logits, int64_t groups);
+int logits_and_quantize(const keepvq_router_logits_args& logits, int64_t groups, const QuantRows& out, cudaStream_t s);
 int group_routes(const uint32_t* served_slot, int64_t routes, int64_t slots, int max_group, const RouteGroups& out, int32_t* clear, cudaStream_t s);
 // Routes per group for a decode call: four while experts rarely get more (the kernels then run one
 // MMA per step for both byte planes), eight beyond.  `live` = routes expected to carry a slot.

@@ -196,13 +196,25 @@ extern "C" int keepvq_moe_decode_stages(const keepvq_moe_layer_args* args, int32
   const bool tensor_path = a.x_dtype != KEEPVQ_F32 && a.codebook_all_odd && residual_fits && fast::shapes_supported(a.inter, a.hidden, a.w1.groups) &&
                            fast::shapes_supported(a.hidden, a.inter, a.w2.groups);
   int rc = KEEPVQ_OK;
+  // many routes per expert: the tcgen05 kernels, which decode a code once per 96 routes
+  const int64_t live = a.expected_routes > 0 && a.expected_routes < routes ? a.expected_routes : routes;
+  const bool prefill = tensor_path && !residual && live >= PREFILL_MIN_ROUTES && live >= PREFILL_MIN_ROUTES_PER_SLOT * a.slots &&
+                       fast::prefill_supported(a.inter, a.hidden, a.w1.groups) && fast::prefill_supported(a.hidden, a.inter, a.w2.groups);
+  fast::QuantRows xq = {reinterpret_cast<uint8_t*>(ws + sc.xq), reinterpret_cast<float*>(ws + sc.xscale), reinterpret_cast<int32_t*>(ws + sc.xsums)};
+  bool x_quantized = false;  // the router's launch took the quantisation of the token rows along
 
   if (stages & KEEPVQ_STAGE_ROUTER) {
     keepvq_router_logits_args rl = {};
     rl.x = a.x; rl.x_dtype = a.x_dtype; rl.router_w = a.router_w; rl.router_dtype = a.router_dtype;
     rl.tokens = a.tokens; rl.pool = a.pool; rl.hidden = a.hidden; rl.gate_temp = a.gate_temp;
     rl.logits = reinterpret_cast<float*>(ws + sc.logits);
-    if ((rc = keepvq_router_logits(&rl, stream))) return rc;
+    // few tokens: the logits and the quantised token rows of the projections in one launch
+    const bool front = (stages & KEEPVQ_STAGE_PREPARE) && tensor_path && !prefill && valid_dtype(a.router_dtype) && a.router_w && a.gate_temp > 0.0f &&
+                       aligned_to(a.x, 16) && aligned_to(a.router_w, 16) && fast::logits_and_quantize_supported(rl, a.w1.groups);
+    if (front) {
+      if ((rc = fast::logits_and_quantize(rl, a.w1.groups, xq, s))) return rc;
+      x_quantized = true;
+    } else if ((rc = keepvq_router_logits(&rl, stream))) return rc;
     keepvq_routed_topk_args tk = {};
     tk.logits = rl.logits; tk.tokens = a.tokens; tk.pool = a.pool; tk.top_k = a.top_k; tk.score_func = a.score_func;
     tk.norm_topk_prob = a.norm_topk_prob; tk.route_scale = a.route_scale; tk.tau = a.tau;
@@ -216,17 +228,12 @@ extern "C" int keepvq_moe_decode_stages(const keepvq_moe_layer_args* args, int32
     fast::RouteGroups groups = {reinterpret_cast<int32_t*>(ws + sc.gcount), reinterpret_cast<int32_t*>(ws + sc.gslot),
                                 reinterpret_cast<int32_t*>(ws + sc.gstart), reinterpret_cast<int32_t*>(ws + sc.gsize),
                                 reinterpret_cast<int32_t*>(ws + sc.groutes)};
-    fast::QuantRows xq = {reinterpret_cast<uint8_t*>(ws + sc.xq), reinterpret_cast<float*>(ws + sc.xscale), reinterpret_cast<int32_t*>(ws + sc.xsums)};
     fast::QuantRows hq = {reinterpret_cast<uint8_t*>(ws + sc.hq), reinterpret_cast<float*>(ws + sc.hscale), reinterpret_cast<int32_t*>(ws + sc.hsums)};
-    // many routes per expert: the tcgen05 kernels, which decode a code once per 128 routes
-    const int64_t live = a.expected_routes > 0 && a.expected_routes < routes ? a.expected_routes : routes;
-    const bool prefill = !residual && live >= PREFILL_MIN_ROUTES && live >= PREFILL_MIN_ROUTES_PER_SLOT * a.slots && fast::prefill_supported(a.inter, a.hidden, a.w1.groups) &&
-                         fast::prefill_supported(a.hidden, a.inter, a.w2.groups);
     int32_t* wait_status = reinterpret_cast<int32_t*>(ws + sc.status);
     const int group_cols = prefill ? fast::PREFILL_GROUP_ROUTES : fast::decode_group_routes(live, a.slots, std::max(a.hidden, a.inter));
     if (stages & KEEPVQ_STAGE_PREPARE) {
       if ((rc = fast::group_routes(a.served_slot, routes, a.slots, group_cols, groups, wait_status, s))) return rc;
-      if ((rc = fast::quantize_rows(a.x, a.x_dtype, a.tokens, a.hidden, a.w1.groups, xq, prefill, s))) return rc;
+      if (!x_quantized && (rc = fast::quantize_rows(a.x, a.x_dtype, a.tokens, a.hidden, a.w1.groups, xq, prefill, s))) return rc;
     }
     fast::FastProjectionArgs p = {};
     p.scales_dtype = a.scales_dtype; p.codebook = a.codebook; p.groups_of_routes = groups; p.max_routes = routes; p.group_cols = group_cols; p.status = wait_status;
