@@ -353,7 +353,7 @@ def operator_legs(layer, device, hbm_gbs, steps=32):
     cpu_s = time.perf_counter() - begin
     out["vq_qmv_2048x4096"] = {"us_per_call": round(us, 2), "code_gbs": round(CODE_BYTES_PER_PROJECTION / (us * 1e-6) / 1e9, 1),
                                "code_frac_of_hbm": round(CODE_BYTES_PER_PROJECTION / (us * 1e-6) / 1e9 / hbm_gbs, 4),
-                               "cpu_us_per_call": round(cpu_s * 1e6, 1), "kernel": "routed_rowdot_kernel (general kernel: one route, 24/16-bit fixed point, dp4a)"}
+                               "cpu_us_per_call": round(cpu_s * 1e6, 1), "kernel": "keepvq_grouped_projection: group_routes, quantize_rows, projection_sweep_kernel (three launches per call)"}
     for tokens in (1, 4, 16):
         xs, picks, uniq = [], [], []
         for j in range(8):

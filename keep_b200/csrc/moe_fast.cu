@@ -108,11 +108,22 @@ __device__ __forceinline__ void quantize_row(const XT* __restrict__ x, int64_t r
   for (int64_t g = threadIdx.x; g < groups; g += 256) out.sums[row * groups + g] = group_sum[g];
 }
 
+// `live` (may be null): the slots of the routes that read the rows, `per_row` of them per row; a row
+// none of whose routes has a slot below `slots` is skipped (no kernel reads it: projections only
+// follow live routes).  An expert-parallel rank quantises 8 x capacity rows of which an eighth is live.
+struct LiveRows { const uint32_t* slot; int32_t per_row; int64_t slots; };
+
 template <typename XT>
-__global__ void __launch_bounds__(256) quantize_rows_kernel(const XT* __restrict__ x, int64_t rows, int64_t in_dim, int64_t groups, QuantRows out, int planes) {
+__global__ void __launch_bounds__(256) quantize_rows_kernel(const XT* __restrict__ x, int64_t rows, int64_t in_dim, int64_t groups, QuantRows out, int planes, LiveRows live) {
   grid_launch_dependents();
   grid_wait();
-  quantize_row<XT>(x, rows, in_dim, groups, out, planes, blockIdx.x);
+  const int64_t row = blockIdx.x;
+  if (live.slot && row < rows) {
+    bool any = false;
+    for (int j = 0; j < live.per_row; ++j) any = any || live.slot[row * live.per_row + j] < static_cast<uint64_t>(live.slots);
+    if (!any) return;  // uniform over the block
+  }
+  quantize_row<XT>(x, rows, in_dim, groups, out, planes, row);
 }
 
 // The front of a decode layer call in one launch: the router's logits (the few-token kernel's
@@ -150,15 +161,17 @@ int logits_and_quantize(const keepvq_router_logits_args& a, int64_t groups, cons
   return KEEPVQ_OK;
 }
 
-int quantize_rows(const void* x, int32_t x_dtype, int64_t rows, int64_t in_dim, int64_t groups, const QuantRows& out, bool planes, cudaStream_t s) {
+int quantize_rows(const void* x, int32_t x_dtype, int64_t rows, int64_t in_dim, int64_t groups, const QuantRows& out, bool planes, cudaStream_t s,
+                  const uint32_t* live_slot, int32_t per_row, int64_t slots) {
+  const LiveRows live = {live_slot, per_row, slots};
   const size_t smem = static_cast<size_t>(groups) * sizeof(int32_t);
   if (smem > 40 * 1024) return KEEPVQ_ERR_CAPACITY;
   const unsigned grid = static_cast<unsigned>(rows + 1);  // + the zero row
   const bool early = rows < EARLY_LAUNCH_MAX_BLOCKS;
   cudaError_t err;
-  if (x_dtype == KEEPVQ_F32) err = launch_after(early, quantize_rows_kernel<float>, grid, 256, smem, s, reinterpret_cast<const float*>(x), rows, in_dim, groups, out, planes ? 1 : 0);
-  else if (x_dtype == KEEPVQ_F16) err = launch_after(early, quantize_rows_kernel<__half>, grid, 256, smem, s, reinterpret_cast<const __half*>(x), rows, in_dim, groups, out, planes ? 1 : 0);
-  else err = launch_after(early, quantize_rows_kernel<__nv_bfloat16>, grid, 256, smem, s, reinterpret_cast<const __nv_bfloat16*>(x), rows, in_dim, groups, out, planes ? 1 : 0);
+  if (x_dtype == KEEPVQ_F32) err = launch_after(early, quantize_rows_kernel<float>, grid, 256, smem, s, reinterpret_cast<const float*>(x), rows, in_dim, groups, out, planes ? 1 : 0, live);
+  else if (x_dtype == KEEPVQ_F16) err = launch_after(early, quantize_rows_kernel<__half>, grid, 256, smem, s, reinterpret_cast<const __half*>(x), rows, in_dim, groups, out, planes ? 1 : 0, live);
+  else err = launch_after(early, quantize_rows_kernel<__nv_bfloat16>, grid, 256, smem, s, reinterpret_cast<const __nv_bfloat16*>(x), rows, in_dim, groups, out, planes ? 1 : 0, live);
   if (err != cudaSuccess) return note_cuda_error(err);
   return KEEPVQ_OK;
 }

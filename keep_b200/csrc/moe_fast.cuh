@@ -151,7 +151,9 @@ bool residual_supported(int64_t routes, int64_t in_dim, int64_t res_groups);
 
 // planes = false: 16 bytes per codeword (hi 8, lo 8), what the mma.sync kernels read;
 // planes = true: all high bytes [rows + 1, in_dim] then all low bytes, what the tcgen05 kernels copy.
-int quantize_rows(const void* x, int32_t x_dtype, int64_t rows, int64_t in_dim, int64_t groups, const QuantRows& out, bool planes, cudaStream_t s);
+// live_slot (may be null): [rows, per_row] slots of the routes that read the rows; rows whose routes are all dead (slot >= slots) are skipped.
+int quantize_rows(const void* x, int32_t x_dtype, int64_t rows, int64_t in_dim, int64_t groups, const QuantRows& out, bool planes, cudaStream_t s,
+                  const uint32_t* live_slot = nullptr, int32_t per_row = 1, int64_t slots = 0);
 // `clear` (may be null): a status word the kernel zeroes for the projection kernels that follow it.
 // The router's logits and quantize_rows (planes = false) of the same token rows in one launch, for
 // calls of at most FRONT_MAX_TOKENS tokens with fp16 / bf16 activations.

@@ -233,7 +233,7 @@ extern "C" int keepvq_moe_decode_stages(const keepvq_moe_layer_args* args, int32
     const int group_cols = prefill ? fast::PREFILL_GROUP_ROUTES : fast::decode_group_routes(live, a.slots, std::max(a.hidden, a.inter));
     if (stages & KEEPVQ_STAGE_PREPARE) {
       if ((rc = fast::group_routes(a.served_slot, routes, a.slots, group_cols, groups, wait_status, s))) return rc;
-      if (!x_quantized && (rc = fast::quantize_rows(a.x, a.x_dtype, a.tokens, a.hidden, a.w1.groups, xq, prefill, s))) return rc;
+      if (!x_quantized && (rc = fast::quantize_rows(a.x, a.x_dtype, a.tokens, a.hidden, a.w1.groups, xq, prefill, s, a.served_slot, a.top_k, a.slots))) return rc;
     }
     fast::FastProjectionArgs p = {};
     p.scales_dtype = a.scales_dtype; p.codebook = a.codebook; p.groups_of_routes = groups; p.max_routes = routes; p.group_cols = group_cols; p.status = wait_status;
@@ -246,7 +246,7 @@ extern "C" int keepvq_moe_decode_stages(const keepvq_moe_layer_args* args, int32
       if ((rc = prefill ? fast::prefill_gate_up(p, wait_status, s) : fast::gate_up(p, s))) return rc;
     }
     if (stages & KEEPVQ_STAGE_DOWN) {
-      if ((rc = fast::quantize_rows(ws + sc.h, a.x_dtype, routes, a.inter, a.w2.groups, hq, prefill, s))) return rc;
+      if ((rc = fast::quantize_rows(ws + sc.h, a.x_dtype, routes, a.inter, a.w2.groups, hq, prefill, s, a.served_slot, 1, a.slots))) return rc;
       p.a = {a.w2.codes, a.w2.scales, a.w2.res_codes, a.w2.res_scales}; p.b = {nullptr, nullptr, nullptr, nullptr};
       if (residual) { p.res_groups = a.w2.res_groups; p.hot_of_slot = a.hot_of_slot; p.res_table = a.res_table; }
       p.out_dim = a.hidden; p.in_dim = a.inter; p.groups = a.w2.groups; p.x = hq; p.x_zero_row = routes; p.x_div = 1; p.out = ws + sc.down;
