@@ -157,7 +157,7 @@ int quantize_rows(const void* x, int32_t x_dtype, int64_t rows, int64_t in_dim, 
 // `clear` (may be null): a status word the kernel zeroes for the projection kernels that follow it.
 // The router's logits and quantize_rows (planes = false) of the same token rows in one launch, for
 // calls of at most FRONT_MAX_TOKENS tokens with fp16 / bf16 activations.
-constexpr int64_t FRONT_MAX_TOKENS = 64;
+constexpr int64_t FRONT_MAX_TOKENS = 23;  // from 24 tokens on the logits have a faster kernel of their own (router.cu)
 bool logits_and_quantize_supported(const keepvq_router_logits_args& logits, int64_t groups);
 int logits_and_quantize(const keepvq_router_logits_args& logits, int64_t groups, const QuantRows& out, cudaStream_t s);
 int group_routes(const uint32_t* served_slot, int64_t routes, int64_t slots, int max_group, const RouteGroups& out, int32_t* clear, cudaStream_t s);

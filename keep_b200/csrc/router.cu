@@ -176,6 +176,116 @@ __global__ void __launch_bounds__(RM_THREADS) router_logits_mma_kernel(keepvq_ro
       }
 }
 
+// 16 to 255 bf16 tokens against a bf16 router: the same 64 x 64 tile and the same arithmetic, with the
+// hidden dimension split over a cluster of eight blocks so that a call of 64 tokens is 48 blocks
+// instead of 6.  Each block sums its eighth of K as above; the eight partial tiles meet through
+// distributed shared memory, every block adding up eight rows of the tile over the ranks in rank
+// order, so a logit is a fixed sequence of additions whatever the batch around it.
+constexpr int RC_SPLIT = 8;
+constexpr int RC_MIN_TOKENS = 24;  // below this the K-split kernel of the fp32 pipes is as fast, and shares its launch with the quantisation of the rows
+
+__global__ void __cluster_dims__(RC_SPLIT, 1, 1) __launch_bounds__(RM_THREADS) router_logits_cluster_kernel(keepvq_router_logits_args a) {
+  grid_launch_dependents();
+  grid_wait();
+  __shared__ __align__(16) __nv_bfloat16 xs[RM_STAGES][RM_TILE][RM_LD], ws[RM_STAGES][RM_TILE][RM_LD];
+  __shared__ __align__(16) float red[RM_TILE][RM_TILE];  // this block's partial tile [token][expert]
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
+  const int wm = (warp & 1) * 32, wn = (warp >> 1) * 32;
+  const int rank = static_cast<int>(blockIdx.x);  // the cluster spans x: the block's share of K
+  const int64_t t0 = static_cast<int64_t>(blockIdx.z) * RM_TILE, e0 = static_cast<int64_t>(blockIdx.y) * RM_TILE;
+  const int64_t k_share = a.hidden / RC_SPLIT, k_first = rank * k_share;
+  const __nv_bfloat16* x = reinterpret_cast<const __nv_bfloat16*>(a.x) + k_first;
+  const __nv_bfloat16* w = reinterpret_cast<const __nv_bfloat16*>(a.router_w) + k_first;
+  const int row_a = tid >> 2, piece = tid & 3, row_b = row_a + 32;
+  const __nv_bfloat16* xsrc[2] = {x + min(t0 + row_a, a.tokens - 1) * a.hidden + piece * 8, x + min(t0 + row_b, a.tokens - 1) * a.hidden + piece * 8};
+  const __nv_bfloat16* wsrc[2] = {w + min(e0 + row_a, a.pool - 1) * a.hidden + piece * 8, w + min(e0 + row_b, a.pool - 1) * a.hidden + piece * 8};
+  const int k_blocks = static_cast<int>(k_share / RM_K);
+  auto stage_in = [&](int kb) {
+    const int st = kb % RM_STAGES;
+    if (kb < k_blocks) {
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int row = h ? row_b : row_a;
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(&xs[st][row][piece * 8]))), "l"(xsrc[h] + kb * RM_K) : "memory");
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(&ws[st][row][piece * 8]))), "l"(wsrc[h] + kb * RM_K) : "memory");
+      }
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  float acc[2][4][4];
+#pragma unroll
+  for (int i = 0; i < 2; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+#pragma unroll
+      for (int r = 0; r < 4; ++r) acc[i][j][r] = 0.0f;
+  stage_in(0);
+  stage_in(1);
+  for (int kb = 0; kb < k_blocks; ++kb) {
+    asm volatile("cp.async.wait_group 1;" ::: "memory");
+    __syncthreads();
+    stage_in(kb + 2);
+    const int st = kb % RM_STAGES;
+#pragma unroll
+    for (int ks = 0; ks < RM_K; ks += 16) {
+      uint32_t af[2][4], bf[4][2];
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        const int r = wm + 16 * i + g;
+        af[i][0] = *reinterpret_cast<const uint32_t*>(&xs[st][r][ks + 2 * t]);
+        af[i][1] = *reinterpret_cast<const uint32_t*>(&xs[st][r + 8][ks + 2 * t]);
+        af[i][2] = *reinterpret_cast<const uint32_t*>(&xs[st][r][ks + 2 * t + 8]);
+        af[i][3] = *reinterpret_cast<const uint32_t*>(&xs[st][r + 8][ks + 2 * t + 8]);
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int n = wn + 8 * j + g;
+        bf[j][0] = *reinterpret_cast<const uint32_t*>(&ws[st][n][ks + 2 * t]);
+        bf[j][1] = *reinterpret_cast<const uint32_t*>(&ws[st][n][ks + 2 * t + 8]);
+      }
+#pragma unroll
+      for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {  // sixteen exact products summed from zero per instruction; running sums in plain fp32 (see the kernel above)
+          float d0, d1, d2, d3;
+          asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+                       : "=f"(d0), "=f"(d1), "=f"(d2), "=f"(d3)
+                       : "r"(af[i][0]), "r"(af[i][1]), "r"(af[i][2]), "r"(af[i][3]), "r"(bf[j][0]), "r"(bf[j][1]), "f"(0.0f));
+          acc[i][j][0] += d0; acc[i][j][1] += d1; acc[i][j][2] += d2; acc[i][j][3] += d3;
+        }
+    }
+  }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 2; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+#pragma unroll
+      for (int r = 0; r < 4; ++r) red[wm + 16 * i + g + (r >= 2 ? 8 : 0)][wn + 8 * j + 2 * t + (r & 1)] = acc[i][j][r];
+  // every partial tile is in place (release / acquire at cluster scope)
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+  // this block adds up tokens 8 * rank .. 8 * rank + 7 of the tile over the ranks in order: 512 logits, four per thread
+  const uint32_t red_local = static_cast<uint32_t>(__cvta_generic_to_shared(&red[0][0]));
+#pragma unroll
+  for (int v = 0; v < 4; ++v) {
+    const int idx = tid + v * RM_THREADS;               // 0..511
+    const int row = rank * (RM_TILE / RC_SPLIT) + idx / RM_TILE, col = idx % RM_TILE;
+    float sum = 0.0f;
+#pragma unroll
+    for (int q = 0; q < RC_SPLIT; ++q) {
+      uint32_t remote;
+      float part;
+      asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(red_local + static_cast<uint32_t>((row * RM_TILE + col) * 4)), "r"(q));
+      asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(part) : "r"(remote) : "memory");
+      sum += part;
+    }
+    const int64_t tok = t0 + row, e = e0 + col;
+    if (tok < a.tokens && e < a.pool) a.logits[tok * a.pool + e] = sum / a.gate_temp;
+  }
+  // nobody leaves while a peer may still be reading its tile
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
 // (value, index) max with ties to the lower index, across a warp.
 __device__ __forceinline__ void warp_argmax(float& v, int& i) {
 #pragma unroll
@@ -423,6 +533,14 @@ extern "C" int keepvq_router_logits(const keepvq_router_logits_args* args, void*
     else if (a.x_dtype == KEEPVQ_F16) launch_logits_tiled<__half>(a, grid, s);
     else launch_logits_tiled<__nv_bfloat16>(a, grid, s);
     KEEPVQ_CHECK_LAUNCH();
+    return KEEPVQ_OK;
+  }
+  if (a.tokens >= RC_MIN_TOKENS && a.x_dtype == KEEPVQ_BF16 && a.router_dtype == KEEPVQ_BF16 && a.hidden % (RC_SPLIT * RM_K) == 0) {
+    // a few dozen tokens: the tensor-core tile with the hidden dimension split over a cluster of eight blocks
+    dim3 grid(RC_SPLIT, static_cast<unsigned>((a.pool + RM_TILE - 1) / RM_TILE), static_cast<unsigned>((a.tokens + RM_TILE - 1) / RM_TILE));
+    if (grid.y > 65535) return KEEPVQ_ERR_CAPACITY;
+    cudaError_t err = launch_after(true, router_logits_cluster_kernel, grid, RM_THREADS, 0, s, a);
+    if (err != cudaSuccess) return note_cuda_error(err);
     return KEEPVQ_OK;
   }
   const int64_t token_tiles = (a.tokens + RL_TOKENS - 1) / RL_TOKENS;
