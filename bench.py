@@ -681,7 +681,7 @@ def run_expert_parallel(ns, rank, world, local, device):
         "nccl_layer_us": round(nccl_ms / layers * 1e3, 1) if nccl_ms else None,
         "strong_scaling_vs_n1": strong,
         "e2e": {"value": round(tokens / (e2e_ms * 1e-3), 1), "unit": UNIT, "h2d_bytes_per_step": EP_BATCH * HIDDEN * 2, "d2h_bytes_per_step": EP_BATCH * HIDDEN * 2},
-        "gpu_launches": (10 if ns.exchange == "peer" else 11) * layers * ns.steps * world, "kernel_path": stack[0].local.kernel_path, "clocks": clocks.summary(),
+        "gpu_launches": (9 if ns.exchange == "peer" else 10) * layers * ns.steps * world, "kernel_path": stack[0].local.kernel_path, "clocks": clocks.summary(),
     }
     print(json.dumps(line))
 

@@ -113,11 +113,20 @@ __device__ __forceinline__ void quantize_row(const XT* __restrict__ x, int64_t r
 // follow live routes).  An expert-parallel rank quantises 8 x capacity rows of which an eighth is live.
 struct LiveRows { const uint32_t* slot; int32_t per_row; int64_t slots; };
 
+// One more block (the last) may group the routes of the call, which needs nothing of the rows:
+// one launch less in front of the projections.
+struct GroupJob { const uint32_t* served_slot; int32_t routes, slots, max_group; RouteGroups out; int32_t* clear; };
+
 template <typename XT>
-__global__ void __launch_bounds__(256) quantize_rows_kernel(const XT* __restrict__ x, int64_t rows, int64_t in_dim, int64_t groups, QuantRows out, int planes, LiveRows live) {
+__global__ void __launch_bounds__(256) quantize_rows_kernel(const XT* __restrict__ x, int64_t rows, int64_t in_dim, int64_t groups, QuantRows out, int planes, LiveRows live, GroupJob job) {
   grid_launch_dependents();
   grid_wait();
   const int64_t row = blockIdx.x;
+  if (row > rows) {  // only launched when there is a job
+    extern __shared__ int32_t group_scratch[];
+    group_routes_block<256>(job.served_slot, job.routes, job.slots, job.max_group, job.out, job.clear, group_scratch);
+    return;
+  }
   if (live.slot && row < rows) {
     bool any = false;
     for (int j = 0; j < live.per_row; ++j) any = any || live.slot[row * live.per_row + j] < static_cast<uint64_t>(live.slots);
@@ -163,15 +172,28 @@ int logits_and_quantize(const keepvq_router_logits_args& a, int64_t groups, cons
 
 int quantize_rows(const void* x, int32_t x_dtype, int64_t rows, int64_t in_dim, int64_t groups, const QuantRows& out, bool planes, cudaStream_t s,
                   const uint32_t* live_slot, int32_t per_row, int64_t slots) {
+  return quantize_rows_and_group(x, x_dtype, rows, in_dim, groups, out, planes, s, live_slot, per_row, slots, nullptr, 0, 0, RouteGroups{}, nullptr);
+}
+
+bool group_with_quantize_supported(int64_t routes, int64_t slots) { return routes <= 4096 && slots * 3 * sizeof(int32_t) <= 40 * 1024; }
+
+int quantize_rows_and_group(const void* x, int32_t x_dtype, int64_t rows, int64_t in_dim, int64_t groups, const QuantRows& out, bool planes, cudaStream_t s,
+                            const uint32_t* live_slot, int32_t per_row, int64_t slots,
+                            const uint32_t* served_slot, int64_t routes, int max_group, const RouteGroups& route_groups, int32_t* clear) {
   const LiveRows live = {live_slot, per_row, slots};
-  const size_t smem = static_cast<size_t>(groups) * sizeof(int32_t);
+  const GroupJob job = {served_slot, static_cast<int32_t>(routes), static_cast<int32_t>(slots), max_group, route_groups, clear};
+  size_t smem = static_cast<size_t>(groups) * sizeof(int32_t);
   if (smem > 40 * 1024) return KEEPVQ_ERR_CAPACITY;
-  const unsigned grid = static_cast<unsigned>(rows + 1);  // + the zero row
+  if (served_slot) {
+    if (!group_with_quantize_supported(routes, slots)) return KEEPVQ_ERR_UNSUPPORTED;
+    smem = std::max(smem, static_cast<size_t>(slots) * 3 * sizeof(int32_t));
+  }
+  const unsigned grid = static_cast<unsigned>(rows + 1 + (served_slot ? 1 : 0));  // + the zero row (+ the grouping block)
   const bool early = rows < EARLY_LAUNCH_MAX_BLOCKS;
   cudaError_t err;
-  if (x_dtype == KEEPVQ_F32) err = launch_after(early, quantize_rows_kernel<float>, grid, 256, smem, s, reinterpret_cast<const float*>(x), rows, in_dim, groups, out, planes ? 1 : 0, live);
-  else if (x_dtype == KEEPVQ_F16) err = launch_after(early, quantize_rows_kernel<__half>, grid, 256, smem, s, reinterpret_cast<const __half*>(x), rows, in_dim, groups, out, planes ? 1 : 0, live);
-  else err = launch_after(early, quantize_rows_kernel<__nv_bfloat16>, grid, 256, smem, s, reinterpret_cast<const __nv_bfloat16*>(x), rows, in_dim, groups, out, planes ? 1 : 0, live);
+  if (x_dtype == KEEPVQ_F32) err = launch_after(early, quantize_rows_kernel<float>, grid, 256, smem, s, reinterpret_cast<const float*>(x), rows, in_dim, groups, out, planes ? 1 : 0, live, job);
+  else if (x_dtype == KEEPVQ_F16) err = launch_after(early, quantize_rows_kernel<__half>, grid, 256, smem, s, reinterpret_cast<const __half*>(x), rows, in_dim, groups, out, planes ? 1 : 0, live, job);
+  else err = launch_after(early, quantize_rows_kernel<__nv_bfloat16>, grid, 256, smem, s, reinterpret_cast<const __nv_bfloat16*>(x), rows, in_dim, groups, out, planes ? 1 : 0, live, job);
   if (err != cudaSuccess) return note_cuda_error(err);
   return KEEPVQ_OK;
 }
@@ -185,62 +207,8 @@ constexpr int GR_THREADS = 1024;
 __global__ void __launch_bounds__(GR_THREADS) group_routes_kernel(const uint32_t* __restrict__ served_slot, int routes, int slots, int max_group, RouteGroups out, int32_t* clear) {
   grid_launch_dependents();
   grid_wait();
-  if (clear && threadIdx.x == 0) *clear = 0;
-  extern __shared__ int32_t sm[];
-  int32_t* count = sm;               // [slots] routes per slot, then running cursor
-  int32_t* first = sm + slots;       // [slots] first position of the slot in `routes`
-  int32_t* gfirst = sm + 2 * slots;  // [slots] first group index of the slot
-  __shared__ int32_t warp_a[32], warp_b[32];
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  for (int s = tid; s < slots; s += GR_THREADS) count[s] = 0;
-  __syncthreads();
-  for (int r = tid; r < routes; r += GR_THREADS) {
-    const uint32_t s = served_slot[r];
-    if (s < static_cast<uint32_t>(slots)) atomicAdd(&count[s], 1);
-  }
-  __syncthreads();
-  // exclusive scans of (routes, groups) per slot: each thread owns a contiguous run of slots
-  const int per = (slots + GR_THREADS - 1) / GR_THREADS;
-  const int lo = min(tid * per, slots), hi = min(lo + per, slots);
-  int a = 0, b = 0;
-  for (int s = lo; s < hi; ++s) { a += count[s]; b += (count[s] + max_group - 1) / max_group; }
-  int ia = a, ib = b;
-#pragma unroll
-  for (int o = 1; o < 32; o <<= 1) {
-    const int ta = __shfl_up_sync(0xFFFFFFFFu, ia, o), tb = __shfl_up_sync(0xFFFFFFFFu, ib, o);
-    if (lane >= o) { ia += ta; ib += tb; }
-  }
-  if (lane == 31) { warp_a[warp] = ia; warp_b[warp] = ib; }
-  __syncthreads();
-  if (warp == 0) {
-    int wa = warp_a[lane], wb = warp_b[lane];
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-      const int ta = __shfl_up_sync(0xFFFFFFFFu, wa, o), tb = __shfl_up_sync(0xFFFFFFFFu, wb, o);
-      if (lane >= o) { wa += ta; wb += tb; }
-    }
-    warp_a[lane] = wa; warp_b[lane] = wb;
-  }
-  __syncthreads();
-  int base_a = ia - a + (warp ? warp_a[warp - 1] : 0), base_b = ib - b + (warp ? warp_b[warp - 1] : 0);
-  for (int s = lo; s < hi; ++s) {
-    first[s] = base_a; gfirst[s] = base_b;
-    const int c = count[s], g = (c + max_group - 1) / max_group;
-    for (int i = 0; i < g; ++i) {
-      out.slot[base_b + i] = s;
-      out.start[base_b + i] = base_a + i * max_group;
-      out.size[base_b + i] = min(max_group, c - i * max_group);
-    }
-    base_a += c; base_b += g;
-  }
-  if (tid == GR_THREADS - 1) out.count[0] = warp_b[31];
-  __syncthreads();
-  for (int s = tid; s < slots; s += GR_THREADS) count[s] = 0;  // reuse as cursors
-  __syncthreads();
-  for (int r = tid; r < routes; r += GR_THREADS) {
-    const uint32_t s = served_slot[r];
-    if (s < static_cast<uint32_t>(slots)) out.routes[first[s] + atomicAdd(&count[s], 1)] = r;
-  }
+  extern __shared__ int32_t group_scratch[];
+  group_routes_block<GR_THREADS>(served_slot, routes, slots, max_group, out, clear, group_scratch);
 }
 
 int group_routes(const uint32_t* served_slot, int64_t routes, int64_t slots, int max_group, const RouteGroups& out, int32_t* clear, cudaStream_t s) {

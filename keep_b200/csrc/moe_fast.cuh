@@ -112,6 +112,71 @@ struct RouteGroups {
   int32_t* routes;       // [routes] route ids ordered by group
 };
 
+// ------------------------------------------------------------------------------------------
+// Route grouping: routes that are served from the same slot share the code stream.  One block;
+// counting sort by slot, then each slot's routes are cut into groups of at most max_group.
+// ------------------------------------------------------------------------------------------
+// One block of THREADS threads (a multiple of 32, at most 1024); `sm`: 3 * slots ints of shared memory.
+template <int THREADS>
+__device__ __forceinline__ void group_routes_block(const uint32_t* __restrict__ served_slot, int routes, int slots, int max_group, const RouteGroups& out, int32_t* clear, int32_t* sm) {
+  constexpr int GR_THREADS = THREADS;
+  if (clear && threadIdx.x == 0) *clear = 0;
+  int32_t* count = sm;               // [slots] routes per slot, then running cursor
+  int32_t* first = sm + slots;       // [slots] first position of the slot in `routes`
+  int32_t* gfirst = sm + 2 * slots;  // [slots] first group index of the slot
+  __shared__ int32_t warp_a[32], warp_b[32];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  for (int s = tid; s < slots; s += GR_THREADS) count[s] = 0;
+  __syncthreads();
+  for (int r = tid; r < routes; r += GR_THREADS) {
+    const uint32_t s = served_slot[r];
+    if (s < static_cast<uint32_t>(slots)) atomicAdd(&count[s], 1);
+  }
+  __syncthreads();
+  // exclusive scans of (routes, groups) per slot: each thread owns a contiguous run of slots
+  const int per = (slots + GR_THREADS - 1) / GR_THREADS;
+  const int lo = min(tid * per, slots), hi = min(lo + per, slots);
+  int a = 0, b = 0;
+  for (int s = lo; s < hi; ++s) { a += count[s]; b += (count[s] + max_group - 1) / max_group; }
+  int ia = a, ib = b;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int ta = __shfl_up_sync(0xFFFFFFFFu, ia, o), tb = __shfl_up_sync(0xFFFFFFFFu, ib, o);
+    if (lane >= o) { ia += ta; ib += tb; }
+  }
+  if (lane == 31) { warp_a[warp] = ia; warp_b[warp] = ib; }
+  __syncthreads();
+  if (warp == 0) {
+    int wa = lane < THREADS / 32 ? warp_a[lane] : 0, wb = lane < THREADS / 32 ? warp_b[lane] : 0;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int ta = __shfl_up_sync(0xFFFFFFFFu, wa, o), tb = __shfl_up_sync(0xFFFFFFFFu, wb, o);
+      if (lane >= o) { wa += ta; wb += tb; }
+    }
+    warp_a[lane] = wa; warp_b[lane] = wb;
+  }
+  __syncthreads();
+  int base_a = ia - a + (warp ? warp_a[warp - 1] : 0), base_b = ib - b + (warp ? warp_b[warp - 1] : 0);
+  for (int s = lo; s < hi; ++s) {
+    first[s] = base_a; gfirst[s] = base_b;
+    const int c = count[s], g = (c + max_group - 1) / max_group;
+    for (int i = 0; i < g; ++i) {
+      out.slot[base_b + i] = s;
+      out.start[base_b + i] = base_a + i * max_group;
+      out.size[base_b + i] = min(max_group, c - i * max_group);
+    }
+    base_a += c; base_b += g;
+  }
+  if (tid == GR_THREADS - 1) out.count[0] = warp_b[31];
+  __syncthreads();
+  for (int s = tid; s < slots; s += GR_THREADS) count[s] = 0;  // reuse as cursors
+  __syncthreads();
+  for (int r = tid; r < routes; r += GR_THREADS) {
+    const uint32_t s = served_slot[r];
+    if (s < static_cast<uint32_t>(slots)) out.routes[first[s] + atomicAdd(&count[s], 1)] = r;
+  }
+}
+
 struct Projection {
   const uint16_t* codes;  // [slots, out_dim, in_dim/8]
   const void* scales;     // [slots, out_dim, groups]
@@ -160,6 +225,11 @@ int quantize_rows(const void* x, int32_t x_dtype, int64_t rows, int64_t in_dim, 
 constexpr int64_t FRONT_MAX_TOKENS = 23;  // from 24 tokens on the logits have a faster kernel of their own (router.cu)
 bool logits_and_quantize_supported(const keepvq_router_logits_args& logits, int64_t groups);
 int logits_and_quantize(const keepvq_router_logits_args& logits, int64_t groups, const QuantRows& out, cudaStream_t s);
+// quantize_rows with one more block that groups the routes (group_routes): calls of at most 4096 routes.
+bool group_with_quantize_supported(int64_t routes, int64_t slots);
+int quantize_rows_and_group(const void* x, int32_t x_dtype, int64_t rows, int64_t in_dim, int64_t groups, const QuantRows& out, bool planes, cudaStream_t s,
+                            const uint32_t* live_slot, int32_t per_row, int64_t slots,
+                            const uint32_t* served_slot, int64_t routes, int max_group, const RouteGroups& route_groups, int32_t* clear);
 int group_routes(const uint32_t* served_slot, int64_t routes, int64_t slots, int max_group, const RouteGroups& out, int32_t* clear, cudaStream_t s);
 // Routes per group for a decode call: four while experts rarely get more (the kernels then run one
 // MMA per step for both byte planes), eight beyond.  `live` = routes expected to carry a slot.

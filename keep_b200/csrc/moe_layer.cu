@@ -202,6 +202,10 @@ extern "C" int keepvq_moe_decode_stages(const keepvq_moe_layer_args* args, int32
                        fast::prefill_supported(a.inter, a.hidden, a.w1.groups) && fast::prefill_supported(a.hidden, a.inter, a.w2.groups);
   fast::QuantRows xq = {reinterpret_cast<uint8_t*>(ws + sc.xq), reinterpret_cast<float*>(ws + sc.xscale), reinterpret_cast<int32_t*>(ws + sc.xsums)};
   bool x_quantized = false;  // the router's launch took the quantisation of the token rows along
+  // a caller that expects few of the routes to be live (an expert-parallel rank's padded receive
+  // buffer) has the quantisation skip the rows no live route reads; otherwise the look at the
+  // slots would only put a dependent load in front of every row
+  const uint32_t* padded = live < routes ? a.served_slot : nullptr;
 
   if (stages & KEEPVQ_STAGE_ROUTER) {
     keepvq_router_logits_args rl = {};
@@ -232,8 +236,13 @@ extern "C" int keepvq_moe_decode_stages(const keepvq_moe_layer_args* args, int32
     int32_t* wait_status = reinterpret_cast<int32_t*>(ws + sc.status);
     const int group_cols = prefill ? fast::PREFILL_GROUP_ROUTES : fast::decode_group_routes(live, a.slots, std::max(a.hidden, a.inter));
     if (stages & KEEPVQ_STAGE_PREPARE) {
-      if ((rc = fast::group_routes(a.served_slot, routes, a.slots, group_cols, groups, wait_status, s))) return rc;
-      if (!x_quantized && (rc = fast::quantize_rows(a.x, a.x_dtype, a.tokens, a.hidden, a.w1.groups, xq, prefill, s, a.served_slot, a.top_k, a.slots))) return rc;
+      if (!x_quantized && !prefill && fast::group_with_quantize_supported(routes, a.slots)) {  // one launch for both
+        if ((rc = fast::quantize_rows_and_group(a.x, a.x_dtype, a.tokens, a.hidden, a.w1.groups, xq, false, s, padded, a.top_k, a.slots,
+                                                a.served_slot, routes, group_cols, groups, wait_status))) return rc;
+      } else {
+        if ((rc = fast::group_routes(a.served_slot, routes, a.slots, group_cols, groups, wait_status, s))) return rc;
+        if (!x_quantized && (rc = fast::quantize_rows(a.x, a.x_dtype, a.tokens, a.hidden, a.w1.groups, xq, prefill, s, padded, a.top_k, a.slots))) return rc;
+      }
     }
     fast::FastProjectionArgs p = {};
     p.scales_dtype = a.scales_dtype; p.codebook = a.codebook; p.groups_of_routes = groups; p.max_routes = routes; p.group_cols = group_cols; p.status = wait_status;
@@ -246,7 +255,7 @@ extern "C" int keepvq_moe_decode_stages(const keepvq_moe_layer_args* args, int32
       if ((rc = prefill ? fast::prefill_gate_up(p, wait_status, s) : fast::gate_up(p, s))) return rc;
     }
     if (stages & KEEPVQ_STAGE_DOWN) {
-      if ((rc = fast::quantize_rows(ws + sc.h, a.x_dtype, routes, a.inter, a.w2.groups, hq, prefill, s, a.served_slot, 1, a.slots))) return rc;
+      if ((rc = fast::quantize_rows(ws + sc.h, a.x_dtype, routes, a.inter, a.w2.groups, hq, prefill, s, padded, 1, a.slots))) return rc;
       p.a = {a.w2.codes, a.w2.scales, a.w2.res_codes, a.w2.res_scales}; p.b = {nullptr, nullptr, nullptr, nullptr};
       if (residual) { p.res_groups = a.w2.res_groups; p.hot_of_slot = a.hot_of_slot; p.res_table = a.res_table; }
       p.out_dim = a.hidden; p.in_dim = a.inter; p.groups = a.w2.groups; p.x = hq; p.x_zero_row = routes; p.x_div = 1; p.out = ws + sc.down;

@@ -165,11 +165,14 @@ class RoutedMoELayer:
 
     def launches_per_call(self, tokens: int, dtype: torch.dtype = torch.bfloat16) -> int:
         """Kernel launches one ``decode`` call of ``tokens`` rows enqueues.  On the tensor-core
-        kernels: logits, top-k, route grouping, quantise x, gate/up, quantise h, down, combine; up
-        to 23 fp16 / bf16 tokens the logits and the quantisation of x share a launch."""
+        kernels: logits, top-k, route grouping, quantise x, gate/up, quantise h, down, combine,
+        of which two share a launch: up to 23 fp16 / bf16 tokens the logits and the quantisation
+        of x, beyond that (up to 4096 routes) the quantisation of x and the route grouping."""
         if self.kernel_path != "tensor":
             return 7
-        return 7 if tokens <= 23 and dtype in (torch.float16, torch.bfloat16) else 8
+        front = tokens <= 23 and dtype in (torch.float16, torch.bfloat16)
+        paired = tokens * self.top_k <= 4096 and self.slots * 12 <= 40 * 1024
+        return 7 if front or paired else 8
 
     def decode_without_scratch(self, x: torch.Tensor, out: torch.Tensor, routing: Routing) -> tuple[torch.Tensor, Routing]:
         """The same layer through ``keepvq_moe_decode_layer_static``: the caller supplies the
