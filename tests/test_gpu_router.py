@@ -35,8 +35,12 @@ def test_golden_gate_masked(cuda, golden, func, mask):
         assert (got_i[~live] == -1).all()
 
 
-@pytest.mark.parametrize("tokens,pool,hidden,k", [(1, 384, 4096, 6), (16, 384, 4096, 6), (37, 100, 256, 3), (5, 1024, 512, 8),
-                                                  (256, 256, 4096, 6), (303, 100, 520, 3), (300, 100, 512, 3)])  # the last three take the tiled logits kernels (tensor-core, fp32, tensor-core with ragged tiles)
+@pytest.mark.parametrize("tokens,pool,hidden,k", [(1, 384, 4096, 6), (16, 384, 4096, 6), (5, 1024, 512, 8),
+                                                  # 24 to 255 bf16 tokens: the tensor-core tile with K split over a cluster of eight blocks
+                                                  # (ragged tiles and one K block per rank; the benchmark shape; three token tiles)
+                                                  (37, 100, 256, 3), (64, 384, 4096, 6), (130, 200, 1024, 4),
+                                                  # the tiled logits kernels: tensor-core, fp32, tensor-core with ragged tiles
+                                                  (256, 256, 4096, 6), (303, 100, 520, 3), (300, 100, 512, 3)])
 @pytest.mark.parametrize("func", ["softmax", "sqrtsoftplus"])
 def test_served_demand_and_admission_match_the_oracle_exactly(cuda, tokens, pool, hidden, k, func):
     from keep_b200 import router
