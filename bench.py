@@ -371,6 +371,38 @@ def operator_legs(layer, device, hbm_gbs, steps=32):
     return out
 
 
+def artifact_shape_leg(device, hbm_gbs, steps=32):
+    """The shape and scale groups of the reference's shipped layers (hidden 5120 in groups of 512,
+    inter 2304 in groups of 256, keep_quant.py:13-15; top-6 over 192 resident experts, the pool its
+    served decode step routes over) at one and at four tokens: microseconds per layer call and
+    GB/s on the distinct code bytes.  The reference's own figure for this step is 0.40-0.42 ms on
+    an M4 Max (router, six lattice experts and the shared expert)."""
+    from keep_b200 import moe
+
+    experts, hidden, inter = 192, 5120, 2304
+    gen = torch.Generator(device=device)
+    gen.manual_seed(31)
+
+    def proj(out, inp, group):
+        codes = torch.randint(0, 1 << 16, (experts, out, inp // 8), generator=gen, device=device, dtype=torch.int32).to(torch.uint16)
+        scales = (0.02 * (0.5 + torch.rand((experts, out, inp // group), generator=gen, device=device))).to(torch.float16)
+        return moe.Projection(codes, scales)
+
+    router = (0.02 * torch.randn((experts, hidden), generator=gen, device=device)).to(torch.bfloat16)
+    layer = moe.RoutedMoELayer(router, proj(inter, hidden, 512), proj(inter, hidden, 512), proj(hidden, inter, 256), top_k=TOP_K)
+    out = {"experts": experts, "hidden": hidden, "inter": inter, "scale_groups": "512 / 256", "kernel_path": layer.kernel_path}
+    per_expert = 3 * hidden * inter // 8 * 2
+    for batch in (1, 4):
+        xs = [torch.randn((batch, hidden), generator=torch.Generator().manual_seed(500 + batch * 16 + j)).to(torch.bfloat16).to(device) for j in range(16)]
+        uniq = statistics.fmean(int(torch.unique(layer.decode(x)[1].served_expert).numel()) for x in xs)
+        ms = time_graph(lambda i: layer.decode(xs[i % 16]), steps, 3)
+        us = ms / steps * 1e3
+        out[str(batch)] = {"layer_us": round(us, 1), "code_frac_of_hbm": round(uniq * per_expert / (us * 1e-6) / 1e9 / hbm_gbs, 4)}
+    del layer
+    torch.cuda.empty_cache()
+    return out
+
+
 def cpu_expert_sample(layer, threads, routes=64):
     """One expert of the prefill leg on the CPU path: decode of its three matrices and the SwiGLU
     path for `routes` token rows (what the reference's CPU code does per expert).  Seconds."""
@@ -810,6 +842,7 @@ def run_ours(ns):
         "residency": residency_leg(layer, device, ns.rotation, ns.steps, hbm_gbs) if not ns.no_prefill else None,
         "prefill": prefill_leg(layer, device) if not ns.no_prefill else None,
         "operators": operator_legs(layer, device, hbm_gbs) if not ns.no_prefill else None,
+        "artifact_shape": artifact_shape_leg(device, hbm_gbs) if not ns.no_prefill else None,
         "ep_n1": None,
         "gpu_launches": layer.launches_per_call(batch) * ns.steps, "kernel_path": layer.kernel_path,
         "clocks": clocks.summary(),

@@ -494,6 +494,9 @@ int keepvq_ep_combine(const keepvq_ep_combine_args* args, void* stream);
  *                          keepvq_ep_combine then runs on the local `back` with the positions
  *                          keepvq_ep_dispatch_peer wrote.
  *
+ * Each of the two calls is one kernel launch: its blocks count themselves off in `arrivals`
+ * behind their stores, and the block that finishes last runs the barrier.
+ *
  * One set of buffers is enough for back-to-back layers: a rank leaves the second barrier of a
  * layer only after every rank has finished reading what the first phase wrote.  A wait that
  * expires (a peer that never arrives) sets *status to 1 and the kernel returns; nothing traps. */
