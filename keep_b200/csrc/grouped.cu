@@ -86,13 +86,15 @@ extern "C" int keepvq_grouped_projection(const keepvq_grouped_projection_args* a
   int rc;
   const int group_cols = many ? fast::PREFILL_GROUP_ROUTES : fast::decode_group_routes(a.routes, a.slots, a.in_dim);
   if ((rc = fast::group_routes(a.rhs, a.routes, a.slots, group_cols, groups, wait_status, s))) return rc;
-  if ((rc = fast::quantize_rows(a.x, a.x_dtype, x_rows, a.in_dim, a.groups, xq, many, s))) return rc;
+  if (many) {  // the tcgen05 kernels copy rows in grouped order
+    if ((rc = fast::quantize_rows_sorted(a.x, a.x_dtype, a.routes, a.in_dim, a.groups, xq, {groups.routes, groups.count, static_cast<int32_t>(x_div)}, s))) return rc;
+  } else if ((rc = fast::quantize_rows(a.x, a.x_dtype, x_rows, a.in_dim, a.groups, xq, false, s))) return rc;
   fast::FastProjectionArgs p = {};
   p.a = {a.codes, a.scales, a.res_codes, a.res_scales}; p.b = {nullptr, nullptr, nullptr, nullptr};
   if (residual) { p.res_groups = a.res_groups; p.hot_of_slot = a.hot_of_slot; p.res_table = a.res_table; }
   p.scales_dtype = a.scales_dtype; p.codebook = a.codebook; p.groups_of_routes = groups; p.max_routes = a.routes; p.group_cols = group_cols; p.status = wait_status;
   p.few_groups = many ? 0 : fast::few_route_groups(a.routes, a.slots);
-  p.out_dim = a.out_dim; p.in_dim = a.in_dim; p.groups = a.groups; p.x = xq; p.x_zero_row = x_rows; p.x_div = x_div;
+  p.out_dim = a.out_dim; p.in_dim = a.in_dim; p.groups = a.groups; p.x = xq; p.x_zero_row = many ? a.routes : x_rows; p.x_div = x_div;
   p.out = a.out; p.out_dtype = a.out_dtype; p.swiglu_limit = 0.0f; p.route_weight = nullptr;
   if (a.routes > 0x7FFFFFFFll) return KEEPVQ_ERR_CAPACITY;
   zero_dead_rows_kernel<<<static_cast<unsigned>(a.routes), 128, 0, s>>>(a.rhs, a.slots, a.out, a.out_dim * dtype_size(a.out_dtype));

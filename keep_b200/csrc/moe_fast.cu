@@ -26,7 +26,7 @@ namespace fast {
 // ------------------------------------------------------------------------------------------
 // One row per block of 256 threads; row == rows is the extra all-zero row.
 template <typename XT>
-__device__ __forceinline__ void quantize_row(const XT* __restrict__ x, int64_t rows, int64_t in_dim, int64_t groups, const QuantRows& out, int planes, int64_t row) {
+__device__ __forceinline__ void quantize_row(const XT* __restrict__ x, int64_t rows, int64_t in_dim, int64_t groups, const QuantRows& out, int planes, int64_t row, int64_t source_row) {
   __shared__ float warp_max[8];
   __shared__ float row_scale;
   extern __shared__ int32_t group_sum[];
@@ -45,7 +45,7 @@ __device__ __forceinline__ void quantize_row(const XT* __restrict__ x, int64_t r
     if (threadIdx.x == 0) out.scale[row] = 1.0f;
     return;
   }
-  const XT* xr = x + row * in_dim;
+  const XT* xr = x + source_row * in_dim;
   for (int64_t g = threadIdx.x; g < groups; g += 256) group_sum[g] = 0;
 
   float amax = 0.0f;
@@ -132,7 +132,17 @@ __global__ void __launch_bounds__(256) quantize_rows_kernel(const XT* __restrict
     for (int j = 0; j < live.per_row; ++j) any = any || live.slot[row * live.per_row + j] < static_cast<uint64_t>(live.slots);
     if (!any) return;  // uniform over the block
   }
-  quantize_row<XT>(x, rows, in_dim, groups, out, planes, row);
+  quantize_row<XT>(x, rows, in_dim, groups, out, planes, row, row);
+}
+
+// Byte planes with the rows in grouped order (what the tcgen05 kernels' TMA boxes copy).
+template <typename XT>
+__global__ void __launch_bounds__(256) quantize_rows_sorted_kernel(const XT* __restrict__ x, int64_t rows, int64_t in_dim, int64_t groups, QuantRows out, SortedRows sorted) {
+  grid_launch_dependents();
+  grid_wait();
+  const int64_t row = blockIdx.x;
+  if (row < rows && row >= sorted.count[1]) return;  // not a grouped route: nothing reads the row (uniform over the block)
+  quantize_row<XT>(x, rows, in_dim, groups, out, 1, row, row < rows ? sorted.routes[row] / sorted.x_div : 0);
 }
 
 // The front of a decode layer call in one launch: the router's logits (the few-token kernel's
@@ -146,7 +156,7 @@ __global__ void __launch_bounds__(256) logits_and_quantize_kernel(keepvq_router_
   grid_wait();
   const int b = static_cast<int>(blockIdx.x);
   if (b < logit_blocks) router_logits_block<XT, WT>(a, b % logit_blocks_x, b / logit_blocks_x);
-  else quantize_row<XT>(reinterpret_cast<const XT*>(a.x), a.tokens, a.hidden, groups, out, 0, b - logit_blocks);
+  else quantize_row<XT>(reinterpret_cast<const XT*>(a.x), a.tokens, a.hidden, groups, out, 0, b - logit_blocks, b - logit_blocks);
 }
 
 template <typename XT>
@@ -173,6 +183,18 @@ int logits_and_quantize(const keepvq_router_logits_args& a, int64_t groups, cons
 int quantize_rows(const void* x, int32_t x_dtype, int64_t rows, int64_t in_dim, int64_t groups, const QuantRows& out, bool planes, cudaStream_t s,
                   const uint32_t* live_slot, int32_t per_row, int64_t slots) {
   return quantize_rows_and_group(x, x_dtype, rows, in_dim, groups, out, planes, s, live_slot, per_row, slots, nullptr, 0, 0, RouteGroups{}, nullptr);
+}
+
+int quantize_rows_sorted(const void* x, int32_t x_dtype, int64_t rows, int64_t in_dim, int64_t groups, const QuantRows& out, const SortedRows& sorted, cudaStream_t s) {
+  const size_t smem = static_cast<size_t>(groups) * sizeof(int32_t);
+  if (smem > 40 * 1024) return KEEPVQ_ERR_CAPACITY;
+  const unsigned grid = static_cast<unsigned>(rows + 1);  // + the zero row
+  cudaError_t err;
+  if (x_dtype == KEEPVQ_F32) err = launch_after(false, quantize_rows_sorted_kernel<float>, grid, 256, smem, s, reinterpret_cast<const float*>(x), rows, in_dim, groups, out, sorted);
+  else if (x_dtype == KEEPVQ_F16) err = launch_after(false, quantize_rows_sorted_kernel<__half>, grid, 256, smem, s, reinterpret_cast<const __half*>(x), rows, in_dim, groups, out, sorted);
+  else err = launch_after(false, quantize_rows_sorted_kernel<__nv_bfloat16>, grid, 256, smem, s, reinterpret_cast<const __nv_bfloat16*>(x), rows, in_dim, groups, out, sorted);
+  if (err != cudaSuccess) return note_cuda_error(err);
+  return KEEPVQ_OK;
 }
 
 bool group_with_quantize_supported(int64_t routes, int64_t slots) { return routes <= 4096 && slots * 3 * sizeof(int32_t) <= 40 * 1024; }

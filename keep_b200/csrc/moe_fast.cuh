@@ -105,7 +105,7 @@ struct QuantRows {
 
 // Routes grouped by the slot they are served from.
 struct RouteGroups {
-  int32_t* count;        // [1] number of groups
+  int32_t* count;        // [2] number of groups, number of routes in them (the live ones)
   int32_t* slot;         // [max_groups]
   int32_t* start;        // [max_groups] first entry in `routes`
   int32_t* size;         // [max_groups] 1..max_group
@@ -167,7 +167,7 @@ __device__ __forceinline__ void group_routes_block(const uint32_t* __restrict__ 
     }
     base_a += c; base_b += g;
   }
-  if (tid == GR_THREADS - 1) out.count[0] = warp_b[31];
+  if (tid == GR_THREADS - 1) { out.count[0] = warp_b[31]; out.count[1] = warp_a[31]; }  // groups, grouped (live) routes
   __syncthreads();
   for (int s = tid; s < slots; s += GR_THREADS) count[s] = 0;  // reuse as cursors
   __syncthreads();
@@ -215,10 +215,16 @@ bool shapes_supported(int64_t out_dim, int64_t in_dim, int64_t groups);
 bool residual_supported(int64_t routes, int64_t in_dim, int64_t res_groups);
 
 // planes = false: 16 bytes per codeword (hi 8, lo 8), what the mma.sync kernels read;
-// planes = true: all high bytes [rows + 1, in_dim] then all low bytes, what the tcgen05 kernels copy.
+// planes = true: all high bytes [rows + 1, in_dim] then all low bytes (quantize_rows_sorted writes that form).
 // live_slot (may be null): [rows, per_row] slots of the routes that read the rows; rows whose routes are all dead (slot >= slots) are skipped.
 int quantize_rows(const void* x, int32_t x_dtype, int64_t rows, int64_t in_dim, int64_t groups, const QuantRows& out, bool planes, cudaStream_t s,
                   const uint32_t* live_slot = nullptr, int32_t per_row = 1, int64_t slots = 0);
+// What the tcgen05 kernels' TMA boxes copy: byte planes (all high bytes [rows + 1, in_dim], then all
+// low bytes) with the rows IN GROUPED ORDER: output row r is input row sorted.routes[r] / x_div for
+// r below sorted.count[1] (group_routes must have run), rows beyond that are left alone; scale and
+// sums are per output row.
+struct SortedRows { const int32_t* routes; const int32_t* count; int32_t x_div; };
+int quantize_rows_sorted(const void* x, int32_t x_dtype, int64_t rows, int64_t in_dim, int64_t groups, const QuantRows& out, const SortedRows& sorted, cudaStream_t s);
 // `clear` (may be null): a status word the kernel zeroes for the projection kernels that follow it.
 // The router's logits and quantize_rows (planes = false) of the same token rows in one launch, for
 // calls of at most FRONT_MAX_TOKENS tokens with fp16 / bf16 activations.

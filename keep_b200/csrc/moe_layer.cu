@@ -58,9 +58,11 @@ static LayerScratch plan_scratch(int64_t tokens, int64_t hidden, int64_t inter, 
   s.up = at;     at += align256(routes * inter * 4);
   s.h = at;      at += align256(routes * inter * 4);
   s.down = at;   at += align256(routes * hidden * 4);
-  s.xq = at;     at += align256((tokens + 1) * hidden * 2);  // + the zero row
-  s.xscale = at; at += align256((tokens + 1) * 4);
-  s.xsums = at;  at += align256((tokens + 1) * (hidden / 8) * 4);  // room for one scale group per codeword
+  // calls large enough for the tcgen05 kernels quantise the token rows once per route, in grouped order
+  const int64_t x_rows = routes >= PREFILL_MIN_ROUTES ? routes : tokens;
+  s.xq = at;     at += align256((x_rows + 1) * hidden * 2);  // + the zero row
+  s.xscale = at; at += align256((x_rows + 1) * 4);
+  s.xsums = at;  at += align256(std::max((tokens + 1) * (hidden / 8) * 4, (x_rows + 1) * 4));  // room for one scale group per codeword (one per row in grouped order)
   s.hq = at;     at += align256((routes + 1) * inter * 2);
   s.hscale = at; at += align256((routes + 1) * 4);
   s.hsums = at;  at += align256((routes + 1) * (inter / 8) * 4);
@@ -241,7 +243,9 @@ extern "C" int keepvq_moe_decode_stages(const keepvq_moe_layer_args* args, int32
                                                 a.served_slot, routes, group_cols, groups, wait_status))) return rc;
       } else {
         if ((rc = fast::group_routes(a.served_slot, routes, a.slots, group_cols, groups, wait_status, s))) return rc;
-        if (!x_quantized && (rc = fast::quantize_rows(a.x, a.x_dtype, a.tokens, a.hidden, a.w1.groups, xq, prefill, s, padded, a.top_k, a.slots))) return rc;
+        if (prefill) {
+          if ((rc = fast::quantize_rows_sorted(a.x, a.x_dtype, routes, a.hidden, a.w1.groups, xq, {groups.routes, groups.count, a.top_k}, s))) return rc;
+        } else if (!x_quantized && (rc = fast::quantize_rows(a.x, a.x_dtype, a.tokens, a.hidden, a.w1.groups, xq, false, s, padded, a.top_k, a.slots))) return rc;
       }
     }
     fast::FastProjectionArgs p = {};
@@ -251,11 +255,13 @@ extern "C" int keepvq_moe_decode_stages(const keepvq_moe_layer_args* args, int32
     if (stages & KEEPVQ_STAGE_GATE_UP) {
       p.a = {a.w1.codes, a.w1.scales, a.w1.res_codes, a.w1.res_scales}; p.b = {a.w3.codes, a.w3.scales, a.w3.res_codes, a.w3.res_scales};
       if (residual) { p.res_groups = a.w1.res_groups; p.hot_of_slot = a.hot_of_slot; p.res_table = a.res_table; }
-      p.out_dim = a.inter; p.in_dim = a.hidden; p.groups = a.w1.groups; p.x = xq; p.x_zero_row = a.tokens; p.x_div = a.top_k; p.out = ws + sc.h;
+      p.out_dim = a.inter; p.in_dim = a.hidden; p.groups = a.w1.groups; p.x = xq; p.x_zero_row = prefill ? routes : a.tokens; p.x_div = a.top_k; p.out = ws + sc.h;
       if ((rc = prefill ? fast::prefill_gate_up(p, wait_status, s) : fast::gate_up(p, s))) return rc;
     }
     if (stages & KEEPVQ_STAGE_DOWN) {
-      if ((rc = fast::quantize_rows(ws + sc.h, a.x_dtype, routes, a.inter, a.w2.groups, hq, prefill, s, padded, 1, a.slots))) return rc;
+      if (prefill) {
+        if ((rc = fast::quantize_rows_sorted(ws + sc.h, a.x_dtype, routes, a.inter, a.w2.groups, hq, {groups.routes, groups.count, 1}, s))) return rc;
+      } else if ((rc = fast::quantize_rows(ws + sc.h, a.x_dtype, routes, a.inter, a.w2.groups, hq, false, s, padded, 1, a.slots))) return rc;
       p.a = {a.w2.codes, a.w2.scales, a.w2.res_codes, a.w2.res_scales}; p.b = {nullptr, nullptr, nullptr, nullptr};
       if (residual) { p.res_groups = a.w2.res_groups; p.hot_of_slot = a.hot_of_slot; p.res_table = a.res_table; }
       p.out_dim = a.hidden; p.in_dim = a.inter; p.groups = a.w2.groups; p.x = hq; p.x_zero_row = routes; p.x_div = 1; p.out = ws + sc.down;

@@ -30,10 +30,17 @@
 //   warp  16     issues the MMAs (one thread): A from tensor memory, B from shared memory.  Its
 //                other lanes gather what the drain needs per route (route id, activation scale
 //                and sum, gate weight) into shared memory.
-//   warps 17-19  cp.async the routes' quantised activations into the B tiles (3 stages).
+//   warp  17     one thread brings the routes' quantised activations into the B tiles (3 stages)
+//                with TMA: the rows were quantised in grouped order, so a group's high bytes and
+//                its low bytes are two runs of rows of one [2 x rows, K] byte matrix, and a K block
+//                of them is a handful of cp.async.bulk.tensor.2d boxes of 16 rows x 128 bytes that
+//                land swizzled, ready for the MMA; the boxes report to the stage's mbarrier
+//                (expect_tx / complete_tx).  Warps 18-19 have nothing to do.
 // mbarrier full/empty pairs carry every dependency.  Every wait is bounded by a deadline on the
 // global timer: on expiry the CTA raises a flag in `status`, stops issuing work, waits (bounded)
 // for the MMAs in flight, frees its tensor memory and returns.
+#include <cuda.h>  // CUtensorMap (types only: the one driver entry point is looked up through the runtime)
+
 #include "moe_fast.cuh"
 
 namespace keepvq {
@@ -125,6 +132,16 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
                : "r"(taddr) : "memory");
 }
 
+// One TMA box of the tensor map -> shared memory; completion is counted on `bar` in bytes.
+// x (bytes along K) is a multiple of 128 here and y a row index: both inside the rules for x.
+__device__ __forceinline__ void tma_box_2d(uint32_t dst, const CUtensorMap* map, int32_t x, int32_t y, uint32_t bar) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+               ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+
 __device__ __forceinline__ void cp_async16_pf(uint32_t dst, const void* src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
 }
@@ -147,7 +164,7 @@ __device__ unsigned long long g_pf_timers[16];
 // `stall` != 0 is the wait self-test: the activation loaders never publish, so the MMA issuer's
 // first wait runs into the deadline.
 template <int M, bool GLU>
-__global__ void __launch_bounds__(PF_THREADS, 1) prefill_projection_kernel(FastProjectionArgs p, int32_t* status, int diag, int stall, uint64_t wait_ns) {
+__global__ void __launch_bounds__(PF_THREADS, 1) prefill_projection_kernel(FastProjectionArgs p, const __grid_constant__ CUtensorMap x_map, int32_t* status, int diag, int stall, uint64_t wait_ns) {
   constexpr int ITEM_ROWS = GLU ? PF_ROWS : PF_ROWS * M;
   extern __shared__ __align__(16) uint8_t smem_raw[];
   enum { A_FULL = 0, A_EMPTY = A_FULL + PF_A_STAGES, B_FULL = A_EMPTY + PF_A_STAGES, B_EMPTY = B_FULL + PF_B_STAGES,
@@ -185,7 +202,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_projection_kernel(FastP
   if (tid == 0) {
     abort_flag = window_ok ? 0 : 1;
     for (int s = 0; s < PF_A_STAGES; ++s) { mbar_init(bar(A_FULL, s), M * 8); mbar_init(bar(A_EMPTY, s), 1); }
-    for (int s = 0; s < PF_B_STAGES; ++s) { mbar_init(bar(B_FULL, s), PF_B_WARPS); mbar_init(bar(B_EMPTY, s), 1); }
+    for (int s = 0; s < PF_B_STAGES; ++s) { mbar_init(bar(B_FULL, s), 1); mbar_init(bar(B_EMPTY, s), 1); }
     mbar_init(bar(ACC_FULL, 0), 1);
     mbar_init(bar(ACC_EMPTY, 0), PF_DECODE_WARPS);
     mbar_init(bar(INFO_FULL, 0), 1);
@@ -380,7 +397,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_projection_kernel(FastP
       {
         for (int n = lane; n < n_pad; n += 32) {
           const int route = n < gsize ? p.groups_of_routes.routes[gstart + n] : -1;
-          const int64_t xrow = route < 0 ? p.x_zero_row : static_cast<int64_t>(route / p.x_div);
+          const int64_t xrow = route < 0 ? p.x_zero_row : static_cast<int64_t>(gstart + n);  // the activation rows were quantised in grouped order
           const float weight = (GLU && route >= 0) ? p.route_weight[route] : 1.0f;
           route_info[item_phase][n] = make_int4(route, __float_as_int(p.x.scale[xrow]), __float_as_int(0.25f * static_cast<float>(p.x.sums[xrow])), __float_as_int(weight));
         }
@@ -430,58 +447,30 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_projection_kernel(FastP
       // stages of item n, and they produce those only after they are done with item n - 1.
       __syncwarp();
     } else {
-      // ================= activation (B operand) loaders =======================================
-      // cp.async straight into the swizzled tiles (16 bytes = two codewords of one route); a K
-      // block is published when its copies have landed, PF_B_LAG later ones already in flight.
-      // A thread keeps one (chunk, plane) and every sixth route: sources and destinations are
-      // worked out once per item, a K block then costs an add and a copy per route.
-      const int loader = tid - (PF_MMA_WARP + 1) * 32;  // 0..95
-      constexpr int ROUTE_LANES = PF_B_WARPS * 32 / 16;                  // threads per (chunk, plane): each takes every sixth route
-      constexpr int SLOTS = (PF_N_MAX + ROUTE_LANES - 1) / ROUTE_LANES;  // routes per thread
-      static_assert((PF_B_WARPS * 32) % 16 == 0, "loader split");
-      const int c = (loader >> 1) & 7, pl = loader & 1, n0 = loader >> 4;
-      const int64_t row_bytes = cw * 8;
-      const uint8_t* plane = p.x.q + (pl ? (p.x_zero_row + 1) * row_bytes : 0) + c * 16;
-      const uint8_t* src[SLOTS];
-      uint32_t dst[SLOTS];
-#pragma unroll
-      for (int i = 0; i < SLOTS; ++i) {
-        const int n = n0 + i * ROUTE_LANES;
-        const int route = n < gsize ? p.groups_of_routes.routes[gstart + n] : -1;
-        src[i] = plane + (route < 0 ? p.x_zero_row : static_cast<int64_t>(route / p.x_div)) * row_bytes;
-        dst[i] = swizzled(pl * n_pad + n, c);
-      }
-      uint32_t it = iter;
-      bool ok = true;
-      auto publish = [&](uint32_t which) {
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        __syncwarp();
-        if (lane == 0 && !stall) mbar_arrive(bar(B_FULL, which % PF_B_STAGES));
-      };
-      for (int kb = 0; kb < k_blocks && ok; ++kb, ++it) {
-        const uint32_t stage = it % PF_B_STAGES, phase = (it / PF_B_STAGES) & 1u;
-        ok = __all_sync(0xFFFFFFFFu, mbar_wait(bar(B_EMPTY, stage), phase ^ 1u, deadline, aborted));
-        if (!ok) break;
-        const uint32_t b_stage = b_stage_addr(stage);
-#pragma unroll
-        for (int i = 0; i < SLOTS; ++i)
-          if (n0 + i * ROUTE_LANES < n_pad && diag != 3) cp_async16_pf(b_stage + dst[i], src[i] + kb * 128);
-        asm volatile("cp.async.commit_group;" ::: "memory");
-        // Publish K block kb - LAG once its copies have landed, with LAG <= stages - 2: the copies
-        // of kb reuse the stage of kb - stages, so publishing kb - LAG then waits on nothing newer
-        // than MMAs two blocks before it.  With LAG = stages - 1 every publication waited for the
-        // MMAs just before it and the whole pipeline ran in lock step.
-        if (kb >= PF_B_LAG) {
-          asm volatile("cp.async.wait_group %0;" ::"n"(PF_B_LAG) : "memory");
-          publish(it - PF_B_LAG);
+      // ================= activation (B operand) loader: TMA ====================================
+      // Rows gstart .. gstart + n_pad - 1 of the high-byte plane and of the low-byte plane, 16 rows
+      // per box (a box lands swizzled at a 2 KB step of the tile); rows past the group's own belong
+      // to the next group or to nobody, and nobody looks at their columns.  One thread issues.
+      if (warp == PF_MMA_WARP + 1 && lane == 0) {
+        uint32_t it = iter;
+        const int32_t plane_rows = static_cast<int32_t>(p.x_zero_row + 1);
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const uint32_t stage = it % PF_B_STAGES, phase = (it / PF_B_STAGES) & 1u;
+          if (!mbar_wait(bar(B_EMPTY, stage), phase ^ 1u, deadline, aborted)) break;
+          if (stall) continue;  // the wait self-test: nothing is ever published
+          const uint32_t b_stage = b_stage_addr(stage), full = bar(B_FULL, stage);
+          mbar_expect_tx(full, static_cast<uint32_t>(2 * n_pad * 128));
+          if (diag != 3) {
+            for (int r = 0; r < n_pad; r += 16) {
+              tma_box_2d(b_stage + r * 128, &x_map, kb * 128, gstart + r, full);
+              tma_box_2d(b_stage + (n_pad + r) * 128, &x_map, kb * 128, plane_rows + gstart + r, full);
+            }
+          } else {
+            // measurement build only: the bytes never come, so count them off by hand
+            asm volatile("mbarrier.complete_tx.shared::cta.b64 [%0], %1;" ::"r"(full), "r"(static_cast<uint32_t>(2 * n_pad * 128)) : "memory");
+          }
         }
       }
-      if (ok) {  // drain: publish the last K blocks in order
-        const int tail = k_blocks < PF_B_LAG ? k_blocks : PF_B_LAG;
-        if (tail >= 2) { asm volatile("cp.async.wait_group 1;" ::: "memory"); publish(it - 2); }
-        if (tail >= 1) { asm volatile("cp.async.wait_group 0;" ::: "memory"); publish(it - 1); }
-      }
-      asm volatile("cp.async.wait_group 0;" ::: "memory");
     }
   }
 
@@ -526,8 +515,34 @@ extern "C" void keepvq_diag_read_timers(unsigned long long* out) {  // host arra
 }
 #endif
 
+// The tensor map of a projection's quantised activations: a [2 * (rows + 1), in_dim] byte matrix
+// (the high-byte plane over the low-byte plane), boxes of 16 rows x 128 bytes, 128-byte swizzle.
+// This GPU's own memory only; no multicast anywhere.
+static int activation_map(const FastProjectionArgs& p, CUtensorMap* map) {
+  typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+  static EncodeTiled encode = nullptr;
+  if (!encode) {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult found = cudaDriverEntryPointSymbolNotFound;
+    const cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &found);
+    if (e != cudaSuccess) return note_cuda_error(e);
+    if (found != cudaDriverEntryPointSuccess || !fn) return KEEPVQ_ERR_UNSUPPORTED;
+    encode = reinterpret_cast<EncodeTiled>(fn);
+  }
+  if (p.in_dim % 128 != 0 || (reinterpret_cast<uintptr_t>(p.x.q) & 15u) != 0) return KEEPVQ_ERR_ALIGN;
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(p.in_dim), static_cast<cuuint64_t>(2 * (p.x_zero_row + 1))};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(p.in_dim)};
+  const cuuint32_t box[2] = {128, 16}, element_strides[2] = {1, 1};
+  const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, p.x.q, dims, strides, box, element_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? KEEPVQ_OK : KEEPVQ_ERR_LAUNCH;
+}
+
 template <int M, bool GLU>
 static int launch_prefill(const FastProjectionArgs& p, int32_t* status, cudaStream_t s, int stall = 0, uint64_t wait_ns = 0, int ctas = 0) {
+  CUtensorMap x_map;
+  if (const int rc = activation_map(p, &x_map)) return rc;
   static uint64_t configured = 0;  // one bit per device: the shared-memory opt-in is a per-device attribute of the function
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
@@ -542,7 +557,7 @@ static int launch_prefill(const FastProjectionArgs& p, int32_t* status, cudaStre
   // measurement build only (outputs meaningless): 1 no drain, 2 no tensor-memory stores, 3 no activation copies, 4 no MMAs, 5 no code fetches
   diag = g_prefill_diag;
 #endif
-  prefill_projection_kernel<M, GLU><<<ctas > 0 ? ctas : sms, PF_THREADS, PF_SMEM_BYTES, s>>>(p, status, diag, stall, wait_ns);
+  prefill_projection_kernel<M, GLU><<<ctas > 0 ? ctas : sms, PF_THREADS, PF_SMEM_BYTES, s>>>(p, x_map, status, diag, stall, wait_ns);
   KEEPVQ_CHECK_LAUNCH();
   return KEEPVQ_OK;
 }
