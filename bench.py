@@ -319,7 +319,7 @@ def prefill_leg(layer, device, steps=6):
                                      for k, m in names.items()}
         layer.pool_bias, layer.served_bias = saved
     out["peak_tflops"], out["useful_flops"] = peak, PREFILL_FLOPS
-    out["kernel"] = "prefill_projection_kernel (tcgen05.mma kind::i8, A from tensor memory, two int8 MMAs per bf16-equivalent product)"
+    out["kernel"] = "prefill_projection_kernel (tcgen05.mma kind::i8, A decoded into tensor memory, B by TMA boxes into swizzled shared memory, two int8 MMAs per bf16-equivalent product)"
     threads = os.cpu_count() or 1
     cpu_s = cpu_expert_sample(layer, threads)
     out["cpu_baseline"] = {"seconds_per_expert": round(cpu_s, 3), "routes": 64, "cores": threads, "kind": "port",
