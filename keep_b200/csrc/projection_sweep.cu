@@ -69,7 +69,7 @@ __device__ __forceinline__ uint32_t sw_word(const uint4& v) {
 // `status` (may be null) is set to 2 if the shared window does not have the expected shape.
 // RAGGED: the output rows are not a multiple of a unit's rows, so the last unit of a group clamps its row indices.
 template <int M, unsigned TABLE_STEPS, int DEPTH, bool RAGGED>
-__global__ void __launch_bounds__(SW_THREADS, 1) projection_sweep_kernel(FastProjectionArgs p, int32_t* status) {
+__global__ void __launch_bounds__(SW_THREADS, 1) projection_sweep_kernel(FastProjectionArgs p, int32_t* status, int ks) {
   extern __shared__ __align__(16) uint8_t smem[];
   grid_launch_dependents();
   // A unit is two MMA row tiles: the same 16 rows of the gate and of the up matrix (M = 2), or 32
@@ -116,10 +116,11 @@ __global__ void __launch_bounds__(SW_THREADS, 1) projection_sweep_kernel(FastPro
   const int64_t N = p.out_dim, cw = p.in_dim / 8;
   const int n_chunks = static_cast<int>(cw / SW_CHUNK);
   const int chunks_per_group = n_chunks / static_cast<int>(p.groups);
-  // warps per row set: as many k parts as the chunks give, in powers of two
-  const int ks = n_chunks >= 12 ? 16 : n_chunks >= 6 ? 8 : n_chunks >= 3 ? 4 : n_chunks >= 2 ? 2 : 1;
+  // `ks` warps per row set (the host picks it from the number of chunks, sweep_k_parts below);
+  // warps beyond row_sets * ks have no units and only help with the epilogues
   const int row_sets = SW_WARPS / ks;
   const int row_set = warp / ks, k_part = warp - row_set * ks;
+  const bool spare = row_set >= row_sets;
   const int c_first = k_part * n_chunks / ks, c_end = (k_part + 1) * n_chunks / ks;
   const int my_chunks = c_end - c_first;
   const int units_per_group = static_cast<int>((N + ROWS - 1) / ROWS);
@@ -147,7 +148,7 @@ __global__ void __launch_bounds__(SW_THREADS, 1) projection_sweep_kernel(FastPro
     w.codes = codes0 + static_cast<uint64_t>(w.slot_rows + w.tile * ROWS) * row_bytes + lane_offset;
   };
   auto start_walk = [&](Walk& w) {
-    w.u = u_begin + row_set;
+    w.u = spare ? u_end : u_begin + row_set;
     w.gi = w.u / units_per_group;
     w.tile = w.u - w.gi * units_per_group;
     w.c = c_first;
@@ -204,7 +205,8 @@ __global__ void __launch_bounds__(SW_THREADS, 1) projection_sweep_kernel(FastPro
   };
   const int local_units = u_end - u_begin;
   const int per_pass = SW_PASS_UNITS * row_sets;  // units of the CTA per pass
-  const uint32_t red_mine = red_base + ((row_set * ks + k_part) * 128u + lane) * 4u;  // + (j * 16 warps * 4 + v) * 128 bytes
+  const uint32_t red_mine = red_base + ((row_set * ks + k_part) * 128u + lane) * 4u;  // + j * pass_stride + v * 128 bytes
+  const uint32_t pass_stride = static_cast<uint32_t>(row_sets * ks) * 512u;         // one partial tile per (unit, k part)
   for (int pass_first = 0; pass_first < local_units; pass_first += per_pass) {
     // ---- this warp's units of the pass: the partial sums of unit j go straight to their place in
     // shared memory, so the loop stays rolled (unrolled eight times it did not fit the instruction cache)
@@ -271,7 +273,7 @@ __global__ void __launch_bounds__(SW_THREADS, 1) projection_sweep_kernel(FastPro
       }
 #pragma unroll
       for (int v = 0; v < VALUES; ++v)
-        asm volatile("st.shared.f32 [%0], %1;" ::"r"(red_mine + j * (SW_WARPS * 512u) + v * 128u), "f"(part[v]) : "memory");
+        asm volatile("st.shared.f32 [%0], %1;" ::"r"(red_mine + j * pass_stride + v * 128u), "f"(part[v]) : "memory");
       next_unit(at);
     }
 
@@ -339,6 +341,21 @@ __global__ void __launch_bounds__(SW_THREADS, 1) projection_sweep_kernel(FastPro
 
 bool sweep_supported(int64_t in_dim) { return in_dim % (8 * SW_CHUNK) == 0; }
 
+// Warps per row set for `n_chunks` chunks of inputs: the split that keeps most of the 16 warps busy.
+// A warp with one chunk per unit keeps its slice of the activations in registers; with more it
+// re-reads a slice per chunk (scattered reads: about a fifth slower, measured), so e.g. 16 chunks
+// are 16 parts of one, 20 chunks four parts of five (not sixteen of one or two), 9 chunks three of three.
+static int sweep_k_parts(int n_chunks) {
+  int best = 1;
+  double best_score = 0.0;
+  for (int ks = 1; ks <= SW_WARPS && ks <= n_chunks; ++ks) {
+    const int most = (n_chunks + ks - 1) / ks, row_sets = SW_WARPS / ks;
+    const double score = static_cast<double>(n_chunks) / (ks * most) * (ks * row_sets) / SW_WARPS * (most == 1 ? 1.0 : 0.8);
+    if (score >= best_score) { best_score = score; best = ks; }
+  }
+  return best;
+}
+
 template <int M, unsigned TABLE_STEPS, int DEPTH, bool RAGGED>
 static int launch_sweep_kernel(const FastProjectionArgs& p, cudaStream_t s) {
   auto kernel = projection_sweep_kernel<M, TABLE_STEPS, DEPTH, RAGGED>;
@@ -358,7 +375,7 @@ static int launch_sweep_kernel(const FastProjectionArgs& p, cudaStream_t s) {
     }
     sms = cached_sms[dev];
   }
-  cudaError_t err = launch_after(true, kernel, sms, SW_THREADS, SW_SMEM_BYTES, s, p, p.status);
+  cudaError_t err = launch_after(true, kernel, sms, SW_THREADS, SW_SMEM_BYTES, s, p, p.status, sweep_k_parts(static_cast<int>(p.in_dim / (8 * SW_CHUNK))));
   if (err != cudaSuccess) return note_cuda_error(err);
   return KEEPVQ_OK;
 }
