@@ -517,7 +517,7 @@ extern "C" void keepvq_diag_read_timers(unsigned long long* out) {  // host arra
 
 // The tensor map of a projection's quantised activations: a [2 * (rows + 1), in_dim] byte matrix
 // (the high-byte plane over the low-byte plane), boxes of 16 rows x 128 bytes, 128-byte swizzle.
-// This GPU's own memory only; no multicast anywhere.
+// The map covers this GPU's own scratch memory only.
 static int activation_map(const FastProjectionArgs& p, CUtensorMap* map) {
   typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
                                   CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
