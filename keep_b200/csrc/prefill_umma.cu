@@ -35,7 +35,7 @@
 //                its low bytes are two runs of rows of one [2 x rows, K] byte matrix, and a K block
 //                of them is a handful of cp.async.bulk.tensor.2d boxes of 16 rows x 128 bytes that
 //                land swizzled, ready for the MMA; the boxes report to the stage's mbarrier
-//                (expect_tx / complete_tx).  Warps 18-19 have nothing to do.
+//                (expect_tx / complete_tx).
 // mbarrier full/empty pairs carry every dependency.  Every wait is bounded by a deadline on the
 // global timer: on expiry the CTA raises a flag in `status`, stops issuing work, waits (bounded)
 // for the MMAs in flight, frees its tensor memory and returns.
@@ -48,12 +48,9 @@ namespace fast {
 
 constexpr int PF_DECODE_WARPS = 16;
 constexpr int PF_MMA_WARP = PF_DECODE_WARPS;
-constexpr int PF_B_WARPS = 3;
-constexpr int PF_THREADS = (PF_DECODE_WARPS + 1 + PF_B_WARPS) * 32;  // 640
+constexpr int PF_THREADS = (PF_DECODE_WARPS + 2) * 32;  // 576: decode warps, the MMA warp, the TMA warp
 constexpr int PF_A_STAGES = 2;                  // in tensor memory: 32 columns per tile and stage
 constexpr int PF_B_STAGES = 3;
-constexpr int PF_B_LAG = 1;                     // K blocks of activation copies in flight behind the one being published
-static_assert(PF_B_LAG >= 1 && PF_B_LAG <= PF_B_STAGES - 2 && PF_B_LAG <= 2, "see the loader's publication rule");
 constexpr int PF_N_MAX = PREFILL_GROUP_ROUTES;  // routes per item
 static_assert(PF_N_MAX % 16 == 0, "an item's routes pad to a multiple of sixteen columns");
 constexpr int PF_ROWS = 128;                    // output rows per tile
@@ -106,10 +103,6 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint64_
 __device__ __forceinline__ uint64_t umma_desc(uint32_t tile_addr) {
   return static_cast<uint64_t>((tile_addr & 0x3FFFFu) >> 4) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
 }
-__device__ __forceinline__ uint32_t swizzled(uint32_t row, uint32_t chunk) {  // byte offset of a 16-byte chunk
-  return (row >> 3) * 1024u + (row & 7u) * 128u + ((chunk ^ (row & 7u)) << 4);
-}
-
 // A operand in tensor memory: row m of the tile in lane m, K packed along the columns (four int8 per column).  B: shared-memory descriptor.
 __device__ __forceinline__ void umma_i8_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
   asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
@@ -161,7 +154,7 @@ __device__ unsigned long long g_pf_timers[16];
 // GLU: the M = 2 A tiles are the gate and the up matrix over the same 128 rows, fused by SwiGLU.
 // !GLU: the M tiles are consecutive 128-row tiles of one matrix, so an item covers 128 * M rows
 // and its activation (B) stages serve all of them (the copies are what bounds a single projection).
-// `stall` != 0 is the wait self-test: the activation loaders never publish, so the MMA issuer's
+// `stall` != 0 is the wait self-test: the activation loader never publishes, so the MMA issuer's
 // first wait runs into the deadline.
 template <int M, bool GLU>
 __global__ void __launch_bounds__(PF_THREADS, 1) prefill_projection_kernel(FastProjectionArgs p, const __grid_constant__ CUtensorMap x_map, int32_t* status, int diag, int stall, uint64_t wait_ns) {
@@ -567,7 +560,7 @@ int prefill_gate_up(const FastProjectionArgs& p, int32_t* status, cudaStream_t s
 int prefill_down(const FastProjectionArgs& p, int32_t* status, cudaStream_t s) {
   return p.out_dim > PF_ROWS ? launch_prefill<2, false>(p, status, s) : launch_prefill<1, false>(p, status, s);
 }
-// One CTA of the single-projection kernel whose activation loaders never publish, with a short
+// One CTA of the single-projection kernel whose activation loader never publishes, with a short
 // deadline: the wait runs out, the CTA reports and returns.  `p` must describe a valid problem.
 int prefill_wait_selftest(const FastProjectionArgs& p, int32_t* status, uint64_t wait_ns, cudaStream_t s) {
   return launch_prefill<1, false>(p, status, s, 1, wait_ns, 1);
