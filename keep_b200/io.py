@@ -6,6 +6,11 @@ The reference writes one ``layer-NN.npz`` per MoE layer: an uncompressed zip of
 and serves from it with positional reads of one expert's slab at a time
 (``scripts/v41_build/omlx_lattice.py:115-150``).
 
+``PoolFile`` reads the JSON that describes a pool wider than the loaded checkpoint
+(``scripts/v41_build/omlx_lattice.py:22-30,461-480``): which directory and which position in its
+layer files holds each expert of the pool, the pool's router rows, and the order in which the
+residents start out.
+
 ``LayerFile`` finds each array inside the zip once and then hands out experts as views of a memory
 map (no decompression, no whole-file read): the bytes an installer copies into a slot are the
 file's own bytes.  ``store`` materialises the whole layer in (pinned) host memory for
@@ -170,3 +175,75 @@ def load_quantized_vq_switch_linear(path, prefix: str, device):
         codebook = get("model.vq_codebook.e8")
     return QuantizedVQSwitchLinear(input_dims=in_dim, output_dims=out_dim, num_experts=experts, codes=codes, scales=scales,
                                    codebook=codebook, bias=bias, group_size=group_size, code_bits=code_bits)
+
+
+class PoolFile:
+    """A pool wider than the loaded checkpoint, as the reference's ``wide_pool`` reads it
+    (``scripts/v41_build/omlx_lattice.py:22-30,461-480``).  The file is JSON::
+
+        {"codes": [[CODES_DIR, IDS.json], ...], "router": "router.safetensors", "mass": "reap-stats.npz",
+         "residual": DIR, "hot": H}            # the last two are optional (the 8-bit residual tier)
+
+    ``IDS.json`` (``{"survivors": {layer: [...]}}``) gives the pool number of each expert of its
+    directory in file order; ``router`` holds ``layers.N.ffn.gate.weight`` / ``.bias`` for every
+    expert of the pool; ``mass`` (``reap__gate_norm_sum`` ``[layers, pool]``) orders the starting
+    residents.  Paths inside the file are relative to it.
+
+    Attributes: ``directories`` (paths), ``where[layer][expert] = (directory index, position in
+    that directory's layer file)``, ``order[layer]`` (experts by descending mass, ties to the lower
+    number), ``residual`` (path or None) and ``hot`` (0 without a residual directory;
+    ``OMLX_LATTICE_HOT`` overrides the file, as in the reference).
+    """
+
+    def __init__(self, path):
+        import json
+        import os
+
+        self.path = Path(path)
+        spec = json.loads(self.path.read_text())
+        at = lambda p: self.path.parent / Path(p).expanduser()  # noqa: E731
+        self.directories = [at(d) for d, _ in spec["codes"]]
+        ids = [json.loads(at(f).read_text())["survivors"] for _, f in spec["codes"]]
+        layers = len(ids[0])
+        self.where = [{int(e): (d, j) for d, per in enumerate(ids) for j, e in enumerate(per[str(i)])} for i in range(layers)]
+        self.first_directory = [[int(e) for e in ids[0][str(i)]] for i in range(layers)]  # the loaded checkpoint's experts, file order
+        mass = np.load(at(spec["mass"]))["reap__gate_norm_sum"]
+        self.pool = int(mass.shape[1])
+        if mass.shape[0] < layers or any(sorted(w) != list(range(self.pool)) for w in self.where):
+            raise ValueError(f"{self.path}: the directories do not cover the pool once")
+        self.order = [np.argsort(-mass[i], kind="stable").tolist() for i in range(layers)]
+        self._router_path = at(spec["router"])
+        self.residual = at(spec["residual"]) if "residual" in spec else None
+        self.hot = int(os.environ.get("OMLX_LATTICE_HOT", spec.get("hot", 0))) if self.residual is not None else 0
+        if self.hot == 0:
+            self.residual = None
+
+    def router(self, layer: int, device="cpu") -> tuple[torch.Tensor, torch.Tensor | None]:
+        """(weight ``[pool, hidden]``, bias ``[pool]`` or None) of the pool's router for one layer."""
+        from safetensors import safe_open
+
+        with safe_open(str(self._router_path), framework="pt", device="cpu") as f:
+            names = set(f.keys())
+            weight = f.get_tensor(f"layers.{layer}.ffn.gate.weight").to(device)
+            bias = f.get_tensor(f"layers.{layer}.ffn.gate.bias").to(device) if f"layers.{layer}.ffn.gate.bias" in names else None
+        if int(weight.shape[0]) != self.pool:
+            raise ValueError(f"{self._router_path}: layer {layer} has {int(weight.shape[0])} router rows for a pool of {self.pool}")
+        return weight, bias
+
+    def check_loaded_router(self, layer: int, weight: torch.Tensor, bias: torch.Tensor | None = None) -> None:
+        """The loaded checkpoint's router rows must be the first directory's rows of the pool router."""
+        full_w, full_b = self.router(layer)
+        rows = torch.tensor(self.first_directory[layer], dtype=torch.long)
+        if not torch.equal(full_w[rows], weight.cpu()):
+            raise ValueError(f"layer {layer}: router weight differs from the pool file's")
+        if bias is not None and full_b is not None and not torch.equal(full_b[rows], bias.cpu()):
+            raise ValueError(f"layer {layer}: router bias differs from the pool file's")
+
+    def layer_file(self, layer: int, expert: int) -> tuple[Path, int]:
+        """(path of the ``layer-NN.npz`` that holds the expert, its position in that file)."""
+        directory, position = self.where[layer][int(expert)]
+        return self.directories[directory] / f"layer-{layer:02d}.npz", position
+
+    def starting_residents(self, layer: int, slots: int) -> list[int]:
+        """The ``slots`` experts a layer starts out with: the heaviest by ``mass``."""
+        return self.order[layer][:slots]

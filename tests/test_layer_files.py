@@ -81,3 +81,45 @@ def test_a_checkpoint_with_a_rotation_or_residual_sidecar_is_refused(tmp_path, s
     save_file(tensors, str(path))
     with pytest.raises(NotImplementedError, match=sidecar):
         layer_io.load_quantized_vq_switch_linear(path, "m.w", "cpu")
+
+
+def test_pool_file_maps_every_expert_and_orders_the_residents(tmp_path, monkeypatch):
+    """The JSON of a pool wider than the loaded checkpoint (scripts/v41_build/omlx_lattice.py:22-30,461-480):
+    two directories of experts, the pool's router, the mass that orders the starting residents."""
+    import json
+
+    from safetensors.torch import save_file
+
+    layers, pool, hidden = 2, 6, 16
+    (tmp_path / "a").mkdir()
+    (tmp_path / "b").mkdir()
+    first = {"0": [4, 1, 5], "1": [0, 2, 3]}    # the loaded checkpoint's experts, in file order
+    second = {"0": [0, 2, 3], "1": [5, 4, 1]}
+    (tmp_path / "a" / "ids.json").write_text(json.dumps({"survivors": first}))
+    (tmp_path / "b" / "ids.json").write_text(json.dumps({"survivors": second}))
+    gen = torch.Generator().manual_seed(0)
+    router = {f"layers.{i}.ffn.gate.weight": torch.randn((pool, hidden), generator=gen) for i in range(layers)}
+    router.update({f"layers.{i}.ffn.gate.bias": torch.randn((pool,), generator=gen) for i in range(layers)})
+    save_file(router, str(tmp_path / "router.safetensors"))
+    mass = np.array([[1.0, 5.0, 2.0, 5.0, 0.5, 3.0], [6.0, 1.0, 2.0, 3.0, 4.0, 5.0]])
+    np.savez(tmp_path / "stats.npz", reap__gate_norm_sum=mass)
+    spec = {"codes": [["a", "a/ids.json"], ["b", "b/ids.json"]], "router": "router.safetensors", "mass": "stats.npz", "residual": "res", "hot": 2}
+    (tmp_path / "pool.json").write_text(json.dumps(spec))
+    monkeypatch.delenv("OMLX_LATTICE_HOT", raising=False)
+    pool_file = layer_io.PoolFile(tmp_path / "pool.json")
+    assert pool_file.pool == pool and pool_file.hot == 2 and pool_file.residual == tmp_path / "res"
+    assert pool_file.where[0][5] == (0, 2) and pool_file.where[0][3] == (1, 2) and pool_file.where[1][4] == (1, 1)
+    assert pool_file.layer_file(1, 4) == (tmp_path / "b" / "layer-01.npz", 1)
+    assert pool_file.order[0] == [1, 3, 5, 2, 0, 4]            # descending mass, ties to the lower number
+    assert pool_file.starting_residents(1, 3) == [0, 5, 4]
+    weight, bias = pool_file.router(0)
+    assert torch.equal(weight, router["layers.0.ffn.gate.weight"]) and torch.equal(bias, router["layers.0.ffn.gate.bias"])
+    pool_file.check_loaded_router(0, weight[[4, 1, 5]], bias[[4, 1, 5]])
+    with pytest.raises(ValueError, match="differs"):
+        pool_file.check_loaded_router(0, weight[[4, 1, 0]])
+    monkeypatch.setenv("OMLX_LATTICE_HOT", "1")
+    assert layer_io.PoolFile(tmp_path / "pool.json").hot == 1
+    # a pool the directories do not cover exactly once is refused
+    (tmp_path / "b" / "ids.json").write_text(json.dumps({"survivors": {"0": [0, 2, 2], "1": [5, 4, 1]}}))
+    with pytest.raises(ValueError, match="cover the pool once"):
+        layer_io.PoolFile(tmp_path / "pool.json")
