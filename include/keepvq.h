@@ -27,7 +27,7 @@
 extern "C" {
 #endif
 
-#define KEEPVQ_ABI_VERSION 2
+#define KEEPVQ_ABI_VERSION 3
 
 typedef enum keepvq_status {
   KEEPVQ_OK = 0,
@@ -268,6 +268,12 @@ typedef struct keepvq_moe_layer_args {
      rows are mostly dead (the fixed-capacity blocks of an expert-parallel exchange) says so here;
      it only picks between kernel families (few or many routes per expert), never the result. */
   int64_t expected_routes;
+  /* [tokens, hidden] fp32, 16-byte aligned, or NULL: the shared expert's output before rounding.
+     The pick sum adds it in fp32 after the picks and rounds once,
+     out[t] = round(sum_j down[t, j] + shared[t]), which is what the reference's shared down kernel
+     does from the other side (it adds the routed sum to its own dot and rounds to bf16,
+     scripts/v41_build/omlx_lattice.py:372-389). */
+  const float* shared;
 } keepvq_moe_layer_args;
 
 /* Bytes of scratch keepvq_moe_decode_layer needs for these sizes (host arithmetic only). */

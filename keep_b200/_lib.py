@@ -86,7 +86,7 @@ class MoELayerArgs(Structure):
         ("hot_of_slot", c_void_p), ("swiglu_limit", c_float), ("codebook_all_odd", c_int32),
         ("out", c_void_p), ("served_expert", c_void_p), ("served_slot", c_void_p), ("served_weight", c_void_p),
         ("want", c_void_p), ("want_score", c_void_p), ("admit", c_void_p),
-        ("workspace", c_void_p), ("workspace_bytes", c_int64), ("expected_routes", c_int64),
+        ("workspace", c_void_p), ("workspace_bytes", c_int64), ("expected_routes", c_int64), ("shared", c_void_p),
     ]
 
 

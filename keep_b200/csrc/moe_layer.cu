@@ -93,11 +93,14 @@ __global__ void __launch_bounds__(256) swiglu_weight_kernel(const T* __restrict_
   }
 }
 
-// out[t, d] = round(sum_j float(down[t*k + j, d])), summed in pick order.  A pick without a slot
-// adds nothing (the grouped kernels never touch its row of `down`).
+// out[t, d] = round(sum_j float(down[t*k + j, d]) + shared[t, d]), summed in pick order.  A pick
+// without a slot adds nothing (the grouped kernels never touch its row of `down`).  `shared` (may
+// be null) is the shared expert's fp32 output: it joins the routed sum before the one rounding, as
+// the reference's shared down kernel adds the routed sum and rounds once
+// (scripts/v41_build/omlx_lattice.py:372-389).
 template <typename T>
 __global__ void __launch_bounds__(256) combine_kernel(const T* __restrict__ down, const uint32_t* __restrict__ served_slot, int64_t slots,
-                                                      T* __restrict__ out, int64_t tokens, int64_t hidden, int top_k) {
+                                                      const float* __restrict__ shared, T* __restrict__ out, int64_t tokens, int64_t hidden, int top_k) {
   grid_launch_dependents();
   grid_wait();
   const int64_t vectors = hidden / 8, total = tokens * vectors;  // eight values (16 or 32 bytes) per thread and step
@@ -110,6 +113,10 @@ __global__ void __launch_bounds__(256) combine_kernel(const T* __restrict__ down
       load8_as_float<T>(down + (t * top_k + j) * hidden + d, v);
 #pragma unroll
       for (int q = 0; q < 8; ++q) y[q] += v[q];
+    }
+    if (shared) {
+      const float4 lo = *reinterpret_cast<const float4*>(shared + t * hidden + d), hi = *reinterpret_cast<const float4*>(shared + t * hidden + d + 4);
+      y[0] += lo.x; y[1] += lo.y; y[2] += lo.z; y[3] += lo.w; y[4] += hi.x; y[5] += hi.y; y[6] += hi.z; y[7] += hi.w;
     }
     store8_from_float<T>(out + t * hidden + d, y);
   }
@@ -128,7 +135,7 @@ static void launch_elementwise(const keepvq_moe_layer_args& a, const LayerScratc
     const int64_t total = a.tokens * (a.hidden / 8);
     const unsigned blocks = static_cast<unsigned>(std::min<int64_t>((total + 255) / 256, 148 * 16));
     launch_after(a.tokens <= 256, combine_kernel<T>, blocks, 256, 0, s, reinterpret_cast<const T*>(ws + sc.down), static_cast<const uint32_t*>(a.served_slot), a.slots,
-                 reinterpret_cast<T*>(a.out), a.tokens, a.hidden, static_cast<int>(a.top_k));
+                 a.shared, reinterpret_cast<T*>(a.out), a.tokens, a.hidden, static_cast<int>(a.top_k));
   }
 }
 
@@ -183,7 +190,7 @@ extern "C" int keepvq_moe_decode_stages(const keepvq_moe_layer_args* args, int32
   if (!a.served_expert || !a.served_slot || !a.served_weight || !a.want || !a.want_score) return KEEPVQ_ERR_NULL;
   if (a.w1.groups <= 0 || a.w3.groups != a.w1.groups || a.w2.groups <= 0) return KEEPVQ_ERR_SHAPE;
   const LayerScratch sc = plan_scratch(a.tokens, a.hidden, a.inter, a.pool, a.top_k);
-  if (!aligned_to(a.workspace, 256)) return KEEPVQ_ERR_ALIGN;
+  if (!aligned_to(a.workspace, 256) || (a.shared && !aligned_to(a.shared, 16))) return KEEPVQ_ERR_ALIGN;
   if (a.workspace_bytes < sc.total) return KEEPVQ_ERR_CAPACITY;
   char* ws = reinterpret_cast<char*>(a.workspace);
   cudaStream_t s = static_cast<cudaStream_t>(stream);

@@ -6,6 +6,11 @@ reference's decode step (``scripts/v41_build/omlx_lattice.py:327-371``: stock ga
 mask, for ``QuantizedVQSwitchGLU`` plus the weighted sum
 (``src/ramp/models/glm4_moe_adapter.py:367-372``, ``deepseek_v4_flash_adapter.py:1781-1784``).
 Everything runs in ``keepvq_moe_decode_layer``: one launch sequence, no host read.
+
+``SharedExpert`` is the dense shared expert next to it (``deepseek_v4_flash_adapter.py:1733-1784``):
+its fp32 output goes into ``decode(x, shared=...)``, where the pick sum adds it before the one
+rounding (the reference's shared down kernel adds the routed sum and rounds once,
+``scripts/v41_build/omlx_lattice.py:372-389``).
 """
 
 from __future__ import annotations
@@ -34,6 +39,40 @@ class Projection:
             codes=_lib.ptr(self.codes), scales=_lib.ptr(self.scales), groups=int(self.scales.shape[2]),
             res_codes=_lib.ptr(self.res_codes), res_scales=_lib.ptr(self.res_scales),
             res_groups=int(self.res_scales.shape[2]) if self.res_scales is not None else 0)
+
+
+class SharedExpert:
+    """The dense shared expert of a layer: ``w2 (silu(w1 x) * (w3 x))`` with the same clamp as the
+    routed experts (``deepseek_v4_flash_adapter.py:963-967,1733-1737``), returned in fp32 and NOT
+    rounded, for ``RoutedMoELayer.decode(x, shared=...)`` to add to the routed sum.
+
+    ``w1`` (gate), ``w3`` (up): ``[inter, hidden]``; ``w2`` (down): ``[hidden, inter]``, fp16 or
+    bf16.  The three products are plain library GEMMs with fp32 accumulation; gate and up run as one
+    GEMM over the stacked weights.  The reference's shared expert runs on oMLX's MXFP4 / MXFP8 /
+    affine kernels, a third-party package that is not part of it: a caller holding such weights
+    expands them to 16 bits first, and no parity with those kernels is claimed.
+    """
+
+    def __init__(self, w1: torch.Tensor, w3: torch.Tensor, w2: torch.Tensor, *, swiglu_limit: float = 0.0):
+        self.device = _lib.require_cuda(w1, w3, w2)
+        if w1.dtype not in (torch.float16, torch.bfloat16) or w3.dtype != w1.dtype or w2.dtype != w1.dtype:
+            raise ValueError("shared expert weights must share one of fp16 / bf16")
+        self.inter, self.hidden = (int(v) for v in w1.shape)
+        if tuple(w3.shape) != tuple(w1.shape) or tuple(w2.shape) != (self.hidden, self.inter):
+            raise ValueError("w1/w3 must be [inter, hidden] and w2 [hidden, inter]")
+        self.gate_up = torch.cat([w1, w3], 0).t().contiguous()  # [hidden, 2 inter]
+        self.down = w2.t().contiguous()                          # [inter, hidden]
+        self.swiglu_limit = float(swiglu_limit)
+
+    def __call__(self, x: torch.Tensor) -> torch.Tensor:
+        """``x`` [tokens, hidden] in the weights' dtype -> fp32 ``[tokens, hidden]``."""
+        if x.ndim != 2 or int(x.shape[1]) != self.hidden or x.dtype != self.down.dtype:
+            raise ValueError(f"x must be [tokens, {self.hidden}] {self.down.dtype}, found {tuple(x.shape)} {x.dtype}")
+        gate, up = torch.mm(x, self.gate_up, out_dtype=torch.float32).split(self.inter, dim=1)
+        if self.swiglu_limit > 0:
+            gate, up = gate.clamp(max=self.swiglu_limit), up.clamp(-self.swiglu_limit, self.swiglu_limit)
+        h = (torch.nn.functional.silu(gate) * up).to(x.dtype)   # the hidden row in 16 bits, as the routed experts keep theirs
+        return torch.mm(h, self.down, out_dtype=torch.float32)
 
 
 class RoutedMoELayer:
@@ -104,7 +143,7 @@ class RoutedMoELayer:
                 routing=Routing(served_expert=i32(), served_slot=i32(), served_weight=f32(), want=i32(), want_score=f32(), admit=i32()))
         return self._buffers[key]
 
-    def _layer_args(self, x, out, r: Routing, *, workspace, nbytes, expected_routes: int = 0) -> _lib.MoELayerArgs:
+    def _layer_args(self, x, out, r: Routing, *, workspace, nbytes, expected_routes: int = 0, shared=None) -> _lib.MoELayerArgs:
         """The argument struct of a layer call over the caller's tensors."""
         return _lib.MoELayerArgs(
             x=_lib.ptr(x), x_dtype=_lib.dtype_tag(x.dtype), tokens=int(x.shape[0]), hidden=self.hidden, inter=self.inter,
@@ -118,7 +157,8 @@ class RoutedMoELayer:
             codebook_all_odd=int(self.codebook_all_odd),
             out=_lib.ptr(out), served_expert=_lib.ptr(r.served_expert), served_slot=_lib.ptr(r.served_slot),
             served_weight=_lib.ptr(r.served_weight), want=_lib.ptr(r.want), want_score=_lib.ptr(r.want_score),
-            admit=_lib.ptr(r.admit), workspace=_lib.ptr(workspace), workspace_bytes=nbytes, expected_routes=int(expected_routes))
+            admit=_lib.ptr(r.admit), workspace=_lib.ptr(workspace), workspace_bytes=nbytes, expected_routes=int(expected_routes),
+            shared=_lib.ptr(shared))
 
     def _scratch_rows(self, which: str, width: int, tokens: int, dtype: torch.dtype, state: int) -> torch.Tensor:
         buf = self._buffers_for(tokens, dtype, state)
@@ -198,7 +238,7 @@ class RoutedMoELayer:
         return out, routing
 
     def decode(self, x: torch.Tensor, *, out: torch.Tensor | None = None, stages: int = _lib.STAGE_ALL,
-               state: int = 0, expected_routes: int = 0) -> tuple[torch.Tensor, Routing]:
+               state: int = 0, expected_routes: int = 0, shared: torch.Tensor | None = None) -> tuple[torch.Tensor, Routing]:
         """``x`` [tokens, hidden] -> (``[tokens, hidden]`` in x's dtype, routing outputs).
 
         Buffers are cached per (tokens, dtype) and reused by the next call of the same shape, so
@@ -207,17 +247,22 @@ class RoutedMoELayer:
         call left behind; profilers and the benchmark use it.  ``state`` picks one of several
         independent buffer sets (each keeps its own scratch and outputs).  ``expected_routes`` (0 =
         all) tells the library how many of the ``tokens * top_k`` routes the caller expects to be
-        live, which only picks the kernel family.
+        live, which only picks the kernel family.  ``shared`` (fp32 ``[tokens, hidden]``, e.g. a
+        ``SharedExpert``'s output) is added to the routed sum before the one rounding.
         """
         _lib.require_cuda(x)
         if x.ndim != 2 or int(x.shape[1]) != self.hidden:
             raise ValueError(f"x must be [tokens, {self.hidden}], found {tuple(x.shape)}")
         x = x.contiguous()
         tokens = int(x.shape[0])
+        if shared is not None:
+            _lib.require_cuda(shared)
+            if shared.dtype != torch.float32 or tuple(shared.shape) != (tokens, self.hidden) or not shared.is_contiguous():
+                raise ValueError(f"shared must be a contiguous fp32 [{tokens}, {self.hidden}] tensor")
         buf = self._buffers_for(tokens, x.dtype, state)
         r: Routing = buf["routing"]
         target = buf["out"] if out is None else out
-        args = self._layer_args(x, target, r, workspace=buf["workspace"], nbytes=buf["nbytes"], expected_routes=expected_routes)
+        args = self._layer_args(x, target, r, workspace=buf["workspace"], nbytes=buf["nbytes"], expected_routes=expected_routes, shared=shared)
         with torch.cuda.device(self.device):
             _lib.check(_lib.load().keepvq_moe_decode_stages(args, int(stages), _lib.stream_handle(self.device)), "keepvq_moe_decode_stages")
         return target, r

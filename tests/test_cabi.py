@@ -26,7 +26,7 @@ def test_library_exports_every_declared_symbol():
     for name in declared_entry_points():
         assert hasattr(lib, name), f"libkeepvq.so lacks {name}"
     assert sorted(declared_entry_points()) == _lib.exported_names(), "ctypes table and header disagree"
-    assert lib.keepvq_abi_version() == 2
+    assert lib.keepvq_abi_version() == 3
     assert lib.keepvq_status_string(-2).decode() == "inconsistent sizes"
 
 

@@ -244,3 +244,37 @@ def test_a_wait_that_nothing_satisfies_runs_out_and_the_kernel_returns(cuda):
     grid = vq.decode_weight_matrix(codes[0], torch.ones((128, 1), dtype=torch.float16, device=cuda), code_bits=16)
     assert torch.isfinite(grid).all()
     assert lib.keepvq_wait_selftest(_lib.ptr(ws), nbytes, 0, _lib.stream_handle(cuda)) == -2  # a deadline is mandatory (and at most a second)
+
+
+@pytest.mark.parametrize("tokens,hidden,inter", [(1, 256, 128), (7, 512, 256), (300, 512, 256)])
+def test_shared_expert_joins_the_routed_sum_before_the_one_rounding(cuda, tokens, hidden, inter):
+    """``decode(x, shared=s)``: out = bf16(sum over the picks of the routes' bf16 outputs, in pick
+    order, + s), fp32 throughout (scripts/v41_build/omlx_lattice.py:372-389 rounds once, after the
+    shared down kernel has added the routed sum).  Checked to the bit against the routes' outputs
+    the call leaves in its scratch; the dense shared expert itself against fp32 torch."""
+    from keep_b200 import moe
+
+    cfg = synthetic.layer(seed=31, experts=8, hidden=hidden, inter=inter)
+    x = synthetic.tokens(32 + tokens, tokens, hidden).to(cuda)
+    layer = build_layer(cuda, cfg, top_k=3, swiglu_limit=7.0)
+    gen = torch.Generator().manual_seed(5)
+    w1, w3 = (torch.randn((inter, hidden), generator=gen).mul(hidden ** -0.5).to(torch.bfloat16).to(cuda) for _ in range(2))
+    w2 = torch.randn((hidden, inter), generator=gen).mul(inter ** -0.5).to(torch.bfloat16).to(cuda)
+    expert = moe.SharedExpert(w1, w3, w2, swiglu_limit=7.0)
+    s = expert(x)
+    assert s.dtype == torch.float32 and tuple(s.shape) == (tokens, hidden)
+    gate, up = x.float() @ w1.float().t(), x.float() @ w3.float().t()
+    h = (torch.nn.functional.silu(gate.clamp(max=7.0)) * up.clamp(-7.0, 7.0)).to(torch.bfloat16).float()
+    want_s = h @ w2.float().t()
+    assert e8.relative_gap(s.cpu().numpy(), want_s.cpu().numpy()) <= 1e-2
+
+    plain = layer.decode(x)[0].clone()
+    out, _ = layer.decode(x, shared=s)
+    routes = layer.route_outputs(tokens, torch.bfloat16).float().view(tokens, 3, hidden)
+    total = torch.zeros((tokens, hidden), dtype=torch.float32, device=cuda)
+    for j in range(3):
+        total = total + routes[:, j]
+    assert torch.equal(plain, total.to(torch.bfloat16))
+    assert torch.equal(out, (total + s).to(torch.bfloat16))
+    with pytest.raises(ValueError, match="shared must be"):
+        layer.decode(x, shared=s.to(torch.bfloat16))
