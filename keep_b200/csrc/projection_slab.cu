@@ -93,6 +93,29 @@ __device__ __forceinline__ void sk_mma(int (&c)[4], uint32_t a0, uint32_t a1, ui
       : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+__device__ __forceinline__ void sk_mma_u8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {  // A unsigned
+  asm("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// The nibble decoder.  Both tables hold an entry as eight 4-bit values in ONE word, u = q + 8 for the
+// abs table (even parity) and the XOR masks of the sign byte for the other (4-bit XOR on q + 8 is
+// the same as on q), 32 replicas each, interleaved in one 64 KB region on a 64 KB boundary:
+//   abs entry  at region + abs byte * 256 + lane * 4,   sign entry at region + 128 + sign byte * 256 + lane * 4,
+// so each address is one byte permute and each read one shared-memory wavefront (a quarter of what the
+// pair of 8-byte entries costs).  The operand bytes are u (0..15, an UNSIGNED A operand); the caller
+// takes 8 * sum(x') off the integer dot product to get back to sum(q x').
+template <bool ODD>
+__device__ __forceinline__ void decode_codeword_nibble(uint32_t word, uint32_t abs_lane, uint32_t sign_lane, uint32_t& lo, uint32_t& hi) {
+  uint32_t e, m;
+  asm("ld.shared.u32 %0, [%1];" : "=r"(e) : "r"(__byte_perm(word, abs_lane, ODD ? 0x7634 : 0x7614)));
+  asm("ld.shared.u32 %0, [%1];" : "=r"(m) : "r"(__byte_perm(word, sign_lane, ODD ? 0x7624 : 0x7604)));
+  const uint32_t x = e ^ m;
+  lo = x & 0x0F0F0F0Fu;
+  hi = (x >> 4) & 0x0F0F0F0Fu;
+}
+__device__ __forceinline__ uint32_t sk_pack_nibbles(uint2 v) { return (v.x & 0x0F0F0F0Fu) | ((v.y & 0x0F0F0F0Fu) << 4); }
+
 template <int I>
 __device__ __forceinline__ uint32_t sk_word(const uint4& v) {
   return (I >> 1) == 0 ? v.x : (I >> 1) == 1 ? v.y : (I >> 1) == 2 ? v.z : v.w;
@@ -108,8 +131,11 @@ __device__ __forceinline__ uint32_t sk_word(const uint4& v) {
 constexpr uint32_t SK_SPLIT_RED_OFF = 48 * 1024;          // from the start of the activation stage
 constexpr int SK_SPLIT_ITEMS_PER_CTA = 4;                 // items per CTA the split factor aims for
 
-template <int M, int TILES, int COLS, unsigned TABLE_STEPS, bool NESTED, bool WIDE_SIGN, bool SPLIT>
+// NIBBLE: the nibble decoder above on every step (plain layers, not the split form): TABLE_STEPS and
+// WIDE_SIGN play no part, and the activations start right behind the one table region.
+template <int M, int TILES, int COLS, unsigned TABLE_STEPS, bool NESTED, bool WIDE_SIGN, bool SPLIT, bool NIBBLE = false>
 __global__ void __launch_bounds__(SK_THREADS, 1) projection_slab_kernel(FastProjectionArgs p, int32_t* status) {
+  static_assert(!NIBBLE || (!NESTED && !WIDE_SIGN && !SPLIT), "the nibble decoder serves the plain form");
   static_assert(COLS == 4 || COLS == 8, "a group is four or eight routes");
   static_assert(!WIDE_SIGN || (COLS == 4 && !NESTED), "the wide sign table leaves room for eight activation columns of 4096 inputs");
   static_assert(!SPLIT || (COLS == 4 && !WIDE_SIGN), "the split form keeps its partial sums at the end of the 64 KB activation stage");
@@ -135,7 +161,13 @@ __global__ void __launch_bounds__(SK_THREADS, 1) projection_slab_kernel(FastProj
   // ---- tables -----------------------------------------------------------------------------
   // every thread computes one entry per pass; the warp then writes its 32 entries two at a time,
   // sixteen lanes storing the sixteen replicas of one entry side by side (no bank conflicts)
-  for (int e = threadIdx.x; e < 768; e += SK_THREADS) {
+  if (NIBBLE) {  // a warp writes the 32 replicas of an entry side by side
+    for (int e = threadIdx.x >> 5; e < 512; e += SK_WARPS) {
+      const uint32_t v = e < 256 ? sk_pack_nibbles(abs_table_entry(p.codebook[e], 0)) ^ 0x88888888u : sk_pack_nibbles(sign_table_entry(e - 256));
+      asm volatile("st.shared.u32 [%0], %1;" ::"r"(a0 + (e & 255) * 256 + (e >> 8) * 128 + (threadIdx.x & 31) * 4), "r"(v) : "memory");
+    }
+  }
+  for (int e = threadIdx.x; e < (NIBBLE ? 0 : 768); e += SK_THREADS) {
     uint32_t lo = 0, hi = 0;
     if (e >= 512 && NESTED) {  // residual entry: byte j of the low word is 2 * v[6 - 2j], of the high word 2 * v[7 - 2j]
       const uint32_t* row = p.res_table + (e - 512) * 4;
@@ -167,9 +199,9 @@ __global__ void __launch_bounds__(SK_THREADS, 1) projection_slab_kernel(FastProj
   grid_wait();  // the tables came from constants; everything below reads what earlier kernels of the stream wrote
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int g = lane >> 2, t = lane & 3;
-  const uint32_t abs_lane = a0 + static_cast<uint32_t>(lane & (SK_REPLICAS - 1)) * 8u;
-  const uint32_t second_lane = a0 + SK_SECOND_OFF + static_cast<uint32_t>(lane & (L::SECOND_REPLICAS - 1)) * 8u;
-  const uint32_t b_base = a0 + L::B_OFF;
+  const uint32_t abs_lane = NIBBLE ? a0 + lane * 4u : a0 + static_cast<uint32_t>(lane & (SK_REPLICAS - 1)) * 8u;
+  const uint32_t second_lane = NIBBLE ? a0 + 128u + lane * 4u : a0 + SK_SECOND_OFF + static_cast<uint32_t>(lane & (L::SECOND_REPLICAS - 1)) * 8u;
+  const uint32_t b_base = a0 + (NIBBLE ? SK_ABS_BYTES : L::B_OFF);
   constexpr int STAGE_BYTES = 4 * 512;                   // per warp
   const uint32_t ring = (warp < low_warps ? smem_base + warp * SK_WARP_RING : a0 + SK_RING_HIGH_OFF + (warp - low_warps) * SK_WARP_RING) + lane * 16;
   const int64_t N = p.out_dim, cw = p.in_dim / 8;
@@ -300,6 +332,7 @@ __global__ void __launch_bounds__(SK_THREADS, 1) projection_slab_kernel(FastProj
     // what the epilogue needs of this lane's routes, asked for now so that the loads fly behind
     // the main loop instead of in front of the stores
     int ep_route[RPL];
+    const int32_t* ep_sums[RPL];  // the lane's routes' sums of x' per scale group
     float ep_xs[RPL], ep_weight[RPL], ep_sum[RPL];
 #pragma unroll
     for (int cc = 0; cc < RPL; ++cc) {
@@ -308,12 +341,16 @@ __global__ void __launch_bounds__(SK_THREADS, 1) projection_slab_kernel(FastProj
       const int64_t xrow = ep_route[cc] < 0 ? p.x_zero_row : static_cast<int64_t>(ep_route[cc] / p.x_div);
       ep_xs[cc] = p.x.scale[xrow];
       ep_weight[cc] = (M == 2 && ep_route[cc] >= 0) ? p.route_weight[ep_route[cc]] : 1.0f;
-      ep_sum[cc] = static_cast<float>(p.x.sums[xrow * p.groups]);  // the only group when the rows have one scale
+      ep_sums[cc] = p.x.sums + xrow * p.groups;
+      ep_sum[cc] = static_cast<float>(ep_sums[cc][0]);  // the only group when the rows have one scale
     }
     float row_scale[M][TILES][2];  // the last scale group's scale of rows g and g + 8
 
     // accumulators -> fp32 partials at the end of a scale group
     auto close_group = [&](const void* const (&scales)[2], int64_t row_base, int64_t groups, int group, float (&into)[M][TILES][PARTS], bool keep_scale) {
+      uint32_t offset[RPL];  // 8 * sum(x') of the group: what the unsigned operand u = q + 8 added to the integer dot product
+#pragma unroll
+      for (int cc = 0; cc < RPL; ++cc) offset[cc] = NIBBLE ? 8u * static_cast<uint32_t>(ep_sums[cc][group]) : 0u;
 #pragma unroll
       for (int m = 0; m < M; ++m)
 #pragma unroll
@@ -333,7 +370,12 @@ __global__ void __launch_bounds__(SK_THREADS, 1) projection_slab_kernel(FastProj
                 hi = acc[0][0][m][tl][2 * rr + cc] + acc[0][1][m][tl][2 * rr + cc];
                 lo = acc[PLANES - 1][0][m][tl][2 * rr + cc] + acc[PLANES - 1][1][m][tl][2 * rr + cc];
               }
-              into[m][tl][rr * RPL + cc] = fmaf(sc, 256.0f * static_cast<float>(hi) + static_cast<float>(lo), into[m][tl][rr * RPL + cc]);
+              if (NIBBLE) {  // 256 hi + lo - 8 sum(x') in wrapping 32-bit arithmetic: the true value, sum(q x'), fits
+                const int dot = static_cast<int>(static_cast<uint32_t>(hi) * 256u + static_cast<uint32_t>(lo) - offset[cc]);
+                into[m][tl][rr * RPL + cc] = fmaf(sc, static_cast<float>(dot), into[m][tl][rr * RPL + cc]);
+              } else {
+                into[m][tl][rr * RPL + cc] = fmaf(sc, 256.0f * static_cast<float>(hi) + static_cast<float>(lo), into[m][tl][rr * RPL + cc]);
+              }
             }
 #pragma unroll
             for (int pl = 0; pl < PLANES; ++pl)
@@ -362,10 +404,17 @@ __global__ void __launch_bounds__(SK_THREADS, 1) projection_slab_kernel(FastProj
 #pragma unroll
           for (int tl = 0; tl < TILES; ++tl) {
             uint32_t a[4];
-            decode_codeword<TABLE, (I & 1) != 0, WIDE_SIGN>(sk_word<I>(cur[(m * TILES + tl) * 2]), abs_lane, second_lane, a[0], a[2]);      // row g
-            decode_codeword<TABLE, (I & 1) != 0, WIDE_SIGN>(sk_word<I>(cur[(m * TILES + tl) * 2 + 1]), abs_lane, second_lane, a[1], a[3]);  // row g + 8
-            sk_mma(acc[0][I & 1][m][tl], a[0], a[1], a[2], a[3], b[0], b[1]);
-            if (PLANES == 2) sk_mma(acc[PLANES - 1][I & 1][m][tl], a[0], a[1], a[2], a[3], b[2], b[3]);
+            if (NIBBLE) {
+              decode_codeword_nibble<(I & 1) != 0>(sk_word<I>(cur[(m * TILES + tl) * 2]), abs_lane, second_lane, a[0], a[2]);      // row g
+              decode_codeword_nibble<(I & 1) != 0>(sk_word<I>(cur[(m * TILES + tl) * 2 + 1]), abs_lane, second_lane, a[1], a[3]);  // row g + 8
+              sk_mma_u8(acc[0][I & 1][m][tl], a[0], a[1], a[2], a[3], b[0], b[1]);
+              if (PLANES == 2) sk_mma_u8(acc[PLANES - 1][I & 1][m][tl], a[0], a[1], a[2], a[3], b[2], b[3]);
+            } else {
+              decode_codeword<TABLE, (I & 1) != 0, WIDE_SIGN>(sk_word<I>(cur[(m * TILES + tl) * 2]), abs_lane, second_lane, a[0], a[2]);      // row g
+              decode_codeword<TABLE, (I & 1) != 0, WIDE_SIGN>(sk_word<I>(cur[(m * TILES + tl) * 2 + 1]), abs_lane, second_lane, a[1], a[3]);  // row g + 8
+              sk_mma(acc[0][I & 1][m][tl], a[0], a[1], a[2], a[3], b[0], b[1]);
+              if (PLANES == 2) sk_mma(acc[PLANES - 1][I & 1][m][tl], a[0], a[1], a[2], a[3], b[2], b[3]);
+            }
           }
       });
       if (--left_in_group == 0) {
@@ -546,9 +595,9 @@ static int device_sm_count(int* device_out) {
   return cached[dev];
 }
 
-template <int M, int TILES, int COLS, unsigned TABLE_STEPS, bool NESTED, bool WIDE_SIGN, bool SPLIT = false>
+template <int M, int TILES, int COLS, unsigned TABLE_STEPS, bool NESTED, bool WIDE_SIGN, bool SPLIT = false, bool NIBBLE = false>
 static int launch_slab(const FastProjectionArgs& p, cudaStream_t s) {
-  auto kernel = projection_slab_kernel<M, TILES, COLS, TABLE_STEPS, NESTED, WIDE_SIGN, SPLIT>;
+  auto kernel = projection_slab_kernel<M, TILES, COLS, TABLE_STEPS, NESTED, WIDE_SIGN, SPLIT, NIBBLE>;
   static uint64_t configured = 0;  // one bit per device: the shared-memory opt-in is a per-device attribute of the function
   int dev = 0;
   const int sms = device_sm_count(&dev);
@@ -562,9 +611,17 @@ static int launch_slab(const FastProjectionArgs& p, cudaStream_t s) {
   return KEEPVQ_OK;
 }
 
+// Plain layers: the nibble decoder, for groups of four routes (inputs up to 8192) or eight (up to 4096).
+template <int M, int TILES>
+static int launch_nibble(const FastProjectionArgs& p, int cols, cudaStream_t s) {
+  if (cols == 8) return launch_slab<M, TILES, 8, 0u, false, false, false, true>(p, s);
+  return launch_slab<M, TILES, 4, 0u, false, false, false, true>(p, s);
+}
+
 #ifdef KEEPVQ_DIAG
-// Measurement build only: which steps of a chunk decode through the sign table, and the table width.
-static unsigned g_table_steps = 0xEAu;
+// Measurement build only: the byte-table decoders (which steps of a chunk decode through the sign
+// table, and the table width) beside the nibble decoder (mask 0x100).
+static unsigned g_table_steps = 0x100u;
 static int g_wide_sign = 1;
 extern "C" void keepvq_diag_set_table_steps(unsigned mask) { g_table_steps = mask; }
 extern "C" void keepvq_diag_set_variant(int wide_sign, int) { g_wide_sign = wide_sign; }
@@ -575,6 +632,7 @@ static int diag_cols4(const FastProjectionArgs& p, cudaStream_t s) {
 }
 template <int M, int TILES>
 static int launch_plain(const FastProjectionArgs& p, int cols, cudaStream_t s) {
+  if (g_table_steps == 0x100u) return launch_nibble<M, TILES>(p, cols, s);
   if (cols == 8) {
     if (g_table_steps == 0xAAu) return launch_slab<M, TILES, 8, 0xAAu, false, false>(p, s);
     return launch_slab<M, TILES, 8, 0xEEu, false, false>(p, s);
@@ -589,13 +647,8 @@ static int launch_plain(const FastProjectionArgs& p, int cols, cudaStream_t s) {
   }
 }
 #else
-constexpr unsigned SK_TABLE_STEPS_4 = 0xAAu, SK_TABLE_STEPS_8 = 0xAAu;  // every other step: measured best of the mixes on a B200
 template <int M, int TILES>
-static int launch_plain(const FastProjectionArgs& p, int cols, cudaStream_t s) {
-  if (cols == 8) return launch_slab<M, TILES, 8, SK_TABLE_STEPS_8, false, false>(p, s);
-  if (p.in_dim <= 4096) return launch_slab<M, TILES, 4, SK_TABLE_STEPS_4, false, true>(p, s);
-  return launch_slab<M, TILES, 4, SK_TABLE_STEPS_4, false, false>(p, s);
-}
+static int launch_plain(const FastProjectionArgs& p, int cols, cudaStream_t s) { return launch_nibble<M, TILES>(p, cols, s); }
 #endif
 
 template <int M, int TILES>
