@@ -96,6 +96,31 @@ __device__ __forceinline__ void decode_codeword(uint32_t word, uint32_t abs_lane
   }
 }
 
+// The nibble decoder.  Both tables hold an entry as eight 4-bit values in ONE word, u = q + 8 for the
+// abs table (even parity) and the XOR masks of the sign byte for the other (4-bit XOR on q + 8 is
+// the same as on q), 32 replicas each, interleaved in one 64 KB region on a 64 KB boundary:
+//   abs entry  at region + abs byte * 256 + lane * 4,   sign entry at region + 128 + sign byte * 256 + lane * 4,
+// so each address is one byte permute and each read one shared-memory wavefront (an 8-byte entry
+// costs two).  The operand bytes are u (0..15, an UNSIGNED A operand); the caller
+// takes 8 * sum(x') off the integer dot product to get back to sum(q x').
+template <bool ODD>
+__device__ __forceinline__ void decode_codeword_nibble(uint32_t word, uint32_t abs_lane, uint32_t sign_lane, uint32_t& lo, uint32_t& hi) {
+  uint32_t e, m;
+  asm("ld.shared.u32 %0, [%1];" : "=r"(e) : "r"(__byte_perm(word, abs_lane, ODD ? 0x7634 : 0x7614)));
+  asm("ld.shared.u32 %0, [%1];" : "=r"(m) : "r"(__byte_perm(word, sign_lane, ODD ? 0x7624 : 0x7604)));
+  lo = (e ^ m) & 0x0F0F0F0Fu;          // one three-input logic operation each,
+  hi = ((e ^ m) & 0xF0F0F0F0u) >> 4;   // and one shift
+}
+__device__ __forceinline__ uint32_t pack_nibbles(uint2 v) { return (v.x & 0x0F0F0F0Fu) | ((v.y & 0x0F0F0F0Fu) << 4); }
+// The CTA's `warps` warps fill the 64 KB region at `region` (shared address on a 64 KB boundary): a
+// warp writes the 32 replicas of an entry side by side.
+__device__ __forceinline__ void build_nibble_tables(uint32_t region, const uint32_t* __restrict__ codebook, int warp, int lane, int warps) {
+  for (int e = warp; e < 512; e += warps) {
+    const uint32_t v = e < 256 ? pack_nibbles(abs_table_entry(codebook[e], 0)) ^ 0x88888888u : pack_nibbles(sign_table_entry(e - 256));
+    asm volatile("st.shared.u32 [%0], %1;" ::"r"(region + (e & 255) * 256 + (e >> 8) * 128 + lane * 4), "r"(v) : "memory");
+  }
+}
+
 // Quantised activation rows: the B operand of the projections.
 struct QuantRows {
   uint8_t* q;       // [rows + 1, in_dim/8, 16] (last row all zero): per codeword 4 words: hi(dims 6,4,2,0) hi(7,5,3,1) lo(...) lo(...)

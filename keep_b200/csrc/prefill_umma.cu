@@ -21,8 +21,8 @@
 //   warps 0-15   decode, then drain.  A thread's row of the tile is its lane of tensor memory
 //                (warp w reaches lanes 32 * (w % 4) ...); warps 0-7 decode the first tile of an
 //                item, warps 8-15 the second, half a row of the K block each (8 codewords).  Codes
-//                arrive through a private cp.async ring; the decode is the slab kernel's (byte-
-//                permute table addresses, every other codeword's signs from the second table);
+//                arrive through a private cp.async ring; the decode is the slab kernel's nibble
+//                decoder (two 4-byte table reads at byte-permute addresses, unsigned bytes q + 8);
 //                the bytes go straight into TENSOR MEMORY (tcgen05.st), two stages deep, so the
 //                A operand never touches shared memory.  When an item's MMAs are done the same
 //                warps read its accumulators (tcgen05.ld: same lanes), dequantise, apply SwiGLU
@@ -60,15 +60,12 @@ constexpr int PF_B_STAGE_BYTES = 2 * PF_N_MAX * 128;  // high-byte rows of the r
 constexpr int PF_RING = 4;                      // K blocks of codes in flight per decode thread
 constexpr int PF_RING_BYTES = PF_RING * PF_DECODE_WARPS * 32 * 16;  // 32 KB
 static_assert(PF_RING == 4, "the decode loop's wait counts are written out for a lookahead of up to three K blocks");
-constexpr unsigned PF_TABLE_STEPS = 0xAAu;      // codewords of a thread's eight whose signs come from the second table
-constexpr int PF_REPLICAS = 16;
-constexpr uint32_t PF_ABS_BYTES = 256 * 2 * PF_REPLICAS * 8;  // 64 KB
-constexpr uint32_t PF_SIGN_BYTES = 256 * PF_REPLICAS * 8;     // 32 KB
-// Shared window, absolute addresses.  A0 = the 64 KB boundary the abs table sits on:
-//   [A0 - 56 KB, A0 - 24 KB) code rings | [A0 - 24 KB, A0) B stage 0 | [A0, +64 KB) abs table |
-//   [+64 KB, +96 KB) sign table | [+96 KB, +144 KB) B stages 1, 2
+constexpr uint32_t PF_TABLE_BYTES = 64 * 1024;  // the nibble decoder's two tables, interleaved (moe_fast.cuh)
+// Shared window, absolute addresses.  A0 = the 64 KB boundary the tables sit on:
+//   [A0 - 56 KB, A0 - 24 KB) code rings | [A0 - 24 KB, A0) B stage 0 | [A0, +64 KB) tables |
+//   [+64 KB, ...) the other B stages
 constexpr uint32_t PF_LOW_BYTES = PF_RING_BYTES + PF_B_STAGE_BYTES;
-constexpr uint32_t PF_HIGH_BYTES = PF_ABS_BYTES + PF_SIGN_BYTES + (PF_B_STAGES - 1) * PF_B_STAGE_BYTES;
+constexpr uint32_t PF_HIGH_BYTES = PF_TABLE_BYTES + (PF_B_STAGES - 1) * PF_B_STAGE_BYTES;
 constexpr int PF_SMEM_BYTES = 220 * 1024;       // dynamic request: covers A0 + 144 KB from any base below A0 - 56 KB
 constexpr uint64_t PF_DEFAULT_WAIT_NS = 2000000000ull;
 
@@ -181,17 +178,10 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_projection_kernel(FastP
   const uint32_t a0 = (dyn_base + PF_LOW_BYTES + 0xFFFFu) & ~0xFFFFu;
   const bool window_ok = a0 + PF_HIGH_BYTES <= dyn_base + PF_SMEM_BYTES;  // uniform over the grid
   const uint32_t ring_base = a0 - PF_LOW_BYTES;
-  const uint32_t sign_base = a0 + PF_ABS_BYTES;
-  auto b_stage_addr = [&](uint32_t stage) { return stage == 0 ? a0 - PF_B_STAGE_BYTES : sign_base + PF_SIGN_BYTES + (stage - 1) * PF_B_STAGE_BYTES; };
+  auto b_stage_addr = [&](uint32_t stage) { return stage == 0 ? a0 - PF_B_STAGE_BYTES : a0 + PF_TABLE_BYTES + (stage - 1) * PF_B_STAGE_BYTES; };
 
   // ---- set-up: tables, barriers, tensor memory ------------------------------------------------
-  if (window_ok) {
-    for (int e = tid; e < 768; e += PF_THREADS) {
-      const uint2 v = e < 512 ? abs_table_entry(p.codebook[e >> 1], e & 1) : sign_table_entry(e - 512);
-      const uint32_t dst = e < 512 ? a0 + e * (PF_REPLICAS * 8) : sign_base + (e - 512) * (PF_REPLICAS * 8);
-      for (int r = 0; r < PF_REPLICAS; ++r) asm volatile("st.shared.v2.u32 [%0], {%1,%2};" ::"r"(dst + r * 8), "r"(v.x), "r"(v.y) : "memory");
-    }
-  }
+  if (window_ok) build_nibble_tables(a0, p.codebook, warp, lane, PF_THREADS / 32);
   if (tid == 0) {
     abort_flag = window_ok ? 0 : 1;
     for (int s = 0; s < PF_A_STAGES; ++s) { mbar_init(bar(A_FULL, s), M * 8); mbar_init(bar(A_EMPTY, s), 1); }
@@ -241,8 +231,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_projection_kernel(FastP
       // ================= decode, then drain =====================================================
       const int quadrant = warp & 3, half = (warp >> 2) & 1, m = warp >> 3;  // m: which tile of the item this warp decodes
       const int row = quadrant * 32 + lane;
-      const uint32_t abs_lane = a0 + static_cast<uint32_t>(lane & (PF_REPLICAS - 1)) * 8u;
-      const uint32_t second_lane = sign_base + static_cast<uint32_t>(lane & (PF_REPLICAS - 1)) * 8u;
+      const uint32_t abs_lane = a0 + lane * 4u, sign_lane = a0 + 128u + lane * 4u;
       bool ok = true;
       if (m < M) {
         auto code_row = [&](int which_item) {  // this thread's code row (its half) of an item
@@ -279,14 +268,14 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_projection_kernel(FastP
                        : "r"(ring + (it % PF_RING) * (PF_DECODE_WARPS * 32 * 16)));
           // decode into registers first, then wait for the stage: the MMAs that read it have had a K block's time to finish
           uint32_t q[16];
-          decode_codeword<((PF_TABLE_STEPS >> 0) & 1u) != 0, false, false>(cur.x, abs_lane, second_lane, q[0], q[1]);
-          decode_codeword<((PF_TABLE_STEPS >> 1) & 1u) != 0, true, false>(cur.x, abs_lane, second_lane, q[2], q[3]);
-          decode_codeword<((PF_TABLE_STEPS >> 2) & 1u) != 0, false, false>(cur.y, abs_lane, second_lane, q[4], q[5]);
-          decode_codeword<((PF_TABLE_STEPS >> 3) & 1u) != 0, true, false>(cur.y, abs_lane, second_lane, q[6], q[7]);
-          decode_codeword<((PF_TABLE_STEPS >> 4) & 1u) != 0, false, false>(cur.z, abs_lane, second_lane, q[8], q[9]);
-          decode_codeword<((PF_TABLE_STEPS >> 5) & 1u) != 0, true, false>(cur.z, abs_lane, second_lane, q[10], q[11]);
-          decode_codeword<((PF_TABLE_STEPS >> 6) & 1u) != 0, false, false>(cur.w, abs_lane, second_lane, q[12], q[13]);
-          decode_codeword<((PF_TABLE_STEPS >> 7) & 1u) != 0, true, false>(cur.w, abs_lane, second_lane, q[14], q[15]);
+          decode_codeword_nibble<false>(cur.x, abs_lane, sign_lane, q[0], q[1]);
+          decode_codeword_nibble<true>(cur.x, abs_lane, sign_lane, q[2], q[3]);
+          decode_codeword_nibble<false>(cur.y, abs_lane, sign_lane, q[4], q[5]);
+          decode_codeword_nibble<true>(cur.y, abs_lane, sign_lane, q[6], q[7]);
+          decode_codeword_nibble<false>(cur.z, abs_lane, sign_lane, q[8], q[9]);
+          decode_codeword_nibble<true>(cur.z, abs_lane, sign_lane, q[10], q[11]);
+          decode_codeword_nibble<false>(cur.w, abs_lane, sign_lane, q[12], q[13]);
+          decode_codeword_nibble<true>(cur.w, abs_lane, sign_lane, q[14], q[15]);
           const uint32_t stage = it % PF_A_STAGES, phase = (it / PF_A_STAGES) & 1u;
           PF_TICK(t1);
           ok = __all_sync(0xFFFFFFFFu, mbar_wait(bar(A_EMPTY, stage), phase ^ 1u, deadline, aborted));
@@ -344,12 +333,14 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_projection_kernel(FastP
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
               const int4 pr = per_route[c0 + j];
-              const float x_scale = __int_as_float(pr.y), x_sum4 = __int_as_float(pr.z);
+              const float x_scale = __int_as_float(pr.y), x_sum4 = 0.25f * static_cast<float>(pr.z);
+              const uint32_t offset = 8u * static_cast<uint32_t>(pr.z);  // the A operand was u = q + 8: 8 * sum(x') too much
               float y[M];
 #pragma unroll
               for (int mm = 0; mm < M; ++mm) {
-                const float dot = 256.0f * static_cast<float>(static_cast<int>(acc[mm][0][j])) + static_cast<float>(static_cast<int>(acc[mm][1][j]));
-                y[mm] = scale[mm] * x_scale * (0.5f * dot + x_sum4);
+                // 256 high + low - 8 sum(x') in wrapping 32-bit arithmetic: the true value, sum(q x'), fits
+                const int dot = static_cast<int>(acc[mm][0][j] * 256u + acc[mm][1][j] - offset);
+                y[mm] = scale[mm] * x_scale * (0.5f * static_cast<float>(dot) + x_sum4);
               }
               if (GLU) {  // round G and U to the activation dtype first, as the separate kernels of the reference do
                 const float gt = fminf(round_out(y[0]), limit);
@@ -392,7 +383,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_projection_kernel(FastP
           const int route = n < gsize ? p.groups_of_routes.routes[gstart + n] : -1;
           const int64_t xrow = route < 0 ? p.x_zero_row : static_cast<int64_t>(gstart + n);  // the activation rows were quantised in grouped order
           const float weight = (GLU && route >= 0) ? p.route_weight[route] : 1.0f;
-          route_info[item_phase][n] = make_int4(route, __float_as_int(p.x.scale[xrow]), __float_as_int(0.25f * static_cast<float>(p.x.sums[xrow])), __float_as_int(weight));
+          route_info[item_phase][n] = make_int4(route, __float_as_int(p.x.scale[xrow]), p.x.sums[xrow], __float_as_int(weight));
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(bar(INFO_FULL, item_phase));
@@ -403,7 +394,8 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_projection_kernel(FastP
       PF_ADD(3, m0, m1);
       if (lane == 0 && ok) {
         // N = 2 * n_pad: the high-byte rows and the low-byte rows of the routes are one B operand
-        const uint32_t idesc = (2u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(n_pad >> 2) << 17) | ((PF_ROWS >> 4) << 24);
+        // accumulator s32, A unsigned bytes (the nibble decoder's u = q + 8), B signed bytes
+        const uint32_t idesc = (2u << 4) | (0u << 7) | (1u << 10) | (static_cast<uint32_t>(n_pad >> 2) << 17) | ((PF_ROWS >> 4) << 24);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         for (int kb = 0; kb < k_blocks && ok; ++kb) {
           const uint32_t sa = issue_a, sb = issue_b;

@@ -98,24 +98,6 @@ __device__ __forceinline__ void sk_mma_u8(int (&c)[4], uint32_t a0, uint32_t a1,
       : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-// The nibble decoder.  Both tables hold an entry as eight 4-bit values in ONE word, u = q + 8 for the
-// abs table (even parity) and the XOR masks of the sign byte for the other (4-bit XOR on q + 8 is
-// the same as on q), 32 replicas each, interleaved in one 64 KB region on a 64 KB boundary:
-//   abs entry  at region + abs byte * 256 + lane * 4,   sign entry at region + 128 + sign byte * 256 + lane * 4,
-// so each address is one byte permute and each read one shared-memory wavefront (a quarter of what the
-// pair of 8-byte entries costs).  The operand bytes are u (0..15, an UNSIGNED A operand); the caller
-// takes 8 * sum(x') off the integer dot product to get back to sum(q x').
-template <bool ODD>
-__device__ __forceinline__ void decode_codeword_nibble(uint32_t word, uint32_t abs_lane, uint32_t sign_lane, uint32_t& lo, uint32_t& hi) {
-  uint32_t e, m;
-  asm("ld.shared.u32 %0, [%1];" : "=r"(e) : "r"(__byte_perm(word, abs_lane, ODD ? 0x7634 : 0x7614)));
-  asm("ld.shared.u32 %0, [%1];" : "=r"(m) : "r"(__byte_perm(word, sign_lane, ODD ? 0x7624 : 0x7604)));
-  const uint32_t x = e ^ m;
-  lo = x & 0x0F0F0F0Fu;
-  hi = (x >> 4) & 0x0F0F0F0Fu;
-}
-__device__ __forceinline__ uint32_t sk_pack_nibbles(uint2 v) { return (v.x & 0x0F0F0F0Fu) | ((v.y & 0x0F0F0F0Fu) << 4); }
-
 template <int I>
 __device__ __forceinline__ uint32_t sk_word(const uint4& v) {
   return (I >> 1) == 0 ? v.x : (I >> 1) == 1 ? v.y : (I >> 1) == 2 ? v.z : v.w;
@@ -131,11 +113,12 @@ __device__ __forceinline__ uint32_t sk_word(const uint4& v) {
 constexpr uint32_t SK_SPLIT_RED_OFF = 48 * 1024;          // from the start of the activation stage
 constexpr int SK_SPLIT_ITEMS_PER_CTA = 4;                 // items per CTA the split factor aims for
 
-// NIBBLE: the nibble decoder above on every step (plain layers, not the split form): TABLE_STEPS and
-// WIDE_SIGN play no part, and the activations start right behind the one table region.
+// NIBBLE: the nibble decoder above on every step of the base pass (not in the split form): TABLE_STEPS
+// and WIDE_SIGN play no part, and the activations start right behind the one table region (with a
+// residual tier: behind the residual codebook that follows it).
 template <int M, int TILES, int COLS, unsigned TABLE_STEPS, bool NESTED, bool WIDE_SIGN, bool SPLIT, bool NIBBLE = false>
 __global__ void __launch_bounds__(SK_THREADS, 1) projection_slab_kernel(FastProjectionArgs p, int32_t* status) {
-  static_assert(!NIBBLE || (!NESTED && !WIDE_SIGN && !SPLIT), "the nibble decoder serves the plain form");
+  static_assert(!NIBBLE || (!WIDE_SIGN && !SPLIT), "the nibble decoder needs whole scale groups per warp, and has one table layout");
   static_assert(COLS == 4 || COLS == 8, "a group is four or eight routes");
   static_assert(!WIDE_SIGN || (COLS == 4 && !NESTED), "the wide sign table leaves room for eight activation columns of 4096 inputs");
   static_assert(!SPLIT || (COLS == 4 && !WIDE_SIGN), "the split form keeps its partial sums at the end of the 64 KB activation stage");
@@ -161,13 +144,8 @@ __global__ void __launch_bounds__(SK_THREADS, 1) projection_slab_kernel(FastProj
   // ---- tables -----------------------------------------------------------------------------
   // every thread computes one entry per pass; the warp then writes its 32 entries two at a time,
   // sixteen lanes storing the sixteen replicas of one entry side by side (no bank conflicts)
-  if (NIBBLE) {  // a warp writes the 32 replicas of an entry side by side
-    for (int e = threadIdx.x >> 5; e < 512; e += SK_WARPS) {
-      const uint32_t v = e < 256 ? sk_pack_nibbles(abs_table_entry(p.codebook[e], 0)) ^ 0x88888888u : sk_pack_nibbles(sign_table_entry(e - 256));
-      asm volatile("st.shared.u32 [%0], %1;" ::"r"(a0 + (e & 255) * 256 + (e >> 8) * 128 + (threadIdx.x & 31) * 4), "r"(v) : "memory");
-    }
-  }
-  for (int e = threadIdx.x; e < (NIBBLE ? 0 : 768); e += SK_THREADS) {
+  if (NIBBLE) build_nibble_tables(a0, p.codebook, threadIdx.x >> 5, threadIdx.x & 31, SK_WARPS);
+  for (int e = threadIdx.x + (NIBBLE ? 512 : 0); e < (NIBBLE && !NESTED ? 0 : 768); e += SK_THREADS) {
     uint32_t lo = 0, hi = 0;
     if (e >= 512 && NESTED) {  // residual entry: byte j of the low word is 2 * v[6 - 2j], of the high word 2 * v[7 - 2j]
       const uint32_t* row = p.res_table + (e - 512) * 4;
@@ -200,8 +178,9 @@ __global__ void __launch_bounds__(SK_THREADS, 1) projection_slab_kernel(FastProj
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int g = lane >> 2, t = lane & 3;
   const uint32_t abs_lane = NIBBLE ? a0 + lane * 4u : a0 + static_cast<uint32_t>(lane & (SK_REPLICAS - 1)) * 8u;
-  const uint32_t second_lane = NIBBLE ? a0 + 128u + lane * 4u : a0 + SK_SECOND_OFF + static_cast<uint32_t>(lane & (L::SECOND_REPLICAS - 1)) * 8u;
-  const uint32_t b_base = a0 + (NIBBLE ? SK_ABS_BYTES : L::B_OFF);
+  const uint32_t sign_lane = a0 + 128u + lane * 4u;  // nibble decoder only
+  const uint32_t second_lane = a0 + SK_SECOND_OFF + static_cast<uint32_t>(lane & (L::SECOND_REPLICAS - 1)) * 8u;
+  const uint32_t b_base = a0 + (NIBBLE && !NESTED ? SK_ABS_BYTES : L::B_OFF);
   constexpr int STAGE_BYTES = 4 * 512;                   // per warp
   const uint32_t ring = (warp < low_warps ? smem_base + warp * SK_WARP_RING : a0 + SK_RING_HIGH_OFF + (warp - low_warps) * SK_WARP_RING) + lane * 16;
   const int64_t N = p.out_dim, cw = p.in_dim / 8;
@@ -348,9 +327,11 @@ __global__ void __launch_bounds__(SK_THREADS, 1) projection_slab_kernel(FastProj
 
     // accumulators -> fp32 partials at the end of a scale group
     auto close_group = [&](const void* const (&scales)[2], int64_t row_base, int64_t groups, int group, float (&into)[M][TILES][PARTS], bool keep_scale) {
-      uint32_t offset[RPL];  // 8 * sum(x') of the group: what the unsigned operand u = q + 8 added to the integer dot product
+      // keep_scale marks the base pass: with the nibble decoder its operand was u = q + 8, which added
+      // 8 * sum(x') of the group to the integer dot product
+      uint32_t offset[RPL];
 #pragma unroll
-      for (int cc = 0; cc < RPL; ++cc) offset[cc] = NIBBLE ? 8u * static_cast<uint32_t>(ep_sums[cc][group]) : 0u;
+      for (int cc = 0; cc < RPL; ++cc) offset[cc] = NIBBLE && keep_scale ? 8u * static_cast<uint32_t>(ep_sums[cc][group]) : 0u;
 #pragma unroll
       for (int m = 0; m < M; ++m)
 #pragma unroll
@@ -405,8 +386,8 @@ __global__ void __launch_bounds__(SK_THREADS, 1) projection_slab_kernel(FastProj
           for (int tl = 0; tl < TILES; ++tl) {
             uint32_t a[4];
             if (NIBBLE) {
-              decode_codeword_nibble<(I & 1) != 0>(sk_word<I>(cur[(m * TILES + tl) * 2]), abs_lane, second_lane, a[0], a[2]);      // row g
-              decode_codeword_nibble<(I & 1) != 0>(sk_word<I>(cur[(m * TILES + tl) * 2 + 1]), abs_lane, second_lane, a[1], a[3]);  // row g + 8
+              decode_codeword_nibble<(I & 1) != 0>(sk_word<I>(cur[(m * TILES + tl) * 2]), abs_lane, sign_lane, a[0], a[2]);      // row g
+              decode_codeword_nibble<(I & 1) != 0>(sk_word<I>(cur[(m * TILES + tl) * 2 + 1]), abs_lane, sign_lane, a[1], a[3]);  // row g + 8
               sk_mma_u8(acc[0][I & 1][m][tl], a[0], a[1], a[2], a[3], b[0], b[1]);
               if (PLANES == 2) sk_mma_u8(acc[PLANES - 1][I & 1][m][tl], a[0], a[1], a[2], a[3], b[2], b[3]);
             } else {
@@ -654,7 +635,7 @@ static int launch_plain(const FastProjectionArgs& p, int cols, cudaStream_t s) {
 template <int M, int TILES>
 static int launch_slab_projection(const FastProjectionArgs& p, int cols, cudaStream_t s) {
   if (p.in_dim > slab_max_in_dim(cols)) return KEEPVQ_ERR_UNSUPPORTED;
-  if (p.res_table) return cols == 4 ? launch_slab<M, TILES, 4, 0u, true, false>(p, s) : launch_slab<M, TILES, 8, 0u, true, false>(p, s);
+  if (p.res_table) return cols == 4 ? launch_slab<M, TILES, 4, 0u, true, false, false, true>(p, s) : launch_slab<M, TILES, 8, 0u, true, false, false, true>(p, s);
   return launch_plain<M, TILES>(p, cols, s);
 }
 
