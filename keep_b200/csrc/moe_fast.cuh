@@ -108,8 +108,12 @@ __device__ __forceinline__ void decode_codeword_nibble(uint32_t word, uint32_t a
   uint32_t e, m;
   asm("ld.shared.u32 %0, [%1];" : "=r"(e) : "r"(__byte_perm(word, abs_lane, ODD ? 0x7634 : 0x7614)));
   asm("ld.shared.u32 %0, [%1];" : "=r"(m) : "r"(__byte_perm(word, sign_lane, ODD ? 0x7624 : 0x7604)));
-  lo = (e ^ m) & 0x0F0F0F0Fu;          // one three-input logic operation each,
-  hi = ((e ^ m) & 0xF0F0F0F0u) >> 4;   // and one shift
+  // (e ^ m) & mask as ONE three-input logic operation each (written out: the compiler otherwise
+  // turns the second into a shift and two operations), and one shift
+  uint32_t top;
+  asm("lop3.b32 %0, %1, %2, 0x0F0F0F0F, 0x28;" : "=r"(lo) : "r"(e), "r"(m));
+  asm("lop3.b32 %0, %1, %2, 0xF0F0F0F0, 0x28;" : "=r"(top) : "r"(e), "r"(m));
+  hi = top >> 4;
 }
 __device__ __forceinline__ uint32_t pack_nibbles(uint2 v) { return (v.x & 0x0F0F0F0Fu) | ((v.y & 0x0F0F0F0Fu) << 4); }
 // The CTA's `warps` warps fill the 64 KB region at `region` (shared address on a 64 KB boundary): a

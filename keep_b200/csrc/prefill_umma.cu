@@ -50,7 +50,7 @@ constexpr int PF_DECODE_WARPS = 16;
 constexpr int PF_MMA_WARP = PF_DECODE_WARPS;
 constexpr int PF_THREADS = (PF_DECODE_WARPS + 2) * 32;  // 576: decode warps, the MMA warp, the TMA warp
 constexpr int PF_A_STAGES = 2;                  // in tensor memory: 32 columns per tile and stage
-constexpr int PF_B_STAGES = 3;
+constexpr int PF_B_STAGES = 4;
 constexpr int PF_N_MAX = PREFILL_GROUP_ROUTES;  // routes per item
 static_assert(PF_N_MAX % 16 == 0, "an item's routes pad to a multiple of sixteen columns");
 constexpr int PF_ROWS = 128;                    // output rows per tile
