@@ -80,8 +80,11 @@ extern "C" int keepvq_grouped_projection(const keepvq_grouped_projection_args* a
   fast::RouteGroups groups = {reinterpret_cast<int32_t*>(ws + sc.gcount), reinterpret_cast<int32_t*>(ws + sc.gslot),
                               reinterpret_cast<int32_t*>(ws + sc.gstart), reinterpret_cast<int32_t*>(ws + sc.gsize),
                               reinterpret_cast<int32_t*>(ws + sc.groutes)};
-  fast::QuantRows xq = {reinterpret_cast<uint8_t*>(ws + sc.xq), reinterpret_cast<float*>(ws + sc.xscale), reinterpret_cast<int32_t*>(ws + sc.xsums)};
   const bool many = !residual && a.routes >= 1024 && a.routes >= 24 * a.slots && fast::prefill_supported(a.out_dim, a.in_dim, a.groups);
+  // (the sums region has room for a scale group per codeword; these kernels' rows have at most one
+  // per 256 inputs, and their sums per 256 inputs go behind those)
+  fast::QuantRows xq = {reinterpret_cast<uint8_t*>(ws + sc.xq), reinterpret_cast<float*>(ws + sc.xscale), reinterpret_cast<int32_t*>(ws + sc.xsums),
+                        many ? nullptr : reinterpret_cast<int32_t*>(ws + sc.xsums) + (x_rows + 1) * a.groups};
   int32_t* wait_status = reinterpret_cast<int32_t*>(ws + sc.status);
   int rc;
   const int group_cols = many ? fast::PREFILL_GROUP_ROUTES : fast::decode_group_routes(a.routes, a.slots, a.in_dim);
@@ -133,7 +136,7 @@ extern "C" int keepvq_wait_selftest(void* workspace, int64_t workspace_bytes, in
   // status 0 | groups 256.. | routes 1280 | table 2048 | scales 3072 | codes 4096 | planes 8192 | x scale 16384 | x sums 16640 | out 20480
   fast::RouteGroups groups = {reinterpret_cast<int32_t*>(ws + 256), reinterpret_cast<int32_t*>(ws + 512), reinterpret_cast<int32_t*>(ws + 768),
                               reinterpret_cast<int32_t*>(ws + 1024), reinterpret_cast<int32_t*>(ws + 1280)};
-  fast::QuantRows xq = {reinterpret_cast<uint8_t*>(ws + 8192), reinterpret_cast<float*>(ws + 16384), reinterpret_cast<int32_t*>(ws + 16640)};
+  fast::QuantRows xq = {reinterpret_cast<uint8_t*>(ws + 8192), reinterpret_cast<float*>(ws + 16384), reinterpret_cast<int32_t*>(ws + 16640), nullptr};
   selftest_init_kernel<<<1, 32, 0, s>>>(groups.count, groups.size, groups.routes, xq.scale);
   KEEPVQ_CHECK_LAUNCH();
   fast::FastProjectionArgs p = {};

@@ -42,6 +42,8 @@ __device__ __forceinline__ void quantize_row(const XT* __restrict__ x, int64_t r
       }
     }
     for (int64_t g = threadIdx.x; g < groups; g += 256) out.sums[row * groups + g] = 0;
+    if (out.chunk_sums)
+      for (int64_t c = threadIdx.x; c < cw / 32; c += 256) out.chunk_sums[row * (cw / 32) + c] = 0;
     if (threadIdx.x == 0) out.scale[row] = 1.0f;
     return;
   }
@@ -85,6 +87,10 @@ __device__ __forceinline__ void quantize_row(const XT* __restrict__ x, int64_t r
       total += q[d];
     }
     atomicAdd(&group_sum[c / per_group], total);
+    if (out.chunk_sums) {  // a warp's 32 codewords are one chunk of 256 inputs (the row is a multiple of that when these are asked for)
+      const int chunk_total = __reduce_add_sync(0xFFFFFFFFu, total);
+      if ((threadIdx.x & 31) == 0) out.chunk_sums[row * (cw / 32) + c / 32] = chunk_total;
+    }
     // byte j of word 0 pairs with table nibble 3-j = dim 6-2j; of word 1 with nibble 7-j = dim 7-2j
     uint32_t hi0 = 0, hi1 = 0, lo0 = 0, lo1 = 0;
 #pragma unroll

@@ -116,20 +116,31 @@ __device__ __forceinline__ void decode_codeword_nibble(uint32_t word, uint32_t a
   hi = top >> 4;
 }
 __device__ __forceinline__ uint32_t pack_nibbles(uint2 v) { return (v.x & 0x0F0F0F0Fu) | ((v.y & 0x0F0F0F0Fu) << 4); }
-// The CTA's `warps` warps fill the 64 KB region at `region` (shared address on a 64 KB boundary): a
-// warp writes the 32 replicas of an entry side by side.
-__device__ __forceinline__ void build_nibble_tables(uint32_t region, const uint32_t* __restrict__ codebook, int warp, int lane, int warps) {
-  for (int e = warp; e < 512; e += warps) {
-    const uint32_t v = e < 256 ? pack_nibbles(abs_table_entry(codebook[e], 0)) ^ 0x88888888u : pack_nibbles(sign_table_entry(e - 256));
-    asm volatile("st.shared.u32 [%0], %1;" ::"r"(region + (e & 255) * 256 + (e >> 8) * 128 + lane * 4), "r"(v) : "memory");
+// All `threads` threads of the CTA (whole warps) fill the 64 KB region at `region` (shared address on
+// a 64 KB boundary): a thread works out one entry (one load of the codebook, all in flight together),
+// then its warp writes its 32 entries one after the other, the 32 replicas of an entry side by side.
+__device__ __forceinline__ void build_nibble_tables(uint32_t region, const uint32_t* __restrict__ codebook, int tid, int threads) {
+  const int lane = tid & 31;
+  for (int base = 0; base < 512; base += threads) {
+    const int e = base + tid;
+    uint32_t v = 0;
+    if (e < 256) v = pack_nibbles(abs_table_entry(codebook[e], 0)) ^ 0x88888888u;
+    else if (e < 512) v = pack_nibbles(sign_table_entry(e - 256));
+    const int first = e - lane;  // the warp's first entry
+#pragma unroll 8
+    for (int i = 0; i < 32; ++i) {
+      const uint32_t vi = __shfl_sync(0xFFFFFFFFu, v, i);
+      const int ee = first + i;
+      if (ee < 512) asm volatile("st.shared.u32 [%0], %1;" ::"r"(region + (ee & 255) * 256 + (ee >> 8) * 128 + lane * 4), "r"(vi) : "memory");
+    }
   }
 }
-
 // Quantised activation rows: the B operand of the projections.
 struct QuantRows {
   uint8_t* q;       // [rows + 1, in_dim/8, 16] (last row all zero): per codeword 4 words: hi(dims 6,4,2,0) hi(7,5,3,1) lo(...) lo(...)
   float* scale;     // [rows + 1] power of two: x ~= scale * x'
   int32_t* sums;    // [rows + 1, groups] sum of x' over each scale group
+  int32_t* chunk_sums;  // [rows + 1, in_dim / 256] sum of x' over every 256 inputs, or null: for kernels whose warps split a scale group
 };
 
 // Routes grouped by the slot they are served from.

@@ -209,7 +209,10 @@ extern "C" int keepvq_moe_decode_stages(const keepvq_moe_layer_args* args, int32
   const int64_t live = a.expected_routes > 0 && a.expected_routes < routes ? a.expected_routes : routes;
   const bool prefill = tensor_path && !residual && live >= PREFILL_MIN_ROUTES && live >= PREFILL_MIN_ROUTES_PER_SLOT * a.slots &&
                        fast::prefill_supported(a.inter, a.hidden, a.w1.groups) && fast::prefill_supported(a.hidden, a.inter, a.w2.groups);
-  fast::QuantRows xq = {reinterpret_cast<uint8_t*>(ws + sc.xq), reinterpret_cast<float*>(ws + sc.xscale), reinterpret_cast<int32_t*>(ws + sc.xsums)};
+  // (the sums regions have room for a scale group per codeword; the tensor-core kernels' rows have at
+  // most one per 256 inputs, and their sums per 256 inputs go behind those)
+  fast::QuantRows xq = {reinterpret_cast<uint8_t*>(ws + sc.xq), reinterpret_cast<float*>(ws + sc.xscale), reinterpret_cast<int32_t*>(ws + sc.xsums),
+                        tensor_path && !prefill ? reinterpret_cast<int32_t*>(ws + sc.xsums) + (a.tokens + 1) * a.w1.groups : nullptr};
   bool x_quantized = false;  // the router's launch took the quantisation of the token rows along
   // a caller that expects few of the routes to be live (an expert-parallel rank's padded receive
   // buffer) has the quantisation skip the rows no live route reads; otherwise the look at the
@@ -241,7 +244,8 @@ extern "C" int keepvq_moe_decode_stages(const keepvq_moe_layer_args* args, int32
     fast::RouteGroups groups = {reinterpret_cast<int32_t*>(ws + sc.gcount), reinterpret_cast<int32_t*>(ws + sc.gslot),
                                 reinterpret_cast<int32_t*>(ws + sc.gstart), reinterpret_cast<int32_t*>(ws + sc.gsize),
                                 reinterpret_cast<int32_t*>(ws + sc.groutes)};
-    fast::QuantRows hq = {reinterpret_cast<uint8_t*>(ws + sc.hq), reinterpret_cast<float*>(ws + sc.hscale), reinterpret_cast<int32_t*>(ws + sc.hsums)};
+    fast::QuantRows hq = {reinterpret_cast<uint8_t*>(ws + sc.hq), reinterpret_cast<float*>(ws + sc.hscale), reinterpret_cast<int32_t*>(ws + sc.hsums),
+                          prefill ? nullptr : reinterpret_cast<int32_t*>(ws + sc.hsums) + (routes + 1) * a.w2.groups};
     int32_t* wait_status = reinterpret_cast<int32_t*>(ws + sc.status);
     const int group_cols = prefill ? fast::PREFILL_GROUP_ROUTES : fast::decode_group_routes(live, a.slots, std::max(a.hidden, a.inter));
     if (stages & KEEPVQ_STAGE_PREPARE) {

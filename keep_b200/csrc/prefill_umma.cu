@@ -181,7 +181,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_projection_kernel(FastP
   auto b_stage_addr = [&](uint32_t stage) { return stage == 0 ? a0 - PF_B_STAGE_BYTES : a0 + PF_TABLE_BYTES + (stage - 1) * PF_B_STAGE_BYTES; };
 
   // ---- set-up: tables, barriers, tensor memory ------------------------------------------------
-  if (window_ok) build_nibble_tables(a0, p.codebook, warp, lane, PF_THREADS / 32);
+  if (window_ok) build_nibble_tables(a0, p.codebook, tid, PF_THREADS);
   if (tid == 0) {
     abort_flag = window_ok ? 0 : 1;
     for (int s = 0; s < PF_A_STAGES; ++s) { mbar_init(bar(A_FULL, s), M * 8); mbar_init(bar(A_EMPTY, s), 1); }

@@ -118,7 +118,7 @@ constexpr int SK_SPLIT_ITEMS_PER_CTA = 4;                 // items per CTA the s
 // residual tier: behind the residual codebook that follows it).
 template <int M, int TILES, int COLS, unsigned TABLE_STEPS, bool NESTED, bool WIDE_SIGN, bool SPLIT, bool NIBBLE = false>
 __global__ void __launch_bounds__(SK_THREADS, 1) projection_slab_kernel(FastProjectionArgs p, int32_t* status) {
-  static_assert(!NIBBLE || (!WIDE_SIGN && !SPLIT), "the nibble decoder needs whole scale groups per warp, and has one table layout");
+  static_assert(!NIBBLE || !WIDE_SIGN, "the nibble decoder has one table layout");
   static_assert(COLS == 4 || COLS == 8, "a group is four or eight routes");
   static_assert(!WIDE_SIGN || (COLS == 4 && !NESTED), "the wide sign table leaves room for eight activation columns of 4096 inputs");
   static_assert(!SPLIT || (COLS == 4 && !WIDE_SIGN), "the split form keeps its partial sums at the end of the 64 KB activation stage");
@@ -144,7 +144,7 @@ __global__ void __launch_bounds__(SK_THREADS, 1) projection_slab_kernel(FastProj
   // ---- tables -----------------------------------------------------------------------------
   // every thread computes one entry per pass; the warp then writes its 32 entries two at a time,
   // sixteen lanes storing the sixteen replicas of one entry side by side (no bank conflicts)
-  if (NIBBLE) build_nibble_tables(a0, p.codebook, threadIdx.x >> 5, threadIdx.x & 31, SK_WARPS);
+  if (NIBBLE) build_nibble_tables(a0, p.codebook, threadIdx.x, SK_THREADS);
   for (int e = threadIdx.x + (NIBBLE ? 512 : 0); e < (NIBBLE && !NESTED ? 0 : 768); e += SK_THREADS) {
     uint32_t lo = 0, hi = 0;
     if (e >= 512 && NESTED) {  // residual entry: byte j of the low word is 2 * v[6 - 2j], of the high word 2 * v[7 - 2j]
@@ -312,6 +312,7 @@ __global__ void __launch_bounds__(SK_THREADS, 1) projection_slab_kernel(FastProj
     // the main loop instead of in front of the stores
     int ep_route[RPL];
     const int32_t* ep_sums[RPL];  // the lane's routes' sums of x' per scale group
+    uint32_t share_sum[RPL];      // split form: sum of x' over this warp's chunks since the last close
     float ep_xs[RPL], ep_weight[RPL], ep_sum[RPL];
 #pragma unroll
     for (int cc = 0; cc < RPL; ++cc) {
@@ -320,8 +321,9 @@ __global__ void __launch_bounds__(SK_THREADS, 1) projection_slab_kernel(FastProj
       const int64_t xrow = ep_route[cc] < 0 ? p.x_zero_row : static_cast<int64_t>(ep_route[cc] / p.x_div);
       ep_xs[cc] = p.x.scale[xrow];
       ep_weight[cc] = (M == 2 && ep_route[cc] >= 0) ? p.route_weight[ep_route[cc]] : 1.0f;
-      ep_sums[cc] = p.x.sums + xrow * p.groups;
-      ep_sum[cc] = static_cast<float>(ep_sums[cc][0]);  // the only group when the rows have one scale
+      ep_sums[cc] = (NIBBLE && SPLIT) ? p.x.chunk_sums + xrow * n_chunks : p.x.sums + xrow * p.groups;  // split form: per 256 inputs, added up over the warp's share
+      ep_sum[cc] = static_cast<float>(p.x.sums[xrow * p.groups]);  // the only group when the rows have one scale
+      share_sum[cc] = 0u;
     }
     float row_scale[M][TILES][2];  // the last scale group's scale of rows g and g + 8
 
@@ -331,7 +333,10 @@ __global__ void __launch_bounds__(SK_THREADS, 1) projection_slab_kernel(FastProj
       // 8 * sum(x') of the group to the integer dot product
       uint32_t offset[RPL];
 #pragma unroll
-      for (int cc = 0; cc < RPL; ++cc) offset[cc] = NIBBLE && keep_scale ? 8u * static_cast<uint32_t>(ep_sums[cc][group]) : 0u;
+      for (int cc = 0; cc < RPL; ++cc) {
+        offset[cc] = NIBBLE && keep_scale ? 8u * (SPLIT ? share_sum[cc] : static_cast<uint32_t>(ep_sums[cc][group])) : 0u;
+        if (keep_scale) share_sum[cc] = 0u;
+      }
 #pragma unroll
       for (int m = 0; m < M; ++m)
 #pragma unroll
@@ -373,6 +378,10 @@ __global__ void __launch_bounds__(SK_THREADS, 1) projection_slab_kernel(FastProj
       uint4 cur[4];
       const uint32_t src = ring + (ring_turn % SK_STAGES) * STAGE_BYTES;
       sk_static_for<4>([&](auto s) { cur[decltype(s)::value] = sk_lds128<decltype(s)::value * 512>(src); });
+      if (NIBBLE && SPLIT) {
+#pragma unroll
+        for (int cc = 0; cc < RPL; ++cc) share_sum[cc] += static_cast<uint32_t>(ep_sums[cc][c]);
+      }
       const uint32_t b_addr = b_lane + c * 8 * B_STEP;
       sk_static_for<8>([&](auto index) {
         constexpr int I = decltype(index)::value;
@@ -647,8 +656,9 @@ int slab_split_max_in_dim() { return static_cast<int>(SK_SPLIT_RED_OFF / 8); }  
 template <int M, int TILES>
 static int launch_split(const FastProjectionArgs& p, cudaStream_t s) {
   if (p.in_dim > slab_split_max_in_dim()) return KEEPVQ_ERR_UNSUPPORTED;
-  if (p.res_table) return launch_slab<M, TILES, 4, 0u, true, false, true>(p, s);
-  return launch_slab<M, TILES, 4, 0xAAu, false, false, true>(p, s);
+  if (!p.x.chunk_sums) return KEEPVQ_ERR_NULL;  // the warps' shares of a scale group need sum(x') per 256 inputs
+  if (p.res_table) return launch_slab<M, TILES, 4, 0u, true, false, true, true>(p, s);
+  return launch_slab<M, TILES, 4, 0u, false, false, true, true>(p, s);
 }
 int slab_split_gate_up(const FastProjectionArgs& p, cudaStream_t s) { return launch_split<2, 1>(p, s); }
 int slab_split_down(const FastProjectionArgs& p, cudaStream_t s) { return launch_split<1, 2>(p, s); }

@@ -27,10 +27,8 @@ constexpr int SW_WARPS = 16;
 constexpr int SW_THREADS = SW_WARPS * 32;
 constexpr int SW_CHUNK = 32;                     // codewords of a row per step of a warp
 constexpr int SW_PASS_UNITS = 8;                 // units a warp carries in registers between two meetings of the CTA
-constexpr int SW_REPLICAS = 16;
 constexpr int SW_SMEM_BYTES = 227 * 1024;
-constexpr uint32_t SW_ABS_BYTES = 256 * 2 * SW_REPLICAS * 8;   // 64 KB, on a 64 KB boundary of the shared window
-constexpr uint32_t SW_SIGN_BYTES = 256 * SW_REPLICAS * 8;      // 32 KB
+constexpr uint32_t SW_TABLE_BYTES = 64 * 1024;   // the nibble decoder's two tables, on a 64 KB boundary of the shared window
 constexpr uint32_t SW_RED_BYTES = SW_PASS_UNITS * SW_WARPS * 4 * 128;  // 64 KB: [unit of the pass][k part][value][lane] fp32
 
 template <int N, typename F, int... I>
@@ -49,12 +47,12 @@ __device__ __forceinline__ uint4 sw_lds128(uint32_t addr) {  // data a cp.async 
   return v;
 }
 __device__ __forceinline__ void sw_mma(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
-  asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+  asm("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
       : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 // The first MMA of a chain: accumulates onto zero, so the accumulators need no clearing.
 __device__ __forceinline__ void sw_mma_first(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
-  asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+  asm("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
       : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
 }
 template <int I>
@@ -63,12 +61,12 @@ __device__ __forceinline__ uint32_t sw_word(const uint4& v) {
 }
 
 // M = 2: gate and up over the same rows, fused by SwiGLU; M = 1: one matrix.
-// TABLE_STEPS: which of a lane's eight codewords per chunk take their sign masks from the second
-// table (the others spread the sign byte on the integer pipe); 0 = no second table, and the room
-// it would take goes to a deeper code ring (DEPTH stages of one chunk per warp).
+// The decode is the nibble decoder (moe_fast.cuh): unsigned operand bytes q + 8, whose offset
+// 8 * sum(x') comes off each chunk's integer dot product (the quantised rows carry sum(x') per 256 inputs).
+// DEPTH: stages of one chunk per warp in the code ring.
 // `status` (may be null) is set to 2 if the shared window does not have the expected shape.
 // RAGGED: the output rows are not a multiple of a unit's rows, so the last unit of a group clamps its row indices.
-template <int M, unsigned TABLE_STEPS, int DEPTH, bool RAGGED>
+template <int M, int DEPTH, bool RAGGED>
 __global__ void __launch_bounds__(SW_THREADS, 1) projection_sweep_kernel(FastProjectionArgs p, int32_t* status, int ks) {
   extern __shared__ __align__(16) uint8_t smem[];
   grid_launch_dependents();
@@ -79,14 +77,13 @@ __global__ void __launch_bounds__(SW_THREADS, 1) projection_sweep_kernel(FastPro
   constexpr int VALUES = 4;                            // per lane and unit: (sub-tile, row g | g + 8) for the lane's route
   constexpr uint32_t STAGE_BYTES = STREAMS * 512;      // per warp: 16 bytes per lane and stream
   constexpr uint32_t RING_BYTES = DEPTH * STAGE_BYTES;
-  constexpr uint32_t SECOND_BYTES = TABLE_STEPS ? SW_SIGN_BYTES : 0u;
 
-  // ---- the shared window: rings below the first 64 KB boundary as far as they fit, then the abs
-  // table on the boundary, the second table, the partial sums, the remaining rings
+  // ---- the shared window: rings below the first 64 KB boundary as far as they fit, then the two
+  // tables (one 64 KB region) on the boundary, the partial sums, the remaining rings
   const uint32_t base = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
   const uint32_t a0 = (base + 0xFFFFu) & ~0xFFFFu;
   const int low_warps = min(SW_WARPS, static_cast<int>((a0 - base) / RING_BYTES));
-  const uint32_t red_base = a0 + SW_ABS_BYTES + SECOND_BYTES;
+  const uint32_t red_base = a0 + SW_TABLE_BYTES;
   const uint32_t high_rings = red_base + SW_RED_BYTES;
   if (high_rings + (SW_WARPS - low_warps) * RING_BYTES > base + SW_SMEM_BYTES) {  // uniform over the grid
     if (status && threadIdx.x == 0) atomicExch(status, 2);
@@ -96,22 +93,11 @@ __global__ void __launch_bounds__(SW_THREADS, 1) projection_sweep_kernel(FastPro
   const int g = lane >> 2, t = lane & 3;
 
   // ---- tables (from constants: before the wait on the previous kernel) -------------------------
-  for (int e = threadIdx.x; e < (TABLE_STEPS ? 768 : 512); e += SW_THREADS) {
-    const uint2 v = e < 512 ? abs_table_entry(p.codebook[e >> 1], e & 1) : sign_table_entry(e - 512);
-    const int e_warp = e & ~31;
-    const uint32_t dst_warp = e < 512 ? a0 + e_warp * (SW_REPLICAS * 8) : a0 + SW_ABS_BYTES + (e_warp - 512) * (SW_REPLICAS * 8);
-#pragma unroll 4
-    for (int i = 0; i < 32; i += 2) {  // sixteen lanes store the sixteen replicas of one entry side by side: no bank conflicts
-      const int from = i + (lane >> 4);
-      const uint32_t lo = __shfl_sync(0xFFFFFFFFu, v.x, from), hi = __shfl_sync(0xFFFFFFFFu, v.y, from);
-      asm volatile("st.shared.v2.u32 [%0], {%1,%2};" ::"r"(dst_warp + from * (SW_REPLICAS * 8) + (lane & 15) * 8), "r"(lo), "r"(hi) : "memory");
-    }
-  }
+  build_nibble_tables(a0, p.codebook, threadIdx.x, SW_THREADS);
   grid_wait();  // everything below reads what earlier kernels of the stream wrote
   __syncthreads();
 
-  const uint32_t abs_lane = a0 + static_cast<uint32_t>(lane & (SW_REPLICAS - 1)) * 8u;
-  const uint32_t second_lane = a0 + SW_ABS_BYTES + static_cast<uint32_t>(lane & (SW_REPLICAS - 1)) * 8u;
+  const uint32_t abs_lane = a0 + lane * 4u, sign_lane = a0 + 128u + lane * 4u;
   const uint32_t ring = (warp < low_warps ? base + warp * RING_BYTES : high_rings + (warp - low_warps) * RING_BYTES) + lane * 16;
   const int64_t N = p.out_dim, cw = p.in_dim / 8;
   const int n_chunks = static_cast<int>(cw / SW_CHUNK);
@@ -194,6 +180,8 @@ __global__ void __launch_bounds__(SW_THREADS, 1) projection_sweep_kernel(FastPro
   Walk at;
   start_walk(at);
   const uint8_t* x_lane = nullptr;
+  const int32_t* chunk_sums = nullptr;
+  int held_sum = 0;  // a warp with one chunk per unit keeps its chunk's sum as it keeps the slice
   int x_group = -1;  // whose activations x_lane points at
   uint2 b[8];
 #pragma unroll
@@ -227,10 +215,13 @@ __global__ void __launch_bounds__(SW_THREADS, 1) projection_sweep_kernel(FastPro
         const int route = p.groups_of_routes.routes[gstart + col_route];
         x_lane = p.x.q + (static_cast<int64_t>(route / p.x_div) * cw + t * 8) * 16 + (g & 1) * 8;
         x_group = at.gi;
-        if (my_chunks == 1) load_slice(c_first);
+        // columns 2t, 2t + 1 of the accumulators are route t's: its sums of x' per chunk
+        const int64_t sums_row = t < gsize ? p.groups_of_routes.routes[gstart + t] / p.x_div : p.x_zero_row;
+        chunk_sums = p.x.chunk_sums + sums_row * n_chunks;
+        if (my_chunks == 1) { load_slice(c_first); held_sum = chunk_sums[c_first]; }
       }
       for (int c = c_first; c < c_end; ++c) {
-        if (my_chunks != 1) load_slice(c);
+        if (my_chunks != 1) { load_slice(c); held_sum = chunk_sums[c]; }
         fetch();
         asm volatile("cp.async.wait_group %0;" ::"n"(DEPTH - 1) : "memory");  // this chunk has landed
         const uint32_t src = ring + (use_turn % DEPTH) * STAGE_BYTES;
@@ -251,12 +242,11 @@ __global__ void __launch_bounds__(SW_THREADS, 1) projection_sweep_kernel(FastPro
         int acc[2][2][4];  // two chains per sub-tile, used by alternate steps: the MMA's dependent latency is long
         sw_static_for<8>([&](auto index) {
           constexpr int I = decltype(index)::value;
-          constexpr bool TABLE = ((TABLE_STEPS >> I) & 1u) != 0;
 #pragma unroll
           for (int sub = 0; sub < 2; ++sub) {
             uint32_t a[4];
-            decode_codeword<TABLE, (I & 1) != 0, false>(sw_word<I>(cur[2 * sub]), abs_lane, second_lane, a[0], a[2]);      // row g
-            decode_codeword<TABLE, (I & 1) != 0, false>(sw_word<I>(cur[2 * sub + 1]), abs_lane, second_lane, a[1], a[3]);  // row g + 8
+            decode_codeword_nibble<(I & 1) != 0>(sw_word<I>(cur[2 * sub]), abs_lane, sign_lane, a[0], a[2]);      // row g
+            decode_codeword_nibble<(I & 1) != 0>(sw_word<I>(cur[2 * sub + 1]), abs_lane, sign_lane, a[1], a[3]);  // row g + 8
             if (I < 2) sw_mma_first(acc[I][sub], a[0], a[1], a[2], a[3], b[I].x, b[I].y);
             else sw_mma(acc[I & 1][sub], a[0], a[1], a[2], a[3], b[I].x, b[I].y);
           }
@@ -266,8 +256,9 @@ __global__ void __launch_bounds__(SW_THREADS, 1) projection_sweep_kernel(FastPro
         for (int sub = 0; sub < 2; ++sub)
 #pragma unroll
           for (int rr = 0; rr < 2; ++rr) {
-            // 256 * high + low of one chunk fits 32 bits (256 products of at most 2^15 each, times 256)
-            const int dot = ((acc[0][sub][2 * rr] + acc[1][sub][2 * rr]) << 8) + acc[0][sub][2 * rr + 1] + acc[1][sub][2 * rr + 1];
+            // 256 * high + low of one chunk fits 32 bits (256 products of at most 2^15 each, times 256);
+            // less 8 * sum(x') it is sum(q x') over the chunk
+            const int dot = ((acc[0][sub][2 * rr] + acc[1][sub][2 * rr]) << 8) + acc[0][sub][2 * rr + 1] + acc[1][sub][2 * rr + 1] - 8 * held_sum;
             part[2 * sub + rr] = fmaf(sc[sub][rr], static_cast<float>(dot), part[2 * sub + rr]);
           }
       }
@@ -356,9 +347,9 @@ static int sweep_k_parts(int n_chunks) {
   return best;
 }
 
-template <int M, unsigned TABLE_STEPS, int DEPTH, bool RAGGED>
+template <int M, int DEPTH, bool RAGGED>
 static int launch_sweep_kernel(const FastProjectionArgs& p, cudaStream_t s) {
-  auto kernel = projection_sweep_kernel<M, TABLE_STEPS, DEPTH, RAGGED>;
+  auto kernel = projection_sweep_kernel<M, DEPTH, RAGGED>;
   static uint64_t configured = 0;  // one bit per device: the shared-memory opt-in is a per-device attribute of the function
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
@@ -380,22 +371,23 @@ static int launch_sweep_kernel(const FastProjectionArgs& p, cudaStream_t s) {
   return KEEPVQ_OK;
 }
 
-template <int M, unsigned TABLE_STEPS, int DEPTH>
+template <int M, int DEPTH>
 static int launch_sweep(const FastProjectionArgs& p, cudaStream_t s) {
-  if (p.out_dim % (M == 2 ? 16 : 32) == 0) return launch_sweep_kernel<M, TABLE_STEPS, DEPTH, false>(p, s);
+  if (!p.x.chunk_sums) return KEEPVQ_ERR_NULL;
+  if (p.out_dim % (M == 2 ? 16 : 32) == 0) return launch_sweep_kernel<M, DEPTH, false>(p, s);
   // a gate/up pair's outputs are the down projection's inputs, which come in multiples of 256
   if (M == 2) return KEEPVQ_ERR_UNSUPPORTED;
-  return launch_sweep_kernel<1, TABLE_STEPS, DEPTH, true>(p, s);
+  return launch_sweep_kernel<1, DEPTH, true>(p, s);
 }
 
 #ifdef KEEPVQ_DIAG
-static int g_sweep_variant = 0;  // measurement build only: 0 = second table + ring of 2, 1 = no second table + ring of 3
+static int g_sweep_variant = 0;  // measurement build only: 0 = code ring of 2 stages, 1 = of 3
 extern "C" void keepvq_diag_set_sweep(int variant) { g_sweep_variant = variant; }
-int sweep_gate_up(const FastProjectionArgs& p, cudaStream_t s) { return g_sweep_variant ? launch_sweep<2, 0u, 3>(p, s) : launch_sweep<2, 0xAAu, 2>(p, s); }
-int sweep_down(const FastProjectionArgs& p, cudaStream_t s) { return g_sweep_variant ? launch_sweep<1, 0u, 3>(p, s) : launch_sweep<1, 0xAAu, 2>(p, s); }
+int sweep_gate_up(const FastProjectionArgs& p, cudaStream_t s) { return g_sweep_variant ? launch_sweep<2, 3>(p, s) : launch_sweep<2, 2>(p, s); }
+int sweep_down(const FastProjectionArgs& p, cudaStream_t s) { return g_sweep_variant ? launch_sweep<1, 3>(p, s) : launch_sweep<1, 2>(p, s); }
 #else
-int sweep_gate_up(const FastProjectionArgs& p, cudaStream_t s) { return launch_sweep<2, 0xAAu, 2>(p, s); }
-int sweep_down(const FastProjectionArgs& p, cudaStream_t s) { return launch_sweep<1, 0xAAu, 2>(p, s); }
+int sweep_gate_up(const FastProjectionArgs& p, cudaStream_t s) { return launch_sweep<2, 2>(p, s); }
+int sweep_down(const FastProjectionArgs& p, cudaStream_t s) { return launch_sweep<1, 2>(p, s); }
 #endif
 
 }  // namespace fast
