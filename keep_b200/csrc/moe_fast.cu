@@ -5,9 +5,9 @@
 // of routes) live in their own files: projection_slab.cu (calls with many route groups, and their
 // split form for a residual tier with few), projection_sweep.cu (few route groups) and
 // prefill_umma.cu (many routes per expert, tcgen05).  They share:
-//   - a codeword becomes the A fragment of an m16n8k32 int8 MMA through a table indexed by
-//     (abs row, parity), replicated 16x so lanes never share a bank, and sign masks from a second
-//     table or from two integer multiplies and byte permutes;
+//   - a codeword becomes the A fragment of an m16n8k32 int8 MMA through two 4-byte table reads
+//     (abs byte, sign byte; 32 replicas each so lanes never share a bank) XORed and spread from
+//     nibbles to bytes: the nibble decoder of moe_fast.cuh;
 //   - the K order inside an MMA is permuted (byte j of the low word is table nibble 3-j, of the
 //     high word nibble 7-j); the activations are stored in that same order by quantize_rows;
 //   - accumulation is exact in int32; one conversion to fp32 per scale group.

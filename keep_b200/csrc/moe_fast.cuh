@@ -6,8 +6,9 @@
 // bit arithmetic on a byte.  So a row's dot product with integer activations x' is
 //     4 * sum_k w_k x'_k = 2 * sum_k q_k x'_k + sum_k x'_k,
 // an exact int8 tensor-core product plus one per-token constant.  Activations are quantised per
-// row to 16-bit fixed point (power-of-two scale) and fed as a signed high byte and an unsigned
-// low byte, two MMAs per tile.  The only rounding in a projection is that fixed-point step.
+// row to 16-bit fixed point (power-of-two scale) and fed as two signed bytes (x' = 256 hi + lo).
+// The only rounding in a projection is that fixed-point step.  The kernels hand the tensor cores
+// u = q + 8 (a 4-bit unsigned value, two table words XORed) and take 8 * sum(x') off afterwards.
 #pragma once
 
 #include "common.cuh"
@@ -23,19 +24,10 @@ constexpr int PREFILL_GROUP_ROUTES = 96;   // routes of one expert per tcgen05 i
 
 
 // ------------------------------------------------------------------------------------------
-// Codeword decoders shared by the slab kernel (projection_slab.cu) and the tcgen05 kernel
-// (prefill_umma.cu).  Tables live in shared memory at addresses the kernels choose:
-//   abs table     [abs row][parity][16 replicas] x 8 bytes, ON A 64 KB BOUNDARY of the shared
-//                 window, so that the abs byte of a code word dropped into byte 1 of
-//                 (table address + lane offset) is the entry's address: one byte permute;
-//   second table  [sign byte][replicas] x 8 bytes: the XOR masks of the sign byte (sign flips,
-//                 the parity bit of every byte, the extra flip of table nibble 0 on odd parity);
-//                 with 32 replicas and a 64 KB boundary of its own it is addressed the same way.
+// The codeword decoder shared by the decode kernels (projection_slab.cu, projection_sweep.cu) and
+// the tcgen05 kernel (prefill_umma.cu), and the entries its tables are built from.
 // Entry bytes: byte j of the low word is table nibble 3 - j, of the high word nibble 7 - j.
 // ------------------------------------------------------------------------------------------
-constexpr uint32_t SK_SPREAD_LO = (1u << 4) | (1u << 13) | (1u << 22) | (1u << 31);  // sign bits 3,2,1,0 -> bits 7,15,23,31
-constexpr uint32_t SK_SPREAD_HI = 1u | (1u << 9) | (1u << 18) | (1u << 27);          // sign bits 7,6,5,4 -> the same places
-
 // The eight bytes q (4w = 2q + 1 for positive signs) of abs row `word` under one parity.
 __device__ __forceinline__ uint2 abs_table_entry(uint32_t word, uint32_t par) {
   uint32_t lo = 0, hi = 0;
@@ -68,32 +60,6 @@ __device__ __forceinline__ uint2 table_entry(uint32_t addr) {  // tables never c
   uint2 v;
   asm("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
   return v;
-}
-__device__ __forceinline__ uint32_t byte_masks(uint32_t v) {  // the top bit of every byte, spread over the byte
-  uint32_t m;
-  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(m) : "r"(v), "r"(0u), "r"(0xBA98u));
-  return m;
-}
-// One codeword -> the two A-fragment words q (4w = 2q + 1).  The codeword is the low (ODD = false)
-// or the high half of `word`.  abs_lane = address of the abs table + this lane's replica offset
-// (byte 1 of it is zero: the table sits on a 64 KB boundary); second_lane likewise for the
-// second table (WIDE_SIGN), or that table's address + replica offset as a plain addend.
-template <bool TABLE, bool ODD, bool WIDE_SIGN>
-__device__ __forceinline__ void decode_codeword(uint32_t word, uint32_t abs_lane, uint32_t second_lane, uint32_t& lo, uint32_t& hi) {
-  const uint32_t entry = __byte_perm(word, abs_lane, ODD ? 0x7634 : 0x7614);  // the abs byte into byte 1 of the address
-  if (TABLE) {
-    uint32_t at;  // sign flips and parity
-    if (WIDE_SIGN) at = __byte_perm(word, second_lane, ODD ? 0x7624 : 0x7604);
-    else at = (ODD ? __byte_perm(word, 0u, 0x4442) : (word & 0xFFu)) * 128u + second_lane;
-    const uint2 e = table_entry(entry), m = table_entry(at);  // even-parity entry
-    lo = e.x ^ m.x;
-    hi = e.y ^ m.y;
-  } else {
-    const uint32_t sign = ODD ? __byte_perm(word, 0u, 0x4442) : (word & 0xFFu);
-    const uint2 e = table_entry(entry | ((static_cast<uint32_t>(__popc(sign)) << 7) & 0x80u));
-    lo = e.x ^ (byte_masks(sign * SK_SPREAD_LO) & 0xFEFEFEFEu);
-    hi = e.y ^ (byte_masks(sign * SK_SPREAD_HI) & 0xFEFEFEFEu);
-  }
 }
 
 // The nibble decoder.  Both tables hold an entry as eight 4-bit values in ONE word, u = q + 8 for the

@@ -9,13 +9,12 @@
 //     as the eight columns of ONE m16n8k32 MMA (a lane ends up with both planes of its route);
 //     groups of up to eight routes (two MMAs per tile and step) serve calls with more routes per
 //     expert;
-//   - a table address is one byte permute: the abs table sits on a 64 KB boundary of the shared
-//     window and an entry is 256 bytes wide (two parities x sixteen replicas x 8 bytes), so the
-//     abs byte of the code word dropped into byte 1 of (table base + lane offset) IS the address;
-//     the sign table gets the same treatment when there is room for 32 replicas of it;
-//   - two decoders share the work so that neither the integer pipe nor shared-memory bandwidth is
-//     the only limit: steps named in TABLE_STEPS read the sign masks (parity folded in) from the
-//     second table, the others spread the sign byte with two multiplies and byte permutes;
+//   - the nibble decoder (moe_fast.cuh): the abs entry and the sign byte's XOR masks are one
+//     32-bit word of eight 4-bit values each, 32 replicas, interleaved in one 64 KB region on a
+//     64 KB boundary of the shared window, so the abs (sign) byte of the code word dropped into
+//     byte 1 of (region + lane offset) IS the entry's address: two byte permutes, two 4-byte
+//     table reads, two masked XORs and a shift per codeword.  The operand bytes are q + 8
+//     (unsigned A), and 8 * sum(x') comes off the integer dot product when a scale group closes;
 //   - codes stream through a private cp.async ring per warp; a group's quantised activations are
 //     staged once per run of items in MMA-fragment order, and a lane whose column carries no
 //     route re-reads a live column's bytes (its own MMA column is never looked at), so the
@@ -35,25 +34,21 @@ namespace fast {
 constexpr int SK_WARPS = 16;
 constexpr int SK_THREADS = SK_WARPS * 32;
 constexpr int SK_CHUNK = 32;                              // codewords of a row per ring stage and lane quartet
-constexpr int SK_REPLICAS = 16;
 constexpr int SK_STAGES = 2;
-constexpr int SK_SMEM_BYTES = 227 * 1024;                 // the whole opt-in window: the tables want fixed 64 KB boundaries inside it
+constexpr int SK_SMEM_BYTES = 227 * 1024;                 // the whole opt-in window: the tables want a fixed 64 KB boundary inside it
 constexpr int SK_WARP_RING = SK_STAGES * 4 * 512;         // four 16-byte streams per lane and stage
-constexpr uint32_t SK_ABS_BYTES = 256 * 2 * SK_REPLICAS * 8;   // 64 KB  [abs row][parity][replica]
+constexpr uint32_t SK_TABLE_BYTES = 64 * 1024;            // the nibble decoder's two tables
+constexpr uint32_t SK_RES_REPLICAS = 16;
+constexpr uint32_t SK_RES_BYTES = 256 * SK_RES_REPLICAS * 8;   // 32 KB: the residual codebook, signed bytes, [code][replica] x 8 bytes
 
 // Shared window, in absolute shared addresses.  A0 = the first 64 KB boundary at or above the
 // dynamic base (the runtime keeps 1 KB below it, so A0 = 64 KB):
 //   [base, A0)            cp.async rings of as many warps as fit (15)
-//   [A0, +64 KB)          abs table
-//   WIDE_SIGN             [+64 KB, +128 KB) sign table, 32 replicas | [+128 KB, +160 KB) activations: 8 columns x 4096 inputs
-//   otherwise             [+64 KB, +96 KB) second table, 16 replicas | [+96 KB, +160 KB) activations: 8 x 8192 or 16 x 4096
+//   [A0, +64 KB)          the two tables
+//   no residual tier      [+64 KB, +128 KB) activations: 8 columns x 8192 inputs or 16 x 4096
+//   residual tier         [+64 KB, +96 KB) residual codebook | [+96 KB, +160 KB) activations
 //   [+160 KB, ...)        the remaining rings
-constexpr uint32_t SK_SECOND_OFF = SK_ABS_BYTES;
 constexpr uint32_t SK_RING_HIGH_OFF = 160 * 1024;
-template <bool WIDE_SIGN> struct SlabLayout {
-  static constexpr uint32_t SECOND_REPLICAS = WIDE_SIGN ? 32 : 16;
-  static constexpr uint32_t B_OFF = SK_SECOND_OFF + 256 * SECOND_REPLICAS * 8;
-};
 
 template <int N, typename F, int... I>
 __device__ __forceinline__ void sk_static_for_impl(F&& f, std::integer_sequence<int, I...>) { (f(std::integral_constant<int, I>{}), ...); }
@@ -104,26 +99,20 @@ __device__ __forceinline__ uint32_t sk_word(const uint4& v) {
 }
 
 // COLS = routes per group: 4 (both byte planes of a route in one MMA) or 8 (one MMA per plane).
-// NESTED: the layer has a residual tier; the second table then holds the residual codebook (the
-// base decode does every step's signs on the integer pipe) and an item whose slot is hot runs a
-// second pass over the residual's 8-bit codes.
+// NESTED: the layer has a residual tier; the residual codebook (signed bytes) sits behind the
+// tables, and an item whose slot is hot runs a second pass over the residual's 8-bit codes.
 // `status` (may be null) is set to 2 if the shared window does not have the expected shape.
 // SPLIT: see the head of the file; the partial sums (16 KB) live at the end of the 64 KB activation
-// stage, which leaves 48 KB for the activations (eight columns of 6144 inputs).
+// stage, which leaves 48 KB for the activations (eight columns of 6144 inputs).  A warp's share of
+// a scale group needs sum(x') over just that share: the quantised rows carry it per 256 inputs.
 constexpr uint32_t SK_SPLIT_RED_OFF = 48 * 1024;          // from the start of the activation stage
 constexpr int SK_SPLIT_ITEMS_PER_CTA = 4;                 // items per CTA the split factor aims for
 
-// NIBBLE: the nibble decoder above on every step of the base pass (not in the split form): TABLE_STEPS
-// and WIDE_SIGN play no part, and the activations start right behind the one table region (with a
-// residual tier: behind the residual codebook that follows it).
-template <int M, int TILES, int COLS, unsigned TABLE_STEPS, bool NESTED, bool WIDE_SIGN, bool SPLIT, bool NIBBLE = false>
+template <int M, int TILES, int COLS, bool NESTED, bool SPLIT>
 __global__ void __launch_bounds__(SK_THREADS, 1) projection_slab_kernel(FastProjectionArgs p, int32_t* status) {
-  static_assert(!NIBBLE || !WIDE_SIGN, "the nibble decoder has one table layout");
   static_assert(COLS == 4 || COLS == 8, "a group is four or eight routes");
-  static_assert(!WIDE_SIGN || (COLS == 4 && !NESTED), "the wide sign table leaves room for eight activation columns of 4096 inputs");
-  static_assert(!SPLIT || (COLS == 4 && !WIDE_SIGN), "the split form keeps its partial sums at the end of the 64 KB activation stage");
+  static_assert(!SPLIT || COLS == 4, "the split form keeps its partial sums at the end of the 64 KB activation stage");
   static_assert(M * 2 * TILES == 4, "four code streams per lane");
-  using L = SlabLayout<WIDE_SIGN>;
   extern __shared__ __align__(16) uint8_t smem[];
   grid_launch_dependents();
   constexpr int PLANES = COLS == 4 ? 1 : 2;     // MMAs per tile and step
@@ -131,7 +120,6 @@ __global__ void __launch_bounds__(SK_THREADS, 1) projection_slab_kernel(FastProj
   constexpr int PARTS = 2 * RPL;                // (row g | g + 8) x routes of the lane
   constexpr int B_LANE = COLS == 4 ? 8 : 16;    // bytes of the B operand a lane reads per step
   constexpr int B_STEP = 32 * B_LANE;
-  constexpr unsigned STEPS = NESTED ? 0u : TABLE_STEPS;
 
   const uint32_t smem_base = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
   const uint32_t a0 = (smem_base + 0xFFFFu) & ~0xFFFFu;
@@ -142,45 +130,37 @@ __global__ void __launch_bounds__(SK_THREADS, 1) projection_slab_kernel(FastProj
   }
 
   // ---- tables -----------------------------------------------------------------------------
-  // every thread computes one entry per pass; the warp then writes its 32 entries two at a time,
-  // sixteen lanes storing the sixteen replicas of one entry side by side (no bank conflicts)
-  if (NIBBLE) build_nibble_tables(a0, p.codebook, threadIdx.x, SK_THREADS);
-  for (int e = threadIdx.x + (NIBBLE ? 512 : 0); e < (NIBBLE && !NESTED ? 0 : 768); e += SK_THREADS) {
-    uint32_t lo = 0, hi = 0;
-    if (e >= 512 && NESTED) {  // residual entry: byte j of the low word is 2 * v[6 - 2j], of the high word 2 * v[7 - 2j]
-      const uint32_t* row = p.res_table + (e - 512) * 4;
+  build_nibble_tables(a0, p.codebook, threadIdx.x, SK_THREADS);
+  if (NESTED) {
+    // the residual codebook: byte j of an entry's low word is 2 * v[6 - 2j], of its high word
+    // 2 * v[7 - 2j].  A thread works out one entry; its warp then writes its 32 entries two at a
+    // time, sixteen lanes storing the sixteen replicas of one entry side by side (no bank conflicts)
+    for (int e = threadIdx.x; e < 256; e += SK_THREADS) {
+      uint32_t lo = 0, hi = 0;
+      const uint32_t* row = p.res_table + e * 4;
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         const __half2 pair = *reinterpret_cast<const __half2*>(&row[3 - j]);  // dims 6 - 2j, 7 - 2j
         lo |= (static_cast<uint32_t>(__float2int_rn(2.0f * __low2float(pair))) & 0xFFu) << (8 * j);
         hi |= (static_cast<uint32_t>(__float2int_rn(2.0f * __high2float(pair))) & 0xFFu) << (8 * j);
       }
-    } else if (e < 512) {  // abs entry (row e / 2, parity e & 1)
-      const uint2 v = abs_table_entry(p.codebook[e >> 1], e & 1);
-      lo = v.x; hi = v.y;
-    } else {
-      const uint2 v = sign_table_entry(e - 512);
-      lo = v.x; hi = v.y;
-    }
-    const uint32_t replicas = e < 512 ? SK_REPLICAS : L::SECOND_REPLICAS;  // uniform over a warp: 512 is a multiple of 32
-    const int e_warp = e & ~31, ln = threadIdx.x & 31;
-    const uint32_t dst_warp = e < 512 ? a0 + e_warp * (SK_REPLICAS * 8) : a0 + SK_SECOND_OFF + (e_warp - 512) * (L::SECOND_REPLICAS * 8);
-    const uint32_t per_store = 32 / replicas;  // entries one warp-wide store covers: 2 or 1
+      const int e_warp = e & ~31, ln = threadIdx.x & 31;
+      const uint32_t dst_warp = a0 + SK_TABLE_BYTES + e_warp * (SK_RES_REPLICAS * 8);
 #pragma unroll 4
-    for (uint32_t i = 0; i < 32; i += per_store) {
-      const int from = static_cast<int>(i + (replicas == 16 ? (ln >> 4) : 0));
-      const uint32_t vlo = __shfl_sync(0xFFFFFFFFu, lo, from), vhi = __shfl_sync(0xFFFFFFFFu, hi, from);
-      sk_sts64(dst_warp + from * replicas * 8 + (ln & (replicas - 1)) * 8, vlo, vhi);
+      for (int i = 0; i < 32; i += 2) {
+        const int from = i + (ln >> 4);
+        const uint32_t vlo = __shfl_sync(0xFFFFFFFFu, lo, from), vhi = __shfl_sync(0xFFFFFFFFu, hi, from);
+        sk_sts64(dst_warp + from * (SK_RES_REPLICAS * 8) + (ln & (SK_RES_REPLICAS - 1)) * 8, vlo, vhi);
+      }
     }
   }
 
   grid_wait();  // the tables came from constants; everything below reads what earlier kernels of the stream wrote
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int g = lane >> 2, t = lane & 3;
-  const uint32_t abs_lane = NIBBLE ? a0 + lane * 4u : a0 + static_cast<uint32_t>(lane & (SK_REPLICAS - 1)) * 8u;
-  const uint32_t sign_lane = a0 + 128u + lane * 4u;  // nibble decoder only
-  const uint32_t second_lane = a0 + SK_SECOND_OFF + static_cast<uint32_t>(lane & (L::SECOND_REPLICAS - 1)) * 8u;
-  const uint32_t b_base = a0 + (NIBBLE && !NESTED ? SK_ABS_BYTES : L::B_OFF);
+  const uint32_t abs_lane = a0 + lane * 4u, sign_lane = a0 + 128u + lane * 4u;
+  const uint32_t res_lane = a0 + SK_TABLE_BYTES + static_cast<uint32_t>(lane & (SK_RES_REPLICAS - 1)) * 8u;
+  const uint32_t b_base = a0 + SK_TABLE_BYTES + (NESTED ? SK_RES_BYTES : 0u);
   constexpr int STAGE_BYTES = 4 * 512;                   // per warp
   const uint32_t ring = (warp < low_warps ? smem_base + warp * SK_WARP_RING : a0 + SK_RING_HIGH_OFF + (warp - low_warps) * SK_WARP_RING) + lane * 16;
   const int64_t N = p.out_dim, cw = p.in_dim / 8;
@@ -321,7 +301,7 @@ __global__ void __launch_bounds__(SK_THREADS, 1) projection_slab_kernel(FastProj
       const int64_t xrow = ep_route[cc] < 0 ? p.x_zero_row : static_cast<int64_t>(ep_route[cc] / p.x_div);
       ep_xs[cc] = p.x.scale[xrow];
       ep_weight[cc] = (M == 2 && ep_route[cc] >= 0) ? p.route_weight[ep_route[cc]] : 1.0f;
-      ep_sums[cc] = (NIBBLE && SPLIT) ? p.x.chunk_sums + xrow * n_chunks : p.x.sums + xrow * p.groups;  // split form: per 256 inputs, added up over the warp's share
+      ep_sums[cc] = SPLIT ? p.x.chunk_sums + xrow * n_chunks : p.x.sums + xrow * p.groups;  // split form: per 256 inputs, added up over the warp's share
       ep_sum[cc] = static_cast<float>(p.x.sums[xrow * p.groups]);  // the only group when the rows have one scale
       share_sum[cc] = 0u;
     }
@@ -329,12 +309,12 @@ __global__ void __launch_bounds__(SK_THREADS, 1) projection_slab_kernel(FastProj
 
     // accumulators -> fp32 partials at the end of a scale group
     auto close_group = [&](const void* const (&scales)[2], int64_t row_base, int64_t groups, int group, float (&into)[M][TILES][PARTS], bool keep_scale) {
-      // keep_scale marks the base pass: with the nibble decoder its operand was u = q + 8, which added
-      // 8 * sum(x') of the group to the integer dot product
+      // keep_scale marks the base pass: its operand was u = q + 8, which added 8 * sum(x') of the
+      // group (of the warp's share of it) to the integer dot product
       uint32_t offset[RPL];
 #pragma unroll
       for (int cc = 0; cc < RPL; ++cc) {
-        offset[cc] = NIBBLE && keep_scale ? 8u * (SPLIT ? share_sum[cc] : static_cast<uint32_t>(ep_sums[cc][group])) : 0u;
+        offset[cc] = keep_scale ? 8u * (SPLIT ? share_sum[cc] : static_cast<uint32_t>(ep_sums[cc][group])) : 0u;
         if (keep_scale) share_sum[cc] = 0u;
       }
 #pragma unroll
@@ -356,12 +336,9 @@ __global__ void __launch_bounds__(SK_THREADS, 1) projection_slab_kernel(FastProj
                 hi = acc[0][0][m][tl][2 * rr + cc] + acc[0][1][m][tl][2 * rr + cc];
                 lo = acc[PLANES - 1][0][m][tl][2 * rr + cc] + acc[PLANES - 1][1][m][tl][2 * rr + cc];
               }
-              if (NIBBLE) {  // 256 hi + lo - 8 sum(x') in wrapping 32-bit arithmetic: the true value, sum(q x'), fits
-                const int dot = static_cast<int>(static_cast<uint32_t>(hi) * 256u + static_cast<uint32_t>(lo) - offset[cc]);
-                into[m][tl][rr * RPL + cc] = fmaf(sc, static_cast<float>(dot), into[m][tl][rr * RPL + cc]);
-              } else {
-                into[m][tl][rr * RPL + cc] = fmaf(sc, 256.0f * static_cast<float>(hi) + static_cast<float>(lo), into[m][tl][rr * RPL + cc]);
-              }
+              // 256 hi + lo - 8 sum(x') in wrapping 32-bit arithmetic: the true value, sum(q x'), fits
+              const int dot = static_cast<int>(static_cast<uint32_t>(hi) * 256u + static_cast<uint32_t>(lo) - offset[cc]);
+              into[m][tl][rr * RPL + cc] = fmaf(sc, static_cast<float>(dot), into[m][tl][rr * RPL + cc]);
             }
 #pragma unroll
             for (int pl = 0; pl < PLANES; ++pl)
@@ -378,14 +355,13 @@ __global__ void __launch_bounds__(SK_THREADS, 1) projection_slab_kernel(FastProj
       uint4 cur[4];
       const uint32_t src = ring + (ring_turn % SK_STAGES) * STAGE_BYTES;
       sk_static_for<4>([&](auto s) { cur[decltype(s)::value] = sk_lds128<decltype(s)::value * 512>(src); });
-      if (NIBBLE && SPLIT) {
+      if (SPLIT) {
 #pragma unroll
         for (int cc = 0; cc < RPL; ++cc) share_sum[cc] += static_cast<uint32_t>(ep_sums[cc][c]);
       }
       const uint32_t b_addr = b_lane + c * 8 * B_STEP;
       sk_static_for<8>([&](auto index) {
         constexpr int I = decltype(index)::value;
-        constexpr bool TABLE = ((STEPS >> I) & 1u) != 0;
         uint32_t b[4];
         if (COLS == 4) { const uint2 v = sk_lds64<I * B_STEP>(b_addr); b[0] = v.x; b[1] = v.y; }
         else { const uint4 v = sk_lds128<I * B_STEP>(b_addr); b[0] = v.x; b[1] = v.y; b[2] = v.z; b[3] = v.w; }
@@ -394,17 +370,10 @@ __global__ void __launch_bounds__(SK_THREADS, 1) projection_slab_kernel(FastProj
 #pragma unroll
           for (int tl = 0; tl < TILES; ++tl) {
             uint32_t a[4];
-            if (NIBBLE) {
-              decode_codeword_nibble<(I & 1) != 0>(sk_word<I>(cur[(m * TILES + tl) * 2]), abs_lane, sign_lane, a[0], a[2]);      // row g
-              decode_codeword_nibble<(I & 1) != 0>(sk_word<I>(cur[(m * TILES + tl) * 2 + 1]), abs_lane, sign_lane, a[1], a[3]);  // row g + 8
-              sk_mma_u8(acc[0][I & 1][m][tl], a[0], a[1], a[2], a[3], b[0], b[1]);
-              if (PLANES == 2) sk_mma_u8(acc[PLANES - 1][I & 1][m][tl], a[0], a[1], a[2], a[3], b[2], b[3]);
-            } else {
-              decode_codeword<TABLE, (I & 1) != 0, WIDE_SIGN>(sk_word<I>(cur[(m * TILES + tl) * 2]), abs_lane, second_lane, a[0], a[2]);      // row g
-              decode_codeword<TABLE, (I & 1) != 0, WIDE_SIGN>(sk_word<I>(cur[(m * TILES + tl) * 2 + 1]), abs_lane, second_lane, a[1], a[3]);  // row g + 8
-              sk_mma(acc[0][I & 1][m][tl], a[0], a[1], a[2], a[3], b[0], b[1]);
-              if (PLANES == 2) sk_mma(acc[PLANES - 1][I & 1][m][tl], a[0], a[1], a[2], a[3], b[2], b[3]);
-            }
+            decode_codeword_nibble<(I & 1) != 0>(sk_word<I>(cur[(m * TILES + tl) * 2]), abs_lane, sign_lane, a[0], a[2]);      // row g
+            decode_codeword_nibble<(I & 1) != 0>(sk_word<I>(cur[(m * TILES + tl) * 2 + 1]), abs_lane, sign_lane, a[1], a[3]);  // row g + 8
+            sk_mma_u8(acc[0][I & 1][m][tl], a[0], a[1], a[2], a[3], b[0], b[1]);
+            if (PLANES == 2) sk_mma_u8(acc[PLANES - 1][I & 1][m][tl], a[0], a[1], a[2], a[3], b[2], b[3]);
           }
       });
       if (--left_in_group == 0) {
@@ -465,7 +434,7 @@ __global__ void __launch_bounds__(SK_THREADS, 1) projection_slab_kernel(FastProj
                 for (int half = 0; half < 2; ++half) {
                   const uint2 v = cur[(m * TILES + tl) * 2 + half];
                   const uint32_t code = ((I < 4 ? v.x : v.y) >> (8 * (I & 3))) & 0xFFu;
-                  const uint2 e = table_entry(code * 128u + second_lane);  // the second table is the residual codebook here
+                  const uint2 e = table_entry(code * 128u + res_lane);
                   a[half] = e.x;
                   a[2 + half] = e.y;
                 }
@@ -585,9 +554,9 @@ static int device_sm_count(int* device_out) {
   return cached[dev];
 }
 
-template <int M, int TILES, int COLS, unsigned TABLE_STEPS, bool NESTED, bool WIDE_SIGN, bool SPLIT = false, bool NIBBLE = false>
+template <int M, int TILES, int COLS, bool NESTED, bool SPLIT = false>
 static int launch_slab(const FastProjectionArgs& p, cudaStream_t s) {
-  auto kernel = projection_slab_kernel<M, TILES, COLS, TABLE_STEPS, NESTED, WIDE_SIGN, SPLIT, NIBBLE>;
+  auto kernel = projection_slab_kernel<M, TILES, COLS, NESTED, SPLIT>;
   static uint64_t configured = 0;  // one bit per device: the shared-memory opt-in is a per-device attribute of the function
   int dev = 0;
   const int sms = device_sm_count(&dev);
@@ -601,51 +570,12 @@ static int launch_slab(const FastProjectionArgs& p, cudaStream_t s) {
   return KEEPVQ_OK;
 }
 
-// Plain layers: the nibble decoder, for groups of four routes (inputs up to 8192) or eight (up to 4096).
-template <int M, int TILES>
-static int launch_nibble(const FastProjectionArgs& p, int cols, cudaStream_t s) {
-  if (cols == 8) return launch_slab<M, TILES, 8, 0u, false, false, false, true>(p, s);
-  return launch_slab<M, TILES, 4, 0u, false, false, false, true>(p, s);
-}
-
-#ifdef KEEPVQ_DIAG
-// Measurement build only: the byte-table decoders (which steps of a chunk decode through the sign
-// table, and the table width) beside the nibble decoder (mask 0x100).
-static unsigned g_table_steps = 0x100u;
-static int g_wide_sign = 1;
-extern "C" void keepvq_diag_set_table_steps(unsigned mask) { g_table_steps = mask; }
-extern "C" void keepvq_diag_set_variant(int wide_sign, int) { g_wide_sign = wide_sign; }
-template <int M, int TILES, unsigned STEPS>
-static int diag_cols4(const FastProjectionArgs& p, cudaStream_t s) {
-  if (g_wide_sign && p.in_dim <= 4096) return launch_slab<M, TILES, 4, STEPS, false, true>(p, s);
-  return launch_slab<M, TILES, 4, STEPS, false, false>(p, s);
-}
-template <int M, int TILES>
-static int launch_plain(const FastProjectionArgs& p, int cols, cudaStream_t s) {
-  if (g_table_steps == 0x100u) return launch_nibble<M, TILES>(p, cols, s);
-  if (cols == 8) {
-    if (g_table_steps == 0xAAu) return launch_slab<M, TILES, 8, 0xAAu, false, false>(p, s);
-    return launch_slab<M, TILES, 8, 0xEEu, false, false>(p, s);
-  }
-  switch (g_table_steps) {
-    case 0x88u: return diag_cols4<M, TILES, 0x88u>(p, s);
-    case 0xAAu: return diag_cols4<M, TILES, 0xAAu>(p, s);
-    case 0xEAu: return diag_cols4<M, TILES, 0xEAu>(p, s);
-    case 0xEEu: return diag_cols4<M, TILES, 0xEEu>(p, s);
-    case 0xFEu: return diag_cols4<M, TILES, 0xFEu>(p, s);
-    default: return KEEPVQ_ERR_UNSUPPORTED;
-  }
-}
-#else
-template <int M, int TILES>
-static int launch_plain(const FastProjectionArgs& p, int cols, cudaStream_t s) { return launch_nibble<M, TILES>(p, cols, s); }
-#endif
-
+// Groups of four routes (inputs up to 8192) or eight (up to 4096).
 template <int M, int TILES>
 static int launch_slab_projection(const FastProjectionArgs& p, int cols, cudaStream_t s) {
   if (p.in_dim > slab_max_in_dim(cols)) return KEEPVQ_ERR_UNSUPPORTED;
-  if (p.res_table) return cols == 4 ? launch_slab<M, TILES, 4, 0u, true, false, false, true>(p, s) : launch_slab<M, TILES, 8, 0u, true, false, false, true>(p, s);
-  return launch_plain<M, TILES>(p, cols, s);
+  if (p.res_table) return cols == 4 ? launch_slab<M, TILES, 4, true>(p, s) : launch_slab<M, TILES, 8, true>(p, s);
+  return cols == 4 ? launch_slab<M, TILES, 4, false>(p, s) : launch_slab<M, TILES, 8, false>(p, s);
 }
 
 int slab_gate_up(const FastProjectionArgs& p, int cols, cudaStream_t s) { return launch_slab_projection<2, 1>(p, cols, s); }
@@ -657,8 +587,8 @@ template <int M, int TILES>
 static int launch_split(const FastProjectionArgs& p, cudaStream_t s) {
   if (p.in_dim > slab_split_max_in_dim()) return KEEPVQ_ERR_UNSUPPORTED;
   if (!p.x.chunk_sums) return KEEPVQ_ERR_NULL;  // the warps' shares of a scale group need sum(x') per 256 inputs
-  if (p.res_table) return launch_slab<M, TILES, 4, 0u, true, false, true, true>(p, s);
-  return launch_slab<M, TILES, 4, 0u, false, false, true, true>(p, s);
+  if (p.res_table) return launch_slab<M, TILES, 4, true, true>(p, s);
+  return launch_slab<M, TILES, 4, false, true>(p, s);
 }
 int slab_split_gate_up(const FastProjectionArgs& p, cudaStream_t s) { return launch_split<2, 1>(p, s); }
 int slab_split_down(const FastProjectionArgs& p, cudaStream_t s) { return launch_split<1, 2>(p, s); }
