@@ -193,7 +193,7 @@ def projection_roofline(layer, xs, steps, hbm_gbs, peak_kind):
     bytes_per_stage = statistics.fmean(uniq[i % len(xs)] for i in range(steps)) * 2 * CODE_BYTES_PER_PROJECTION
     achieved = bytes_per_stage / (ms / steps * 1e-3) / 1e9
     # DRAM bytes per launch are not measured in this run: they come from one ncu capture of this kernel
-    # at batch 64 (dram__bytes_read.sum + dram__bytes_write.sum = 999.9 MB for 1025.4 MB of distinct code
+    # at batch 64 (dram__bytes_read.sum + dram__bytes_write.sum = 999.2 MB for 1025.4 MB of distinct code
     # bytes) and are scaled by the code bytes of the launch timed here.
     traffic = int(NCU_TRAFFIC_PER_CODE_BYTE * bytes_per_stage) if tensor else None
     return {"bound": "hbm", "achieved": round(achieved, 1), "peak": hbm_gbs, "unit": "GB/s", "frac": round(achieved / hbm_gbs, 4),
@@ -204,7 +204,7 @@ def projection_roofline(layer, xs, steps, hbm_gbs, peak_kind):
             "us_per_launch": round(ms / steps * 1e3, 2)}
 
 
-NCU_TRAFFIC_PER_CODE_BYTE = 999.9 / 1025.4
+NCU_TRAFFIC_PER_CODE_BYTE = 999.2 / 1025.4
 
 
 def batch_sweep(layer, device, rotation, steps, hbm_gbs, batches=(1, 4, 16)):
