@@ -123,3 +123,35 @@ def test_pool_file_maps_every_expert_and_orders_the_residents(tmp_path, monkeypa
     (tmp_path / "b" / "ids.json").write_text(json.dumps({"survivors": {"0": [0, 2, 2], "1": [5, 4, 1]}}))
     with pytest.raises(ValueError, match="cover the pool once"):
         layer_io.PoolFile(tmp_path / "pool.json")
+
+
+def test_pool_file_positions_lead_to_the_experts_own_bytes(tmp_path):
+    """A pool of six experts in two directories of three: ``PoolFile.layer_file`` names the file
+    and the position, and the ``LayerFile`` slab read there is that expert's codes."""
+    import json
+
+    from safetensors.torch import save_file
+
+    (tmp_path / "a").mkdir()
+    (tmp_path / "b").mkdir()
+    ids = [{"0": [4, 1, 5]}, {"0": [0, 2, 3]}]
+    written = []
+    for name, per in zip("ab", ids):
+        (tmp_path / name / "ids.json").write_text(json.dumps({"survivors": per}))
+        rng_seed = 11 if name == "a" else 12
+        arrays = write_layer(tmp_path / name / "layer-00.npz", experts=3)
+        # make the two directories' contents differ
+        arrays["w1_codes"] = (arrays["w1_codes"].astype(np.int64) + rng_seed).astype(np.uint16)
+        np.savez(tmp_path / name / "layer-00.npz", **arrays)
+        written.append(arrays)
+    save_file({"layers.0.ffn.gate.weight": torch.zeros((6, 8))}, str(tmp_path / "router.safetensors"))
+    np.savez(tmp_path / "stats.npz", reap__gate_norm_sum=np.arange(6, dtype=np.float64)[None])
+    (tmp_path / "pool.json").write_text(json.dumps({"codes": [["a", "a/ids.json"], ["b", "b/ids.json"]], "router": "router.safetensors", "mass": "stats.npz"}))
+    pool = layer_io.PoolFile(tmp_path / "pool.json")
+    assert pool.residual is None and pool.hot == 0 and pool.starting_residents(0, 2) == [5, 4]
+    for expert in range(6):
+        directory, position = pool.where[0][expert]
+        path, at = pool.layer_file(0, expert)
+        assert at == position and path.parent.name == "ab"[directory]
+        np.testing.assert_array_equal(layer_io.LayerFile(path).read("w1_codes", [at])[0], written[directory]["w1_codes"][position])
+        assert ids[directory]["0"][position] == expert
